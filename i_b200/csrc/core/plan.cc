@@ -1,0 +1,439 @@
+// Recogniser: Graph -> Plan.
+//
+// Pass 1 turns every node into a Map or Reduce step (scalar semantics of the
+// reference's compiler/src/lower/exec_plan_to_module.rs:592-640).
+// Pass 2 folds `Mul node -> Add-reduce node` pairs into Contract steps
+// (the reference's `ik*jk~ijk >> +ijk~ij`, README.md:16).
+// Pass 3 folds `max, sub, exp, sum, div` chains into RowSoftmax steps
+// (README.md:19-25).
+// Pass 4 folds Contract -> RowSoftmax -> Contract into one Attention step
+// (README.md:31), the graph the reference emits as one kernel in
+// ilang-python/annotated-flashattn.c:52-310.
+#include "plan.h"
+
+#include <algorithm>
+#include <cstdlib>
+#include <map>
+#include <set>
+#include <sstream>
+
+namespace ib {
+namespace {
+
+std::string lower_error(const std::string& message) {
+  return "LowerError { message: \"" + message + "\" }";
+}
+
+// I_B200_FUSE_ATTENTION=always fuses every recognised attention chain,
+// whatever its schedule says.
+bool fuse_always() {
+  const char* env = std::getenv("I_B200_FUSE_ATTENTION");
+  return env && std::string(env) == "always";
+}
+
+bool supported(Op op) {
+  switch (op) {
+    case Op::Add: case Op::Mul: case Op::Sub: case Op::Div:
+    case Op::Max: case Op::Min: case Op::Pow: case Op::Log:
+      return true;
+    default:
+      return false;
+  }
+}
+
+bool is_iota(const std::vector<size_t>& v, size_t n) {
+  if (v.size() != n) return false;
+  for (size_t i = 0; i < n; ++i)
+    if (v[i] != i) return false;
+  return true;
+}
+
+bool has_repeat(const std::vector<size_t>& v) {
+  std::set<size_t> s(v.begin(), v.end());
+  return s.size() != v.size();
+}
+
+struct Builder {
+  const Graph& g;
+  std::vector<bool> is_output;
+  std::vector<Step> steps;           // indexed by owning node; kind valid if alive
+  std::vector<bool> alive;
+
+  explicit Builder(const Graph& graph) : g(graph) {
+    is_output.assign(g.nodes.size(), false);
+    for (const auto& src : g.outputs)
+      if (!src.is_input) is_output[src.index] = true;
+  }
+
+  // Live steps that read node `n`, each listed once.
+  std::vector<size_t> readers(size_t n) const {
+    std::vector<size_t> out;
+    for (size_t i = 0; i < g.nodes.size(); ++i) {
+      if (!alive[i]) continue;
+      for (const auto& acc : steps[i].in)
+        if (!acc.buffer.is_input && acc.buffer.index == n) {
+          out.push_back(i);
+          break;
+        }
+    }
+    return out;
+  }
+
+  // The only live step reading node `n`, provided `n` is not a graph output.
+  std::optional<size_t> sole_reader(size_t n) const {
+    if (is_output[n]) return std::nullopt;
+    std::vector<size_t> r = readers(n);
+    if (r.size() != 1) return std::nullopt;
+    return r[0];
+  }
+};
+
+std::optional<std::string> basic_steps(Builder& b) {
+  const Graph& g = b.g;
+  b.steps.resize(g.nodes.size());
+  b.alive.assign(g.nodes.size(), true);
+  for (size_t n = 0; n < g.nodes.size(); ++n) {
+    const Node& node = g.nodes[n].inner;
+    if (!supported(node.op))
+      return lower_error(std::string("operator `") + op_name(node.op) +
+                         "` is outside the B200 target's hot path (supported: + * - / > < ^ $)");
+    for (size_t i = 0; i < node.inputs.size(); ++i)
+      if (g.nodes[n].inputs[i].is_input && node.compute_sites[i])
+        return lower_error("node " + std::to_string(n) + " input " + std::to_string(i) +
+                           " is a graph input with a compute site");
+    Step& s = b.steps[n];
+    s.kind = node.is_reduction() ? StepKind::Reduce : StepKind::Map;
+    s.op = node.op;
+    s.rank = node.rank;
+    for (size_t i = 0; i < node.inputs.size(); ++i)
+      s.in.push_back(Access{g.nodes[n].inputs[i], node.inputs[i]});
+    s.out = Access{Source{false, n}, node.output};
+    s.nodes = {n};
+    // Staging at the root hoists the producer in front of the loops, which
+    // materialises it; only a site inside the loops fuses.
+    for (const auto& site : node.compute_sites)
+      if (site && !site->root) s.hint.staged = true;
+  }
+  return std::nullopt;
+}
+
+// Classifies a fused Mul/Add-reduce pair as a batched GEMM, if it is one.
+bool classify_contraction(const Step& mul, const std::vector<size_t>& out_idx, ContractForm* form) {
+  const auto& a = mul.in[0].index;
+  const auto& bb = mul.in[1].index;
+  if (has_repeat(a) || has_repeat(bb) || has_repeat(out_idx)) return false;
+  auto in = [](const std::vector<size_t>& v, size_t x) {
+    return std::find(v.begin(), v.end(), x) != v.end();
+  };
+  std::vector<size_t> batch, ms, ns, ks;
+  for (size_t x = 0; x < mul.rank; ++x) {
+    bool i0 = in(a, x), i1 = in(bb, x), o = in(out_idx, x);
+    if (i0 && i1 && o) batch.push_back(x);
+    else if (i0 && !i1 && o) ms.push_back(x);
+    else if (!i0 && i1 && o) ns.push_back(x);
+    else if (i0 && i1 && !o) ks.push_back(x);
+    else return false;
+  }
+  if (ks.size() != 1 || ms.size() > 1 || ns.size() > 1) return false;
+  const size_t nb = batch.size();
+  // Batch axes lead all three tensors in the same order.
+  std::vector<size_t> lead(a.begin(), a.begin() + std::min(nb, a.size()));
+  if (lead.size() != nb) return false;
+  for (size_t x : lead)
+    if (std::find(batch.begin(), batch.end(), x) == batch.end()) return false;
+  if (bb.size() < nb || out_idx.size() < nb) return false;
+  for (size_t i = 0; i < nb; ++i)
+    if (bb[i] != lead[i] || out_idx[i] != lead[i]) return false;
+
+  form->n_batch = nb;
+  form->k = ks[0];
+  form->has_m = !ms.empty();
+  form->has_n = !ns.empty();
+  form->m = form->has_m ? ms[0] : 0;
+  form->n = form->has_n ? ns[0] : 0;
+  // Operand 0: [.., m, k] or [.., k, m] (or [.., k] without m).
+  std::vector<size_t> ta(a.begin() + nb, a.end());
+  if (form->has_m) {
+    if (ta == std::vector<size_t>{form->m, form->k}) form->a_kmajor = true;
+    else if (ta == std::vector<size_t>{form->k, form->m}) form->a_kmajor = false;
+    else return false;
+  } else {
+    if (ta != std::vector<size_t>{form->k}) return false;
+    form->a_kmajor = true;
+  }
+  std::vector<size_t> tb(bb.begin() + nb, bb.end());
+  if (form->has_n) {
+    if (tb == std::vector<size_t>{form->n, form->k}) form->b_kmajor = true;
+    else if (tb == std::vector<size_t>{form->k, form->n}) form->b_kmajor = false;
+    else return false;
+  } else {
+    if (tb != std::vector<size_t>{form->k}) return false;
+    form->b_kmajor = true;
+  }
+  std::vector<size_t> to(out_idx.begin() + nb, out_idx.end());
+  std::vector<size_t> want;
+  if (form->has_m) want.push_back(form->m);
+  if (form->has_n) want.push_back(form->n);
+  if (to == want) {
+    form->swap_out = false;
+  } else {
+    std::reverse(want.begin(), want.end());
+    if (to != want) return false;
+    form->swap_out = true;
+  }
+  return true;
+}
+
+void fuse_contractions(Builder& b) {
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n]) continue;
+    Step& mul = b.steps[n];
+    if (mul.kind != StepKind::Map || mul.op != Op::Mul || mul.in.size() != 2) continue;
+    auto reader = b.sole_reader(n);
+    if (!reader) continue;
+    Step& red = b.steps[*reader];
+    if (red.kind != StepKind::Reduce || red.op != Op::Add || red.in.size() != 1) continue;
+    const auto& view = red.in[0].index;           // reducer's index per dim of the product
+    if (view.size() != mul.out.index.size() || has_repeat(view)) continue;
+    std::map<size_t, size_t> to_mul;              // reducer index -> multiplier index
+    for (size_t p = 0; p < view.size(); ++p) to_mul[view[p]] = mul.out.index[p];
+    std::vector<size_t> out_idx;
+    for (size_t x : red.out.index) out_idx.push_back(to_mul[x]);
+    ContractForm form;
+    if (!classify_contraction(mul, out_idx, &form)) continue;
+
+    Step fused;
+    fused.kind = StepKind::Contract;
+    fused.op = Op::Add;
+    fused.rank = mul.rank;
+    fused.in = mul.in;
+    fused.out = Access{red.out.buffer, out_idx};
+    fused.form = form;
+    fused.nodes = {n, *reader};
+    fused.hint.staged = red.hint.staged;
+    const Node& mnode = b.g.nodes[n].inner;
+    if (form.has_m && !mnode.splits[form.m].empty()) fused.hint.row_split = mnode.splits[form.m][0];
+    if (form.has_n && !mnode.splits[form.n].empty()) fused.hint.col_split = mnode.splits[form.n][0];
+    if (!mnode.order.empty()) fused.hint.reduce_outer = form.has_n && mnode.order[0].index == form.n;
+    b.steps[*reader] = std::move(fused);
+    b.alive[n] = false;
+  }
+}
+
+// A reduce over exactly the last axis of its operand, leading axes kept in order.
+bool is_row_reduce(const Step& s, Op op) {
+  if (s.kind != StepKind::Reduce || s.op != op || s.in.size() != 1) return false;
+  return s.rank >= 1 && is_iota(s.in[0].index, s.rank) && is_iota(s.out.index, s.rank - 1);
+}
+
+// x[.., r, c] (op) v[.., r] -> [.., r, c]
+bool is_row_broadcast(const Step& s, Op op) {
+  if (s.kind != StepKind::Map || s.op != op || s.in.size() != 2) return false;
+  return s.rank >= 1 && is_iota(s.in[0].index, s.rank) && is_iota(s.in[1].index, s.rank - 1) &&
+         is_iota(s.out.index, s.rank);
+}
+
+void fuse_softmax(Builder& b) {
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n] || !is_row_reduce(b.steps[n], Op::Max)) continue;
+    const Step& mx = b.steps[n];
+    auto r_sub = b.sole_reader(n);
+    if (!r_sub || !is_row_broadcast(b.steps[*r_sub], Op::Sub)) continue;
+    const Step& sub = b.steps[*r_sub];
+    if (!(sub.in[0].buffer == mx.in[0].buffer) || sub.in[1].buffer.is_input ||
+        sub.in[1].buffer.index != n)
+      continue;
+    auto r_exp = b.sole_reader(*r_sub);
+    if (!r_exp) continue;
+    const Step& ex = b.steps[*r_exp];
+    if (ex.kind != StepKind::Map || ex.op != Op::Pow || ex.in.size() != 1 ||
+        !is_iota(ex.in[0].index, ex.rank) || !is_iota(ex.out.index, ex.rank))
+      continue;
+    if (b.is_output[*r_exp]) continue;
+    std::vector<size_t> rd = b.readers(*r_exp);
+    if (rd.size() != 2) continue;
+    size_t i_sum = rd[0], i_div = rd[1];
+    if (!is_row_reduce(b.steps[i_sum], Op::Add)) std::swap(i_sum, i_div);
+    if (!is_row_reduce(b.steps[i_sum], Op::Add) || !is_row_broadcast(b.steps[i_div], Op::Div))
+      continue;
+    const Step& dv = b.steps[i_div];
+    if (dv.in[0].buffer.is_input || dv.in[0].buffer.index != *r_exp || dv.in[1].buffer.is_input ||
+        dv.in[1].buffer.index != i_sum)
+      continue;
+    if (b.is_output[i_sum] || b.readers(i_sum).size() != 1) continue;
+
+    Step fused;
+    fused.kind = StepKind::RowSoftmax;
+    fused.op = Op::Div;
+    fused.rank = mx.rank;
+    fused.in = {mx.in[0]};
+    fused.out = dv.out;
+    fused.nodes = {n, *r_sub, *r_exp, i_sum, i_div};
+    const Node& mnode = b.g.nodes[n].inner;
+    const size_t col = mx.rank - 1;
+    if (mx.rank >= 2 && !mnode.splits[col - 1].empty()) fused.hint.row_split = mnode.splits[col - 1][0];
+    if (!mnode.splits[col].empty()) fused.hint.col_split = mnode.splits[col][0];
+    if (!mnode.order.empty()) fused.hint.reduce_outer = mnode.order[0].index == col;
+    fused.hint.staged = b.steps[*r_sub].hint.staged || ex.hint.staged || dv.hint.staged;
+    const size_t last = std::max(std::max(*r_sub, *r_exp), std::max(i_sum, i_div));
+    for (size_t dead : fused.nodes) b.alive[dead] = false;
+    fused.out.buffer = Source{false, i_div};
+    // The fused step takes the slot of the last node of the group; its result
+    // still belongs to the divide node.
+    b.steps[last] = std::move(fused);
+    b.alive[last] = true;
+  }
+}
+
+void fuse_attention(Builder& b) {
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n] || b.steps[n].kind != StepKind::Contract) continue;
+    const Step& qk = b.steps[n];
+    const ContractForm& f1 = qk.form;
+    if (!f1.has_m || !f1.has_n || !f1.a_kmajor || !f1.b_kmajor || f1.swap_out) continue;
+    const size_t s_node = qk.out.buffer.index;
+    auto r_sm = b.sole_reader(s_node);
+    if (!r_sm || b.steps[*r_sm].kind != StepKind::RowSoftmax) continue;
+    const Step& sm = b.steps[*r_sm];
+    if (sm.rank != f1.n_batch + 2) continue;
+    const size_t p_node = sm.out.buffer.index;
+    auto r_pv = b.sole_reader(p_node);
+    if (!r_pv || b.steps[*r_pv].kind != StepKind::Contract) continue;
+    const Step& pv = b.steps[*r_pv];
+    const ContractForm& f2 = pv.form;
+    if (pv.in[0].buffer.is_input || pv.in[0].buffer.index != p_node) continue;
+    if (!f2.has_m || !f2.has_n || !f2.a_kmajor || f2.swap_out || f2.n_batch != f1.n_batch) continue;
+    // The schedule decides fusion, as in the reference: the chain becomes one
+    // kernel only when the second contraction stages its P operand inside its
+    // loops (README.md:28, `ji0i'kj'`); the naive schedule of
+    // ilang-python/flash-attn.py:57-65 keeps S and P as full intermediates.
+    const Node& pv_mul = b.g.nodes[pv.nodes[0]].inner;
+    const bool p_staged = pv_mul.compute_sites[0] && !pv_mul.compute_sites[0]->root;
+    if (!p_staged && !fuse_always()) continue;
+
+    Step fused;
+    fused.kind = StepKind::Attention;
+    fused.op = Op::Add;
+    fused.rank = qk.rank;
+    fused.in = {qk.in[0], qk.in[1], pv.in[1]};
+    fused.out = pv.out;
+    fused.form = f1;
+    fused.form2 = f2;
+    fused.hint = sm.hint;
+    fused.hint.staged = pv.hint.staged || sm.hint.staged;
+    fused.nodes = qk.nodes;
+    fused.nodes.insert(fused.nodes.end(), sm.nodes.begin(), sm.nodes.end());
+    fused.nodes.insert(fused.nodes.end(), pv.nodes.begin(), pv.nodes.end());
+    const size_t slot = *r_pv, sm_slot = *r_sm;
+    b.alive[n] = false;
+    b.alive[sm_slot] = false;
+    b.steps[slot] = std::move(fused);
+  }
+}
+
+const char* kind_name(StepKind k) {
+  switch (k) {
+    case StepKind::Map: return "map";
+    case StepKind::Reduce: return "reduce";
+    case StepKind::Contract: return "contract";
+    case StepKind::RowSoftmax: return "row_softmax";
+    case StepKind::Attention: return "attention";
+  }
+  return "?";
+}
+
+std::string buffer_name(const Source& s) {
+  return (s.is_input ? "in" : "t") + std::to_string(s.index);
+}
+
+std::string index_text(const std::vector<size_t>& idx) {
+  if (idx.empty()) return ".";
+  std::string out;
+  for (size_t x : idx) out += std::to_string(x);
+  return out;
+}
+
+}  // namespace
+
+std::string Plan::describe() const {
+  std::ostringstream os;
+  os << "// i component compiled for the B200 target (sm_100a)\n";
+  os << "// inputs: " << n_inputs << ", outputs: " << outputs.size() << ", kernel steps: "
+     << steps.size() << "\n";
+  for (size_t i = 0; i < steps.size(); ++i) {
+    const Step& s = steps[i];
+    os << "step " << i << ": " << kind_name(s.kind);
+    if (s.kind == StepKind::Map || s.kind == StepKind::Reduce) os << " `" << op_token(s.op) << "`";
+    os << "  " << buffer_name(s.out.buffer) << "[" << index_text(s.out.index) << "] <-";
+    for (const auto& a : s.in) os << " " << buffer_name(a.buffer) << "[" << index_text(a.index) << "]";
+    os << "\n";
+    switch (s.kind) {
+      case StepKind::Contract:
+        os << "    kernel: ib_contract (tcgen05 kind::tf32 + TMA when shapes allow, SIMT fp32 "
+              "otherwise); batch axes "
+           << s.form.n_batch << ", A " << (s.form.a_kmajor ? "[m,k]" : "[k,m]") << ", B "
+           << (s.form.b_kmajor ? "[n,k]" : "[k,n]") << (s.form.swap_out ? ", output [n,m]" : "")
+           << "\n";
+        break;
+      case StepKind::RowSoftmax:
+        os << "    kernel: ib_row_softmax (row resident on chip, one read + one write)\n";
+        break;
+      case StepKind::Attention:
+        os << "    kernel: ib_attention (fused online softmax, both contractions on tcgen05, S/P/O "
+              "in TMEM); batch axes "
+           << s.form.n_batch << ", V " << (s.form2.b_kmajor ? "[dv,j]" : "[j,dv]") << "\n";
+        break;
+      case StepKind::Reduce:
+        os << "    kernel: ib_reduce\n";
+        break;
+      case StepKind::Map:
+        os << "    kernel: ib_map\n";
+        break;
+    }
+    if (s.hint.row_split || s.hint.col_split || s.hint.staged)
+      os << "    schedule: row granule " << s.hint.row_split << ", column granule "
+         << s.hint.col_split << ", " << (s.hint.reduce_outer ? "reduced-axis tiles outermost" : "row tiles outermost")
+         << ", " << (s.hint.staged ? "producers staged (fused)" : "producers materialised") << "\n";
+    os << "    nodes:";
+    for (size_t n : s.nodes) os << " n" << n;
+    os << "\n";
+  }
+  os << "outputs:";
+  for (const auto& o : outputs) os << " " << buffer_name(o);
+  os << "\n";
+  return os.str();
+}
+
+Result<Plan> make_plan(const Graph& g) {
+  Builder b(g);
+  if (auto err = basic_steps(b)) return Result<Plan>::failure(*err);
+  fuse_contractions(b);
+  fuse_softmax(b);
+  fuse_attention(b);
+
+  Plan plan;
+  plan.n_inputs = g.n_inputs;
+  plan.n_nodes = g.nodes.size();
+  plan.outputs = g.outputs;
+  for (size_t n = 0; n < g.nodes.size(); ++n)
+    if (b.alive[n]) plan.steps.push_back(b.steps[n]);
+
+  plan.input_ranks.assign(g.n_inputs, static_cast<size_t>(-1));
+  for (const auto& node : g.nodes)
+    for (size_t i = 0; i < node.inputs.size(); ++i)
+      if (node.inputs[i].is_input) {
+        size_t& r = plan.input_ranks[node.inputs[i].index];
+        if (r == static_cast<size_t>(-1)) r = node.inner.inputs[i].size();
+      }
+  for (const auto& out : g.outputs) {
+    if (out.is_input) {
+      // An identity-wired output has the rank of whatever is passed in.
+      plan.output_ranks.push_back(static_cast<size_t>(-1));
+    } else {
+      plan.output_ranks.push_back(g.nodes[out.index].inner.output.size());
+    }
+  }
+  return Result<Plan>::success(std::move(plan));
+}
+
+}  // namespace ib

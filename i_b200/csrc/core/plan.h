@@ -1,0 +1,76 @@
+// Graph -> execution plan for the B200 target.
+//
+// The reference lowers a graph through a generic loop-nest planner
+// (compiler/src/lower/node_to_stage.rs, stage_to_kernel_program.rs) and emits C.
+// This target instead recognises the sub-graphs of the hot path and maps each
+// to one hand-written kernel; anything it cannot map is a compile error (there
+// is no CPU fallback).  Recognition works on canonical index numbers, never on
+// axis letters, so `bhij*bhkj~bhikj` and `ik*jk~ijk` are the same contraction
+// with two extra leading batch axes.
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "ir.h"
+
+namespace ib {
+
+enum class StepKind {
+  Map,          // pointwise unary or binary, any broadcast / permutation
+  Reduce,       // fold over the axes missing from the output
+  Contract,     // Mul node + Add-reduce node = batched GEMM
+  RowSoftmax,   // max, shift, exp, sum, divide over the last axis
+  Attention     // Contract -> RowSoftmax -> Contract, fused online softmax
+};
+
+// One tensor access of a step: which buffer, and which step-local index each
+// of its dimensions runs over.
+struct Access {
+  Source buffer;
+  std::vector<size_t> index;
+};
+
+struct ContractForm {
+  size_t n_batch = 0;          // leading axes shared by both operands and the output
+  bool has_m = true, has_n = true;
+  size_t m = 0, n = 0, k = 0;  // step-local index numbers
+  bool a_kmajor = true;        // operand 0 stored [.., m, k]; false = [.., k, m]
+  bool b_kmajor = true;        // operand 1 stored [.., n, k]; false = [.., k, n]
+  bool swap_out = false;       // output stored [.., n, m]
+};
+
+// Schedule facts the kernels read (granules, loop preference, staging).
+struct ScheduleHint {
+  size_t row_split = 0;        // split factor on the output-row axis (0 = none)
+  size_t col_split = 0;        // split factor on the reduced / column axis
+  bool reduce_outer = false;   // the reduced (KV) tile loop is outermost
+  bool staged = false;         // producers are staged into the consumer's loops
+};
+
+struct Step {
+  StepKind kind = StepKind::Map;
+  Op op = Op::Add;
+  size_t rank = 0;                 // size of the step-local index space
+  std::vector<Access> in;
+  Access out;                      // out.buffer.index = node that owns the result
+  ContractForm form;               // Contract; Attention uses form (QK) and form2 (PV)
+  ContractForm form2;
+  ScheduleHint hint;
+  std::vector<size_t> nodes;       // graph nodes folded into this step
+};
+
+struct Plan {
+  size_t n_inputs = 0;
+  size_t n_nodes = 0;
+  std::vector<Step> steps;
+  std::vector<Source> outputs;
+  std::vector<size_t> output_ranks;
+  // For every graph input: its rank as implied by the patterns that read it.
+  std::vector<size_t> input_ranks;
+  std::string describe() const;    // text returned by i_code
+};
+
+Result<Plan> make_plan(const Graph& g);
+
+}  // namespace ib

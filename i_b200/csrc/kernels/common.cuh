@@ -1,0 +1,101 @@
+// Shared device helpers and host-side launch bookkeeping for the ib_* kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "i_b200.h"
+
+namespace ib {
+
+// Implemented in core/runtime.cc: records the thread-local message i_error() returns.
+void set_error(const std::string& message);
+// Bumps the counter behind i_b200_launch_count().
+void count_launch(size_t n = 1);
+
+inline int fail(const std::string& message) {
+  set_error(message);
+  return -1;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(std::string(what) + ": " + cudaGetErrorString(err));
+  count_launch();
+  return 0;
+}
+
+constexpr int kNumSMs = 148;  // B200
+
+// powf(2.71828175f, x), the reference C backend's exp
+// (compiler/src/backends/c/expr.rs:350-366 prints e as 2.71828175f).  x*log2(e32)
+// is carried as a two-float product so the result stays within a few ulp of the
+// libm value over the whole range a softmax sees.
+__device__ __forceinline__ float exp_e32(float x) {
+  const float l_hi = 1.4426950216293335f;      // fp32(log2(2.71828175))
+  const float l_lo = -2.4551930266625277e-08f; // log2(2.71828175) - l_hi
+  if (!(fabsf(x) < 200.0f)) return x > 0.0f ? CUDART_INF_F : (x < 0.0f ? 0.0f : x);
+  float hi = x * l_hi;
+  float lo = fmaf(x, l_lo, fmaf(x, l_hi, -hi));
+  float n = rintf(hi);
+  float f = (hi - n) + lo;
+  return ldexpf(exp2f(f), static_cast<int>(n));
+}
+
+__device__ __forceinline__ float apply_binary(int op, float a, float b) {
+  switch (op) {
+    case IB_OP_ADD: return a + b;
+    case IB_OP_MUL: return a * b;
+    case IB_OP_SUB: return a - b;
+    case IB_OP_DIV: return a / b;
+    case IB_OP_MAX: return fmaxf(a, b);
+    case IB_OP_MIN: return fminf(a, b);
+    case IB_OP_POW: return powf(a, b);
+    default: return logf(a);  // IB_OP_LOG: the C backend drops the second operand
+  }
+}
+
+__device__ __forceinline__ float apply_unary(int op, float x) {
+  switch (op) {
+    case IB_OP_ADD:
+    case IB_OP_MUL: return x;
+    case IB_OP_SUB: return 0.0f - x;
+    case IB_OP_DIV: return 1.0f / x;
+    case IB_OP_MAX: return fmaxf(0.0f, x);
+    case IB_OP_MIN: return fminf(0.0f, x);
+    case IB_OP_POW: return exp_e32(x);
+    default: return logf(x);
+  }
+}
+
+__device__ __forceinline__ float reduce_identity(int op) {
+  switch (op) {
+    case IB_OP_ADD: return 0.0f;
+    case IB_OP_MUL: return 1.0f;
+    case IB_OP_MAX: return -CUDART_INF_F;
+    default: return CUDART_INF_F;  // IB_OP_MIN
+  }
+}
+
+template <int OP>
+__device__ __forceinline__ float fold(float a, float b) {
+  if (OP == IB_OP_ADD) return a + b;
+  if (OP == IB_OP_MUL) return a * b;
+  if (OP == IB_OP_MAX) return fmaxf(a, b);
+  return fminf(a, b);
+}
+
+template <int OP>
+__device__ __forceinline__ float warp_fold(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v = fold<OP>(v, __shfl_xor_sync(0xffffffffu, v, s));
+  return v;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace ib

@@ -1,0 +1,129 @@
+// CUDA-core fp32 contraction and layout helpers.
+//
+// ib::contract_simt is the IB_PRECISION_FP32 arm of ib_contract: shared-memory
+// tiled FMA GEMM for problems that are too small or too ragged for the tensor
+// path (odd K, tiny tiles such as the 8x16x7 product of ilang-python/test.py:
+// 52-56).  It computes C[b][i][j] = sum_k A(b,i,k) B(b,j,k) in fp32, the same
+// arithmetic as the reference's loop nest (ilang-python/annotated-flashattn.c:
+// 57-89) up to summation order and FMA contraction.
+//
+// ib::transpose_batched rewrites [b][r][c] as [b][c][r]; the tensor path uses
+// it to give tcgen05 K-major operands.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ib {
+namespace {
+
+constexpr int kTile = 64;
+constexpr int kTileK = 16;
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(256)
+contract_simt_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                     float* __restrict__ c, size_t m, size_t n, size_t k) {
+  __shared__ float sa[kTileK][kTile + 1];
+  __shared__ float sb[kTileK][kTile + 1];
+  const size_t batch = blockIdx.z;
+  a += batch * m * k;
+  b += batch * n * k;
+  c += batch * m * n;
+  const size_t i0 = static_cast<size_t>(blockIdx.y) * kTile;
+  const size_t j0 = static_cast<size_t>(blockIdx.x) * kTile;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[4][4] = {};
+  for (size_t k0 = 0; k0 < k; k0 += kTileK) {
+    for (int e = threadIdx.x; e < kTile * kTileK; e += 256) {
+      // Walk the operand along its contiguous axis.
+      int row, kk;
+      if (A_KMAJOR) { row = e / kTileK; kk = e % kTileK; } else { kk = e / kTile; row = e % kTile; }
+      size_t gi = i0 + row, gk = k0 + kk;
+      float v = 0.0f;
+      if (gi < m && gk < k) v = A_KMAJOR ? a[gi * k + gk] : a[gk * m + gi];
+      sa[kk][row] = v;
+      if (B_KMAJOR) { row = e / kTileK; kk = e % kTileK; } else { kk = e / kTile; row = e % kTile; }
+      size_t gj = j0 + row;
+      gk = k0 + kk;
+      v = 0.0f;
+      if (gj < n && gk < k) v = B_KMAJOR ? b[gj * k + gk] : b[gk * n + gj];
+      sb[kk][row] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kTileK; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        av[u] = sa[kk][ty * 4 + u];
+        bv[u] = sb[kk][tx * 4 + u];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc[u][w] = fmaf(av[u], bv[w], acc[u][w]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    size_t gi = i0 + ty * 4 + u;
+    if (gi >= m) continue;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      size_t gj = j0 + tx * 4 + w;
+      if (gj < n) c[gi * n + gj] = acc[u][w];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+transpose_kernel(const float* __restrict__ in, float* __restrict__ out, size_t rows, size_t cols,
+                 size_t out_pitch) {
+  __shared__ float tile[32][33];
+  const size_t batch = blockIdx.z;
+  in += batch * rows * cols;
+  out += batch * cols * out_pitch;
+  const size_t c0 = static_cast<size_t>(blockIdx.x) * 32, r0 = static_cast<size_t>(blockIdx.y) * 32;
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  for (int j = ty; j < 32; j += 8) {
+    size_t r = r0 + j, cc = c0 + tx;
+    if (r < rows && cc < cols) tile[j][tx] = in[r * cols + cc];
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    size_t cc = c0 + j, r = r0 + tx;
+    if (r < rows && cc < cols) out[cc * out_pitch + r] = tile[tx][j];
+  }
+}
+
+}  // namespace
+
+int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
+                  size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s) {
+  if (batch == 0 || m == 0 || n == 0) return 0;
+  if (batch > 65535) return fail("ib_contract: more than 65535 batch entries");
+  dim3 grid(static_cast<unsigned>((n + kTile - 1) / kTile),
+            static_cast<unsigned>((m + kTile - 1) / kTile), static_cast<unsigned>(batch));
+  if (grid.y > 65535) return fail("ib_contract: row count too large for the fp32 arm");
+  if (a_kmajor && b_kmajor)
+    contract_simt_kernel<true, true><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+  else if (a_kmajor && !b_kmajor)
+    contract_simt_kernel<true, false><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+  else if (!a_kmajor && b_kmajor)
+    contract_simt_kernel<false, true><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+  else
+    contract_simt_kernel<false, false><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+  return check_launch("ib_contract (fp32)");
+}
+
+int transpose_batched(const float* in, float* out, size_t batch, size_t rows, size_t cols,
+                      size_t out_pitch, cudaStream_t s) {
+  if (batch == 0 || rows == 0 || cols == 0) return 0;
+  if (batch > 65535 || (rows + 31) / 32 > 65535) return fail("transpose: shape too large");
+  dim3 grid(static_cast<unsigned>((cols + 31) / 32), static_cast<unsigned>((rows + 31) / 32),
+            static_cast<unsigned>(batch));
+  transpose_kernel<<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch);
+  return check_launch("transpose");
+}
+
+}  // namespace ib

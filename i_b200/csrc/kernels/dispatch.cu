@@ -1,0 +1,160 @@
+// ib_contract and ib_attention: precision choice, workspace carving and the
+// layout fix-ups that give the tensor-core kernels K-major operands.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ib {
+namespace {
+
+constexpr double kTensorMinFlop = 268435456.0;  // 2^28: below this the fp32 arm is used
+
+size_t round_up(size_t x, size_t to) { return (x + to - 1) / to * to; }
+
+// Sub-allocator over the caller's workspace (256-byte granules).
+struct Carver {
+  uint8_t* base;
+  size_t size, used = 0;
+  Carver(void* p, size_t n) : base(static_cast<uint8_t*>(p)), size(n) {}
+  float* take(size_t floats) {
+    size_t bytes = round_up(floats * sizeof(float), 256);
+    if (!base || used + bytes > size) return nullptr;
+    float* out = reinterpret_cast<float*>(base + used);
+    used += bytes;
+    return out;
+  }
+};
+
+size_t carve_bytes(size_t floats) { return round_up(floats * sizeof(float), 256); }
+
+bool wants_tensor(int precision, double flop) {
+  if (precision == IB_PRECISION_FP32) return false;
+  if (precision == IB_PRECISION_AUTO) return flop >= kTensorMinFlop;
+  return true;
+}
+
+// Shape-only test (no pointers): can the tensor arm take this contraction?
+bool contract_shape_ok(size_t k) { return k % 4 == 0 && k >= 4; }
+
+bool attention_shape_ok(size_t d, size_t dv) {
+  return d % 4 == 0 && d >= 4 && d <= 128 && dv >= 1 && dv <= 128;
+}
+
+}  // namespace
+}  // namespace ib
+
+extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, size_t k,
+                                              int a_kmajor, int b_kmajor, int precision) {
+  using namespace ib;
+  const double flop = 2.0 * batch * m * n * k;
+  if (!wants_tensor(precision, flop) || !contract_shape_ok(k)) return 0;
+  size_t bytes = 0;
+  if (!a_kmajor) bytes += carve_bytes(batch * m * k);
+  if (!b_kmajor) bytes += carve_bytes(batch * n * k);
+  return bytes;
+}
+
+extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batch, size_t m,
+                           size_t n, size_t k, int a_kmajor, int b_kmajor, int precision,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace ib;
+  if (batch == 0 || m == 0 || n == 0) return 0;
+  if (!a || !b || !c) return fail("ib_contract: null pointer");
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
+    return fail("ib_contract: unknown precision");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (k == 0) {
+    cudaError_t err = cudaMemsetAsync(c, 0, batch * m * n * sizeof(float), s);
+    return err == cudaSuccess ? 0 : fail("ib_contract: memset failed");
+  }
+  const double flop = 2.0 * batch * m * n * k;
+  if (wants_tensor(precision, flop) && contract_shape_ok(k)) {
+    Carver ws(workspace, workspace_bytes);
+    const float* ak = a;
+    const float* bk = b;
+    if (!a_kmajor) {
+      float* t = ws.take(batch * m * k);
+      if (!t) return fail("ib_contract: workspace too small (see ib_contract_workspace_bytes)");
+      if (int rc = transpose_batched(a, t, batch, k, m, k, s)) return rc;   // [k][m] -> [m][k]
+      ak = t;
+    }
+    if (!b_kmajor) {
+      float* t = ws.take(batch * n * k);
+      if (!t) return fail("ib_contract: workspace too small (see ib_contract_workspace_bytes)");
+      if (int rc = transpose_batched(b, t, batch, k, n, k, s)) return rc;   // [k][n] -> [n][k]
+      bk = t;
+    }
+    if (gemm_tcgen05_supported(ak, bk, c, m, n, k)) return gemm_tcgen05(ak, bk, c, batch, m, n, k, s);
+    // Misaligned base pointers: the fp32 arm takes any layout.
+    return contract_simt(ak, bk, c, batch, m, n, k, true, true, s);
+  }
+  return contract_simt(a, b, c, batch, m, n, k, a_kmajor != 0, b_kmajor != 0, s);
+}
+
+extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t nk, size_t d,
+                                               size_t dv, int v_kmajor, int precision) {
+  using namespace ib;
+  const double flop = 4.0 * batch * nq * nk * d;
+  if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
+    size_t bytes = 0;
+    if (!v_kmajor || nk % 4 != 0) bytes += carve_bytes(batch * dv * round_up(nk, 4));
+    bytes += carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
+    return bytes;
+  }
+  // Unfused: S = Q K^T, softmax in place, O = S V.
+  size_t bytes = carve_bytes(batch * nq * nk);
+  const int sub = wants_tensor(precision, flop) ? IB_PRECISION_TF32 : IB_PRECISION_FP32;
+  bytes += ib_contract_workspace_bytes(batch, nq, dv, nk, 1, v_kmajor, sub);
+  return bytes;
+}
+
+extern "C" int ib_attention(const float* q, const float* k, const float* v, float* o, size_t batch,
+                            size_t nq, size_t nk, size_t d, size_t dv, int v_kmajor, int precision,
+                            size_t kv_tile, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  using namespace ib;
+  (void)kv_tile;
+  if (batch == 0 || nq == 0 || dv == 0) return 0;
+  if (!q || !k || !v || !o) return fail("ib_attention: null pointer");
+  if (nk == 0 || d == 0) return fail("ib_attention: empty key or feature axis");
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
+    return fail("ib_attention: unknown precision");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Carver ws(workspace, workspace_bytes);
+  const double flop = 4.0 * batch * nq * nk * d;
+  const bool tensor = wants_tensor(precision, flop);
+
+  if (tensor && attention_shape_ok(d, dv) && attention_tcgen05_supported(q, k, o, d, dv)) {
+    const size_t pitch = round_up(nk, 4);
+    const float* vt = v;
+    if (!v_kmajor || nk % 4 != 0) {
+      float* t = ws.take(batch * dv * pitch);
+      if (!t) return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
+      if (!v_kmajor) {
+        if (int rc = transpose_batched(v, t, batch, nk, dv, pitch, s)) return rc;
+      } else {
+        cudaError_t err = cudaMemcpy2DAsync(t, pitch * sizeof(float), v, nk * sizeof(float),
+                                            nk * sizeof(float), batch * dv,
+                                            cudaMemcpyDeviceToDevice, s);
+        if (err != cudaSuccess) return fail("ib_attention: re-pitching V failed");
+      }
+      vt = t;
+    }
+    float* partials = nullptr;
+    const size_t part_floats = attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr);
+    if (part_floats) {
+      partials = ws.take(part_floats);
+      if (!partials)
+        return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
+    }
+    return attention_tcgen05(q, k, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
+  }
+
+  float* scores = ws.take(batch * nq * nk);
+  if (!scores) return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
+  const int sub = tensor ? IB_PRECISION_TF32 : IB_PRECISION_FP32;
+  if (int rc = ib_contract(q, k, scores, batch, nq, nk, d, 1, 1, sub, nullptr, 0, stream)) return rc;
+  if (int rc = ib_row_softmax(scores, scores, batch * nq, nk, stream)) return rc;
+  uint8_t* rest = ws.base ? ws.base + ws.used : nullptr;
+  return ib_contract(scores, v, o, batch, nq, dv, nk, 1, v_kmajor, sub, rest,
+                     workspace_bytes - ws.used, stream);
+}

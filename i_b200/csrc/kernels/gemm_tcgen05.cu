@@ -1,0 +1,268 @@
+// Tensor-core contraction C[b][i][j] = sum_k A[b][i][k] * B[b][j][k]
+// (`ik*jk~ijk >> +ijk~ij`, reference README.md:16; the reference's scalar nest
+// is ilang-python/annotated-flashattn.c:57-89).
+//
+// Persistent, warp-specialised sm_100a kernel:
+//   warp 0   TMA producer: 128-byte-swizzled boxes of A (128 x 32 fp32) and
+//            B (BN x 32 fp32) into a 4-deep shared-memory ring
+//   warp 1   MMA issuer: tcgen05.mma kind::tf32, 128 x BN x 8 per instruction,
+//            fp32 accumulators in tensor memory, double-buffered per tile
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator and store it,
+//            overlapping the next tile's main loop
+// fp32 operands are read by the tensor core as TF32 (10-bit mantissa), products
+// accumulate in fp32.  Out-of-range rows/columns/K are zero-filled by TMA and
+// masked at the store, so M, N need no padding; K must be a multiple of 4
+// (16-byte row pitch).  Tiles are walked in column groups so that a wave of 148
+// CTAs shares its A and B panels through L2.
+// Roofline: tensor-bound, 2*M*N*K FLOP per batch entry.
+#include "common.cuh"
+#include "kernels.h"
+#include "sm100.cuh"
+
+namespace ib {
+namespace {
+
+using namespace sm100;
+
+constexpr int kBM = 128;
+constexpr int kBK = 32;            // fp32 per 128-byte swizzled row
+constexpr int kStages = 4;
+constexpr int kGroupN = 12;        // n-tiles per raster group
+constexpr int kThreads = 192;
+
+template <int BN>
+struct Smem {
+  static constexpr int kABytes = kBM * kBK * 4;
+  static constexpr int kBBytes = BN * kBK * 4;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+struct TileCoord {
+  int batch, m_tile, n_tile;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(long long id, int tiles_m, int tiles_n) {
+  const long long per_batch = static_cast<long long>(tiles_m) * tiles_n;
+  TileCoord t;
+  t.batch = static_cast<int>(id / per_batch);
+  long long within = id - t.batch * per_batch;
+  const long long group_span = static_cast<long long>(tiles_m) * kGroupN;
+  int group = static_cast<int>(within / group_span);
+  long long in_group = within - group * group_span;
+  int width = tiles_n - group * kGroupN;
+  if (width > kGroupN) width = kGroupN;
+  t.m_tile = static_cast<int>(in_group / width);
+  t.n_tile = group * kGroupN + static_cast<int>(in_group % width);
+  return t;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 float* __restrict__ c, int m, int n, int k, int batch, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  using L = Smem<BN>;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * L::kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_full = empty + kStages;      // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  AbortState* abort = reinterpret_cast<AbortState*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (m + kBM - 1) / kBM;
+  const int tiles_n = (n + BN - 1) / BN;
+  const long long total_tiles = static_cast<long long>(tiles_m) * tiles_n * batch;
+  const int k_blocks = (k + kBK - 1) / kBK;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
+    abort->flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_descriptor(&map_a);
+      tma_prefetch_descriptor(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
+        const TileCoord t = tile_coord(id, tiles_m, tiles_n);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort, status, 101))) break;
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
+          tma_load_3d(sa, &map_a, &full[stage], kb * kBK, t.m_tile * kBM, t.batch);
+          tma_load_3d(sb, &map_b, &full[stage], kb * kBK, t.n_tile * BN, t.batch);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(Kind::TF32, kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
+        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort, status, 102))) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&full[stage], phase, abort, status, 103))) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint64_t a_desc = make_smem_desc_sw128(sa);
+          const uint64_t b_desc = make_smem_desc_sw128(sa + L::kABytes);
+#pragma unroll
+          for (int ks = 0; ks < kBK / 8; ++ks) {
+            // 8 fp32 = 32 bytes along K inside the swizzled row: +2 in the
+            // descriptor's 16-byte address units.
+            mma_ss<Kind::TF32>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
+                               (kb | ks) != 0 ? 1u : 0u);
+          }
+          mma_commit(&empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        mma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // Epilogue warps 2..5; TMEM lane quadrant is warp % 4.
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool vec_ok = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+    for (long long id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
+      const TileCoord t = tile_coord(id, tiles_m, tiles_n);
+      ok = mbar_wait(&acc_full[acc], acc_phase, abort, status, 104);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = t.m_tile * kBM + quad * 32 + lane;
+      float* crow = c + (static_cast<size_t>(t.batch) * m + row) * n;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + chunk * 32, r);
+        tmem_wait_ld();
+        const int col0 = t.n_tile * BN + chunk * 32;
+        if (row < m) {
+          if (vec_ok && col0 + 32 <= n) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<float4*>(crow + col0 + 4 * v) =
+                  make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                              __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+          } else {
+#pragma unroll
+            for (int v = 0; v < 32; ++v)
+              if (col0 + v < n) crow[col0 + v] = __uint_as_float(r[v]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
+           size_t n, size_t k, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tf32_kernel<BN>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Smem<BN>::kTotal);
+    if (err != cudaSuccess)
+      return fail(std::string("ib_contract: cannot reserve shared memory: ") +
+                  cudaGetErrorString(err));
+    configured = true;
+  }
+  int* status = device_status_word(s);
+  if (!status) return fail("ib_contract: cannot allocate the device status word");
+  const size_t tiles = ((m + kBM - 1) / kBM) * ((n + BN - 1) / BN) * batch;
+  int sms = kNumSMs;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = static_cast<int>(tiles < static_cast<size_t>(sms) ? tiles : sms);
+  gemm_tf32_kernel<BN><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
+      map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
+      static_cast<int>(batch), status);
+  return check_launch("ib_contract (tcgen05 tf32)");
+}
+
+}  // namespace
+
+bool gemm_tcgen05_supported(const float* a, const float* b, const float* c, size_t m, size_t n,
+                            size_t k) {
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  return aligned(a) && aligned(b) && c != nullptr && k % 4 == 0 && k >= 4 && m >= 1 && n >= 1 &&
+         m < (1u << 30) && n < (1u << 30) && k < (1u << 30);
+}
+
+int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
+                 size_t k, cudaStream_t s) {
+  if (batch == 0 || m == 0 || n == 0) return 0;
+  if (!gemm_tcgen05_supported(a, b, c, m, n, k))
+    return fail("ib_contract: shape or alignment not supported by the tensor-core arm");
+  if (batch >= (1u << 30)) return fail("ib_contract: too many batch entries");
+  const bool wide = n > 128;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_tensor_map_f32(&map_a, a, batch, m, k, k, m * k, kBM)) return rc;
+  if (int rc = make_tensor_map_f32(&map_b, b, batch, n, k, k, n * k, wide ? 256 : 128)) return rc;
+  return wide ? launch<256>(map_a, map_b, c, batch, m, n, k, s)
+              : launch<128>(map_a, map_b, c, batch, m, n, k, s);
+}
+
+}  // namespace ib

@@ -1,0 +1,49 @@
+// Internal interfaces between the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace ib {
+
+// contract_simt.cu
+int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
+                  size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s);
+// out[b][c][r] = in[b][r][c]; rows of `out` are `out_pitch` elements apart.
+int transpose_batched(const float* in, float* out, size_t batch, size_t rows, size_t cols,
+                      size_t out_pitch, cudaStream_t s);
+
+// tensor_map.cu — encodes a TMA descriptor for a dense fp32 tensor
+// [batch][rows][cols] (cols contiguous, `row_pitch` elements between rows) read
+// in boxes of 32 columns (128 bytes, 128-byte swizzle) x box_rows rows.
+// Returns 0, or -1 with the error recorded.
+int make_tensor_map_f32(CUtensorMap* map, const float* base, size_t batch, size_t rows,
+                        size_t cols, size_t row_pitch, size_t batch_pitch, unsigned box_rows);
+
+// Per-launch status word the tcgen05 kernels report bounded-wait timeouts into.
+// Lives in device memory owned by the library; zeroed before each launch that
+// uses it and read back only on demand.
+int* device_status_word(cudaStream_t s);
+int check_device_status(const char* what, cudaStream_t s);
+
+// gemm_tcgen05.cu — C[b][i][j] = sum_k A[b][i][k] B[b][j][k], both operands
+// K-major fp32 fed to tcgen05 kind::tf32.
+bool gemm_tcgen05_supported(const float* a, const float* b, const float* c, size_t m, size_t n,
+                            size_t k);
+int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
+                 size_t k, cudaStream_t s);
+
+// attention_tcgen05.cu — fused online-softmax attention; vt is V transposed to
+// [b][dv][nk_pitch].
+bool attention_tcgen05_supported(const float* q, const float* k, const float* o, size_t d,
+                                 size_t dv);
+// Floats of scratch the KV-split partials need (0 when one CTA covers all keys).
+size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv,
+                                        int* splits_out);
+int attention_tcgen05(const float* q, const float* k, const float* vt, float* o, size_t batch,
+                      size_t nq, size_t nk, size_t d, size_t dv, size_t nk_pitch, float* partials,
+                      cudaStream_t s);
+
+}  // namespace ib

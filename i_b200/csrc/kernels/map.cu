@@ -1,0 +1,256 @@
+// Pointwise maps: memory-bound, 128-bit vectorised, grid sized in SM multiples.
+//
+// Scalar semantics follow the reference's lowering
+// (compiler/src/lower/exec_plan_to_module.rs:605-640 for unary defaults,
+// compiler/src/backends/c/expr.rs:127-148 for the binary spelling).
+// Algorithmic traffic: (operands + 1) * elements * 4 bytes, a broadcast operand
+// counted at its own size.
+#include "common.cuh"
+
+namespace ib {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVecPerThread = 4;  // float4 loads in flight per thread
+
+inline int grid_for(size_t work_items, size_t per_block) {
+  size_t blocks = (work_items + per_block - 1) / per_block;
+  size_t cap = static_cast<size_t>(kNumSMs) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+map_unary_vec(const float4* __restrict__ x, float4* __restrict__ y, size_t nvec) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads * kVecPerThread;
+  for (size_t base = (static_cast<size_t>(blockIdx.x) * kThreads) * kVecPerThread + threadIdx.x;
+       base < nvec; base += stride) {
+    float4 v[kVecPerThread];
+#pragma unroll
+    for (int u = 0; u < kVecPerThread; ++u) {
+      size_t i = base + static_cast<size_t>(u) * kThreads;
+      if (i < nvec) v[u] = __ldcs(x + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kVecPerThread; ++u) {
+      size_t i = base + static_cast<size_t>(u) * kThreads;
+      if (i < nvec) {
+        float4 r;
+        r.x = apply_unary(OP, v[u].x);
+        r.y = apply_unary(OP, v[u].y);
+        r.z = apply_unary(OP, v[u].z);
+        r.w = apply_unary(OP, v[u].w);
+        __stcs(y + i, r);
+      }
+    }
+  }
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+map_unary_scalar(const float* __restrict__ x, float* __restrict__ y, size_t begin, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = begin + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+       i += stride)
+    y[i] = apply_unary(OP, x[i]);
+}
+
+// Element e of a rows x cols result reads a[e] or a[r] or a[c] depending on mode.
+template <int OP, int MODE>
+__device__ __forceinline__ float binary_at(const float* __restrict__ a, const float* __restrict__ b,
+                                           size_t e, size_t r, size_t c) {
+  float lhs = (MODE == 2) ? a[r] : (MODE == 4) ? a[c] : a[e];
+  float rhs = (MODE == 1) ? b[r] : (MODE == 3) ? b[c] : b[e];
+  return apply_binary(OP, lhs, rhs);
+}
+
+// cols % 4 == 0 and 16-byte aligned full operands: one float4 of the result per step.
+template <int OP, int MODE>
+__global__ void __launch_bounds__(kThreads)
+map_binary_vec(const float* __restrict__ a, const float* __restrict__ b, float4* __restrict__ y,
+               size_t nvec, size_t cols) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  const size_t cvec = cols / 4;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+    size_t r = i / cvec;
+    size_t c = (i - r * cvec) * 4;
+    float4 va, vb;
+    if (MODE == 2) {
+      float s = a[r];
+      va = make_float4(s, s, s, s);
+    } else if (MODE == 4) {
+      va = *reinterpret_cast<const float4*>(a + c);
+    } else {
+      va = __ldcs(reinterpret_cast<const float4*>(a) + i);
+    }
+    if (MODE == 1) {
+      float s = b[r];
+      vb = make_float4(s, s, s, s);
+    } else if (MODE == 3) {
+      vb = *reinterpret_cast<const float4*>(b + c);
+    } else {
+      vb = __ldcs(reinterpret_cast<const float4*>(b) + i);
+    }
+    float4 out;
+    out.x = apply_binary(OP, va.x, vb.x);
+    out.y = apply_binary(OP, va.y, vb.y);
+    out.z = apply_binary(OP, va.z, vb.z);
+    out.w = apply_binary(OP, va.w, vb.w);
+    __stcs(y + i, out);
+  }
+}
+
+template <int OP, int MODE>
+__global__ void __launch_bounds__(kThreads)
+map_binary_scalar(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y,
+                  size_t n, size_t cols) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t e = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; e < n; e += stride) {
+    size_t r = e / cols;
+    size_t c = e - r * cols;
+    y[e] = binary_at<OP, MODE>(a, b, e, r, c);
+  }
+}
+
+struct StridedArgs {
+  int rank;
+  size_t extent[IB_MAX_RANK];
+  ptrdiff_t sa[IB_MAX_RANK];
+  ptrdiff_t sb[IB_MAX_RANK];
+};
+
+template <int OP, bool BINARY>
+__global__ void __launch_bounds__(kThreads)
+map_strided(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y,
+            size_t n, StridedArgs args) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t e = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; e < n; e += stride) {
+    size_t rest = e;
+    ptrdiff_t oa = 0, ob = 0;
+    for (int d = args.rank - 1; d >= 0; --d) {
+      size_t q = rest / args.extent[d];
+      size_t coord = rest - q * args.extent[d];
+      rest = q;
+      oa += static_cast<ptrdiff_t>(coord) * args.sa[d];
+      if (BINARY) ob += static_cast<ptrdiff_t>(coord) * args.sb[d];
+    }
+    y[e] = BINARY ? apply_binary(OP, a[oa], b[ob]) : apply_unary(OP, a[oa]);
+  }
+}
+
+template <int OP>
+int launch_unary(const float* x, float* y, size_t n, cudaStream_t s) {
+  size_t done = 0;
+  if (aligned16(x) && aligned16(y) && n >= 4) {
+    size_t nvec = n / 4;
+    map_unary_vec<OP><<<grid_for(nvec, kThreads * kVecPerThread), kThreads, 0, s>>>(
+        reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), nvec);
+    if (int rc = check_launch("ib_map_unary")) return rc;
+    done = nvec * 4;
+  }
+  if (done < n) {
+    map_unary_scalar<OP><<<grid_for(n - done, kThreads), kThreads, 0, s>>>(x, y, done, n);
+    if (int rc = check_launch("ib_map_unary")) return rc;
+  }
+  return 0;
+}
+
+template <int OP, int MODE>
+int launch_binary(const float* a, const float* b, float* y, size_t rows, size_t cols,
+                  cudaStream_t s) {
+  const size_t n = rows * cols;
+  const bool a_full = MODE != 2 && MODE != 4, b_full = MODE != 1 && MODE != 3;
+  bool vec = cols % 4 == 0 && aligned16(y) && (!a_full || aligned16(a)) &&
+             (!b_full || aligned16(b)) && (MODE != 4 || aligned16(a)) &&
+             (MODE != 3 || aligned16(b));
+  if (vec) {
+    size_t nvec = n / 4;
+    map_binary_vec<OP, MODE><<<grid_for(nvec, kThreads), kThreads, 0, s>>>(
+        a, b, reinterpret_cast<float4*>(y), nvec, cols);
+  } else {
+    map_binary_scalar<OP, MODE><<<grid_for(n, kThreads), kThreads, 0, s>>>(a, b, y, n, cols);
+  }
+  return check_launch("ib_map_binary");
+}
+
+template <int OP>
+int dispatch_mode(int mode, const float* a, const float* b, float* y, size_t rows, size_t cols,
+                  cudaStream_t s) {
+  switch (mode) {
+    case 0: return launch_binary<OP, 0>(a, b, y, rows, cols, s);
+    case 1: return launch_binary<OP, 1>(a, b, y, rows, cols, s);
+    case 2: return launch_binary<OP, 2>(a, b, y, rows, cols, s);
+    case 3: return launch_binary<OP, 3>(a, b, y, rows, cols, s);
+    case 4: return launch_binary<OP, 4>(a, b, y, rows, cols, s);
+  }
+  return fail("ib_map_binary: mode must be 0..4");
+}
+
+template <int OP>
+int launch_strided(const float* a, const float* b, float* y, size_t n, const StridedArgs& args,
+                   cudaStream_t s) {
+  if (b)
+    map_strided<OP, true><<<grid_for(n, kThreads), kThreads, 0, s>>>(a, b, y, n, args);
+  else
+    map_strided<OP, false><<<grid_for(n, kThreads), kThreads, 0, s>>>(a, b, y, n, args);
+  return check_launch("ib_map_strided");
+}
+
+}  // namespace
+}  // namespace ib
+
+#define IB_DISPATCH_OP(op, CALL)                                   \
+  switch (op) {                                                    \
+    case IB_OP_ADD: return CALL(IB_OP_ADD);                        \
+    case IB_OP_MUL: return CALL(IB_OP_MUL);                        \
+    case IB_OP_SUB: return CALL(IB_OP_SUB);                        \
+    case IB_OP_DIV: return CALL(IB_OP_DIV);                        \
+    case IB_OP_MAX: return CALL(IB_OP_MAX);                        \
+    case IB_OP_MIN: return CALL(IB_OP_MIN);                        \
+    case IB_OP_POW: return CALL(IB_OP_POW);                        \
+    case IB_OP_LOG: return CALL(IB_OP_LOG);                        \
+    default: return ib::fail("unknown operator code");             \
+  }
+
+extern "C" int ib_map_unary(int op, const float* x, float* y, size_t n, void* stream) {
+  if (n == 0) return 0;
+  if (!x || !y) return ib::fail("ib_map_unary: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CALL(OP) ib::launch_unary<OP>(x, y, n, s)
+  IB_DISPATCH_OP(op, CALL)
+#undef CALL
+}
+
+extern "C" int ib_map_binary(int op, int mode, const float* a, const float* b, float* y,
+                             size_t rows, size_t cols, void* stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (!a || !b || !y) return ib::fail("ib_map_binary: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CALL(OP) ib::dispatch_mode<OP>(mode, a, b, y, rows, cols, s)
+  IB_DISPATCH_OP(op, CALL)
+#undef CALL
+}
+
+extern "C" int ib_map_strided(int op, const float* a, const float* b, float* y, int rank,
+                              const size_t* extent, const ptrdiff_t* stride_a,
+                              const ptrdiff_t* stride_b, void* stream) {
+  if (rank < 0 || rank > IB_MAX_RANK) return ib::fail("ib_map_strided: rank out of range");
+  if (!a || !y || (rank > 0 && (!extent || !stride_a)) || (b && rank > 0 && !stride_b))
+    return ib::fail("ib_map_strided: null pointer");
+  ib::StridedArgs args{};
+  args.rank = rank;
+  size_t n = 1;
+  for (int d = 0; d < rank; ++d) {
+    args.extent[d] = extent[d];
+    args.sa[d] = stride_a[d];
+    args.sb[d] = b ? stride_b[d] : 0;
+    n *= extent[d];
+  }
+  if (n == 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CALL(OP) ib::launch_strided<OP>(a, b, y, n, args, s)
+  IB_DISPATCH_OP(op, CALL)
+#undef CALL
+}

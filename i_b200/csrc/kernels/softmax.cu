@@ -1,0 +1,149 @@
+// Fused row softmax: the reference's three naive kernels
+// (ilang-python/flash-attn.py:60-62 — `>ij~i`, `ij-i~ij`, `^ij~ij`, `+ij~i`,
+// `ij/i~ij`) collapsed into one pass that keeps the row on chip.
+//
+// Per row: m = max_c x; e_c = powf(2.71828175f, x_c - m); l = sum_c e_c;
+// y_c = e_c / l.  The reference moves 8 matrix-sized streams through memory for
+// this chain (two full intermediates); here the row is read once into
+// registers and written once, so the algorithmic traffic is 2*rows*cols*4 bytes.
+#include "common.cuh"
+
+namespace ib {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int OP, int TPR>
+__device__ __forceinline__ float row_fold(float v, float* scratch, int row_in_block) {
+  v = warp_fold<OP>(v);
+  if (TPR == 32) return v;
+  // TPR == kThreads: one row per CTA.
+  const int warp = threadIdx.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = scratch[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) r = fold<OP>(r, scratch[w]);
+  return r;
+}
+
+// Row held in registers: VPT float4 per thread, TPR threads per row.
+template <int VPT, int TPR, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+row_softmax_regs(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols) {
+  __shared__ float scratch[kThreads / 32];
+  constexpr int kRowsPerBlock = kThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int row_in_block = threadIdx.x / TPR;
+  const size_t row_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  for (size_t rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    const size_t r = rb * kRowsPerBlock + row_in_block;
+    const bool live = r < rows;
+    const float* xr = x + r * cols;
+    float* yr = y + r * cols;
+    float v[VPT * 4];
+    float m = -CUDART_INF_F;
+    if (VEC) {
+      const size_t nvec = cols / 4;
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        size_t i = static_cast<size_t>(u) * TPR + t;
+        float4 q = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+        if (live && i < nvec) q = __ldcs(reinterpret_cast<const float4*>(xr) + i);
+        v[4 * u + 0] = q.x; v[4 * u + 1] = q.y; v[4 * u + 2] = q.z; v[4 * u + 3] = q.w;
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < VPT * 4; ++u) {
+        size_t i = static_cast<size_t>(u) * TPR + t;
+        v[u] = (live && i < cols) ? xr[i] : -CUDART_INF_F;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < VPT * 4; ++u) m = fmaxf(m, v[u]);
+    m = row_fold<IB_OP_MAX, TPR>(m, scratch, row_in_block);
+    float l = 0.0f;
+#pragma unroll
+    for (int u = 0; u < VPT * 4; ++u) {
+      // Padding lanes hold -inf and contribute exp(-inf) = 0.
+      v[u] = exp_e32(v[u] - m);
+      l += v[u];
+    }
+    l = row_fold<IB_OP_ADD, TPR>(l, scratch, row_in_block);
+    if (VEC) {
+      const size_t nvec = cols / 4;
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        size_t i = static_cast<size_t>(u) * TPR + t;
+        if (live && i < nvec)
+          __stcs(reinterpret_cast<float4*>(yr) + i,
+                 make_float4(v[4 * u] / l, v[4 * u + 1] / l, v[4 * u + 2] / l, v[4 * u + 3] / l));
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < VPT * 4; ++u) {
+        size_t i = static_cast<size_t>(u) * TPR + t;
+        if (live && i < cols) yr[i] = v[u] / l;
+      }
+    }
+  }
+}
+
+// Rows too long for registers: three streaming passes, one CTA per row.
+__global__ void __launch_bounds__(kThreads)
+row_softmax_stream(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols) {
+  __shared__ float scratch[kThreads / 32];
+  for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* xr = x + r * cols;
+    float* yr = y + r * cols;
+    float m = -CUDART_INF_F;
+    for (size_t i = threadIdx.x; i < cols; i += kThreads) m = fmaxf(m, xr[i]);
+    m = row_fold<IB_OP_MAX, kThreads>(m, scratch, 0);
+    float l = 0.0f;
+    for (size_t i = threadIdx.x; i < cols; i += kThreads) {
+      float e = exp_e32(xr[i] - m);
+      yr[i] = e;
+      l += e;
+    }
+    l = row_fold<IB_OP_ADD, kThreads>(l, scratch, 0);
+    for (size_t i = threadIdx.x; i < cols; i += kThreads) yr[i] = yr[i] / l;
+    __syncthreads();
+  }
+}
+
+template <int VPT, int TPR>
+int launch_regs(const float* x, float* y, size_t rows, size_t cols, cudaStream_t s) {
+  constexpr int kRowsPerBlock = kThreads / TPR;
+  size_t blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  size_t cap = static_cast<size_t>(kNumSMs) * 64;
+  int grid = static_cast<int>(blocks < cap ? blocks : cap);
+  const bool vec = cols % 4 == 0 && aligned16(x) && aligned16(y);
+  if (vec)
+    row_softmax_regs<VPT, TPR, true><<<grid, kThreads, 0, s>>>(x, y, rows, cols);
+  else
+    row_softmax_regs<VPT, TPR, false><<<grid, kThreads, 0, s>>>(x, y, rows, cols);
+  return check_launch("ib_row_softmax");
+}
+
+}  // namespace
+}  // namespace ib
+
+extern "C" int ib_row_softmax(const float* x, float* y, size_t rows, size_t cols, void* stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (!x || !y) return ib::fail("ib_row_softmax: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  using namespace ib;
+  if (cols <= 128) return launch_regs<1, 32>(x, y, rows, cols, s);
+  if (cols <= 256) return launch_regs<2, 32>(x, y, rows, cols, s);
+  if (cols <= 512) return launch_regs<4, 32>(x, y, rows, cols, s);
+  if (cols <= 1024) return launch_regs<8, 32>(x, y, rows, cols, s);
+  if (cols <= 2048) return launch_regs<2, 256>(x, y, rows, cols, s);
+  if (cols <= 4096) return launch_regs<4, 256>(x, y, rows, cols, s);
+  if (cols <= 8192) return launch_regs<8, 256>(x, y, rows, cols, s);
+  if (cols <= 16384) return launch_regs<16, 256>(x, y, rows, cols, s);
+  size_t cap = static_cast<size_t>(kNumSMs) * 8;
+  row_softmax_stream<<<static_cast<int>(rows < cap ? rows : cap), kThreads, 0, s>>>(x, y, rows,
+                                                                                    cols);
+  return check_launch("ib_row_softmax");
+}
