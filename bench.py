@@ -1,0 +1,413 @@
+"""Benchmark of the hot path: the fused i-attention component on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 4): one head, seq_q = seq_kv = 16384, head dim 128,
+fp32 Q/K/V ~ N(0,1) from seed 3 with Q scaled by 1/sqrt(128), no mask.  A step
+is one invocation of the compiled README attention component on one head.  At
+N > 1 every rank runs its own head per step (heads are the independent units,
+weak scaling) and the outputs are all-gathered over NCCL on a side stream so the
+gather of step s overlaps the kernel of step s+1.  Inputs rotate over several
+distinct sets whose total size exceeds L2, so no step starts with its operands
+cached.
+
+One JSON line is printed by rank 0:
+  value      TFLOP/s over all ranks with inputs resident in HBM (4*Nq*Nk*d FLOP
+             per head), timed with CUDA events, max over ranks
+  e2e        the same metric through the host-pointer C ABI (i_exec_into): every
+             step copies Q, K, V from pinned host memory and O back
+  roofline   tensor-bound: achieved = FLOP per step / average step time; the
+             peak is MEASURED_PEAKS.json's dense bf16 figure halved (the TF32
+             MMA issues at half the bf16 rate)
+  cpu_baseline  the reference's own emitted C (oracle/_ref) on the host cores,
+             on a bounded row sample of the same workload
+--impl reference times only that CPU program (rank 0; other ranks exit).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SEQ, DIM = 16384, 128
+FLOP_PER_HEAD = 4.0 * SEQ * SEQ * DIM
+METRIC = "fused i-attention TFLOP/s at seq16K d128"
+WORKLOAD = "config4: single-head fused i-attention, seq_q=seq_kv=16384, d=128, fp32 N(0,1) seed 3, Q*1/sqrt(128)"
+ROTATION = 8          # distinct input sets: 8 x 32 MiB = 256 MiB > 126 MB L2
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+def make_inputs(seed=3, heads=1):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((heads, SEQ, DIM), dtype=np.float32)
+    k = rng.standard_normal((heads, SEQ, DIM), dtype=np.float32)
+    v = rng.standard_normal((heads, SEQ, DIM), dtype=np.float32)
+    q *= np.float32(1.0 / np.sqrt(DIM))
+    return q, k, v
+
+
+def readme_attention(ilang):
+    i, I = ilang.i, ilang.I
+    mm_t = i("ik*jk~ijk | i:16,j:16 | jii'j'k") >> i("+ijk~ij | i:16,j:16 | jii'j'k0")
+    row_max_shift = (I & i(">ij~i | i:16,j:16 | ji0i'j'")) >> i("ij-i~ij | i:16,j:16 | ji01i'j'")
+    exp = i("^ij~ij | i:16,j:16 | ji0i'j'")
+    row_normalize = (I & i("+ij~i | i:16,j:16 | ji0i'j'")) >> i("ij/i~ij | i:16,j:16 | ji01i'j'")
+    mm = i("ij*jk~ikj | i:16,j:16 | ji0i'kj'") >> i("+ikj~ik | i:16,j:16 | jii'kj'0")
+    return mm_t >> row_max_shift >> exp >> row_normalize >> mm
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the reference's own emitted C on the host cores.
+# ---------------------------------------------------------------------------
+
+def cpu_reference_sample(rows_per_core, repeats=1):
+    """Times oracle/_ref (or the restated oracle when _ref is absent) on
+    cores x rows_per_core query rows against the full 16384 keys."""
+    import numpy as np
+    import oracle
+    cores = os.cpu_count() or 1
+    q, k, v = make_inputs()
+    q, k, v = q[0], k[0], v[0]
+    kind = "reference" if oracle.have_reference() else "port"
+    fn = oracle.reference_attention if kind == "reference" else oracle.attention_fused
+    stride = SEQ // cores
+    blocks = [(c * stride, c * stride + rows_per_core) for c in range(cores)]
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.reference_attention_rows(q, k, v, blocks, threads=cores, fn=fn)
+        times.append(time.perf_counter() - t0)
+    rows = cores * rows_per_core
+    flop = 4.0 * rows * SEQ * DIM
+    return {"kind": kind, "cores": cores, "rows": rows, "times": times, "flop": flop,
+            "sample": "%d query rows (%d per core) x all 16384 keys of the config-4 head; "
+                      "rows are independent, so cost is linear in rows" % (rows, rows_per_core)}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows_per_core = 32         # about a third of a second per step on each core
+    for _ in range(args.warmup):
+        cpu_reference_sample(rows_per_core)
+    res = cpu_reference_sample(rows_per_core, repeats=args.steps)
+    total = sum(res["times"])
+    value = res["flop"] * args.steps / total / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "step": res["sample"]},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": res["cores"],
+                         "kind": res["kind"], "sample": res["sample"]},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# Clock sampling through NVML (read-only).
+# ---------------------------------------------------------------------------
+
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            # CUDA ordinals follow CUDA_VISIBLE_DEVICES; NVML's do not.  Match by UUID.
+            import torch
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        n = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+                mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._nvml:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ---------------------------------------------------------------------------
+# GPU arm.
+# ---------------------------------------------------------------------------
+
+def secondary_metrics(torch, ilang, peaks):
+    """Map / reduce / contraction figures of the other BASELINE configs (N = 1 only)."""
+    import ctypes
+    lib = ilang.core()
+    vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    lib.ib_map_unary.argtypes = [ci, vp, vp, sz, vp]
+    lib.ib_reduce_rows.argtypes = [ci, vp, vp, sz, sz, vp]
+    lib.ib_row_softmax.argtypes = [vp, vp, sz, sz, vp]
+    lib.ib_contract.argtypes = [vp, vp, vp, sz, sz, sz, sz, ci, ci, ci, vp, sz, vp]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, iters, flush):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(iters):
+            flush.zero_()                      # 256 MiB write: evicts L2
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / iters
+
+    out = {}
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    x = 2.0 * torch.randn(8192, 8192, device="cuda", generator=g)
+    y = torch.empty_like(x)
+    nbytes = 2.0 * x.numel() * 4
+    ms = timed(lambda: lib.ib_row_softmax(x.data_ptr(), y.data_ptr(), 8192, 8192, stream), 10, flush)
+    out["row_softmax_8192x8192"] = {"gbs": nbytes / ms / 1e6, "ms": ms,
+                                    "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    ms = timed(lambda: lib.ib_map_unary(6, x.data_ptr(), y.data_ptr(), x.numel(), stream), 10, flush)
+    out["map_exp_8192x8192"] = {"gbs": nbytes / ms / 1e6, "ms": ms,
+                                "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    r = torch.empty(8192, device="cuda")
+    rbytes = x.numel() * 4.0 + 8192 * 4
+    ms = timed(lambda: lib.ib_reduce_rows(0, x.data_ptr(), r.data_ptr(), 8192, 8192, stream), 10, flush)
+    out["reduce_sum_rows_8192x8192"] = {"gbs": rbytes / ms / 1e6, "ms": ms,
+                                        "frac_hbm": rbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del x, y
+    g.manual_seed(2)
+    a = 2 * torch.rand(8192, 4096, device="cuda", generator=g) - 1
+    b = 2 * torch.rand(8192, 4096, device="cuda", generator=g) - 1
+    c = torch.empty(8192, 8192, device="cuda")
+    flop = 2.0 * 8192 * 8192 * 4096
+    ms = timed(lambda: lib.ib_contract(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, 8192, 8192, 4096,
+                                       1, 1, 2, None, 0, stream), 10, flush)
+    out["mm_t_8192x8192x4096_tf32"] = {"tflops": flop / ms / 1e9, "ms": ms,
+                                       "frac_tf32_peak": flop / ms / 1e9 / (peaks["bf16_tflops"] / 2)}
+    torch.backends.cuda.matmul.allow_tf32 = True
+    ms = timed(lambda: torch.matmul(a, b.t(), out=c), 10, flush)
+    out["cublas_tf32_8192x8192x4096"] = {"tflops": flop / ms / 1e9, "ms": ms}
+    return out
+
+
+def run_gpu_arm(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the hot path has no CPU fallback)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from i_b200 import build as lib_build
+    if not os.path.exists(lib_build.LIB):
+        lib_build.build()
+    from i_b200 import ilang
+
+    peaks = load_peaks()
+    attn = readme_attention(ilang).set_precision("tf32")
+
+    # Distinct input sets per rank (seed 3 for set 0 of rank 0, as BASELINE names).
+    sets = []
+    for s in range(ROTATION):
+        q, k, v = make_inputs(seed=3 + 1000 * rank + s)
+        sets.append(tuple(torch.from_numpy(t[0]).cuda() for t in (q, k, v)))
+    gathered = [torch.empty(world, SEQ, DIM, device="cuda") for _ in range(2)]
+    outs = [g[rank] for g in gathered]
+    main = torch.cuda.current_stream()
+    side = torch.cuda.Stream() if world > 1 else None
+    gather_done = [None, None]
+    computed = torch.cuda.Event()
+
+    def step(s):
+        q, k, v = sets[s % ROTATION]
+        buf = s % 2
+        if gather_done[buf] is not None:
+            main.wait_event(gather_done[buf])  # the gather of step s-2 still reads this buffer
+        attn.into(outs[buf], q, k, v)
+        if side is not None:
+            computed.record(main)
+            side.wait_event(computed)
+            with torch.cuda.stream(side):
+                dist.all_gather_into_tensor(gathered[buf].view(-1), outs[buf].reshape(-1))
+                gather_done[buf] = torch.cuda.Event()
+                gather_done[buf].record(side)
+
+    for s in range(max(args.warmup, 3)):
+        step(s)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = ilang.launch_count()
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin.record(main)
+    for s in range(args.steps):
+        step(s)
+    if side is not None:
+        main.wait_stream(side)
+    t_end.record(main)
+    torch.cuda.synchronize()
+    launches = ilang.launch_count() - launches0
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = world * FLOP_PER_HEAD / ms_per_step / 1e9
+
+    # End to end through the host-pointer C ABI (i_exec_into), pinned host buffers.
+    hq, hk, hv = (torch.from_numpy(t[0]).pin_memory() for t in make_inputs(seed=3 + 1000 * rank))
+    ho = torch.empty(SEQ, DIM).pin_memory()
+    nq, nk, nv, no = (t.numpy() for t in (hq, hk, hv, ho))
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        attn.into(no, nq, nk, nv)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        attn.into(no, nq, nk, nv)              # returns when O is back in host memory
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    sampler.stop()
+    e2e_value = world * FLOP_PER_HEAD * e2e_steps / e2e_s / 1e12
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # Parity spot check of the timed kernel against the CPU oracle (never timed).
+    import oracle
+    q0, k0, v0 = (t.cpu().numpy() for t in sets[0])
+    got = attn.exec_torch(*sets[0]).cpu().numpy()
+    rows = np.array([0, 255, 4096, 8191, 16383])
+    ref = oracle.attention_fused(q0[rows], k0, v0)
+    parity = float(np.abs(got[rows] - ref).max() / np.abs(ref).max())
+
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    achieved = FLOP_PER_HEAD / ms_per_step / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f).get("attention_tf32_kernel", {}).get("dram_bytes_per_launch")
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "units_per_rank_per_step": 1,
+                   "l2": "inputs rotate over %d distinct sets (256 MiB) > 126 MB L2" % ROTATION,
+                   "multi_gpu": "one head per rank per step, NCCL all-gather of O on a side stream",
+                   "precision": "tcgen05 kind::tf32, fp32 accumulate",
+                   "parity_max_rel_to_peak_vs_oracle": parity},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+                     "frac": achieved / tf32_peak, "traffic": traffic,
+                     "peak_source": "%s bf16_tflops %.1f / 2 (TF32 MMA issues at half the bf16 rate)"
+                                    % (peaks["source"], peaks["bf16_tflops"]),
+                     "frac_of_bf16_peak": achieved / peaks["bf16_tflops"],
+                     "note": "achieved = 4*Nq*Nk*d FLOP / average step time on one rank; a step "
+                             "launches the operand-preparation, attention and merge kernels"},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * SEQ * DIM * 4,
+                "d2h_bytes_per_step": SEQ * DIM * 4, "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": sampler.summary(),
+    }
+    if world == 1:
+        res = cpu_reference_sample(256)        # ~20 s of CPU work over all cores
+        line["cpu_baseline"] = {"value": res["flop"] / res["times"][0] / 1e12, "unit": "TFLOP/s",
+                                "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]}
+        if not args.no_secondary:
+            line["secondary"] = secondary_metrics(torch, ilang, peaks)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the map/reduce/contraction side measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

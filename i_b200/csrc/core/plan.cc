@@ -404,6 +404,24 @@ std::string Plan::describe() const {
   return os.str();
 }
 
+std::string describe_graph(const Graph& g) {
+  std::ostringstream os;
+  os << "graph: " << g.n_inputs << " inputs, " << g.nodes.size() << " nodes\n";
+  for (size_t n = 0; n < g.nodes.size(); ++n) {
+    const Node& node = g.nodes[n].inner;
+    os << "  n" << n << " " << op_name(node.op) << " ";
+    for (size_t i = 0; i < node.inputs.size(); ++i)
+      os << (i ? "," : "") << "[" << index_text(node.inputs[i]) << "]";
+    os << "~[" << index_text(node.output) << "] <-";
+    for (const auto& src : g.nodes[n].inputs) os << " " << (src.is_input ? "in" : "n") << src.index;
+    os << "\n";
+  }
+  os << "  outputs:";
+  for (const auto& src : g.outputs) os << " " << (src.is_input ? "in" : "n") << src.index;
+  os << "\n";
+  return os.str();
+}
+
 Result<Plan> make_plan(const Graph& g) {
   Builder b(g);
   if (auto err = basic_steps(b)) return Result<Plan>::failure(*err);

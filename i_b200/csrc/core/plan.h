@@ -73,4 +73,8 @@ struct Plan {
 
 Result<Plan> make_plan(const Graph& g);
 
+// Text form of the wired graph: one line per node (op, index patterns, sources)
+// and the output list.  Printed by i_code ahead of the plan.
+std::string describe_graph(const Graph& g);
+
 }  // namespace ib

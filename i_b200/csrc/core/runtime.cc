@@ -647,9 +647,10 @@ i_component* i_swap(const i_component* component) {
 
 char* i_code(const i_component* component) {
   if (!component) return null_with_error<char>("null component");
-  ib::Result<ib::Plan> plan = plan_component(component, nullptr);
+  ib::Graph graph;
+  ib::Result<ib::Plan> plan = plan_component(component, &graph);
   if (!plan.ok()) return null_with_error<char>(plan.error.text);
-  std::string text = plan.value->describe();
+  std::string text = plan.value->describe() + ib::describe_graph(graph);
   char* out = static_cast<char*>(std::malloc(text.size() + 1));
   if (!out) return null_with_error<char>("out of memory");
   std::memcpy(out, text.c_str(), text.size() + 1);

@@ -72,7 +72,7 @@ struct Barriers {
   uint64_t kv_empty[kMaxRing];
   uint64_t s_full[2][2];
   uint64_t p_full[2][2];
-  uint64_t pv_done[2];
+  uint64_t pv_done[2][2];   // [tile][KV tile parity]: see the note at its wait
   uint32_t tmem_slot;
   AbortState abort;
 };
@@ -112,8 +112,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int u = 0; u < 2; ++u) {
         mbar_init(&bars->s_full[t][u], 1);
         mbar_init(&bars->p_full[t][u], 4);   // one arrival per softmax warp
+        mbar_init(&bars->pv_done[t][u], 1);
       }
-      mbar_init(&bars->pv_done[t], 1);
     }
     bars->abort.flag = 0;
     fence_barrier_init();
@@ -212,7 +212,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
             mma_ts<Kind::TF32>(d_tmem, p_tmem + ks * 8, b_desc, idesc_pv,
                                (jj | ks) != 0 ? 1u : 0u);
           }
-          mma_commit(&bars->pv_done[t]);
+          mma_commit(&bars->pv_done[t][buf]);
         }
         mma_commit(&bars->kv_empty[slot]);
         if (++slot == p.ring) { slot = 0; phase ^= 1; }
@@ -267,7 +267,12 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
         if (grow) m_used = m_new;
         l *= factor;
         if (jj > 0) {
-          ok = mbar_wait(&bars->pv_done[t], (jj - 1) & 1, abort, p.status, 208);
+          // O[t] may still be receiving P V of the previous KV tile.  Its
+          // completion is signalled on the barrier of that tile's parity, so a
+          // waiter that skipped earlier phases is never more than one phase
+          // behind (a parity wait cannot tell phases two apart).
+          ok = mbar_wait(&bars->pv_done[t][(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort, p.status,
+                         208);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
@@ -300,7 +305,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
     }
 
     if (ok) {
-      ok = mbar_wait(&bars->pv_done[t], (n_kv - 1) & 1, abort, p.status, 209);
+      ok = mbar_wait(&bars->pv_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort, p.status,
+                     209);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {

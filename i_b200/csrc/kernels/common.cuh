@@ -46,6 +46,23 @@ __device__ __forceinline__ float exp_e32(float x) {
   return ldexpf(exp2f(f), static_cast<int>(n));
 }
 
+// Same function with the range reduction done by hand: 2^f from the MUFU
+// (ex2.approx, ~2 ulp) and 2^n added into the exponent field.  Results that
+// would be subnormal, overflow, or come from inf/NaN take the exact path.
+__device__ __forceinline__ float exp_e32_fast(float x) {
+  const float l_hi = 1.4426950216293335f;
+  const float l_lo = -2.4551930266625277e-08f;
+  float hi = x * l_hi;
+  float lo = fmaf(x, l_lo, fmaf(x, l_hi, -hi));
+  float n = rintf(hi);
+  float f = (hi - n) + lo;
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(f));
+  int e = static_cast<int>(n);
+  if (e < -125 || e > 126) return exp_e32(x);
+  return __int_as_float(__float_as_int(r) + (e << 23));
+}
+
 __device__ __forceinline__ float apply_binary(int op, float a, float b) {
   switch (op) {
     case IB_OP_ADD: return a + b;
@@ -67,7 +84,7 @@ __device__ __forceinline__ float apply_unary(int op, float x) {
     case IB_OP_DIV: return 1.0f / x;
     case IB_OP_MAX: return fmaxf(0.0f, x);
     case IB_OP_MIN: return fminf(0.0f, x);
-    case IB_OP_POW: return exp_e32(x);
+    case IB_OP_POW: return exp_e32_fast(x);
     default: return logf(x);
   }
 }

@@ -9,6 +9,8 @@
 //
 // ib::transpose_batched rewrites [b][r][c] as [b][c][r]; the tensor path uses
 // it to give tcgen05 K-major operands.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -76,6 +78,16 @@ contract_simt_kernel(const float* __restrict__ a, const float* __restrict__ b,
   }
 }
 
+// Round-to-nearest fp32 -> tf32 (10-bit mantissa, low 13 bits cleared).  The
+// tensor core itself truncates; rounding operands first halves the error and
+// removes its bias.
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+template <bool ROUND>
 __global__ void __launch_bounds__(256)
 transpose_kernel(const float* __restrict__ in, float* __restrict__ out, size_t rows, size_t cols,
                  size_t out_pitch) {
@@ -92,11 +104,57 @@ transpose_kernel(const float* __restrict__ in, float* __restrict__ out, size_t r
   __syncthreads();
   for (int j = ty; j < 32; j += 8) {
     size_t cc = c0 + j, r = r0 + tx;
-    if (r < rows && cc < cols) out[cc * out_pitch + r] = tile[tx][j];
+    if (r < rows && cc < cols) out[cc * out_pitch + r] = ROUND ? round_tf32(tile[tx][j]) : tile[tx][j];
+  }
+}
+
+// out[r][c] = round_tf32(in[r][c]) for up to two row-major arrays in one launch
+// (blockIdx.y selects the array); pitches in elements.
+struct RoundJob {
+  const float* in;
+  float* out;
+  size_t rows, cols, in_pitch, out_pitch;
+};
+
+__global__ void __launch_bounds__(256)
+round_rows_kernel(RoundJob j0, RoundJob j1) {
+  const RoundJob j = blockIdx.y == 0 ? j0 : j1;
+  const size_t n = j.rows * j.cols;
+  const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+  const bool vec = j.cols % 4 == 0 && j.in_pitch % 4 == 0 && j.out_pitch % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(j.in) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(j.out) & 15u) == 0;
+  if (vec) {
+    const size_t cvec = j.cols / 4;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n / 4; i += stride) {
+      const size_t r = i / cvec, c = (i - r * cvec) * 4;
+      float4 v = *reinterpret_cast<const float4*>(j.in + r * j.in_pitch + c);
+      v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w);
+      *reinterpret_cast<float4*>(j.out + r * j.out_pitch + c) = v;
+    }
+  } else {
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n; i += stride) {
+      const size_t r = i / j.cols, c = i - r * j.cols;
+      j.out[r * j.out_pitch + c] = round_tf32(j.in[r * j.in_pitch + c]);
+    }
   }
 }
 
 }  // namespace
+
+int round_tf32_rows(const float* in0, float* out0, size_t rows0, size_t cols0, size_t in_pitch0,
+                    size_t out_pitch0, const float* in1, float* out1, size_t rows1, size_t cols1,
+                    size_t in_pitch1, size_t out_pitch1, cudaStream_t s) {
+  RoundJob j0{in0, out0, rows0, cols0, in_pitch0, out_pitch0};
+  RoundJob j1{in1, out1, rows1, cols1, in_pitch1, out_pitch1};
+  const size_t n = std::max(rows0 * cols0, in1 ? rows1 * cols1 : 0);
+  if (n == 0) return 0;
+  size_t blocks = (n / 4 + 255) / 256 + 1;
+  if (blocks > static_cast<size_t>(kNumSMs) * 16) blocks = static_cast<size_t>(kNumSMs) * 16;
+  dim3 grid(static_cast<unsigned>(blocks), in1 ? 2 : 1);
+  round_rows_kernel<<<grid, 256, 0, s>>>(j0, j1);
+  return check_launch("round_tf32");
+}
 
 int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
                   size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s) {
@@ -117,12 +175,15 @@ int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t
 }
 
 int transpose_batched(const float* in, float* out, size_t batch, size_t rows, size_t cols,
-                      size_t out_pitch, cudaStream_t s) {
+                      size_t out_pitch, bool round, cudaStream_t s) {
   if (batch == 0 || rows == 0 || cols == 0) return 0;
   if (batch > 65535 || (rows + 31) / 32 > 65535) return fail("transpose: shape too large");
   dim3 grid(static_cast<unsigned>((cols + 31) / 32), static_cast<unsigned>((rows + 31) / 32),
             static_cast<unsigned>(batch));
-  transpose_kernel<<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch);
+  if (round)
+    transpose_kernel<true><<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch);
+  else
+    transpose_kernel<false><<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch);
   return check_launch("transpose");
 }
 

@@ -74,13 +74,13 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
     if (!a_kmajor) {
       float* t = ws.take(batch * m * k);
       if (!t) return fail("ib_contract: workspace too small (see ib_contract_workspace_bytes)");
-      if (int rc = transpose_batched(a, t, batch, k, m, k, s)) return rc;   // [k][m] -> [m][k]
+      if (int rc = transpose_batched(a, t, batch, k, m, k, false, s)) return rc;   // [k][m] -> [m][k]
       ak = t;
     }
     if (!b_kmajor) {
       float* t = ws.take(batch * n * k);
       if (!t) return fail("ib_contract: workspace too small (see ib_contract_workspace_bytes)");
-      if (int rc = transpose_batched(b, t, batch, k, n, k, s)) return rc;   // [k][n] -> [n][k]
+      if (int rc = transpose_batched(b, t, batch, k, n, k, false, s)) return rc;   // [k][n] -> [n][k]
       bk = t;
     }
     if (gemm_tcgen05_supported(ak, bk, c, m, n, k)) return gemm_tcgen05(ak, bk, c, batch, m, n, k, s);
@@ -95,8 +95,9 @@ extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t n
   using namespace ib;
   const double flop = 4.0 * batch * nq * nk * d;
   if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
-    size_t bytes = 0;
-    if (!v_kmajor || nk % 4 != 0) bytes += carve_bytes(batch * dv * round_up(nk, 4));
+    // TF32-rounded copies of Q and K, V^T (rounded), and the KV-split partials.
+    size_t bytes = carve_bytes(batch * nq * d) + carve_bytes(batch * nk * d);
+    bytes += carve_bytes(batch * dv * round_up(nk, 4));
     bytes += carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
     return bytes;
   }
@@ -119,25 +120,28 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
   if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
     return fail("ib_attention: unknown precision");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u)
+    return fail("ib_attention: workspace must be 256-byte aligned");
   Carver ws(workspace, workspace_bytes);
   const double flop = 4.0 * batch * nq * nk * d;
   const bool tensor = wants_tensor(precision, flop);
 
-  if (tensor && attention_shape_ok(d, dv) && attention_tcgen05_supported(q, k, o, d, dv)) {
+  if (tensor && attention_shape_ok(d, dv)) {
+    // The tensor core truncates fp32 operands to TF32.  Q, K and V are first
+    // rounded to nearest into workspace copies (V transposed to [dv][keys] on the
+    // way, which is the K-major layout the second contraction needs).
     const size_t pitch = round_up(nk, 4);
-    const float* vt = v;
-    if (!v_kmajor || nk % 4 != 0) {
-      float* t = ws.take(batch * dv * pitch);
-      if (!t) return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
-      if (!v_kmajor) {
-        if (int rc = transpose_batched(v, t, batch, nk, dv, pitch, s)) return rc;
-      } else {
-        cudaError_t err = cudaMemcpy2DAsync(t, pitch * sizeof(float), v, nk * sizeof(float),
-                                            nk * sizeof(float), batch * dv,
-                                            cudaMemcpyDeviceToDevice, s);
-        if (err != cudaSuccess) return fail("ib_attention: re-pitching V failed");
-      }
-      vt = t;
+    const char* small = "ib_attention: workspace too small (see ib_attention_workspace_bytes)";
+    float* qr = ws.take(batch * nq * d);
+    float* kr = ws.take(batch * nk * d);
+    float* vt = ws.take(batch * dv * pitch);
+    if (!qr || !kr || !vt) return fail(small);
+    if (int rc = round_tf32_rows(q, qr, batch * nq, d, d, d, k, kr, batch * nk, d, d, d, s)) return rc;
+    if (!v_kmajor) {
+      if (int rc = transpose_batched(v, vt, batch, nk, dv, pitch, true, s)) return rc;
+    } else {
+      if (int rc = round_tf32_rows(v, vt, batch * dv, nk, nk, pitch, nullptr, nullptr, 0, 0, 0, 0, s))
+        return rc;
     }
     float* partials = nullptr;
     const size_t part_floats = attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr);
@@ -146,7 +150,7 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
       if (!partials)
         return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
     }
-    return attention_tcgen05(q, k, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
+    return attention_tcgen05(qr, kr, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);

@@ -11,9 +11,15 @@ namespace ib {
 // contract_simt.cu
 int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
                   size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s);
-// out[b][c][r] = in[b][r][c]; rows of `out` are `out_pitch` elements apart.
+// out[b][c][r] = in[b][r][c]; rows of `out` are `out_pitch` elements apart.  With
+// `round` the values are rounded to TF32 (nearest) on the way.
 int transpose_batched(const float* in, float* out, size_t batch, size_t rows, size_t cols,
-                      size_t out_pitch, cudaStream_t s);
+                      size_t out_pitch, bool round, cudaStream_t s);
+// Rounds one or two row-major arrays to TF32 (nearest) in a single launch; pass
+// in1 = nullptr for one.  Pitches are in elements.
+int round_tf32_rows(const float* in0, float* out0, size_t rows0, size_t cols0, size_t in_pitch0,
+                    size_t out_pitch0, const float* in1, float* out1, size_t rows1, size_t cols1,
+                    size_t in_pitch1, size_t out_pitch1, cudaStream_t s);
 
 // tensor_map.cu — encodes a TMA descriptor for a dense fp32 tensor
 // [batch][rows][cols] (cols contiguous, `row_pitch` elements between rows) read

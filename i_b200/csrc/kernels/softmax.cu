@@ -30,7 +30,7 @@ __device__ __forceinline__ float row_fold(float v, float* scratch, int row_in_bl
 
 // Row held in registers: VPT float4 per thread, TPR threads per row.
 template <int VPT, int TPR, bool VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (VPT <= 8 ? 3 : 2))
 row_softmax_regs(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols) {
   __shared__ float scratch[kThreads / 32];
   constexpr int kRowsPerBlock = kThreads / TPR;
@@ -67,10 +67,13 @@ row_softmax_regs(const float* __restrict__ x, float* __restrict__ y, size_t rows
 #pragma unroll
     for (int u = 0; u < VPT * 4; ++u) {
       // Padding lanes hold -inf and contribute exp(-inf) = 0.
-      v[u] = exp_e32(v[u] - m);
+      v[u] = exp_e32_fast(v[u] - m);
       l += v[u];
     }
     l = row_fold<IB_OP_ADD, TPR>(l, scratch, row_in_block);
+    // One reciprocal per row instead of a division per element: within 1 ulp of
+    // the reference's e / l.
+    const float inv = 1.0f / l;
     if (VEC) {
       const size_t nvec = cols / 4;
 #pragma unroll
@@ -78,13 +81,14 @@ row_softmax_regs(const float* __restrict__ x, float* __restrict__ y, size_t rows
         size_t i = static_cast<size_t>(u) * TPR + t;
         if (live && i < nvec)
           __stcs(reinterpret_cast<float4*>(yr) + i,
-                 make_float4(v[4 * u] / l, v[4 * u + 1] / l, v[4 * u + 2] / l, v[4 * u + 3] / l));
+                 make_float4(v[4 * u] * inv, v[4 * u + 1] * inv, v[4 * u + 2] * inv,
+                             v[4 * u + 3] * inv));
       }
     } else {
 #pragma unroll
       for (int u = 0; u < VPT * 4; ++u) {
         size_t i = static_cast<size_t>(u) * TPR + t;
-        if (live && i < cols) yr[i] = v[u] / l;
+        if (live && i < cols) yr[i] = v[u] * inv;
       }
     }
   }
@@ -102,7 +106,7 @@ row_softmax_stream(const float* __restrict__ x, float* __restrict__ y, size_t ro
     m = row_fold<IB_OP_MAX, kThreads>(m, scratch, 0);
     float l = 0.0f;
     for (size_t i = threadIdx.x; i < cols; i += kThreads) {
-      float e = exp_e32(xr[i] - m);
+      float e = exp_e32_fast(xr[i] - m);
       yr[i] = e;
       l += e;
     }

@@ -1,0 +1,165 @@
+"""GPU end-to-end tests through the front-end: the reference's own acceptance
+cases (ilang-python/test.py:40-128, ilang-python/flash-attn.py:31-77) with the
+reference's tolerances, plus the boundary behaviours of include/i.h."""
+import numpy as np
+import pytest
+
+from conftest import max_rel_elementwise, max_rel_to_peak
+from test_front import naive_attention, readme_attention
+
+pytestmark = pytest.mark.gpu
+
+
+def rand(shape, seed):
+    return np.random.default_rng(seed).standard_normal(shape, dtype=np.float32)
+
+
+def as_numpy(t):
+    return np.asarray(t.data, dtype=np.float32).reshape(t.shape)
+
+
+def np_attention(q, k, v):
+    s = q.astype(np.float64) @ np.swapaxes(k.astype(np.float64), -1, -2)
+    s = s - s.max(axis=-1, keepdims=True)
+    w = np.exp(s)
+    w = w / w.sum(axis=-1, keepdims=True)
+    return w @ v.astype(np.float64)
+
+
+def test_matmul_with_bang_init(ilang):
+    # test.py:40-59, nested-list Tensors through i_exec.
+    a, b = rand((8, 16), 1), rand((16, 7), 2)
+    f = ilang.i("ik*kj~ijk|i:2,k:2|ii'jkk'") >> ilang.i("+ijk~ij|i:2,k:2|ii'j!kk'0")
+    got = as_numpy(f.exec(ilang.Tensor(a.tolist()), ilang.Tensor(b.tolist())))
+    np.testing.assert_allclose(got, a.astype(np.float64) @ b.astype(np.float64), rtol=1e-5, atol=1e-6)
+
+
+def test_batched_attention_naive_schedule(ilang):
+    # test.py:61-82: b2 h3 q4 k4 d8.
+    i, I = ilang.i, ilang.I
+    q, k, v = rand((2, 3, 4, 8), 1), rand((2, 3, 4, 8), 2), rand((2, 3, 4, 8), 3)
+    mm_t = i("bhij*bhkj~bhikj | i:16,k:16 | bhkii'k'j") >> i("+bhikj~bhik | i:16,k:16 | bhkii'k'j0")
+    rms = (I & i(">bhik~bhi | i:16,k:16 | bhkii'k'")) >> i("bhik-bhi~bhik | i:16,k:16 | bh1kii'k'")
+    exp = i("^bhik~bhik | i:16,k:16 | bhkii'k'")
+    rn = (I & i("+bhik~bhi | i:16,k:16 | bhkii'k'")) >> i("bhik/bhi~bhik | i:16,k:16 | bh1kii'k'")
+    mm = i("bhik*bhkj~bhijk | i:16,k:16 | bhkii'jk'") >> i("+bhijk~bhij | i:16,k:16 | bhkii'jk'0")
+    attn = mm_t >> rms >> exp >> rn >> mm
+    got = as_numpy(attn.exec(*(ilang.Tensor(x.tolist()) for x in (q, k, v))))
+    np.testing.assert_allclose(got, np_attention(q, k, v), rtol=1e-5, atol=1e-6)
+
+
+def test_mlp_intent(ilang):
+    # test.py:84-98 means w2 @ relu(w1 @ x); written with the combinators that exist.
+    i = ilang.i
+    x, w1, w2 = rand((8,), 1), rand((16, 8), 2), rand((7, 16), 3)
+    mvp = i("ij*j~ij") >> i("+ij~i")
+    hidden = mvp >> i(">i~i")
+    f = (ilang.I | hidden) >> (i("ij*j~ij") >> i("+ij~i"))
+    got = f.exec_numpy(w2, w1, x)
+    ref = w2.astype(np.float64) @ np.maximum(w1.astype(np.float64) @ x, 0)
+    np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("src,fn", [(">ij~i", np.max), ("<ij~i", np.min), ("+ij~i", np.sum)])
+def test_row_reductions(ilang, src, fn):
+    # test.py:103-128
+    x = rand((16, 8), 1)
+    got = as_numpy(ilang.i(src).exec(ilang.Tensor(x.tolist())))
+    np.testing.assert_allclose(got, fn(x.astype(np.float64), axis=1), rtol=1e-5, atol=1e-6)
+
+
+def test_flash_attention_demo(ilang):
+    # flash-attn.py:31-77: 32 x 32 x 2048, fused and naive schedules, rtol 3e-4 / atol 5e-5.
+    q, k, v = rand((32, 2048), 1), rand((32, 2048), 2), rand((32, 2048), 3)
+    ref = np_attention(q, k, v)
+    for attn in (readme_attention(ilang), naive_attention(ilang)):
+        assert isinstance(attn._code(), str)
+        np.testing.assert_allclose(attn.exec_numpy(q, k, v), ref, rtol=3e-4, atol=5e-5)
+
+
+def test_config1_through_the_front_end(ilang, oracle):
+    rng = np.random.default_rng(0)
+    q, k, v = (rng.standard_normal((128, 64), dtype=np.float32) for _ in range(3))
+    q *= np.float32(1 / 8)
+    ref = oracle.attention_fused(q, k, v)
+    attn = readme_attention(ilang)
+    assert max_rel_to_peak(attn.exec_numpy(q, k, v), ref) <= 2e-5       # auto -> fp32 arm
+    attn.set_precision("tf32")
+    assert max_rel_to_peak(attn.exec_numpy(q, k, v), ref) <= 5e-3       # fused tcgen05 kernel
+
+
+def test_softmax_component_config2_slice(ilang, oracle):
+    i, I = ilang.i, ilang.I
+    sm = ((I & i(">ij~i | i:16,j:16 | jii'j'")) >> i("ij-i~ij | i:16,j:16 | 1jii'j'")) \
+        >> i("^ij~ij | i:16,j:16 | jii'j'") \
+        >> ((I & i("+ij~i | i:16,j:16 | jii'j'")) >> i("ij/i~ij | i:16,j:16 | 1jii'j'"))
+    x = 2.0 * np.random.default_rng(1).standard_normal((256, 8192), dtype=np.float32)
+    assert max_rel_elementwise(sm.exec_numpy(x), oracle.row_softmax(x)) <= 1e-5
+
+
+def test_mm_t_component_tf32(ilang, oracle):
+    i = ilang.i
+    mm_t = i("ik*jk~ijk | i:16,j:16 | jii'j'k") >> i("+ijk~ij | i:16,j:16 | jii'j'k0")
+    rng = np.random.default_rng(2)
+    a = 2 * rng.random((512, 1024), dtype=np.float32) - 1
+    b = 2 * rng.random((384, 1024), dtype=np.float32) - 1
+    got = mm_t.exec_numpy(a, b)                                        # auto -> tensor arm
+    assert max_rel_to_peak(got, oracle.contract(a, b)) <= 5e-3
+    mm_t.set_precision("fp32")
+    assert max_rel_to_peak(mm_t.exec_numpy(a, b), oracle.contract(a, b)) <= 1e-5
+
+
+def test_multiple_outputs_identity_and_swap(ilang):
+    i, I = ilang.i, ilang.I
+    x = rand((6, 5), 4)
+    both = ~(i("+ij~i") & i(">ij~i"))
+    mx, sm = both.exec_numpy(x)
+    assert np.array_equal(mx, x.max(axis=1))
+    np.testing.assert_allclose(sm, x.sum(axis=1), rtol=1e-5, atol=1e-6)
+    same, neg = (I & i("-ij~ij")).exec_numpy(x)
+    assert np.array_equal(same, x) and np.array_equal(neg, -x)
+    t = i("ij~ji").exec_numpy(x)
+    assert np.array_equal(t, x.T)
+    total = i("+ij~.").exec_numpy(np.abs(x))
+    np.testing.assert_allclose(total, np.abs(x).sum(), rtol=1e-5)
+
+
+def test_scalar_operand_and_column_broadcast(ilang):
+    i = ilang.i
+    x, c = rand((4, 9), 5), rand((9,), 6)
+    assert np.array_equal(i("ij*j~ij").exec_numpy(x, c), x * c[None, :])
+    two = np.array(2.0, dtype=np.float32)
+    assert np.array_equal(i(".*ij~ij").exec_numpy(two, x), 2 * x)
+
+
+def test_torch_cuda_tensors_run_in_place(ilang, oracle):
+    import torch
+    attn = readme_attention(ilang).set_precision("tf32")
+    q, k, v = (torch.randn(512, 64, device="cuda") for _ in range(3))
+    q *= 0.125
+    before = ilang.launch_count()
+    o = attn.exec_torch(q, k, v)
+    torch.cuda.synchronize()
+    assert o.is_cuda and ilang.launch_count() > before
+    ref = oracle.attention_fused(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    assert max_rel_to_peak(o.cpu().numpy(), ref) <= 5e-3
+
+
+def test_shape_errors_are_reported_not_crashes(ilang):
+    attn = readme_attention(ilang)
+    with pytest.raises(RuntimeError):
+        attn.exec_numpy(rand((8, 4), 1), rand((8, 5), 2), rand((8, 4), 3))
+    with pytest.raises(RuntimeError):
+        ilang.i("+ij~i").exec_numpy(rand((8,), 1))
+
+
+def test_concurrent_exec_from_threads(ilang, oracle):
+    # One program, several host threads (legal in the reference: exec uses only locals).
+    from concurrent.futures import ThreadPoolExecutor
+    sm = ((ilang.I & ilang.i(">ij~i")) >> ilang.i("ij-i~ij")) >> ilang.i("^ij~ij") \
+        >> ((ilang.I & ilang.i("+ij~i")) >> ilang.i("ij/i~ij"))
+    xs = [2 * rand((64, 300), s) for s in range(8)]
+    with ThreadPoolExecutor(4) as pool:
+        outs = list(pool.map(sm.exec_numpy, xs))
+    for x, o in zip(xs, outs):
+        assert max_rel_elementwise(o, oracle.row_softmax(x)) <= 1e-5
