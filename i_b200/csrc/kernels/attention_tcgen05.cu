@@ -64,6 +64,7 @@ struct Params {
   float* part_m;       // [splits][batch][nq]
   float* part_l;
   int* status;
+  unsigned long long* prof;   // optional per-CTA wait-cycle counters (debugging aid), or null
 };
 
 struct Barriers {
@@ -141,8 +142,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long waited = 0;
       auto load_k = [&](int j) {
+        const long long t0 = clock64();
         if (!(ok = mbar_wait(&bars->kv_empty[slot], phase ^ 1, abort, p.status, 201))) return;
+        waited += clock64() - t0;
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&bars->kv_full[slot], d_chunks * kKChunkBytes);
         for (int c = 0; c < d_chunks; ++c)
@@ -150,7 +154,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
         if (++slot == p.ring) { slot = 0; phase ^= 1; }
       };
       auto load_v = [&](int j) {
+        const long long t0 = clock64();
         if (!(ok = mbar_wait(&bars->kv_empty[slot], phase ^ 1, abort, p.status, 202))) return;
+        waited += clock64() - t0;
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&bars->kv_full[slot], 2 * kVChunkBytes);
         for (int c = 0; c < 2; ++c)
@@ -163,6 +169,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
         if (jj + 1 < n_kv) load_k(kv_lo + jj + 1);
         if (ok) load_v(kv_lo + jj);
       }
+      if (p.prof) p.prof[blockIdx.x * 8 + 0] = waited;
     }
   } else if (warp == 1) {
     if (lane == 0 && n_kv > 0) {
@@ -177,8 +184,12 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t ring_addr = smem_u32(ring);
 
       // S[t][buf] = Q[t] K^T for both tiles from the K tile in the current slot.
+      long long wait_k = 0, wait_v = 0, wait_p = 0;
+      const long long t_start = clock64();
       auto issue_qk = [&](int buf) {
+        const long long t0 = clock64();
         if (!(ok = mbar_wait(&bars->kv_full[slot], phase, abort, p.status, 204))) return;
+        wait_k += clock64() - t0;
         tc_fence_after_sync();
         const uint32_t k_addr = ring_addr + slot * kSlotBytes;
         for (int t = 0; t < 2; ++t) {
@@ -198,10 +209,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       // O[t] += P[t][buf] V for both tiles from the V^T tile in the current slot.
       auto issue_pv = [&](int jj) {
         const int buf = jj & 1;
+        long long t0 = clock64();
         if (!(ok = mbar_wait(&bars->kv_full[slot], phase, abort, p.status, 205))) return;
+        wait_v += clock64() - t0;
         const uint32_t v_addr = ring_addr + slot * kSlotBytes;
         for (int t = 0; t < 2; ++t) {
+          t0 = clock64();
           if (!(ok = mbar_wait(&bars->p_full[t][buf], (jj >> 1) & 1, abort, p.status, 206))) return;
+          wait_p += clock64() - t0;
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + kTmemO + static_cast<uint32_t>(t * 128);
           const uint32_t p_tmem = tmem_base + kTmemS + static_cast<uint32_t>((t * 2 + buf) * kBKV);
@@ -223,6 +238,12 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
         if (jj + 1 < n_kv) issue_qk((jj + 1) & 1);
         if (ok) issue_pv(jj);
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 1] = wait_k;
+        p.prof[blockIdx.x * 8 + 2] = wait_v;
+        p.prof[blockIdx.x * 8 + 3] = wait_p;
+        p.prof[blockIdx.x * 8 + 4] = clock64() - t_start;
+      }
     }
   } else if (warp >= 4 && n_kv > 0) {
     const int t = (warp - 4) >> 2;            // query tile of this warpgroup
@@ -236,9 +257,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
     float l = 0.0f;
     bool ok = true;
 
+    long long wait_s = 0;
+    const long long t_start = clock64();
     for (int jj = 0; jj < n_kv; ++jj) {
       const int buf = jj & 1;
+      const long long t0 = clock64();
       ok = mbar_wait(&bars->s_full[t][buf], (jj >> 1) & 1, abort, p.status, 207);
+      wait_s += clock64() - t0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -304,6 +329,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
     }
 
+    if (p.prof && (warp & 3) == 0 && lane == 0) {
+      p.prof[blockIdx.x * 8 + 5 + t] = wait_s;
+      if (t == 0) p.prof[blockIdx.x * 8 + 7] = clock64() - t_start;
+    }
     if (ok) {
       ok = mbar_wait(&bars->pv_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort, p.status,
                      209);
@@ -355,28 +384,45 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
 }
 
 // Merges KV-split partials: O = sum_s w_s O_s / sum_s w_s, w_s = l_s 2^(m_s - max m).
+// One thread per four output columns; dv4 = ceil(dv / 4).
 __global__ void __launch_bounds__(256)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_m,
                          const float* __restrict__ part_l, float* __restrict__ o, size_t rows,
-                         int dv, int splits) {
-  const int lane = threadIdx.x & 31;
-  const size_t warps_total = static_cast<size_t>(gridDim.x) * 8;
-  for (size_t r = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); r < rows;
-       r += warps_total) {
+                         int dv, int splits, bool vec) {
+  const int dv4 = (dv + 3) / 4;
+  const size_t total = rows * dv4;
+  const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / dv4;
+    const int c = static_cast<int>(i - r * dv4) * 4;
     float m = -CUDART_INF_F;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, part_m[s * rows + r]);
     float wsum = 0.0f;
-    for (int s = 0; s < splits; ++s) wsum += part_l[s * rows + r] * exp2f(part_m[s * rows + r] - m);
-    for (int c = lane; c < dv; c += 32) {
-      float acc = 0.0f;
-      for (int s = 0; s < splits; ++s) {
-        float w = part_l[s * rows + r] * exp2f(part_m[s * rows + r] - m);
-        acc += w * part_o[(s * rows + r) * dv + c];
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s = 0; s < splits; ++s) {
+      const float w = part_l[s * rows + r] * exp2f(part_m[s * rows + r] - m);
+      wsum += w;
+      const float* src = part_o + (s * rows + r) * dv + c;
+      if (vec) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(src));
+        acc[0] += w * v.x; acc[1] += w * v.y; acc[2] += w * v.z; acc[3] += w * v.w;
+      } else {
+        for (int e = 0; e < 4 && c + e < dv; ++e) acc[e] += w * src[e];
       }
-      o[r * dv + c] = acc / wsum;
+    }
+    const float inv = 1.0f / wsum;
+    float* dst = o + r * dv + c;
+    if (vec) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    } else {
+      for (int e = 0; e < 4 && c + e < dv; ++e) dst[e] = acc[e] * inv;
     }
   }
 }
+
+// Debugging aid: when set (device pointer to 8 counters per CTA), the kernel
+// records how many cycles each role spent waiting on its barriers.
+unsigned long long* g_attention_profile = nullptr;
 
 int choose_splits(size_t units, int kv_blocks, int sms) {
   if (units >= static_cast<size_t>(sms) || kv_blocks < 8) return 1;
@@ -388,6 +434,8 @@ int choose_splits(size_t units, int kv_blocks, int sms) {
 }
 
 }  // namespace
+
+void set_attention_profile(unsigned long long* p) { g_attention_profile = p; }
 
 bool attention_tcgen05_supported(const float* q, const float* k, const float* o, size_t d,
                                  size_t dv) {
@@ -454,6 +502,7 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   (void)part_floats;
   p.status = device_status_word(s);
   if (!p.status) return fail("ib_attention: cannot allocate the device status word");
+  p.prof = g_attention_profile;
 
   const int d_chunks = static_cast<int>((d + 31) / 32);
   const int q_bytes = 2 * d_chunks * kQChunkBytes;
@@ -476,13 +525,20 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   if (int rc = check_launch("ib_attention (tcgen05 tf32)")) return rc;
   if (p.splits > 1) {
     const size_t rows = batch * nq;
-    size_t blocks = (rows + 7) / 8;
+    size_t blocks = (rows * ((dv + 3) / 4) + 255) / 256;
     if (blocks > static_cast<size_t>(kNumSMs) * 16) blocks = static_cast<size_t>(kNumSMs) * 16;
+    const bool vec = dv % 4 == 0 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.part_o) & 15u) == 0;
     attention_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        p.part_o, p.part_m, p.part_l, o, rows, p.dv, p.splits);
+        p.part_o, p.part_m, p.part_l, o, rows, p.dv, p.splits, vec);
     return check_launch("ib_attention (combine)");
   }
   return 0;
 }
 
 }  // namespace ib
+
+// Undocumented hook for performance work: see g_attention_profile.
+extern "C" void ib_debug_set_attention_profile(unsigned long long* device_counters) {
+  ib::set_attention_profile(device_counters);
+}

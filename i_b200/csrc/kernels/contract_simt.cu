@@ -140,7 +140,66 @@ round_rows_kernel(RoundJob j0, RoundJob j1) {
   }
 }
 
+// Operand preparation for the fused attention kernel in one launch:
+// blockIdx.y = 0 rounds Q, 1 rounds K (both plain copies with TF32 rounding),
+// 2 writes V^T = round(V)^T with 64x64 tiles through shared memory.
+struct PrepareArgs {
+  const float* q; float* qr; size_t q_elems;
+  const float* k; float* kr; size_t k_elems;
+  const float* v; float* vt; size_t batch, nk, dv, pitch;
+};
+
+__global__ void __launch_bounds__(256)
+prepare_attention_kernel(PrepareArgs a) {
+  __shared__ float tile[64][65];
+  if (blockIdx.y < 2) {
+    const float* in = blockIdx.y == 0 ? a.q : a.k;
+    float* out = blockIdx.y == 0 ? a.qr : a.kr;
+    const size_t n4 = (blockIdx.y == 0 ? a.q_elems : a.k_elems) / 4;   // element counts are multiples of 4
+    const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n4; i += stride) {
+      float4 x = __ldcs(reinterpret_cast<const float4*>(in) + i);
+      x.x = round_tf32(x.x); x.y = round_tf32(x.y); x.z = round_tf32(x.z); x.w = round_tf32(x.w);
+      reinterpret_cast<float4*>(out)[i] = x;
+    }
+    return;
+  }
+  const size_t tiles_k = (a.nk + 63) / 64, tiles_d = (a.dv + 63) / 64;
+  const size_t total = a.batch * tiles_k * tiles_d;
+  for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const size_t b = t / (tiles_k * tiles_d);
+    const size_t rem = t - b * tiles_k * tiles_d;
+    const size_t k0 = (rem / tiles_d) * 64, d0 = (rem % tiles_d) * 64;
+    const float* src = a.v + b * a.nk * a.dv;
+    float* dst = a.vt + b * a.dv * a.pitch;
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+      const int r = e >> 6, c = e & 63;                 // r: key, c: feature (contiguous in V)
+      float x = 0.0f;
+      if (k0 + r < a.nk && d0 + c < a.dv) x = src[(k0 + r) * a.dv + d0 + c];
+      tile[r][c] = round_tf32(x);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+      const int c = e >> 6, r = e & 63;                 // r: key (contiguous in V^T)
+      if (k0 + r < a.nk && d0 + c < a.dv) dst[(d0 + c) * a.pitch + k0 + r] = tile[r][c];
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
+
+int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const float* k,
+                               float* kr, size_t k_elems, const float* v, float* vt, size_t batch,
+                               size_t nk, size_t dv, size_t pitch, cudaStream_t s) {
+  PrepareArgs a{q, qr, q_elems, k, kr, k_elems, v, vt, batch, nk, dv, pitch};
+  const size_t most = std::max(std::max(q_elems, k_elems) / 4 / 256 + 1,
+                               batch * ((nk + 63) / 64) * ((dv + 63) / 64));
+  const size_t cap = static_cast<size_t>(kNumSMs) * 8;
+  dim3 grid(static_cast<unsigned>(std::min(most, cap)), 3);
+  prepare_attention_kernel<<<grid, 256, 0, s>>>(a);
+  return check_launch("prepare_attention_operands");
+}
 
 int round_tf32_rows(const float* in0, float* out0, size_t rows0, size_t cols0, size_t in_pitch0,
                     size_t out_pitch0, const float* in1, float* out1, size_t rows1, size_t cols1,

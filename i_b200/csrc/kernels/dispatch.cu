@@ -136,10 +136,16 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
     float* kr = ws.take(batch * nk * d);
     float* vt = ws.take(batch * dv * pitch);
     if (!qr || !kr || !vt) return fail(small);
-    if (int rc = round_tf32_rows(q, qr, batch * nq, d, d, d, k, kr, batch * nk, d, d, d, s)) return rc;
-    if (!v_kmajor) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15u) == 0;
+    if (!v_kmajor && aligned) {
+      if (int rc = prepare_attention_operands(q, qr, batch * nq * d, k, kr, batch * nk * d, v, vt,
+                                              batch, nk, dv, pitch, s))
+        return rc;
+    } else if (!v_kmajor) {
+      if (int rc = round_tf32_rows(q, qr, batch * nq, d, d, d, k, kr, batch * nk, d, d, d, s)) return rc;
       if (int rc = transpose_batched(v, vt, batch, nk, dv, pitch, true, s)) return rc;
     } else {
+      if (int rc = round_tf32_rows(q, qr, batch * nq, d, d, d, k, kr, batch * nk, d, d, d, s)) return rc;
       if (int rc = round_tf32_rows(v, vt, batch * dv, nk, nk, pitch, nullptr, nullptr, 0, 0, 0, 0, s))
         return rc;
     }

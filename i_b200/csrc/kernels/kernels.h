@@ -21,7 +21,13 @@ int round_tf32_rows(const float* in0, float* out0, size_t rows0, size_t cols0, s
                     size_t out_pitch0, const float* in1, float* out1, size_t rows1, size_t cols1,
                     size_t in_pitch1, size_t out_pitch1, cudaStream_t s);
 
-// tensor_map.cu — encodes a TMA descriptor for a dense fp32 tensor
+// One launch: qr = round_tf32(q), kr = round_tf32(k) (element counts multiples
+// of 4, 16-byte aligned), vt[b][c][r] = round_tf32(v[b][r][c]) with row pitch `pitch`.
+int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const float* k,
+                               float* kr, size_t k_elems, const float* v, float* vt, size_t batch,
+                               size_t nk, size_t dv, size_t pitch, cudaStream_t s);
+
+// device_util.cu — encodes a TMA descriptor for a dense fp32 tensor
 // [batch][rows][cols] (cols contiguous, `row_pitch` elements between rows) read
 // in boxes of 32 columns (128 bytes, 128-byte swizzle) x box_rows rows.
 // Returns 0, or -1 with the error recorded.
@@ -51,5 +57,7 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 int attention_tcgen05(const float* q, const float* k, const float* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t nk_pitch, float* partials,
                       cudaStream_t s);
+
+void set_attention_profile(unsigned long long* device_counters);
 
 }  // namespace ib

@@ -159,7 +159,7 @@ int launch_strided(const float* x, float* y, size_t n_out, size_t n_red, const F
 extern "C" int ib_reduce_rows(int op, const float* x, float* y, size_t rows, size_t cols,
                               void* stream) {
   if (rows == 0) return 0;
-  if (!x || !y) return ib::fail("ib_reduce_rows: null pointer");
+  if (!y || (!x && cols != 0)) return ib::fail("ib_reduce_rows: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define CALL(OP) ib::launch_rows<OP>(x, y, rows, cols, s)
   IB_DISPATCH_FOLD(op, CALL)
