@@ -35,6 +35,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 SEQ, DIM = 16384, 128
+HEADS = 1             # heads per rank per step (one component invocation)
 FLOP_PER_HEAD = 4.0 * SEQ * SEQ * DIM
 METRIC = "fused i-attention TFLOP/s at seq16K d128"
 WORKLOAD = "config4: single-head fused i-attention, seq_q=seq_kv=16384, d=128, fp32 N(0,1) seed 3, Q*1/sqrt(128)"
@@ -62,13 +63,31 @@ def make_inputs(seed=3, heads=1):
     return q, k, v
 
 
-def readme_attention(ilang):
+def readme_attention(ilang, batched=False):
+    """The README attention component; with `batched`, the same chain with a
+    leading head axis `h` so several heads are one invocation."""
     i, I = ilang.i, ilang.I
-    mm_t = i("ik*jk~ijk | i:16,j:16 | jii'j'k") >> i("+ijk~ij | i:16,j:16 | jii'j'k0")
-    row_max_shift = (I & i(">ij~i | i:16,j:16 | ji0i'j'")) >> i("ij-i~ij | i:16,j:16 | ji01i'j'")
-    exp = i("^ij~ij | i:16,j:16 | ji0i'j'")
-    row_normalize = (I & i("+ij~i | i:16,j:16 | ji0i'j'")) >> i("ij/i~ij | i:16,j:16 | ji01i'j'")
-    mm = i("ij*jk~ikj | i:16,j:16 | ji0i'kj'") >> i("+ikj~ik | i:16,j:16 | jii'kj'0")
+    h = "h" if batched else ""
+
+    def e(src):
+        # Prefix every index pattern and the loop order with the head axis.
+        if not h:
+            return i(src)
+        expr, splits, order = (part.strip() for part in src.split("|"))
+        out = ""
+        for tok in expr.replace("~", " ~ ").replace("*", " * ").replace("-", " - ").replace(
+                "/", " / ").split():
+            out += (h + tok) if tok.isalpha() else tok
+        for op in "+>^":
+            if expr.startswith(op):
+                out = op + h + out[len(op):]
+        return i("%s | %s | %s" % (out, splits, h + order))
+
+    mm_t = e("ik*jk~ijk | i:16,j:16 | jii'j'k") >> e("+ijk~ij | i:16,j:16 | jii'j'k0")
+    row_max_shift = (I & e(">ij~i | i:16,j:16 | ji0i'j'")) >> e("ij-i~ij | i:16,j:16 | ji01i'j'")
+    exp = e("^ij~ij | i:16,j:16 | ji0i'j'")
+    row_normalize = (I & e("+ij~i | i:16,j:16 | ji0i'j'")) >> e("ij/i~ij | i:16,j:16 | ji01i'j'")
+    mm = e("ij*jk~ikj | i:16,j:16 | ji0i'kj'") >> e("+ikj~ik | i:16,j:16 | jii'kj'0")
     return mm_t >> row_max_shift >> exp >> row_normalize >> mm
 
 
@@ -78,7 +97,7 @@ def readme_attention(ilang):
 
 def cpu_reference_sample(rows_per_core, repeats=1):
     """Times oracle/_ref (or the restated oracle when _ref is absent) on
-    cores x rows_per_core query rows against the full 16384 keys."""
+    cores x rows_per_core query rows against all the keys of one head."""
     import numpy as np
     import oracle
     cores = os.cpu_count() or 1
@@ -96,8 +115,8 @@ def cpu_reference_sample(rows_per_core, repeats=1):
     rows = cores * rows_per_core
     flop = 4.0 * rows * SEQ * DIM
     return {"kind": kind, "cores": cores, "rows": rows, "times": times, "flop": flop,
-            "sample": "%d query rows (%d per core) x all 16384 keys of the config-4 head; "
-                      "rows are independent, so cost is linear in rows" % (rows, rows_per_core)}
+            "sample": "%d query rows (%d per core) x all %d keys of one head; "
+                      "rows are independent, so cost is linear in rows" % (rows, rows_per_core, SEQ)}
 
 
 def run_reference_arm(args):
@@ -264,14 +283,24 @@ def run_gpu_arm(args):
     from i_b200 import ilang
 
     peaks = load_peaks()
-    attn = readme_attention(ilang).set_precision("tf32")
+    heads = args.heads
+    batched = heads > 1
+    attn = readme_attention(ilang, batched=batched).set_precision("tf32")
+    flop_per_step = heads * FLOP_PER_HEAD
 
-    # Distinct input sets per rank (seed 3 for set 0 of rank 0, as BASELINE names).
+    def shaped(t):
+        return t if batched else t[0]
+
+    # Distinct input sets per rank (seed 3 for set 0 of rank 0, as BASELINE names);
+    # enough of them that one pass over all sets exceeds L2.
+    set_bytes = 4 * heads * SEQ * DIM * 4
+    rotation = max(2, min(ROTATION, -(-256 * 1024 * 1024 // set_bytes)))
     sets = []
-    for s in range(ROTATION):
-        q, k, v = make_inputs(seed=3 + 1000 * rank + s)
-        sets.append(tuple(torch.from_numpy(t[0]).cuda() for t in (q, k, v)))
-    gathered = [torch.empty(world, SEQ, DIM, device="cuda") for _ in range(2)]
+    for s in range(rotation):
+        q, k, v = make_inputs(seed=3 + 1000 * rank + s, heads=heads)
+        sets.append(tuple(shaped(torch.from_numpy(t)).cuda() for t in (q, k, v)))
+    out_shape = (heads, SEQ, DIM) if batched else (SEQ, DIM)
+    gathered = [torch.empty((world,) + out_shape, device="cuda") for _ in range(2)]
     outs = [g[rank] for g in gathered]
     main = torch.cuda.current_stream()
     side = torch.cuda.Stream() if world > 1 else None
@@ -279,7 +308,7 @@ def run_gpu_arm(args):
     computed = torch.cuda.Event()
 
     def step(s):
-        q, k, v = sets[s % ROTATION]
+        q, k, v = sets[s % rotation]
         buf = s % 2
         if gather_done[buf] is not None:
             main.wait_event(gather_done[buf])  # the gather of step s-2 still reads this buffer
@@ -318,11 +347,23 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
-    value = world * FLOP_PER_HEAD / ms_per_step / 1e9
+    value = world * flop_per_step / ms_per_step / 1e9
+
+    if args.kernel_only:
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                              "steps": args.steps, "ms_per_step": ms_per_step, "heads": heads,
+                              "seq": SEQ, "note": "kernel-only run for profiling"}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # End to end through the host-pointer C ABI (i_exec_into), pinned host buffers.
-    hq, hk, hv = (torch.from_numpy(t[0]).pin_memory() for t in make_inputs(seed=3 + 1000 * rank))
-    ho = torch.empty(SEQ, DIM).pin_memory()
+    hq, hk, hv = (shaped(torch.from_numpy(t)).pin_memory()
+                  for t in make_inputs(seed=3 + 1000 * rank, heads=heads))
+    ho = torch.empty(out_shape).pin_memory()
     nq, nk, nv, no = (t.numpy() for t in (hq, hk, hv, ho))
     e2e_steps = max(3, min(args.steps, 20))
     for _ in range(2):
@@ -338,7 +379,7 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     sampler.stop()
-    e2e_value = world * FLOP_PER_HEAD * e2e_steps / e2e_s / 1e12
+    e2e_value = world * flop_per_step * e2e_steps / e2e_s / 1e12
 
     if rank != 0:
         if world > 1:
@@ -348,14 +389,14 @@ def run_gpu_arm(args):
 
     # Parity spot check of the timed kernel against the CPU oracle (never timed).
     import oracle
-    q0, k0, v0 = (t.cpu().numpy() for t in sets[0])
-    got = attn.exec_torch(*sets[0]).cpu().numpy()
+    q0, k0, v0 = (t.cpu().numpy().reshape(-1, SEQ, DIM)[0] for t in sets[0])
+    got = attn.exec_torch(*sets[0]).cpu().numpy().reshape(-1, SEQ, DIM)[0]
     rows = np.array([0, 255, 4096, 8191, 16383])
     ref = oracle.attention_fused(q0[rows], k0, v0)
     parity = float(np.abs(got[rows] - ref).max() / np.abs(ref).max())
 
     tf32_peak = peaks["bf16_tflops"] / 2.0
-    achieved = FLOP_PER_HEAD / ms_per_step / 1e9
+    achieved = flop_per_step / ms_per_step / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
     if os.path.exists(tpath):
@@ -365,8 +406,12 @@ def run_gpu_arm(args):
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "units_per_rank_per_step": 1,
-                   "l2": "inputs rotate over %d distinct sets (256 MiB) > 126 MB L2" % ROTATION,
+        "config": {"workload": WORKLOAD if (heads == 1 and SEQ == 16384) else
+                   "%d heads x seq %d x d %d per rank per step (batched README attention)"
+                   % (heads, SEQ, DIM),
+                   "units_per_rank_per_step": heads,
+                   "l2": "inputs rotate over %d distinct sets (%d MiB) > 126 MB L2"
+                         % (rotation, rotation * set_bytes // 2 ** 20),
                    "multi_gpu": "one head per rank per step, NCCL all-gather of O on a side stream",
                    "precision": "tcgen05 kind::tf32, fp32 accumulate",
                    "parity_max_rel_to_peak_vs_oracle": parity},
@@ -377,8 +422,9 @@ def run_gpu_arm(args):
                      "frac_of_bf16_peak": achieved / peaks["bf16_tflops"],
                      "note": "achieved = 4*Nq*Nk*d FLOP / average step time on one rank; a step "
                              "launches the operand-preparation, attention and merge kernels"},
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * SEQ * DIM * 4,
-                "d2h_bytes_per_step": SEQ * DIM * 4, "steps": e2e_steps},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": 3 * heads * SEQ * DIM * 4,
+                "d2h_bytes_per_step": heads * SEQ * DIM * 4, "steps": e2e_steps},
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }
@@ -386,7 +432,7 @@ def run_gpu_arm(args):
         res = cpu_reference_sample(256)        # ~20 s of CPU work over all cores
         line["cpu_baseline"] = {"value": res["flop"] / res["times"][0] / 1e12, "unit": "TFLOP/s",
                                 "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]}
-        if not args.no_secondary:
+        if not args.no_secondary and heads == 1 and SEQ == 16384:
             line["secondary"] = secondary_metrics(torch, ilang, peaks)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -402,7 +448,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the map/reduce/contraction side measurements")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="device-timed loop only (no end-to-end, CPU or side measurements); "
+                         "for profiler captures")
+    ap.add_argument("--heads", type=int, default=1,
+                    help="heads per rank per step (default 1 = BASELINE config 4)")
+    ap.add_argument("--seq", type=int, default=16384, help="sequence length (default 16384)")
     args = ap.parse_args()
+    global SEQ, FLOP_PER_HEAD
+    SEQ = args.seq
+    FLOP_PER_HEAD = 4.0 * SEQ * SEQ * DIM
     if args.impl == "reference":
         run_reference_arm(args)
     else:

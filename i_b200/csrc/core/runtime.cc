@@ -13,6 +13,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -201,6 +202,35 @@ bool infer_shapes(const Plan& plan, const i_tensor* inputs, size_t input_count, 
 
 // ---- execution ------------------------------------------------------------
 
+// Scratch and staging buffers come from a per-device memory pool owned by this
+// library.  Its release threshold is unlimited, so memory freed at the end of
+// one call is reused by the next instead of going back to the driver at every
+// stream synchronisation (the default pool does that, at milliseconds a call).
+cudaMemPool_t library_pool() {
+  static std::mutex mutex;
+  static std::map<int, cudaMemPool_t> pools;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(mutex);
+  auto it = pools.find(dev);
+  if (it != pools.end()) return it->second;
+  cudaMemPoolProps props = {};
+  props.allocType = cudaMemAllocationTypePinned;
+  props.handleTypes = cudaMemHandleTypeNone;
+  props.location.type = cudaMemLocationTypeDevice;
+  props.location.id = dev;
+  cudaMemPool_t pool = nullptr;
+  if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+    cudaGetLastError();
+    pool = nullptr;
+  } else {
+    unsigned long long keep = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+  pools[dev] = pool;
+  return pool;
+}
+
 struct DeviceBuffers {
   std::vector<const float*> inputs;
   std::vector<float*> nodes;
@@ -212,7 +242,9 @@ struct DeviceBuffers {
   float* alloc(size_t bytes, std::string* err) {
     void* p = nullptr;
     if (bytes == 0) bytes = 4;
-    cudaError_t rc = cudaMallocAsync(&p, bytes, stream);
+    cudaMemPool_t pool = library_pool();
+    cudaError_t rc = pool ? cudaMallocFromPoolAsync(&p, bytes, pool, stream)
+                          : cudaMallocAsync(&p, bytes, stream);
     if (rc != cudaSuccess) {
       *err = std::string("device allocation of ") + std::to_string(bytes) +
              " bytes failed: " + cudaGetErrorString(rc);

@@ -9,23 +9,31 @@
 // dividing once at the end is the same quantity.  exp is powf(2.71828175f, x)
 // in the reference; here it is 2^(x * log2(2.71828175)).
 //
-// Layout of one CTA (384 threads, 256 query rows = two 128-row tiles):
-//   warp 0      TMA producer.  Q tiles once; then K and V^T tiles of 64 keys
-//               through a ring of 32 KB slots (128-byte swizzled rows).
-//   warp 1      MMA issuer.  S[t] = Q[t] K^T with tcgen05.mma kind::tf32
-//               (A, B from shared memory), O[t] += P[t] V with A = P read from
-//               tensor memory.  S is double-buffered per tile so the QK^T of
-//               the next KV tile runs while the softmax of this one is in
-//               flight.
-//   warps 4-7   softmax for tile 0, warps 8-11 for tile 1: one thread per
-//               query row; S is read from tensor memory, P written back over
-//               it; the row maximum/sum live in registers.  O is rescaled in
-//               tensor memory only when the maximum grows by more than 2^8.
-// Tensor memory: S[tile][buf] 4 x 64 columns, O[tile] 2 x 128 columns.
-// K/V rows past the end are zero-filled by TMA and masked to -inf; query rows
-// past the end are computed and not stored.
+// One CTA (384 threads) owns 128 query rows and walks the keys in tiles of 128:
+//   warp 0      TMA producer: K tiles ([128 keys][d]) and V^T tiles
+//               ([dv][128 keys]) as 128-byte-swizzled rows through a ring of
+//               three 64 KB slots.
+//   warp 1      MMA issuer.  Both contractions take their A operand from
+//               tensor memory (measured on B200: an M=128 tcgen05.mma with A
+//               in shared memory never costs less than ~124 cycles, with A in
+//               tensor memory ~71 for N=128, against 64 ideal):
+//               S = Q K^T with Q resident in tensor memory for the whole
+//               kernel, O += P V with P read where the softmax wrote it.  S is
+//               double-buffered so Q K^T of the next tile overlaps the softmax
+//               of this one.
+//   warps 4-11  softmax: two warpgroups share every row, warpgroup h taking
+//               key columns [64h, 64h+64) of the tile (a warp can only reach
+//               its own 32-lane quadrant of tensor memory, so rows cannot be
+//               split).  The halves of the row maximum meet through shared
+//               memory and a 256-thread named barrier; each half keeps its own
+//               partial row sum until the end.  O is rescaled in tensor memory
+//               only when the maximum grows by more than 2^8.
+// Tensor memory (512 columns): Q 128 | S buffer 0 128 | S buffer 1 128 | O 128.
+// Q is loaded from global memory by the softmax threads, rounded to TF32 and
+// stored to tensor memory once.  K/V rows past the end are zero-filled by TMA
+// and masked to -inf; query rows past the end are computed and not stored.
 //
-// When one head has too few 256-row blocks to fill the GPU, the KV range is
+// When one head has too few 128-row tiles to fill the GPU, the KV range is
 // split across CTAs; each writes a normalised partial O with its (m, l) and a
 // small second kernel merges them.
 // Roofline: tensor-bound, 4*Nq*Nk*d FLOP per head.
@@ -38,27 +46,26 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBQ = 128;          // rows per query tile
-constexpr int kBKV = 64;          // keys per KV tile
+constexpr int kBQ = 128;           // query rows per CTA
+constexpr int kBKV = 128;          // keys per KV tile
 constexpr int kThreads = 384;
-constexpr int kQChunkBytes = kBQ * 128;    // 128 rows x 32 fp32
-constexpr int kKChunkBytes = kBKV * 128;   // 64 rows x 32 fp32
-constexpr int kVChunkBytes = 128 * 128;    // 128 dv rows x 32 keys
-constexpr int kSlotBytes = 32768;
-constexpr int kMaxRing = 8;
+constexpr int kChunkBytes = 128 * 128;     // 128 rows x 32 fp32
+constexpr int kSlotBytes = 4 * kChunkBytes;
+constexpr int kRing = 3;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;             // + (tile * 2 + buf) * 64
-constexpr uint32_t kTmemO = 256;           // + tile * 128
+constexpr uint32_t kTmemQ = 0;
+constexpr uint32_t kTmemS = 128;           // + buf * 128
+constexpr uint32_t kTmemO = 384;
 constexpr float kLog2E32 = 1.4426950216293335f;  // log2(2.71828175f)
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Params {
+  const float* q;      // [batch][nq][d], original fp32
   int nq, nk, d, dv, batch;
-  int q_blocks;        // 256-row blocks per head
-  int splits;          // KV splits per block
-  int kv_blocks;       // 64-key tiles per head
+  int q_tiles;         // 128-row tiles per head
+  int splits;          // KV splits per tile
+  int kv_tiles;        // 128-key tiles per head
   int kv_per_split;
-  int ring;            // ring slots
   float* o;            // [batch][nq][dv]
   float* part_o;       // [splits][batch][nq][dv] when splits > 1
   float* part_m;       // [splits][batch][nq]
@@ -67,103 +74,101 @@ struct Params {
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (debugging aid), or null
 };
 
-struct Barriers {
-  uint64_t q_full;
-  uint64_t kv_full[kMaxRing];
-  uint64_t kv_empty[kMaxRing];
-  uint64_t s_full[2][2];
-  uint64_t p_full[2][2];
-  uint64_t pv_done[2][2];   // [tile][KV tile parity]: see the note at its wait
+struct Shared {
+  uint64_t kv_full[kRing];
+  uint64_t kv_empty[kRing];
+  uint64_t q_ready;
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t pv_done[2];       // [KV tile parity]: see the note at its wait
   uint32_t tmem_slot;
   AbortState abort;
+  int give_up;               // raised before a named barrier, read after it
+  float half_max[2][2][kBQ]; // [iteration parity][warpgroup][row]
+  float half_sum[2][kBQ];
 };
 
+__device__ __forceinline__ void softmax_pair_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
-attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
-                      const __grid_constant__ CUtensorMap map_k,
+attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vt, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const int d_chunks = (p.d + 31) / 32;
-  uint8_t* q_smem = smem;                                   // [2][d_chunks][128 rows][128 B]
-  uint8_t* ring = q_smem + 2 * d_chunks * kQChunkBytes;     // [ring][32 KB]
-  Barriers* bars = reinterpret_cast<Barriers*>(ring + p.ring * kSlotBytes);
+  uint8_t* ring = smem;                                     // [kRing][64 KB]
+  Shared* sh = reinterpret_cast<Shared*>(ring + kRing * kSlotBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int d_chunks = (p.d + 31) / 32;
 
   // Work unit of this CTA.
   int unit = blockIdx.x;
   const int split = unit % p.splits;
   unit /= p.splits;
-  const int qb = unit % p.q_blocks;
-  const int b = unit / p.q_blocks;
+  const int qt = unit % p.q_tiles;
+  const int b = unit / p.q_tiles;
   const int kv_lo = split * p.kv_per_split;
-  const int kv_hi = min(p.kv_blocks, kv_lo + p.kv_per_split);
+  const int kv_hi = min(p.kv_tiles, kv_lo + p.kv_per_split);
   const int n_kv = kv_hi - kv_lo;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
-    for (int s = 0; s < p.ring; ++s) {
-      mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(&sh->kv_full[s], 1);
+      mbar_init(&sh->kv_empty[s], 1);
     }
-    for (int t = 0; t < 2; ++t) {
-      for (int u = 0; u < 2; ++u) {
-        mbar_init(&bars->s_full[t][u], 1);
-        mbar_init(&bars->p_full[t][u], 4);   // one arrival per softmax warp
-        mbar_init(&bars->pv_done[t][u], 1);
-      }
+    mbar_init(&sh->q_ready, 8);            // one arrival per softmax warp
+    for (int u = 0; u < 2; ++u) {
+      mbar_init(&sh->s_full[u], 1);
+      mbar_init(&sh->p_full[u], 8);
+      mbar_init(&sh->pv_done[u], 1);
     }
-    bars->abort.flag = 0;
+    sh->abort.flag = 0;
+    sh->give_up = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bars->tmem_slot, kTmemCols);
+    tmem_alloc(&sh->tmem_slot, kTmemCols);
     tmem_relinquish_alloc_permit();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_slot;
-  AbortState* abort = &bars->abort;
+  const uint32_t tmem_base = sh->tmem_slot;
+  AbortState* abort = &sh->abort;
 
   if (warp == 0) {
     if (lane == 0 && n_kv > 0) {
-      tma_prefetch_descriptor(&map_q);
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_vt);
-      mbar_arrive_expect_tx(&bars->q_full, 2 * d_chunks * kQChunkBytes);
-      for (int t = 0; t < 2; ++t)
-        for (int c = 0; c < d_chunks; ++c)
-          tma_load_3d(q_smem + (t * d_chunks + c) * kQChunkBytes, &map_q, &bars->q_full, c * 32,
-                      qb * 2 * kBQ + t * kBQ, b);
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
       long long waited = 0;
       auto load_k = [&](int j) {
         const long long t0 = clock64();
-        if (!(ok = mbar_wait(&bars->kv_empty[slot], phase ^ 1, abort, p.status, 201))) return;
+        if (!(ok = mbar_wait(&sh->kv_empty[slot], phase ^ 1, abort, p.status, 201))) return;
         waited += clock64() - t0;
         uint8_t* dst = ring + slot * kSlotBytes;
-        mbar_arrive_expect_tx(&bars->kv_full[slot], d_chunks * kKChunkBytes);
+        mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
         for (int c = 0; c < d_chunks; ++c)
-          tma_load_3d(dst + c * kKChunkBytes, &map_k, &bars->kv_full[slot], c * 32, j * kBKV, b);
-        if (++slot == p.ring) { slot = 0; phase ^= 1; }
+          tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * 32, j * kBKV, b);
+        if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
       auto load_v = [&](int j) {
         const long long t0 = clock64();
-        if (!(ok = mbar_wait(&bars->kv_empty[slot], phase ^ 1, abort, p.status, 202))) return;
+        if (!(ok = mbar_wait(&sh->kv_empty[slot], phase ^ 1, abort, p.status, 202))) return;
         waited += clock64() - t0;
         uint8_t* dst = ring + slot * kSlotBytes;
-        mbar_arrive_expect_tx(&bars->kv_full[slot], 2 * kVChunkBytes);
-        for (int c = 0; c < 2; ++c)
-          tma_load_3d(dst + c * kVChunkBytes, &map_vt, &bars->kv_full[slot], j * kBKV + c * 32, 0,
-                      b);
-        if (++slot == p.ring) { slot = 0; phase ^= 1; }
+        mbar_arrive_expect_tx(&sh->kv_full[slot], 4 * kChunkBytes);
+        for (int c = 0; c < 4; ++c)
+          tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot], j * kBKV + c * 32, 0, b);
+        if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
+      // Consumption order: K(0), then per tile K(j+1) before V(j).
       load_k(kv_lo);
       for (int jj = 0; ok && jj < n_kv; ++jj) {
         if (jj + 1 < n_kv) load_k(kv_lo + jj + 1);
@@ -179,58 +184,64 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       const int k_steps = (p.d + 7) / 8;
       int slot = 0;
       uint32_t phase = 0;
-      bool ok = mbar_wait(&bars->q_full, 0, abort, p.status, 203);
-      const uint32_t q_addr = smem_u32(q_smem);
       const uint32_t ring_addr = smem_u32(ring);
-
-      // S[t][buf] = Q[t] K^T for both tiles from the K tile in the current slot.
-      long long wait_k = 0, wait_v = 0, wait_p = 0;
+      long long wait_k = 0, wait_v = 0, wait_p = 0, issue_qk_cycles = 0, issue_pv_cycles = 0;
       const long long t_start = clock64();
+      bool ok = mbar_wait(&sh->q_ready, 0, abort, p.status, 203);
+      tc_fence_after_sync();
+
+      // S[buf] = Q K^T from the K tile in the current slot (A = Q in tensor memory).
       auto issue_qk = [&](int buf) {
         const long long t0 = clock64();
-        if (!(ok = mbar_wait(&bars->kv_full[slot], phase, abort, p.status, 204))) return;
+        if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 204))) return;
         wait_k += clock64() - t0;
         tc_fence_after_sync();
-        const uint32_t k_addr = ring_addr + slot * kSlotBytes;
-        for (int t = 0; t < 2; ++t) {
-          const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>((t * 2 + buf) * kBKV);
-          for (int ks = 0; ks < k_steps; ++ks) {
-            const int c = ks >> 2, r = ks & 3;
-            const uint64_t a_desc =
-                make_smem_desc_sw128(q_addr + (t * d_chunks + c) * kQChunkBytes + r * 32);
-            const uint64_t b_desc = make_smem_desc_sw128(k_addr + c * kKChunkBytes + r * 32);
-            mma_ss<Kind::TF32>(d_tmem, a_desc, b_desc, idesc_qk, ks != 0 ? 1u : 0u);
-          }
-          mma_commit(&bars->s_full[t][buf]);
+        // One descriptor per slot; a K step moves it by a compile-time constant
+        // (32 bytes inside the swizzled row, 16 KB to the next 32-feature chunk),
+        // so the issuing thread spends one 64-bit add per MMA.
+        const long long ti = clock64();
+        const uint64_t k_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
+        const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
+        const uint32_t q_tmem = tmem_base + kTmemQ;
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+          if (ks < k_steps)
+            mma_ts<Kind::TF32>(d_tmem, q_tmem + ks * 8,
+                               k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
+                               ks != 0 ? 1u : 0u);
         }
-        mma_commit(&bars->kv_empty[slot]);
-        if (++slot == p.ring) { slot = 0; phase ^= 1; }
+        mma_commit(&sh->s_full[buf]);
+        mma_commit(&sh->kv_empty[slot]);
+        issue_qk_cycles += clock64() - ti;
+        if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
-      // O[t] += P[t][buf] V for both tiles from the V^T tile in the current slot.
+      // O += P[buf] V from the V^T tile in the current slot (A = P in tensor memory).
       auto issue_pv = [&](int jj) {
         const int buf = jj & 1;
         long long t0 = clock64();
-        if (!(ok = mbar_wait(&bars->kv_full[slot], phase, abort, p.status, 205))) return;
+        if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) return;
         wait_v += clock64() - t0;
-        const uint32_t v_addr = ring_addr + slot * kSlotBytes;
-        for (int t = 0; t < 2; ++t) {
-          t0 = clock64();
-          if (!(ok = mbar_wait(&bars->p_full[t][buf], (jj >> 1) & 1, abort, p.status, 206))) return;
-          wait_p += clock64() - t0;
-          tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + kTmemO + static_cast<uint32_t>(t * 128);
-          const uint32_t p_tmem = tmem_base + kTmemS + static_cast<uint32_t>((t * 2 + buf) * kBKV);
-#pragma unroll
-          for (int ks = 0; ks < kBKV / 8; ++ks) {
-            const int c = ks >> 2, r = ks & 3;
-            const uint64_t b_desc = make_smem_desc_sw128(v_addr + c * kVChunkBytes + r * 32);
-            mma_ts<Kind::TF32>(d_tmem, p_tmem + ks * 8, b_desc, idesc_pv,
-                               (jj | ks) != 0 ? 1u : 0u);
-          }
-          mma_commit(&bars->pv_done[t][buf]);
+        t0 = clock64();
+        if (!(ok = mbar_wait(&sh->p_full[buf], (jj >> 1) & 1, abort, p.status, 206))) return;
+        wait_p += clock64() - t0;
+        tc_fence_after_sync();
+        const long long ti = clock64();
+        const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
+        const uint32_t d_tmem = tmem_base + kTmemO;
+        const uint32_t p_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
+        if (jj == 0) {
+          mma_ts<Kind::TF32>(d_tmem, p_tmem, v_desc, idesc_pv, 0u);
+        } else {
+          mma_ts<Kind::TF32>(d_tmem, p_tmem, v_desc, idesc_pv, 1u);
         }
-        mma_commit(&bars->kv_empty[slot]);
-        if (++slot == p.ring) { slot = 0; phase ^= 1; }
+#pragma unroll
+        for (int ks = 1; ks < kBKV / 8; ++ks)
+          mma_ts<Kind::TF32>(d_tmem, p_tmem + ks * 8,
+                             v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
+        mma_commit(&sh->pv_done[buf]);
+        mma_commit(&sh->kv_empty[slot]);
+        issue_pv_cycles += clock64() - ti;
+        if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
 
       if (ok) issue_qk(0);
@@ -241,50 +252,101 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
       if (p.prof) {
         p.prof[blockIdx.x * 8 + 1] = wait_k;
         p.prof[blockIdx.x * 8 + 2] = wait_v;
+        p.prof[blockIdx.x * 8 + 5] = issue_qk_cycles;
+        p.prof[blockIdx.x * 8 + 6] = issue_pv_cycles;
         p.prof[blockIdx.x * 8 + 3] = wait_p;
         p.prof[blockIdx.x * 8 + 4] = clock64() - t_start;
       }
     }
   } else if (warp >= 4 && n_kv > 0) {
-    const int t = (warp - 4) >> 2;            // query tile of this warpgroup
+    const int h = (warp - 4) >> 2;            // column half of this warpgroup
     const int quad = warp & 3;                // TMEM lane quadrant
-    const int row_in_tile = quad * 32 + lane;
-    const long long row = static_cast<long long>(qb) * 2 * kBQ + t * kBQ + row_in_tile;
+    const int r = quad * 32 + lane;           // row within the tile
+    const long long row = static_cast<long long>(qt) * kBQ + r;
     const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO + static_cast<uint32_t>(t * 128);
+    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
     const int dv_chunks = (p.dv + 31) / 32;
-    float m_used = -CUDART_INF_F;             // running maximum, log2 domain
-    float l = 0.0f;
-    bool ok = true;
 
+    // ---- Q: global -> TF32 (nearest) -> tensor memory, columns [64h, 64h+64) ----
+    {
+      const float* qrow = p.q + (static_cast<size_t>(b) * p.nq + row) * p.d;
+      const bool live = row < p.nq;
+      const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = h * 64 + c * 32;
+        uint32_t v[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (live && vec && col0 + e + 4 <= p.d) {
+            x = *reinterpret_cast<const float4*>(qrow + col0 + e);
+          } else if (live) {
+            if (col0 + e + 0 < p.d) x.x = qrow[col0 + e + 0];
+            if (col0 + e + 1 < p.d) x.y = qrow[col0 + e + 1];
+            if (col0 + e + 2 < p.d) x.z = qrow[col0 + e + 2];
+            if (col0 + e + 3 < p.d) x.w = qrow[col0 + e + 3];
+          }
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
+        }
+        tmem_st_32x32(tmem_base + lane_bits + kTmemQ + col0, v);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->q_ready);
+    }
+
+    float m_used = -CUDART_INF_F;             // running maximum, log2 domain
+    float l = 0.0f;                           // this half's share of the row sum
+    bool dead = false;                        // a wait gave up; keep hitting the barriers only
     long long wait_s = 0;
     const long long t_start = clock64();
+
     for (int jj = 0; jj < n_kv; ++jj) {
       const int buf = jj & 1;
-      const long long t0 = clock64();
-      ok = mbar_wait(&bars->s_full[t][buf], (jj >> 1) & 1, abort, p.status, 207);
-      wait_s += clock64() - t0;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t * 2 + buf) * kBKV);
+      const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>(buf * kBKV) +
+                              static_cast<uint32_t>(h * 64);
       uint32_t s0[32], s1[32];
-      tmem_ld_32x32(s_tmem, s0);
-      tmem_ld_32x32(s_tmem + 32, s1);
-      tmem_wait_ld();
-
-      const int col0 = (kv_lo + jj) * kBKV;
-      if (col0 + kBKV > p.nk) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (col0 + c >= p.nk) s0[c] = __float_as_uint(-CUDART_INF_F);
-          if (col0 + 32 + c >= p.nk) s1[c] = __float_as_uint(-CUDART_INF_F);
-        }
+      if (!dead) {
+        const long long t0 = clock64();
+        dead = !mbar_wait_warp(&sh->s_full[buf], (jj >> 1) & 1, abort, p.status, 207);
+        wait_s += clock64() - t0;
       }
       float mx = -CUDART_INF_F;
+      if (!dead) {
+        tc_fence_after_sync();
+        tmem_ld_32x32(s_tmem, s0);
+        tmem_ld_32x32(s_tmem + 32, s1);
+        tmem_wait_ld();
+        const int col0 = (kv_lo + jj) * kBKV + h * 64;
+        if (col0 + 64 > p.nk) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
-        mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+          for (int c = 0; c < 32; ++c) {
+            if (col0 + c >= p.nk) s0[c] = __float_as_uint(-CUDART_INF_F);
+            if (col0 + 32 + c >= p.nk) s1[c] = __float_as_uint(-CUDART_INF_F);
+          }
+        }
+        float mx0 = -CUDART_INF_F, mx1 = mx0, mx2 = mx0, mx3 = mx0;
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(s0[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(s1[c]));
+          mx3 = fmaxf(mx3, __uint_as_float(s1[c + 1]));
+        }
+        mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        sh->half_max[buf][h][r] = mx;
+      } else {
+        sh->give_up = 1;
+      }
+      softmax_pair_sync();
+      if (sh->give_up) break;                 // uniform: every writer wrote before the barrier
+      mx = fmaxf(mx, sh->half_max[buf][h ^ 1][r]);
+
       const float m_new = fmaxf(m_used, mx * kLog2E32);
       const bool grow = m_new > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow)) {
@@ -292,68 +354,75 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_q,
         if (grow) m_used = m_new;
         l *= factor;
         if (jj > 0) {
-          // O[t] may still be receiving P V of the previous KV tile.  Its
-          // completion is signalled on the barrier of that tile's parity, so a
-          // waiter that skipped earlier phases is never more than one phase
-          // behind (a parity wait cannot tell phases two apart).
-          ok = mbar_wait(&bars->pv_done[t][(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort, p.status,
-                         208);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
-          for (int c = 0; c < dv_chunks; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(o_tmem + c * 32, o);
-            tmem_wait_ld();
+          // O may still be receiving P V of the previous KV tile.  Its completion
+          // is signalled on the barrier of that tile's parity, so a waiter that
+          // skipped earlier phases is never more than one phase behind (a parity
+          // wait cannot tell phases two apart).
+          dead = !mbar_wait_warp(&sh->pv_done[(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort, p.status,
+                                 208);
+          if (!dead) {
+            tc_fence_after_sync();
+            // Each half rescales its own 64 output columns.
+            for (int c = h * 2; c < h * 2 + 2 && c < dv_chunks; ++c) {
+              uint32_t o[32];
+              tmem_ld_32x32(o_tmem + c * 32, o);
+              tmem_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
-            tmem_st_32x32(o_tmem + c * 32, o);
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+              tmem_st_32x32(o_tmem + c * 32, o);
+            }
           }
         }
       }
-      float sum = 0.0f;
+      if (dead) continue;
+      float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         float e0 = ex2_approx(fmaf(__uint_as_float(s0[c]), kLog2E32, -m_used));
         float e1 = ex2_approx(fmaf(__uint_as_float(s1[c]), kLog2E32, -m_used));
-        sum += e0 + e1;
+        sum0 += e0;
+        sum1 += e1;
         s0[c] = __float_as_uint(e0);
         s1[c] = __float_as_uint(e1);
       }
-      l += sum;
+      l += sum0 + sum1;
       tmem_st_32x32(s_tmem, s0);
       tmem_st_32x32(s_tmem + 32, s1);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
+      if (lane == 0) mbar_arrive(&sh->p_full[buf]);
     }
 
-    if (p.prof && (warp & 3) == 0 && lane == 0) {
-      p.prof[blockIdx.x * 8 + 5 + t] = wait_s;
-      if (t == 0) p.prof[blockIdx.x * 8 + 7] = clock64() - t_start;
+    if (p.prof && quad == 0 && lane == 0) {
+      if (h == 0) p.prof[blockIdx.x * 8 + 7] = clock64() - t_start - wait_s;
     }
-    if (ok) {
-      ok = mbar_wait(&bars->pv_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort, p.status,
-                     209);
-      ok = __all_sync(0xffffffffu, ok);
+
+    // ---- epilogue: total row sum, normalise, store columns [64h, 64h+64) of O ----
+    if (!sh->give_up && !dead) {
+      dead = !mbar_wait_warp(&sh->pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort, p.status,
+                             209);
     }
-    if (ok) {
+    sh->half_sum[h][r] = l;
+    if (dead) sh->give_up = 1;
+    softmax_pair_sync();
+    if (!sh->give_up) {
       tc_fence_after_sync();
-      const float inv = 1.0f / l;
+      const float l_total = l + sh->half_sum[h ^ 1][r];
+      const float inv = 1.0f / l_total;
       float* dst;
       if (p.splits == 1) {
         dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
       } else {
         const size_t prow = (static_cast<size_t>(split) * p.batch + b) * p.nq + row;
         dst = p.part_o + prow * p.dv;
-        if (row < p.nq) {
+        if (row < p.nq && h == 0) {
           p.part_m[prow] = m_used;
-          p.part_l[prow] = l;
+          p.part_l[prow] = l_total;
         }
       }
       const bool vec_ok = (p.dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
-      for (int c = 0; c < dv_chunks; ++c) {
+      for (int c = h * 2; c < h * 2 + 2 && c < dv_chunks; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(o_tmem + c * 32, o);
         tmem_wait_ld();
@@ -424,11 +493,11 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
 // records how many cycles each role spent waiting on its barriers.
 unsigned long long* g_attention_profile = nullptr;
 
-int choose_splits(size_t units, int kv_blocks, int sms) {
-  if (units >= static_cast<size_t>(sms) || kv_blocks < 8) return 1;
+int choose_splits(size_t units, int kv_tiles, int sms) {
+  if (units >= static_cast<size_t>(sms) || kv_tiles < 8) return 1;
   int s = static_cast<int>(sms / units);
   if (s < 1) s = 1;
-  if (s > kv_blocks / 4) s = kv_blocks / 4;
+  if (s > kv_tiles / 4) s = kv_tiles / 4;
   if (s > 16) s = 16;
   return s < 1 ? 1 : s;
 }
@@ -437,21 +506,14 @@ int choose_splits(size_t units, int kv_blocks, int sms) {
 
 void set_attention_profile(unsigned long long* p) { g_attention_profile = p; }
 
-bool attention_tcgen05_supported(const float* q, const float* k, const float* o, size_t d,
-                                 size_t dv) {
-  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  return aligned(q) && aligned(k) && o != nullptr && d % 4 == 0 && d >= 4 && d <= 128 && dv >= 1 &&
-         dv <= 128;
-}
-
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv, int* splits_out) {
   int sms = kNumSMs;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess)
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const size_t q_blocks = (nq + 2 * kBQ - 1) / (2 * kBQ);
-  const int kv_blocks = static_cast<int>((nk + kBKV - 1) / kBKV);
-  const int splits = choose_splits(q_blocks * batch, kv_blocks, sms);
+  const size_t q_tiles = (nq + kBQ - 1) / kBQ;
+  const int kv_tiles = static_cast<int>((nk + kBKV - 1) / kBKV);
+  const int splits = choose_splits(q_tiles * batch, kv_tiles, sms);
   if (splits_out) *splits_out = splits;
   if (splits == 1) return 0;
   return static_cast<size_t>(splits) * batch * nq * (dv + 2);
@@ -464,34 +526,34 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   if (nk == 0) return fail("ib_attention: no keys");
   if (nq >= (1u << 30) || nk >= (1u << 30) || batch >= (1u << 20))
     return fail("ib_attention: shape too large");
+  if (d % 4 != 0 || d < 4 || d > 128 || dv < 1 || dv > 128)
+    return fail("ib_attention: head dimensions outside the fused kernel's range");
+  const int smem_bytes = 1024 + kRing * kSlotBytes + static_cast<int>(sizeof(Shared)) + 64;
   static bool configured = false;
-  static int max_smem = 0;
   if (!configured) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     cudaError_t err = cudaFuncSetAttribute(attention_tf32_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess)
       return fail(std::string("ib_attention: cannot reserve shared memory: ") +
                   cudaGetErrorString(err));
     configured = true;
   }
   Params p{};
+  p.q = q;
   p.nq = static_cast<int>(nq);
   p.nk = static_cast<int>(nk);
   p.d = static_cast<int>(d);
   p.dv = static_cast<int>(dv);
   p.batch = static_cast<int>(batch);
-  p.q_blocks = static_cast<int>((nq + 2 * kBQ - 1) / (2 * kBQ));
-  p.kv_blocks = static_cast<int>((nk + kBKV - 1) / kBKV);
+  p.q_tiles = static_cast<int>((nq + kBQ - 1) / kBQ);
+  p.kv_tiles = static_cast<int>((nk + kBKV - 1) / kBKV);
   int splits = 1;
-  const size_t part_floats = attention_tcgen05_partial_floats(batch, nq, nk, dv, &splits);
+  attention_tcgen05_partial_floats(batch, nq, nk, dv, &splits);
   if (splits > 1 && !partials) return fail("ib_attention: workspace for KV splits is missing");
   p.splits = splits;
-  p.kv_per_split = (p.kv_blocks + splits - 1) / splits;
+  p.kv_per_split = (p.kv_tiles + splits - 1) / splits;
   // Every split must own at least one KV tile.
-  while (p.splits > 1 && (p.splits - 1) * p.kv_per_split >= p.kv_blocks) --p.splits;
+  while (p.splits > 1 && (p.splits - 1) * p.kv_per_split >= p.kv_tiles) --p.splits;
   p.o = o;
   if (p.splits > 1) {
     const size_t rows = static_cast<size_t>(p.splits) * batch * nq;
@@ -499,29 +561,18 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
     p.part_m = partials + rows * dv;
     p.part_l = p.part_m + rows;
   }
-  (void)part_floats;
   p.status = device_status_word(s);
   if (!p.status) return fail("ib_attention: cannot allocate the device status word");
   p.prof = g_attention_profile;
 
-  const int d_chunks = static_cast<int>((d + 31) / 32);
-  const int q_bytes = 2 * d_chunks * kQChunkBytes;
-  int ring = (max_smem - 1024 - static_cast<int>(sizeof(Barriers)) - 64 - q_bytes) / kSlotBytes;
-  if (ring > kMaxRing) ring = kMaxRing;
-  if (ring < 3) return fail("ib_attention: not enough shared memory for the K/V ring");
-  p.ring = ring;
-  const int smem_bytes = 1024 + q_bytes + ring * kSlotBytes + static_cast<int>(sizeof(Barriers)) + 64;
-
-  CUtensorMap map_q, map_k, map_vt;
-  if (int rc = make_tensor_map_f32(&map_q, q, batch, nq, d, d, nq * d, kBQ)) return rc;
+  CUtensorMap map_k, map_vt;
   if (int rc = make_tensor_map_f32(&map_k, k, batch, nk, d, d, nk * d, kBKV)) return rc;
   if (int rc = make_tensor_map_f32(&map_vt, vt, batch, dv, nk, nk_pitch, dv * nk_pitch, 128))
     return rc;
 
-  const size_t grid = static_cast<size_t>(p.q_blocks) * p.splits * batch;
+  const size_t grid = static_cast<size_t>(p.q_tiles) * p.splits * batch;
   if (grid >= (1u << 31)) return fail("ib_attention: too many work units");
-  attention_tf32_kernel<<<static_cast<unsigned>(grid), kThreads, smem_bytes, s>>>(map_q, map_k,
-                                                                                 map_vt, p);
+  attention_tf32_kernel<<<static_cast<unsigned>(grid), kThreads, smem_bytes, s>>>(map_k, map_vt, p);
   if (int rc = check_launch("ib_attention (tcgen05 tf32)")) return rc;
   if (p.splits > 1) {
     const size_t rows = batch * nq;

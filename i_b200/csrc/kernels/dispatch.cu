@@ -95,8 +95,8 @@ extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t n
   using namespace ib;
   const double flop = 4.0 * batch * nq * nk * d;
   if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
-    // TF32-rounded copies of Q and K, V^T (rounded), and the KV-split partials.
-    size_t bytes = carve_bytes(batch * nq * d) + carve_bytes(batch * nk * d);
+    // TF32-rounded copy of K, V^T (rounded), and the KV-split partials.
+    size_t bytes = carve_bytes(batch * nk * d);
     bytes += carve_bytes(batch * dv * round_up(nk, 4));
     bytes += carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
     return bytes;
@@ -127,27 +127,29 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
   const bool tensor = wants_tensor(precision, flop);
 
   if (tensor && attention_shape_ok(d, dv)) {
-    // The tensor core truncates fp32 operands to TF32.  Q, K and V are first
-    // rounded to nearest into workspace copies (V transposed to [dv][keys] on the
-    // way, which is the K-major layout the second contraction needs).
+    // The tensor core truncates fp32 operands to TF32.  K and V are first rounded
+    // to nearest into workspace copies (V transposed to [dv][keys] on the way,
+    // the K-major layout the second contraction needs); the kernel rounds Q
+    // itself while moving it into tensor memory.
     const size_t pitch = round_up(nk, 4);
     const char* small = "ib_attention: workspace too small (see ib_attention_workspace_bytes)";
-    float* qr = ws.take(batch * nq * d);
     float* kr = ws.take(batch * nk * d);
     float* vt = ws.take(batch * dv * pitch);
-    if (!qr || !kr || !vt) return fail(small);
-    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15u) == 0;
+    if (!kr || !vt) return fail(small);
+    const bool aligned = (reinterpret_cast<uintptr_t>(k) & 15u) == 0;
     if (!v_kmajor && aligned) {
-      if (int rc = prepare_attention_operands(q, qr, batch * nq * d, k, kr, batch * nk * d, v, vt,
+      if (int rc = prepare_attention_operands(nullptr, nullptr, 0, k, kr, batch * nk * d, v, vt,
                                               batch, nk, dv, pitch, s))
         return rc;
-    } else if (!v_kmajor) {
-      if (int rc = round_tf32_rows(q, qr, batch * nq, d, d, d, k, kr, batch * nk, d, d, d, s)) return rc;
-      if (int rc = transpose_batched(v, vt, batch, nk, dv, pitch, true, s)) return rc;
     } else {
-      if (int rc = round_tf32_rows(q, qr, batch * nq, d, d, d, k, kr, batch * nk, d, d, d, s)) return rc;
-      if (int rc = round_tf32_rows(v, vt, batch * dv, nk, nk, pitch, nullptr, nullptr, 0, 0, 0, 0, s))
+      if (int rc = round_tf32_rows(k, kr, batch * nk, d, d, d, nullptr, nullptr, 0, 0, 0, 0, s))
         return rc;
+      if (!v_kmajor) {
+        if (int rc = transpose_batched(v, vt, batch, nk, dv, pitch, true, s)) return rc;
+      } else {
+        if (int rc = round_tf32_rows(v, vt, batch * dv, nk, nk, pitch, nullptr, nullptr, 0, 0, 0, 0, s))
+          return rc;
+      }
     }
     float* partials = nullptr;
     const size_t part_floats = attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr);
@@ -156,7 +158,7 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
       if (!partials)
         return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
     }
-    return attention_tcgen05(qr, kr, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
+    return attention_tcgen05(q, kr, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);

@@ -47,10 +47,8 @@ bool gemm_tcgen05_supported(const float* a, const float* b, const float* c, size
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
                  size_t k, cudaStream_t s);
 
-// attention_tcgen05.cu — fused online-softmax attention; vt is V transposed to
-// [b][dv][nk_pitch].
-bool attention_tcgen05_supported(const float* q, const float* k, const float* o, size_t d,
-                                 size_t dv);
+// attention_tcgen05.cu — fused online-softmax attention; q is the caller's fp32
+// Q, k a TF32-rounded copy of K, vt the rounded V transposed to [b][dv][nk_pitch].
 // Floats of scratch the KV-split partials need (0 when one CTA covers all keys).
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv,
                                         int* splits_out);

@@ -93,6 +93,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, AbortS
   }
 }
 
+// Whole-warp wait: lane 0 polls, the result is broadcast.  Keeps 31 of 32 lanes
+// from hammering the barrier's shared-memory word while the tensor core is
+// streaming operands out of the same shared memory.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, AbortState* abort,
+                                               int* status, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort, status, code) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();
+  return ok != 0;
+}
+
 // ---- TMA ------------------------------------------------------------------
 
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
