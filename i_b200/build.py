@@ -32,6 +32,7 @@ SOURCES = [
     "kernels/gemm_tcgen05.cu",
     "kernels/attention_tcgen05.cu",
     "kernels/dispatch.cu",
+    "kernels/attention_static.cu",
 ]
 
 NVCC_FLAGS = [
