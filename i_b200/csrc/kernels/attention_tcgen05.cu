@@ -33,9 +33,13 @@
 // stored to tensor memory once.  K/V rows past the end are zero-filled by TMA
 // and masked to -inf; query rows past the end are computed and not stored.
 //
-// When one head has too few 128-row tiles to fill the GPU, the KV range is
-// split across CTAs; each writes a normalised partial O with its (m, l) and a
-// small second kernel merges them.
+// Work is balanced over the SMs.  CTA g of G first takes whole row tiles
+// g, g+G, g+2G, ... (neighbouring CTAs then stream the same head's K/V at the
+// same time, which keeps them in L2).  The row tiles left over when their number
+// is not a multiple of G are split stream-K style: their (row tile, key tile)
+// pairs form one flat sequence cut into G equal contiguous ranges.  A range
+// piece that does not cover its row tile completely is written as a normalised
+// partial O with its (m, l); a small second kernel merges the pieces.
 // Roofline: tensor-bound, 4*Nq*Nk*d FLOP per head.
 #include "common.cuh"
 #include "kernels.h"
@@ -63,12 +67,14 @@ struct Params {
   const float* q;      // [batch][nq][d], original fp32
   int nq, nk, d, dv, batch;
   int q_tiles;         // 128-row tiles per head
-  int splits;          // KV splits per tile
   int kv_tiles;        // 128-key tiles per head
-  int kv_per_split;
+  int ctas;               // G
+  int full_waves;         // whole row tiles every CTA takes before the tail
+  long long iters_base;   // tail (row tile, key tile) pairs per CTA: CTA g takes iters_base, plus
+  int iters_rem;          // one more when g < iters_rem
   float* o;            // [batch][nq][dv]
-  float* part_o;       // [splits][batch][nq][dv] when splits > 1
-  float* part_m;       // [splits][batch][nq]
+  float* part_o;       // [2 * ctas][128][dv]: slot 2g + (0: first piece, 1: last piece of CTA g)
+  float* part_m;       // [2 * ctas][128]
   float* part_l;
   int* status;
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (debugging aid), or null
@@ -88,10 +94,62 @@ struct Shared {
   float half_sum[2][kBQ];
 };
 
+// One contiguous run of key tiles of one row tile.
+struct Piece {
+  int unit;        // row tile index over the whole call (head * q_tiles + tile)
+  int kv_lo, n_kv;
+  bool whole;      // covers every key tile: the result is final
+  int ordinal;     // 0 = first tail piece of this CTA, 1 = a later one
+};
+
+struct PieceCursor {
+  int wave;
+  long long lo, cur, hi;
+};
+
+__device__ __forceinline__ PieceCursor pieces_begin(const Params& p) {
+  PieceCursor c;
+  const int g = static_cast<int>(blockIdx.x);
+  c.wave = 0;
+  c.lo = g * p.iters_base + min(g, p.iters_rem);
+  c.hi = c.lo + p.iters_base + (g < p.iters_rem ? 1 : 0);
+  c.cur = c.lo;
+  return c;
+}
+
+// Every role of a CTA walks the same sequence of pieces.
+__device__ __forceinline__ bool next_piece(const Params& p, PieceCursor& c, Piece& out) {
+  if (c.wave < p.full_waves) {
+    out.unit = c.wave * p.ctas + static_cast<int>(blockIdx.x);
+    out.kv_lo = 0;
+    out.n_kv = p.kv_tiles;
+    out.whole = true;
+    out.ordinal = 0;
+    ++c.wave;
+    return true;
+  }
+  if (c.cur >= c.hi) return false;
+  const int tail_unit = static_cast<int>(c.cur / p.kv_tiles);
+  out.unit = p.full_waves * p.ctas + tail_unit;
+  out.kv_lo = static_cast<int>(c.cur - static_cast<long long>(tail_unit) * p.kv_tiles);
+  out.n_kv = static_cast<int>(min(static_cast<long long>(p.kv_tiles - out.kv_lo), c.hi - c.cur));
+  out.whole = out.kv_lo == 0 && out.n_kv == p.kv_tiles;
+  out.ordinal = c.cur == c.lo ? 0 : 1;
+  c.cur += out.n_kv;
+  return true;
+}
+
+template <bool PROF>
+__device__ __forceinline__ long long tick() {
+  return PROF ? clock64() : 0ll;
+}
+
 __device__ __forceinline__ void softmax_pair_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
+// PROF = true compiles in the cycle counters written to Params::prof.
+template <bool PROF>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vt, const Params p) {
@@ -104,16 +162,6 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int d_chunks = (p.d + 31) / 32;
-
-  // Work unit of this CTA.
-  int unit = blockIdx.x;
-  const int split = unit % p.splits;
-  unit /= p.splits;
-  const int qt = unit % p.q_tiles;
-  const int b = unit / p.q_tiles;
-  const int kv_lo = split * p.kv_per_split;
-  const int kv_hi = min(p.kv_tiles, kv_lo + p.kv_per_split);
-  const int n_kv = kv_hi - kv_lo;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRing; ++s) {
@@ -141,17 +189,18 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
   AbortState* abort = &sh->abort;
 
   if (warp == 0) {
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0) {
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_vt);
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
       long long waited = 0;
+      int b = 0;
       auto load_k = [&](int j) {
-        const long long t0 = clock64();
+        const long long t0 = tick<PROF>();
         if (!(ok = mbar_wait(&sh->kv_empty[slot], phase ^ 1, abort, p.status, 201))) return;
-        waited += clock64() - t0;
+        waited += tick<PROF>() - t0;
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
         for (int c = 0; c < d_chunks; ++c)
@@ -159,25 +208,30 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
       auto load_v = [&](int j) {
-        const long long t0 = clock64();
+        const long long t0 = tick<PROF>();
         if (!(ok = mbar_wait(&sh->kv_empty[slot], phase ^ 1, abort, p.status, 202))) return;
-        waited += clock64() - t0;
+        waited += tick<PROF>() - t0;
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&sh->kv_full[slot], 4 * kChunkBytes);
         for (int c = 0; c < 4; ++c)
           tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot], j * kBKV + c * 32, 0, b);
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
-      // Consumption order: K(0), then per tile K(j+1) before V(j).
-      load_k(kv_lo);
-      for (int jj = 0; ok && jj < n_kv; ++jj) {
-        if (jj + 1 < n_kv) load_k(kv_lo + jj + 1);
-        if (ok) load_v(kv_lo + jj);
+      // Per piece, consumption order is K(0), then per tile K(j+1) before V(j).
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      while (ok && next_piece(p, cursor, pc)) {
+        b = pc.unit / p.q_tiles;
+        load_k(pc.kv_lo);
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj) {
+          if (jj + 1 < pc.n_kv) load_k(pc.kv_lo + jj + 1);
+          if (ok) load_v(pc.kv_lo + jj);
+        }
       }
-      if (p.prof) p.prof[blockIdx.x * 8 + 0] = waited;
+      if (PROF && p.prof) p.prof[blockIdx.x * 16 + 0] = waited;
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(Kind::TF32, kBQ, kBKV);
       const uint32_t n_pv = static_cast<uint32_t>((p.dv + 15) / 16 * 16);
       const uint32_t idesc_pv = make_idesc(Kind::TF32, kBQ, n_pv);
@@ -185,21 +239,21 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       int slot = 0;
       uint32_t phase = 0;
       const uint32_t ring_addr = smem_u32(ring);
-      long long wait_k = 0, wait_v = 0, wait_p = 0, issue_qk_cycles = 0, issue_pv_cycles = 0;
-      const long long t_start = clock64();
-      bool ok = mbar_wait(&sh->q_ready, 0, abort, p.status, 203);
-      tc_fence_after_sync();
+      long long wait_k = 0, wait_v = 0, wait_p = 0, wait_q = 0, issue_qk_cycles = 0, issue_pv_cycles = 0;
+      const long long t_start = tick<PROF>();
+      bool ok = true;
+      long long it = 0;                       // key tiles issued so far by this CTA
 
       // S[buf] = Q K^T from the K tile in the current slot (A = Q in tensor memory).
       auto issue_qk = [&](int buf) {
-        const long long t0 = clock64();
+        const long long t0 = tick<PROF>();
         if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 204))) return;
-        wait_k += clock64() - t0;
+        wait_k += tick<PROF>() - t0;
         tc_fence_after_sync();
         // One descriptor per slot; a K step moves it by a compile-time constant
         // (32 bytes inside the swizzled row, 16 KB to the next 32-feature chunk),
         // so the issuing thread spends one 64-bit add per MMA.
-        const long long ti = clock64();
+        const long long ti = tick<PROF>();
         const uint64_t k_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
         const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
         const uint32_t q_tmem = tmem_base + kTmemQ;
@@ -212,24 +266,24 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         mma_commit(&sh->s_full[buf]);
         mma_commit(&sh->kv_empty[slot]);
-        issue_qk_cycles += clock64() - ti;
+        issue_qk_cycles += tick<PROF>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
       // O += P[buf] V from the V^T tile in the current slot (A = P in tensor memory).
-      auto issue_pv = [&](int jj) {
-        const int buf = jj & 1;
-        long long t0 = clock64();
+      auto issue_pv = [&](long long t, bool first_of_piece) {
+        const int buf = static_cast<int>(t & 1);
+        long long t0 = tick<PROF>();
         if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) return;
-        wait_v += clock64() - t0;
-        t0 = clock64();
-        if (!(ok = mbar_wait(&sh->p_full[buf], (jj >> 1) & 1, abort, p.status, 206))) return;
-        wait_p += clock64() - t0;
+        wait_v += tick<PROF>() - t0;
+        t0 = tick<PROF>();
+        if (!(ok = mbar_wait(&sh->p_full[buf], (t >> 1) & 1, abort, p.status, 206))) return;
+        wait_p += tick<PROF>() - t0;
         tc_fence_after_sync();
-        const long long ti = clock64();
+        const long long ti = tick<PROF>();
         const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
         const uint32_t d_tmem = tmem_base + kTmemO;
         const uint32_t p_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
-        if (jj == 0) {
+        if (first_of_piece) {
           mma_ts<Kind::TF32>(d_tmem, p_tmem, v_desc, idesc_pv, 0u);
         } else {
           mma_ts<Kind::TF32>(d_tmem, p_tmem, v_desc, idesc_pv, 1u);
@@ -240,32 +294,57 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                              v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
         mma_commit(&sh->pv_done[buf]);
         mma_commit(&sh->kv_empty[slot]);
-        issue_pv_cycles += clock64() - ti;
+        issue_pv_cycles += tick<PROF>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
 
-      if (ok) issue_qk(0);
-      for (int jj = 0; ok && jj < n_kv; ++jj) {
-        if (jj + 1 < n_kv) issue_qk((jj + 1) & 1);
-        if (ok) issue_pv(jj);
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
+        const int n_kv = pc.n_kv;
+        // Q of this piece is in tensor memory (and the previous piece's O has been read).
+        const long long tq = tick<PROF>();
+        if (!(ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 203))) break;
+        wait_q += tick<PROF>() - tq;
+        tc_fence_after_sync();
+        issue_qk(static_cast<int>(it & 1));
+        for (int jj = 0; ok && jj < n_kv; ++jj) {
+          if (jj + 1 < n_kv) issue_qk(static_cast<int>((it + jj + 1) & 1));
+          if (ok) issue_pv(it + jj, jj == 0);
+        }
+        it += n_kv;
       }
-      if (p.prof) {
-        p.prof[blockIdx.x * 8 + 1] = wait_k;
-        p.prof[blockIdx.x * 8 + 2] = wait_v;
-        p.prof[blockIdx.x * 8 + 5] = issue_qk_cycles;
-        p.prof[blockIdx.x * 8 + 6] = issue_pv_cycles;
-        p.prof[blockIdx.x * 8 + 3] = wait_p;
-        p.prof[blockIdx.x * 8 + 4] = clock64() - t_start;
+      if (PROF && p.prof) {
+        p.prof[blockIdx.x * 16 + 1] = wait_k;
+        p.prof[blockIdx.x * 16 + 2] = wait_v;
+        p.prof[blockIdx.x * 16 + 5] = issue_qk_cycles;
+        p.prof[blockIdx.x * 16 + 6] = issue_pv_cycles;
+        p.prof[blockIdx.x * 16 + 3] = wait_p;
+        p.prof[blockIdx.x * 16 + 4] = tick<PROF>() - t_start;
+        p.prof[blockIdx.x * 16 + 8] = wait_q;
       }
     }
-  } else if (warp >= 4 && n_kv > 0) {
+  } else if (warp >= 4) {
     const int h = (warp - 4) >> 2;            // column half of this warpgroup
     const int quad = warp & 3;                // TMEM lane quadrant
     const int r = quad * 32 + lane;           // row within the tile
-    const long long row = static_cast<long long>(qt) * kBQ + r;
     const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
     const int dv_chunks = (p.dv + 31) / 32;
+    long long it = 0;                         // key tiles consumed so far by this CTA
+    long long wait_s = 0;
+    const long long t_start = tick<PROF>();
+    bool dead = false;                        // a wait gave up; keep hitting the barriers only
+
+    PieceCursor cursor = pieces_begin(p);
+    Piece pc;
+    while (next_piece(p, cursor, pc)) {
+    const int kv_lo = pc.kv_lo, n_kv = pc.n_kv;
+    const int b = pc.unit / p.q_tiles;
+    const int qt = pc.unit - b * p.q_tiles;
+    const long long row = static_cast<long long>(qt) * kBQ + r;
+    const bool whole = pc.whole;
+    const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
 
     // ---- Q: global -> TF32 (nearest) -> tensor memory, columns [64h, 64h+64) ----
     {
@@ -302,19 +381,17 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
 
     float m_used = -CUDART_INF_F;             // running maximum, log2 domain
     float l = 0.0f;                           // this half's share of the row sum
-    bool dead = false;                        // a wait gave up; keep hitting the barriers only
-    long long wait_s = 0;
-    const long long t_start = clock64();
 
     for (int jj = 0; jj < n_kv; ++jj) {
-      const int buf = jj & 1;
+      const long long t = it + jj;            // position in this CTA's sequence of key tiles
+      const int buf = static_cast<int>(t & 1);
       const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>(buf * kBKV) +
                               static_cast<uint32_t>(h * 64);
       uint32_t s0[32], s1[32];
       if (!dead) {
-        const long long t0 = clock64();
-        dead = !mbar_wait_warp(&sh->s_full[buf], (jj >> 1) & 1, abort, p.status, 207);
-        wait_s += clock64() - t0;
+        const long long t0 = tick<PROF>();
+        dead = !mbar_wait_warp(&sh->s_full[buf], (t >> 1) & 1, abort, p.status, 207);
+        wait_s += tick<PROF>() - t0;
       }
       float mx = -CUDART_INF_F;
       if (!dead) {
@@ -358,7 +435,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
           // is signalled on the barrier of that tile's parity, so a waiter that
           // skipped earlier phases is never more than one phase behind (a parity
           // wait cannot tell phases two apart).
-          dead = !mbar_wait_warp(&sh->pv_done[(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort, p.status,
+          dead = !mbar_wait_warp(&sh->pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, abort, p.status,
                                  208);
           if (!dead) {
             tc_fence_after_sync();
@@ -394,14 +471,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       if (lane == 0) mbar_arrive(&sh->p_full[buf]);
     }
 
-    if (p.prof && quad == 0 && lane == 0) {
-      if (h == 0) p.prof[blockIdx.x * 8 + 7] = clock64() - t_start - wait_s;
-    }
-
     // ---- epilogue: total row sum, normalise, store columns [64h, 64h+64) of O ----
     if (!sh->give_up && !dead) {
-      dead = !mbar_wait_warp(&sh->pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort, p.status,
-                             209);
+      const long long last = it + n_kv - 1;
+      dead = !mbar_wait_warp(&sh->pv_done[last & 1], (last >> 1) & 1, abort, p.status, 209);
     }
     sh->half_sum[h][r] = l;
     if (dead) sh->give_up = 1;
@@ -411,12 +484,12 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       const float l_total = l + sh->half_sum[h ^ 1][r];
       const float inv = 1.0f / l_total;
       float* dst;
-      if (p.splits == 1) {
+      if (whole) {
         dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
       } else {
-        const size_t prow = (static_cast<size_t>(split) * p.batch + b) * p.nq + row;
+        const size_t prow = static_cast<size_t>(part_slot) * kBQ + r;
         dst = p.part_o + prow * p.dv;
-        if (row < p.nq && h == 0) {
+        if (h == 0) {
           p.part_m[prow] = m_used;
           p.part_l[prow] = l_total;
         }
@@ -426,7 +499,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         uint32_t o[32];
         tmem_ld_32x32(o_tmem + c * 32, o);
         tmem_wait_ld();
-        if (row < p.nq) {
+        if (row < p.nq || !whole) {
           if (vec_ok && c * 32 + 32 <= p.dv) {
 #pragma unroll
             for (int v = 0; v < 8; ++v)
@@ -441,6 +514,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         }
       }
     }
+    if (sh->give_up) break;
+    // The epilogue's reads of O must land before the next piece's P V overwrites it;
+    // they are ordered before this thread's next arrival on q_ready.
+    tc_fence_before_sync();
+    it += n_kv;
+    }  // pieces
+    if (PROF && p.prof && quad == 0 && lane == 0 && h == 0)
+      p.prof[blockIdx.x * 16 + 7] = tick<PROF>() - t_start - wait_s;
   }
 
   tc_fence_before_sync();
@@ -452,71 +533,111 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
   }
 }
 
-// Merges KV-split partials: O = sum_s w_s O_s / sum_s w_s, w_s = l_s 2^(m_s - max m).
-// One thread per four output columns; dv4 = ceil(dv / 4).
+// Merges the pieces of every row tile that more than one CTA range touched:
+// O = sum_s w_s O_s / sum_s w_s with w_s = l_s 2^(m_s - max m).  One CTA per row
+// tile; which pieces exist follows from the same range arithmetic the main
+// kernel uses.
+struct CombineArgs {
+  const float* part_o;
+  const float* part_m;
+  const float* part_l;
+  float* o;
+  int nq, dv, q_tiles, kv_tiles, ctas;
+  int first_tail_unit;     // row tiles before it were taken whole
+  long long iters_base;    // the tail's flat (row tile, key tile) sequence, cut as in the main kernel
+  int iters_rem;
+};
+
+__device__ __forceinline__ long long range_start(const CombineArgs& a, int g) {
+  return g * a.iters_base + min(g, a.iters_rem);
+}
+
+__device__ __forceinline__ int cta_of(const CombineArgs& a, long long it) {
+  const long long fat = static_cast<long long>(a.iters_rem) * (a.iters_base + 1);
+  if (it < fat) return static_cast<int>(it / (a.iters_base + 1));
+  return a.iters_rem + static_cast<int>((it - fat) / max(a.iters_base, 1ll));
+}
+
 __global__ void __launch_bounds__(256)
-attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_m,
-                         const float* __restrict__ part_l, float* __restrict__ o, size_t rows,
-                         int dv, int splits, bool vec) {
-  const int dv4 = (dv + 3) / 4;
-  const size_t total = rows * dv4;
-  const size_t stride = static_cast<size_t>(gridDim.x) * 256;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
-    const size_t r = i / dv4;
-    const int c = static_cast<int>(i - r * dv4) * 4;
+attention_combine_kernel(const CombineArgs a) {
+  constexpr int kRowsPerCta = 16;
+  const int tail_unit = blockIdx.x / (kBQ / kRowsPerCta);
+  const int row0 = (blockIdx.x % (kBQ / kRowsPerCta)) * kRowsPerCta;
+  const int unit = a.first_tail_unit + tail_unit;
+  const long long lo = static_cast<long long>(tail_unit) * a.kv_tiles, hi = lo + a.kv_tiles;
+  const int g_first = cta_of(a, lo), g_last = cta_of(a, hi - 1);
+  if (g_first == g_last) return;            // one CTA covered the whole tile and stored O itself
+  const int b = unit / a.q_tiles, qt = unit - b * a.q_tiles;
+  const int dv4 = (a.dv + 3) / 4;
+  const bool vec = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.o) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(a.part_o) & 15u) == 0;
+  for (int i = threadIdx.x; i < kRowsPerCta * dv4; i += 256) {
+    const int r = row0 + i / dv4, c = (i % dv4) * 4;
+    const long long row = static_cast<long long>(qt) * kBQ + r;
+    if (row >= a.nq) continue;
     float m = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_m[s * rows + r]);
+    for (int g = g_first; g <= g_last; ++g) {
+      const int slot = 2 * g + (range_start(a, g) >= lo ? 0 : 1);
+      m = fmaxf(m, a.part_m[static_cast<size_t>(slot) * kBQ + r]);
+    }
     float wsum = 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int s = 0; s < splits; ++s) {
-      const float w = part_l[s * rows + r] * exp2f(part_m[s * rows + r] - m);
+    for (int g = g_first; g <= g_last; ++g) {
+      const int slot = 2 * g + (range_start(a, g) >= lo ? 0 : 1);
+      const size_t prow = static_cast<size_t>(slot) * kBQ + r;
+      const float w = a.part_l[prow] * exp2f(a.part_m[prow] - m);
       wsum += w;
-      const float* src = part_o + (s * rows + r) * dv + c;
+      const float* src = a.part_o + prow * a.dv + c;
       if (vec) {
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(src));
+        const float4 v = *reinterpret_cast<const float4*>(src);
         acc[0] += w * v.x; acc[1] += w * v.y; acc[2] += w * v.z; acc[3] += w * v.w;
       } else {
-        for (int e = 0; e < 4 && c + e < dv; ++e) acc[e] += w * src[e];
+        for (int e = 0; e < 4 && c + e < a.dv; ++e) acc[e] += w * src[e];
       }
     }
     const float inv = 1.0f / wsum;
-    float* dst = o + r * dv + c;
+    float* dst = a.o + (static_cast<size_t>(b) * a.nq + row) * a.dv + c;
     if (vec) {
       *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
     } else {
-      for (int e = 0; e < 4 && c + e < dv; ++e) dst[e] = acc[e] * inv;
+      for (int e = 0; e < 4 && c + e < a.dv; ++e) dst[e] = acc[e] * inv;
     }
   }
 }
 
-// Debugging aid: when set (device pointer to 8 counters per CTA), the kernel
+// Debugging aid: when set (device pointer to 16 counters per CTA), the kernel
 // records how many cycles each role spent waiting on its barriers.
 unsigned long long* g_attention_profile = nullptr;
 
-int choose_splits(size_t units, int kv_tiles, int sms) {
-  if (units >= static_cast<size_t>(sms) || kv_tiles < 8) return 1;
-  int s = static_cast<int>(sms / units);
-  if (s < 1) s = 1;
-  if (s > kv_tiles / 4) s = kv_tiles / 4;
-  if (s > 16) s = 16;
-  return s < 1 ? 1 : s;
+// Number of CTAs for a call: one per SM, fewer when there is too little work to
+// give each at least two key tiles.
+int choose_ctas(long long units, long long kv_tiles, int sms) {
+  if (units >= sms) return sms;
+  long long g = units * kv_tiles / 2;
+  if (g < 1) g = 1;
+  if (g > sms) g = sms;
+  return static_cast<int>(g);
+}
+
+int device_sms() {
+  int sms = kNumSMs;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
 }
 
 }  // namespace
 
 void set_attention_profile(unsigned long long* p) { g_attention_profile = p; }
 
-size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv, int* splits_out) {
-  int sms = kNumSMs;
-  int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess)
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const size_t q_tiles = (nq + kBQ - 1) / kBQ;
-  const int kv_tiles = static_cast<int>((nk + kBKV - 1) / kBKV);
-  const int splits = choose_splits(q_tiles * batch, kv_tiles, sms);
-  if (splits_out) *splits_out = splits;
-  if (splits == 1) return 0;
-  return static_cast<size_t>(splits) * batch * nq * (dv + 2);
+size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv, int* ctas_out) {
+  const long long units = static_cast<long long>((nq + kBQ - 1) / kBQ) * static_cast<long long>(batch);
+  const long long kv_tiles = static_cast<long long>((nk + kBKV - 1) / kBKV);
+  const int ctas = choose_ctas(units, kv_tiles, device_sms());
+  if (ctas_out) *ctas_out = ctas;
+  // Two pieces per CTA (the ends of its range), 128 rows each, O plus (m, l).
+  return static_cast<size_t>(2) * ctas * kBQ * (dv + 2);
 }
 
 int attention_tcgen05(const float* q, const float* k, const float* vt, float* o, size_t batch,
@@ -531,8 +652,11 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   const int smem_bytes = 1024 + kRing * kSlotBytes + static_cast<int>(sizeof(Shared)) + 64;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_tf32_kernel,
+    cudaError_t err = cudaFuncSetAttribute(attention_tf32_kernel<false>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(attention_tf32_kernel<true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess)
       return fail(std::string("ib_attention: cannot reserve shared memory: ") +
                   cudaGetErrorString(err));
@@ -547,20 +671,21 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   p.batch = static_cast<int>(batch);
   p.q_tiles = static_cast<int>((nq + kBQ - 1) / kBQ);
   p.kv_tiles = static_cast<int>((nk + kBKV - 1) / kBKV);
-  int splits = 1;
-  attention_tcgen05_partial_floats(batch, nq, nk, dv, &splits);
-  if (splits > 1 && !partials) return fail("ib_attention: workspace for KV splits is missing");
-  p.splits = splits;
-  p.kv_per_split = (p.kv_tiles + splits - 1) / splits;
-  // Every split must own at least one KV tile.
-  while (p.splits > 1 && (p.splits - 1) * p.kv_per_split >= p.kv_tiles) --p.splits;
+  int ctas = 1;
+  attention_tcgen05_partial_floats(batch, nq, nk, dv, &ctas);
+  if (!partials) return fail("ib_attention: workspace for partial results is missing");
+  const long long units = static_cast<long long>(p.q_tiles) * p.batch;
+  p.ctas = ctas;
+  p.full_waves = static_cast<int>(units / ctas);
+  const long long tail_units = units - static_cast<long long>(p.full_waves) * ctas;
+  const long long tail_iters = tail_units * p.kv_tiles;
+  p.iters_base = tail_iters / ctas;
+  p.iters_rem = static_cast<int>(tail_iters % ctas);
   p.o = o;
-  if (p.splits > 1) {
-    const size_t rows = static_cast<size_t>(p.splits) * batch * nq;
-    p.part_o = partials;
-    p.part_m = partials + rows * dv;
-    p.part_l = p.part_m + rows;
-  }
+  const size_t slots_rows = static_cast<size_t>(2) * ctas * kBQ;
+  p.part_o = partials;
+  p.part_m = partials + slots_rows * dv;
+  p.part_l = p.part_m + slots_rows;
   p.status = device_status_word(s);
   if (!p.status) return fail("ib_attention: cannot allocate the device status word");
   p.prof = g_attention_profile;
@@ -570,18 +695,16 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   if (int rc = make_tensor_map_f32(&map_vt, vt, batch, dv, nk, nk_pitch, dv * nk_pitch, 128))
     return rc;
 
-  const size_t grid = static_cast<size_t>(p.q_tiles) * p.splits * batch;
-  if (grid >= (1u << 31)) return fail("ib_attention: too many work units");
-  attention_tf32_kernel<<<static_cast<unsigned>(grid), kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+  if (p.prof)
+    attention_tf32_kernel<true><<<static_cast<unsigned>(ctas), kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+  else
+    attention_tf32_kernel<false><<<static_cast<unsigned>(ctas), kThreads, smem_bytes, s>>>(map_k, map_vt, p);
   if (int rc = check_launch("ib_attention (tcgen05 tf32)")) return rc;
-  if (p.splits > 1) {
-    const size_t rows = batch * nq;
-    size_t blocks = (rows * ((dv + 3) / 4) + 255) / 256;
-    if (blocks > static_cast<size_t>(kNumSMs) * 16) blocks = static_cast<size_t>(kNumSMs) * 16;
-    const bool vec = dv % 4 == 0 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0 &&
-                     (reinterpret_cast<uintptr_t>(p.part_o) & 15u) == 0;
-    attention_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        p.part_o, p.part_m, p.part_l, o, rows, p.dv, p.splits, vec);
+  // Tail row tiles shared by several CTA ranges exist unless the ranges fall on tile boundaries.
+  if (tail_units > 0 && !(p.iters_rem == 0 && p.iters_base % p.kv_tiles == 0)) {
+    CombineArgs a{p.part_o, p.part_m, p.part_l, o, p.nq, p.dv, p.q_tiles, p.kv_tiles, ctas,
+                  p.full_waves * ctas, p.iters_base, p.iters_rem};
+    attention_combine_kernel<<<static_cast<unsigned>(tail_units * 8), 256, 0, s>>>(a);
     return check_launch("ib_attention (combine)");
   }
   return 0;

@@ -166,22 +166,49 @@ prepare_attention_kernel(PrepareArgs a) {
   }
   const size_t tiles_k = (a.nk + 63) / 64, tiles_d = (a.dv + 63) / 64;
   const size_t total = a.batch * tiles_k * tiles_d;
+  const bool vec_in = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
+  const bool vec_out = a.pitch % 4 == 0 && (reinterpret_cast<uintptr_t>(a.vt) & 15u) == 0;
   for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
     const size_t b = t / (tiles_k * tiles_d);
     const size_t rem = t - b * tiles_k * tiles_d;
     const size_t k0 = (rem / tiles_d) * 64, d0 = (rem % tiles_d) * 64;
     const float* src = a.v + b * a.nk * a.dv;
     float* dst = a.vt + b * a.dv * a.pitch;
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-      const int r = e >> 6, c = e & 63;                 // r: key, c: feature (contiguous in V)
-      float x = 0.0f;
-      if (k0 + r < a.nk && d0 + c < a.dv) x = src[(k0 + r) * a.dv + d0 + c];
-      tile[r][c] = round_tf32(x);
+    // 64 keys x 64 features in: 16 float4 per key row, 4 rows per thread.
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int r = e >> 4, c = (e & 15) * 4;           // r: key, c: feature (contiguous in V)
+      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (k0 + r < a.nk) {
+        const float* row = src + (k0 + r) * a.dv + d0 + c;
+        if (vec_in && d0 + c + 4 <= a.dv) {
+          x = __ldcs(reinterpret_cast<const float4*>(row));
+        } else {
+          if (d0 + c + 0 < a.dv) x.x = row[0];
+          if (d0 + c + 1 < a.dv) x.y = row[1];
+          if (d0 + c + 2 < a.dv) x.z = row[2];
+          if (d0 + c + 3 < a.dv) x.w = row[3];
+        }
+      }
+      tile[r][c + 0] = round_tf32(x.x);
+      tile[r][c + 1] = round_tf32(x.y);
+      tile[r][c + 2] = round_tf32(x.z);
+      tile[r][c + 3] = round_tf32(x.w);
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-      const int c = e >> 6, r = e & 63;                 // r: key (contiguous in V^T)
-      if (k0 + r < a.nk && d0 + c < a.dv) dst[(d0 + c) * a.pitch + k0 + r] = tile[r][c];
+    // 64 features x 64 keys out: 16 float4 per feature row.
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int c = e >> 4, r = (e & 15) * 4;           // c: feature, r: key (contiguous in V^T)
+      if (d0 + c >= a.dv) continue;
+      float* row = dst + (d0 + c) * a.pitch + k0 + r;
+      const float4 x = make_float4(tile[r][c], tile[r + 1][c], tile[r + 2][c], tile[r + 3][c]);
+      if (vec_out && k0 + r + 4 <= a.nk) {
+        *reinterpret_cast<float4*>(row) = x;
+      } else {
+        if (k0 + r + 0 < a.nk) row[0] = x.x;
+        if (k0 + r + 1 < a.nk) row[1] = x.y;
+        if (k0 + r + 2 < a.nk) row[2] = x.z;
+        if (k0 + r + 3 < a.nk) row[3] = x.w;
+      }
     }
     __syncthreads();
   }

@@ -151,13 +151,8 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
           return rc;
       }
     }
-    float* partials = nullptr;
-    const size_t part_floats = attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr);
-    if (part_floats) {
-      partials = ws.take(part_floats);
-      if (!partials)
-        return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
-    }
+    float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
+    if (!partials) return fail(small);
     return attention_tcgen05(q, kr, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
   }
 

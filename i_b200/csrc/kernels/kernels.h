@@ -49,9 +49,9 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
 
 // attention_tcgen05.cu — fused online-softmax attention; q is the caller's fp32
 // Q, k a TF32-rounded copy of K, vt the rounded V transposed to [b][dv][nk_pitch].
-// Floats of scratch the KV-split partials need (0 when one CTA covers all keys).
+// Floats of scratch for the partial results of row tiles shared between CTAs.
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv,
-                                        int* splits_out);
+                                        int* ctas_out);
 int attention_tcgen05(const float* q, const float* k, const float* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t nk_pitch, float* partials,
                       cudaStream_t s);
