@@ -52,15 +52,17 @@ __device__ __forceinline__ float exp_e32(float x) {
 __device__ __forceinline__ float exp_e32_fast(float x) {
   const float l_hi = 1.4426950216293335f;
   const float l_lo = -2.4551930266625277e-08f;
+  const float magic = 12582912.0f;             // 1.5 * 2^23: adding it rounds to the nearest integer
   float hi = x * l_hi;
   float lo = fmaf(x, l_lo, fmaf(x, l_hi, -hi));
-  float n = rintf(hi);
+  if (!(fabsf(hi) < 125.0f)) return exp_e32(x);   // subnormal or overflowing results, inf, NaN
+  float shifted = hi + magic;                  // integer part now sits in the low mantissa bits
+  float n = shifted - magic;
   float f = (hi - n) + lo;
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(f));
-  int e = static_cast<int>(n);
-  if (e < -125 || e > 126) return exp_e32(x);
-  return __int_as_float(__float_as_int(r) + (e << 23));
+  // 2^n: add n to the exponent field (the low bits of `shifted` are n in two's complement).
+  return __int_as_float(__float_as_int(r) + (__float_as_int(shifted) << 23));
 }
 
 __device__ __forceinline__ float apply_binary(int op, float a, float b) {
