@@ -303,12 +303,41 @@ def run_gpu_arm(args):
         q, k, v = make_inputs(seed=3 + 1000 * rank + s, heads=heads)
         sets.append(tuple(shaped(torch.from_numpy(t)).cuda() for t in (q, k, v)))
     out_shape = (heads, SEQ, DIM) if batched else (SEQ, DIM)
-    gathered = [torch.empty((world,) + out_shape, device="cuda") for _ in range(2)]
-    outs = [g[rank] for g in gathered]
     main = torch.cuda.current_stream()
-    side = torch.cuda.Stream() if world > 1 else None
-    gather_done = [None, None]
     computed = torch.cuda.Event()
+
+    # Output assembly at N > 1.  Preferred: copy engines over NVLink into peer-mapped
+    # buffers (no SM is taken from the persistent attention kernel).  Fallback: NCCL
+    # all-gather on a side stream with a few SMs reserved for its kernels.
+    gather_mode = "none"
+    peer = None
+    if world > 1:
+        from i_b200.sharding import PeerGather
+        want_ce = args.gather in ("auto", "ce") and PeerGather.available()
+        ok = torch.tensor([1 if want_ce else 0], device="cuda")
+        if want_ce:
+            try:
+                peer = PeerGather(out_shape, slots=2)
+            except Exception as exc:                      # noqa: BLE001
+                if rank == 0:
+                    sys.stderr.write("peer-mapped gather unavailable (%s); using NCCL\n" % exc)
+                ok[0] = 0
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            gather_mode = "copy-engine peer writes"
+        else:
+            peer = None
+            gather_mode = "nccl all_gather_into_tensor, %d SMs reserved" % args.reserve_sms
+            ilang.set_reserved_sms(args.reserve_sms)
+    if peer is not None:
+        outs = [peer.local(0), peer.local(1)]
+        gathered = None
+        side = None
+    else:
+        gathered = [torch.empty((world,) + out_shape, device="cuda") for _ in range(2)]
+        outs = [g[rank] for g in gathered]
+        side = torch.cuda.Stream() if world > 1 else None
+    gather_done = [None, None]
 
     def step(s):
         q, k, v = sets[s % rotation]
@@ -316,7 +345,10 @@ def run_gpu_arm(args):
         if gather_done[buf] is not None:
             main.wait_event(gather_done[buf])  # the gather of step s-2 still reads this buffer
         attn.into(outs[buf], q, k, v)
-        if side is not None:
+        if peer is not None:
+            computed.record(main)
+            gather_done[buf] = peer.publish(buf, computed)
+        elif side is not None:
             computed.record(main)
             side.wait_event(computed)
             with torch.cuda.stream(side):
@@ -338,13 +370,31 @@ def run_gpu_arm(args):
     t_begin.record(main)
     for s in range(args.steps):
         step(s)
-    if side is not None:
+    if peer is not None:
+        main.wait_stream(peer.stream)
+    elif side is not None:
         main.wait_stream(side)
     t_end.record(main)
     torch.cuda.synchronize()
     launches = ilang.launch_count() - launches0
     elapsed_ms = t_begin.elapsed_time(t_end)
+    gather_ok = None
+    if peer is not None:
+        peer.finish()
     if world > 1:
+        # Every rank must now hold every rank's output of the last step: compare a
+        # checksum of each gathered row with the checksum its owner computed.
+        last = (args.steps - 1) % 2
+        full = peer.gathered(last) if peer is not None else gathered[last]
+        torch.cuda.synchronize()
+        # Integer sums of the raw bits: exact whatever the reduction order.
+        mine = outs[last].contiguous().view(torch.int32).to(torch.int64).sum().reshape(1)
+        owners = torch.empty(world, dtype=torch.int64, device="cuda")
+        dist.all_gather_into_tensor(owners, mine)
+        seen = full.contiguous().view(torch.int32).to(torch.int64).reshape(world, -1).sum(dim=1)
+        good = torch.tensor([1 if torch.equal(seen, owners) else 0], device="cuda")
+        dist.all_reduce(good, op=dist.ReduceOp.MIN)
+        gather_ok = bool(good.item())
         dist.barrier()
         t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -411,7 +461,8 @@ def run_gpu_arm(args):
                    "units_per_rank_per_step": heads,
                    "l2": "inputs rotate over %d distinct sets (%d MiB) > 126 MB L2"
                          % (rotation, rotation * set_bytes // 2 ** 20),
-                   "multi_gpu": "one head per rank per step, NCCL all-gather of O on a side stream",
+                   "multi_gpu": "one head per rank per step; output assembly: " + gather_mode,
+                   "gathered_output_verified": gather_ok,
                    "precision": "tcgen05 kind::tf32, fp32 accumulate",
                    "parity_max_rel_to_peak_vs_oracle": parity},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
@@ -450,6 +501,10 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed loop only (no end-to-end, CPU or side measurements); "
                          "for profiler captures")
+    ap.add_argument("--gather", default="auto", choices=["auto", "ce", "nccl"],
+                    help="output assembly at N > 1: copy-engine peer writes or NCCL all-gather")
+    ap.add_argument("--reserve-sms", type=int, default=20,
+                    help="SMs left free for NCCL kernels when the NCCL gather is used")
     ap.add_argument("--heads", type=int, default=1,
                     help="heads per rank per step (default 1 = BASELINE config 4)")
     ap.add_argument("--seq", type=int, default=16384, help="sequence length (default 16384)")

@@ -41,6 +41,8 @@
 // piece that does not cover its row tile completely is written as a normalised
 // partial O with its (m, l); a small second kernel merges the pieces.
 // Roofline: tensor-bound, 4*Nq*Nk*d FLOP per head.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "sm100.cuh"
@@ -619,17 +621,23 @@ int choose_ctas(long long units, long long kv_tiles, int sms) {
   return static_cast<int>(g);
 }
 
+// SMs the persistent kernel leaves free (for a communication kernel running next to it).
+std::atomic<int> g_reserved_sms{0};
+
 int device_sms() {
   int sms = kNumSMs;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess)
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return sms;
+  const int reserved = g_reserved_sms.load();
+  return sms - reserved > 8 ? sms - reserved : 8;
 }
 
 }  // namespace
 
 void set_attention_profile(unsigned long long* p) { g_attention_profile = p; }
+void set_reserved_sms(int n) { g_reserved_sms.store(n < 0 ? 0 : n); }
+int reserved_sms() { return g_reserved_sms.load(); }
 
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv, int* ctas_out) {
   const long long units = static_cast<long long>((nq + kBQ - 1) / kBQ) * static_cast<long long>(batch);

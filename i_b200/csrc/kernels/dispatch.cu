@@ -165,3 +165,11 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
   return ib_contract(scores, v, o, batch, nq, dv, nk, 1, v_kmajor, sub, rest,
                      workspace_bytes - ws.used, stream);
 }
+
+extern "C" int i_b200_set_reserved_sms(int n) {
+  if (n < 0) return ib::fail("i_b200_set_reserved_sms: negative count");
+  ib::set_reserved_sms(n);
+  return 0;
+}
+
+extern "C" int i_b200_reserved_sms(void) { return ib::reserved_sms(); }

@@ -57,5 +57,7 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
                       cudaStream_t s);
 
 void set_attention_profile(unsigned long long* device_counters);
+void set_reserved_sms(int n);
+int reserved_sms();
 
 }  // namespace ib

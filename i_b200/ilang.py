@@ -93,6 +93,8 @@ def load_core(path=None):
     lib.i_b200_program_precision.restype = ctypes.c_int
     lib.i_b200_device_count.argtypes = []
     lib.i_b200_device_count.restype = ctypes.c_int
+    lib.i_b200_set_reserved_sms.argtypes = [ctypes.c_int]
+    lib.i_b200_set_reserved_sms.restype = ctypes.c_int
     lib.i_b200_launch_count.argtypes = []
     lib.i_b200_launch_count.restype = sz
     return lib
@@ -109,6 +111,11 @@ def core():
 def launch_count():
     """Kernels launched by the library in this process so far."""
     return int(_core.i_b200_launch_count())
+
+
+def set_reserved_sms(n):
+    """Leave n SMs free next to the persistent attention kernel (for collectives)."""
+    _check(_core.i_b200_set_reserved_sms(int(n)))
 
 
 def _raise_last():
@@ -261,6 +268,8 @@ class Component:
     def __del__(self):
         program = getattr(self, "_program", None)
         ptr = getattr(self, "_ptr", None)
+        if _core is None:          # interpreter shutdown: the library is already gone
+            return
         if program:
             _core.i_program_free(program)
             self._program = None

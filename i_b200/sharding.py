@@ -98,3 +98,71 @@ def sharded_attention(attend, q, k, v, group=None, out=None):
         out[s.head_lo:s.head_hi, s.row_lo:s.row_hi] = gathered[r * widest: r * widest + n].view(
             s.head_hi - s.head_lo, s.row_hi - s.row_lo, dv)
     return out
+
+
+class PeerGather:
+    """All-gather of per-rank output shards by copy engines over NVLink.
+
+    Every rank owns a symmetric buffer `[slots][world][*shape]`; rank r computes
+    into `local(slot)` (= its own row of its own buffer) and `publish(slot)`
+    queues one device-to-device copy per peer into row r of that peer's buffer.
+    The copies are DMA transfers: they use no SM, so they run entirely under the
+    next step's kernel, which a collective made of SM kernels cannot do while a
+    persistent kernel holds every SM.  `finish()` waits for this rank's copies
+    and then for everybody's (host barrier); after it every rank holds all rows.
+
+    Needs torch symmetric memory (peer-mapped allocations); `available()` tells.
+    """
+
+    @staticmethod
+    def available():
+        try:
+            import torch.distributed._symmetric_memory as symm  # noqa: F401
+            return True
+        except Exception:
+            return False
+
+    def __init__(self, shape, slots=2, group=None, device=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        full = (slots, self.world) + tuple(shape)
+        self.buffer = symm.empty(full, dtype=torch.float32, device=device)
+        self.handle = symm.rendezvous(self.buffer, self.group)
+        self.peers = [self.buffer if r == self.rank else
+                      self.handle.get_buffer(r, full, torch.float32) for r in range(self.world)]
+        self.stream = torch.cuda.Stream(device=device)
+        self._done = [None] * slots
+
+    def local(self, slot):
+        return self.buffer[slot, self.rank]
+
+    def gathered(self, slot):
+        return self.buffer[slot]
+
+    def publish(self, slot, after):
+        """Queue the copies of `local(slot)` to every peer once event `after` has fired."""
+        import torch
+        self.stream.wait_event(after)
+        with torch.cuda.stream(self.stream):
+            src = self.buffer[slot, self.rank]
+            for step in range(1, self.world):
+                peer = (self.rank + step) % self.world
+                self.peers[peer][slot, self.rank].copy_(src, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        self._done[slot] = done
+        return done
+
+    def reusable(self, slot):
+        """Event after which `local(slot)` may be overwritten (its last copies have read it)."""
+        return self._done[slot]
+
+    def finish(self):
+        import torch.distributed as dist
+        self.stream.synchronize()
+        dist.barrier(self.group)
