@@ -260,6 +260,12 @@ def secondary_metrics(torch, ilang, peaks):
                                        1, 1, 2, None, 0, stream), 10, flush)
     out["mm_t_8192x8192x4096_tf32"] = {"tflops": flop / ms / 1e9, "ms": ms,
                                        "frac_tf32_peak": flop / ms / 1e9 / (peaks["bf16_tflops"] / 2)}
+    ws = torch.empty(2 * 8192 * 4096 * 2 + 4096, dtype=torch.uint8, device="cuda")
+    ms = timed(lambda: lib.ib_contract(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, 8192, 8192, 4096,
+                                       1, 1, 3, ws.data_ptr(), ws.numel(), stream), 10, flush)
+    out["mm_t_8192x8192x4096_bf16_optin"] = {"tflops": flop / ms / 1e9, "ms": ms,
+                                             "frac_bf16_peak": flop / ms / 1e9 / peaks["bf16_tflops"],
+                                             "note": "includes the fp32->bf16 conversion of A and B"}
     torch.backends.cuda.matmul.allow_tf32 = True
     ms = timed(lambda: torch.matmul(a, b.t(), out=c), 10, flush)
     out["cublas_tf32_8192x8192x4096"] = {"tflops": flop / ms / 1e9, "ms": ms}

@@ -9,6 +9,8 @@
 //
 // ib::transpose_batched rewrites [b][r][c] as [b][c][r]; the tensor path uses
 // it to give tcgen05 K-major operands.
+#include <cuda_bf16.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -214,7 +216,32 @@ prepare_attention_kernel(PrepareArgs a) {
   }
 }
 
+__global__ void __launch_bounds__(256)
+convert_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t rows,
+                    size_t cols, size_t out_pitch) {
+  // One thread per pair of output columns.
+  const size_t pairs = out_pitch / 2;
+  const size_t total = rows * pairs;
+  const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / pairs, c = (i - r * pairs) * 2;
+    const float x = c < cols ? in[r * cols + c] : 0.0f;
+    const float y = c + 1 < cols ? in[r * cols + c + 1] : 0.0f;
+    reinterpret_cast<__nv_bfloat162*>(out + r * out_pitch)[c / 2] = __floats2bfloat162_rn(x, y);
+  }
+}
+
 }  // namespace
+
+int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,
+                      cudaStream_t s) {
+  if (rows == 0 || cols == 0) return 0;
+  size_t blocks = (rows * (out_pitch / 2) + 255) / 256;
+  if (blocks > static_cast<size_t>(kNumSMs) * 16) blocks = static_cast<size_t>(kNumSMs) * 16;
+  convert_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+      in, static_cast<__nv_bfloat16*>(out), rows, cols, out_pitch);
+  return check_launch("convert_bf16");
+}
 
 int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const float* k,
                                float* kr, size_t k_elems, const float* v, float* vt, size_t batch,

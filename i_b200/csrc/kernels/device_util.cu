@@ -51,6 +51,24 @@ int make_tensor_map_f32(CUtensorMap* map, const float* base, size_t batch, size_
   return 0;
 }
 
+int make_tensor_map_bf16(CUtensorMap* map, const void* base, size_t batch, size_t rows,
+                         size_t cols, size_t row_pitch, size_t batch_pitch, unsigned box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return fail("cuTensorMapEncodeTiled is not available from this CUDA driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_pitch * 2) % 16 || (batch_pitch * 2) % 16)
+    return fail("tensor map: base and pitches must be 16-byte aligned");
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {row_pitch * 2, batch_pitch * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};          // 64 bf16 = one 128-byte swizzled row
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                   strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return fail("cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(rc)));
+  return 0;
+}
+
 int* device_status_word(cudaStream_t) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;

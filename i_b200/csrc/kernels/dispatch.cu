@@ -46,7 +46,16 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
                                               int a_kmajor, int b_kmajor, int precision) {
   using namespace ib;
   const double flop = 2.0 * batch * m * n * k;
-  if (!wants_tensor(precision, flop) || !contract_shape_ok(k)) return 0;
+  if (!wants_tensor(precision, flop)) return 0;
+  if (precision == IB_PRECISION_BF16) {
+    // bf16 copies of both operands ([rows][k rounded up to 8]); fp32 transposes first when needed.
+    const size_t kp = round_up(k, 8);
+    size_t bytes = carve_bytes((batch * m * kp + 1) / 2) + carve_bytes((batch * n * kp + 1) / 2);
+    if (!a_kmajor) bytes += carve_bytes(batch * m * k);
+    if (!b_kmajor) bytes += carve_bytes(batch * n * k);
+    return bytes;
+  }
+  if (!contract_shape_ok(k)) return 0;
   size_t bytes = 0;
   if (!a_kmajor) bytes += carve_bytes(batch * m * k);
   if (!b_kmajor) bytes += carve_bytes(batch * n * k);
@@ -67,6 +76,33 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
     return err == cudaSuccess ? 0 : fail("ib_contract: memset failed");
   }
   const double flop = 2.0 * batch * m * n * k;
+  if (precision == IB_PRECISION_BF16) {
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u)
+      return fail("ib_contract: workspace must be 256-byte aligned");
+    Carver ws(workspace, workspace_bytes);
+    const char* small = "ib_contract: workspace too small (see ib_contract_workspace_bytes)";
+    const size_t kp = round_up(k, 8);
+    float* a16 = ws.take((batch * m * kp + 1) / 2);
+    float* b16 = ws.take((batch * n * kp + 1) / 2);
+    if (!a16 || !b16) return fail(small);
+    const float* ak = a;
+    const float* bk = b;
+    if (!a_kmajor) {
+      float* t = ws.take(batch * m * k);
+      if (!t) return fail(small);
+      if (int rc = transpose_batched(a, t, batch, k, m, k, false, s)) return rc;
+      ak = t;
+    }
+    if (!b_kmajor) {
+      float* t = ws.take(batch * n * k);
+      if (!t) return fail(small);
+      if (int rc = transpose_batched(b, t, batch, k, n, k, false, s)) return rc;
+      bk = t;
+    }
+    if (int rc = convert_bf16_rows(ak, a16, batch * m, k, kp, s)) return rc;
+    if (int rc = convert_bf16_rows(bk, b16, batch * n, k, kp, s)) return rc;
+    return gemm_tcgen05_bf16(a16, b16, c, batch, m, n, k, kp, s);
+  }
   if (wants_tensor(precision, flop) && contract_shape_ok(k)) {
     Carver ws(workspace, workspace_bytes);
     const float* ak = a;

@@ -58,7 +58,10 @@ __device__ __forceinline__ TileCoord tile_coord(long long id, int tiles_m, int t
   return t;
 }
 
-template <int BN>
+// KIND selects the operand type: TF32 reads fp32 operands (32 per 128-byte row,
+// K = 8 per MMA), BF16 reads bf16 operands (64 per row, K = 16 per MMA).  Either
+// way one MMA consumes 32 bytes of every operand row and a stage holds 128 bytes.
+template <int BN, Kind KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  float* __restrict__ c, int m, int n, int k, int batch, int* status) {
@@ -78,7 +81,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int tiles_m = (m + kBM - 1) / kBM;
   const int tiles_n = (n + BN - 1) / BN;
   const long long total_tiles = static_cast<long long>(tiles_m) * tiles_n * batch;
-  const int k_blocks = (k + kBK - 1) / kBK;
+  constexpr int kBKElems = KIND == Kind::TF32 ? kBK : 2 * kBK;   // elements per 128-byte row
+  const int k_blocks = (k + kBKElems - 1) / kBKElems;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512
 
   if (threadIdx.x == 0) {
@@ -116,8 +120,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
-          tma_load_3d(sa, &map_a, &full[stage], kb * kBK, t.m_tile * kBM, t.batch);
-          tma_load_3d(sb, &map_b, &full[stage], kb * kBK, t.n_tile * BN, t.batch);
+          tma_load_3d(sa, &map_a, &full[stage], kb * kBKElems, t.m_tile * kBM, t.batch);
+          tma_load_3d(sb, &map_b, &full[stage], kb * kBKElems, t.n_tile * BN, t.batch);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -127,7 +131,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(Kind::TF32, kBM, BN);
+      constexpr uint32_t idesc = make_idesc(KIND, kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -147,7 +151,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           for (int ks = 0; ks < kBK / 8; ++ks) {
             // 8 fp32 = 32 bytes along K inside the swizzled row: +2 in the
             // descriptor's 16-byte address units.
-            mma_ss<Kind::TF32>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
+            mma_ss<KIND>(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
                                (kb | ks) != 0 ? 1u : 0u);
           }
           mma_commit(&empty[stage]);
@@ -215,12 +219,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-template <int BN>
+template <int BN, Kind KIND>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
            size_t n, size_t k, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tf32_kernel<BN>,
+    cudaError_t err = cudaFuncSetAttribute(gemm_tf32_kernel<BN, KIND>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Smem<BN>::kTotal);
     if (err != cudaSuccess)
@@ -236,7 +240,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t 
   if (cudaGetDevice(&dev) == cudaSuccess)
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = static_cast<int>(tiles < static_cast<size_t>(sms) ? tiles : sms);
-  gemm_tf32_kernel<BN><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
+  gemm_tf32_kernel<BN, KIND><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
       map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
       static_cast<int>(batch), status);
   return check_launch("ib_contract (tcgen05 tf32)");
@@ -261,8 +265,23 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
   CUtensorMap map_a, map_b;
   if (int rc = make_tensor_map_f32(&map_a, a, batch, m, k, k, m * k, kBM)) return rc;
   if (int rc = make_tensor_map_f32(&map_b, b, batch, n, k, k, n * k, wide ? 256 : 128)) return rc;
-  return wide ? launch<256>(map_a, map_b, c, batch, m, n, k, s)
-              : launch<128>(map_a, map_b, c, batch, m, n, k, s);
+  return wide ? launch<256, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s)
+              : launch<128, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s);
+}
+
+int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
+                      size_t k, size_t k_pitch, cudaStream_t s) {
+  if (batch == 0 || m == 0 || n == 0) return 0;
+  if (k_pitch % 8 != 0 || k_pitch < k || !c || m >= (1u << 30) || n >= (1u << 30) ||
+      k >= (1u << 30) || batch >= (1u << 30))
+    return fail("ib_contract: shape not supported by the bf16 tensor-core arm");
+  const bool wide = n > 128;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_tensor_map_bf16(&map_a, a16, batch, m, k, k_pitch, m * k_pitch, kBM)) return rc;
+  if (int rc = make_tensor_map_bf16(&map_b, b16, batch, n, k, k_pitch, n * k_pitch, wide ? 256 : 128))
+    return rc;
+  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s)
+              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s);
 }
 
 }  // namespace ib

@@ -34,6 +34,10 @@ int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const 
 int make_tensor_map_f32(CUtensorMap* map, const float* base, size_t batch, size_t rows,
                         size_t cols, size_t row_pitch, size_t batch_pitch, unsigned box_rows);
 
+// Same for a bf16 tensor, boxes of 64 columns (128 bytes).
+int make_tensor_map_bf16(CUtensorMap* map, const void* base, size_t batch, size_t rows,
+                         size_t cols, size_t row_pitch, size_t batch_pitch, unsigned box_rows);
+
 // Per-launch status word the tcgen05 kernels report bounded-wait timeouts into.
 // Lives in device memory owned by the library; zeroed before each launch that
 // uses it and read back only on demand.
@@ -46,6 +50,14 @@ bool gemm_tcgen05_supported(const float* a, const float* b, const float* c, size
                             size_t k);
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
                  size_t k, cudaStream_t s);
+// Same contraction with bf16 operands a16 / b16 ([b][rows][k_pitch] bf16, k_pitch a multiple of 8)
+// fed to tcgen05 kind::f16, fp32 accumulation.
+int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
+                      size_t k, size_t k_pitch, cudaStream_t s);
+// out[r][c] = bf16(in[r][c]) (round to nearest even) for a [rows][cols] fp32 array; `out_pitch` in
+// elements, columns cols..out_pitch-1 are zeroed.
+int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,
+                      cudaStream_t s);
 
 // attention_tcgen05.cu — fused online-softmax attention; q is the caller's fp32
 // Q, k a TF32-rounded copy of K, vt the rounded V transposed to [b][dv][nk_pitch].

@@ -18,10 +18,11 @@ from conftest import last_error, max_rel_elementwise, max_rel_to_peak
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-FP32, TF32 = 1, 2
+FP32, TF32, BF16 = 1, 2, 3
 TOL_MAP = 1e-5
 TOL_FP32 = 1e-5
 TOL_TF32 = 5e-3
+TOL_BF16 = 2e-2
 
 
 @pytest.fixture(scope="module")
@@ -237,6 +238,22 @@ def test_contract_tf32_arm(lib, oracle, torch, m, n, k, akm, bkm):
     got = run_contract(lib, torch, a, b, akm, bkm, TF32)
     assert not np.isnan(got).any()
     assert max_rel_to_peak(got, oracle.contract(a, b, akm, bkm)) <= TOL_TF32
+
+
+@pytest.mark.parametrize("m,n,k,akm,bkm", [
+    (128, 128, 64, True, True), (256, 512, 256, True, True), (200, 300, 100, True, True),
+    (130, 70, 36, True, True), (3, 5, 7, True, True),      # K not a multiple of 8: padded copy
+    (256, 256, 128, True, False), (96, 200, 64, False, False),
+])
+def test_contract_bf16_arm(lib, oracle, torch, m, n, k, akm, bkm):
+    rng = np.random.default_rng(2)
+    a = (2 * rng.random((m, k) if akm else (k, m), dtype=np.float32) - 1)
+    b = (2 * rng.random((n, k) if bkm else (k, n), dtype=np.float32) - 1)
+    got = run_contract(lib, torch, a, b, akm, bkm, BF16)
+    assert not np.isnan(got).any()
+    err = max_rel_to_peak(got, oracle.contract(a, b, akm, bkm))
+    assert err <= TOL_BF16
+    assert err > 1e-6 or k < 8          # really bf16 arithmetic, not the fp32 arm
 
 
 def test_contract_tf32_batched(lib, oracle, torch):

@@ -107,6 +107,8 @@ def test_mm_t_component_tf32(ilang, oracle):
     assert max_rel_to_peak(got, oracle.contract(a, b)) <= 5e-3
     mm_t.set_precision("fp32")
     assert max_rel_to_peak(mm_t.exec_numpy(a, b), oracle.contract(a, b)) <= 1e-5
+    mm_t.set_precision("bf16")                                         # opt-in BF16 arm
+    assert max_rel_to_peak(mm_t.exec_numpy(a, b), oracle.contract(a, b)) <= 2e-2
 
 
 def test_multiple_outputs_identity_and_swap(ilang):
