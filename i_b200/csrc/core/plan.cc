@@ -214,7 +214,11 @@ void fuse_contractions(Builder& b) {
     const Node& mnode = b.g.nodes[n].inner;
     if (form.has_m && !mnode.splits[form.m].empty()) fused.hint.row_split = mnode.splits[form.m][0];
     if (form.has_n && !mnode.splits[form.n].empty()) fused.hint.col_split = mnode.splits[form.n][0];
-    if (!mnode.order.empty()) fused.hint.reduce_outer = form.has_n && mnode.order[0].index == form.n;
+    for (const auto& level : mnode.order)
+      if ((form.has_n && level.index == form.n) || (form.has_m && level.index == form.m)) {
+        fused.hint.reduce_outer = form.has_n && level.index == form.n;
+        break;
+      }
     b.steps[*reader] = std::move(fused);
     b.alive[n] = false;
   }
@@ -273,7 +277,12 @@ void fuse_softmax(Builder& b) {
     const size_t col = mx.rank - 1;
     if (mx.rank >= 2 && !mnode.splits[col - 1].empty()) fused.hint.row_split = mnode.splits[col - 1][0];
     if (!mnode.splits[col].empty()) fused.hint.col_split = mnode.splits[col][0];
-    if (!mnode.order.empty()) fused.hint.reduce_outer = mnode.order[0].index == col;
+    // Which of the row / reduced axes has the outermost loop (batch axes aside).
+    for (const auto& level : mnode.order)
+      if (level.index == col || (mx.rank >= 2 && level.index == col - 1)) {
+        fused.hint.reduce_outer = level.index == col;
+        break;
+      }
     fused.hint.staged = b.steps[*r_sub].hint.staged || ex.hint.staged || dv.hint.staged;
     const size_t last = std::max(std::max(*r_sub, *r_exp), std::max(i_sum, i_div));
     for (size_t dead : fused.nodes) b.alive[dead] = false;
@@ -389,6 +398,17 @@ std::string Plan::describe() const {
       case StepKind::Map:
         os << "    kernel: ib_map\n";
         break;
+    }
+    if (s.kind == StepKind::Attention || s.kind == StepKind::Contract) {
+      const size_t row_tile = 128, col_tile = s.kind == StepKind::Attention ? 128 : 256;
+      os << "    tiles: " << row_tile << " rows x " << col_tile
+         << (s.kind == StepKind::Attention ? " keys per step, K/V ring of 3 x 64 KB"
+                                            : " columns x 32 deep, 4-stage TMA ring");
+      auto fits = [](size_t tile, size_t granule) { return granule == 0 || tile % granule == 0; };
+      if (fits(row_tile, s.hint.row_split) && fits(col_tile, s.hint.col_split))
+        os << "; whole multiples of the schedule's granules\n";
+      else
+        os << "; the schedule's granules do not divide them, results are unaffected\n";
     }
     if (s.hint.row_split || s.hint.col_split || s.hint.staged)
       os << "    schedule: row granule " << s.hint.row_split << ", column granule "
