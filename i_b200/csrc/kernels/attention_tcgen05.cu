@@ -84,7 +84,6 @@ struct Params {
 
 struct Shared {
   uint64_t kv_full[kRing];
-  uint64_t kv_empty[kRing];
   uint64_t q_ready;
   uint64_t s_full[2];
   uint64_t p_full[2];
@@ -168,7 +167,6 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRing; ++s) {
       mbar_init(&sh->kv_full[s], 1);
-      mbar_init(&sh->kv_empty[s], 1);
     }
     mbar_init(&sh->q_ready, 8);            // one arrival per softmax warp
     for (int u = 0; u < 2; ++u) {
@@ -195,29 +193,48 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_vt);
       int slot = 0;
-      uint32_t phase = 0;
       bool ok = true;
       long long waited = 0;
       int b = 0;
-      auto load_k = [&](int j) {
+      // A ring slot is free again when the MMAs that read its tile have completed:
+      // Q K^T of tile t for a K tile (signalled on s_full[t & 1]), P V of tile t for
+      // a V tile (pv_done[t & 1]); t counts this CTA's key tiles.  The producer
+      // remembers who occupies each slot and waits for that event before reuse.  It
+      // meets every event once and in order, and the next-but-one event on the same
+      // barrier needs a tile this producer has not loaded yet, so a parity wait is
+      // never two phases behind.
+      uint64_t* occupant_bar[kRing] = {nullptr, nullptr, nullptr};
+      uint32_t occupant_parity[kRing] = {0, 0, 0};
+      long long tile_k = 0, tile_v = 0;       // tile counters of the next K / V load
+      auto acquire = [&](int code) {
+        if (!occupant_bar[slot]) return;
         const long long t0 = tick<PROF>();
-        if (!(ok = mbar_wait(&sh->kv_empty[slot], phase ^ 1, abort, p.status, 201))) return;
+        ok = mbar_wait(occupant_bar[slot], occupant_parity[slot], abort, p.status, code);
         waited += tick<PROF>() - t0;
+      };
+      auto load_k = [&](int j) {
+        acquire(201);
+        if (!ok) return;
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
         for (int c = 0; c < d_chunks; ++c)
           tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * 32, j * kBKV, b);
-        if (++slot == kRing) { slot = 0; phase ^= 1; }
+        occupant_bar[slot] = &sh->s_full[tile_k & 1];
+        occupant_parity[slot] = static_cast<uint32_t>((tile_k >> 1) & 1);
+        ++tile_k;
+        if (++slot == kRing) slot = 0;
       };
       auto load_v = [&](int j) {
-        const long long t0 = tick<PROF>();
-        if (!(ok = mbar_wait(&sh->kv_empty[slot], phase ^ 1, abort, p.status, 202))) return;
-        waited += tick<PROF>() - t0;
+        acquire(202);
+        if (!ok) return;
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&sh->kv_full[slot], 4 * kChunkBytes);
         for (int c = 0; c < 4; ++c)
           tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot], j * kBKV + c * 32, 0, b);
-        if (++slot == kRing) { slot = 0; phase ^= 1; }
+        occupant_bar[slot] = &sh->pv_done[tile_v & 1];
+        occupant_parity[slot] = static_cast<uint32_t>((tile_v >> 1) & 1);
+        ++tile_v;
+        if (++slot == kRing) slot = 0;
       };
       // Per piece, consumption order is K(0), then per tile K(j+1) before V(j).
       PieceCursor cursor = pieces_begin(p);
@@ -266,8 +283,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                                k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
                                ks != 0 ? 1u : 0u);
         }
-        mma_commit(&sh->s_full[buf]);
-        mma_commit(&sh->kv_empty[slot]);
+        mma_commit(&sh->s_full[buf]);          // S ready, and the K tile's slot is free
         issue_qk_cycles += tick<PROF>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
@@ -294,8 +310,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         for (int ks = 1; ks < kBKV / 8; ++ks)
           mma_ts<Kind::TF32>(d_tmem, p_tmem + ks * 8,
                              v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
-        mma_commit(&sh->pv_done[buf]);
-        mma_commit(&sh->kv_empty[slot]);
+        mma_commit(&sh->pv_done[buf]);         // O updated, and the V tile's slot is free
         issue_pv_cycles += tick<PROF>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
