@@ -55,9 +55,25 @@ using namespace sm100;
 constexpr int kBQ = 128;           // query rows per CTA
 constexpr int kBKV = 128;          // keys per KV tile
 constexpr int kThreads = 384;
-constexpr int kChunkBytes = 128 * 128;     // 128 rows x 32 fp32
-constexpr int kSlotBytes = 4 * kChunkBytes;
-constexpr int kRing = 3;
+constexpr int kChunkBytes = 128 * 128;     // 128 rows of 128 bytes: 32 fp32 or 64 bf16 per row
+constexpr int kMaxRing = 3;
+
+// Per operand type: a K or V^T tile of 128 keys is 4 chunks (TF32) or 2 (BF16);
+// the ring always has three slots (the producer's slot-reuse waits rely on that
+// distance, see there).  One MMA consumes 32 bytes of
+// every operand row (8 TF32 or 16 BF16 along K) and 8 tensor-memory columns of
+// its A operand (bf16 pairs are packed two to a column), so a 128-deep
+// contraction is 16 or 8 instructions.
+template <Kind KIND>
+struct Geometry {
+  static constexpr int kChunkElems = KIND == Kind::TF32 ? 32 : 64;
+  static constexpr int kTileChunks = 128 / kChunkElems;            // 4 or 2
+  static constexpr int kSlotBytes = kTileChunks * kChunkBytes;     // 64 KB or 32 KB
+  static constexpr int kRing = 3;
+  static constexpr int kStepElems = KIND == Kind::TF32 ? 8 : 16;   // K per MMA
+  static constexpr int kSteps = 128 / kStepElems;                  // 16 or 8
+};
+constexpr int kRingBytes = 3 * 4 * kChunkBytes;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemQ = 0;
 constexpr uint32_t kTmemS = 128;           // + buf * 128
@@ -83,7 +99,7 @@ struct Params {
 };
 
 struct Shared {
-  uint64_t kv_full[kRing];
+  uint64_t kv_full[kMaxRing];
   uint64_t q_ready;
   uint64_t s_full[2];
   uint64_t p_full[2];
@@ -140,6 +156,13 @@ __device__ __forceinline__ bool next_piece(const Params& p, PieceCursor& c, Piec
   return true;
 }
 
+// Two floats -> one 32-bit word of bf16 (round to nearest even), first value in the low half.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t out;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+
 template <bool PROF>
 __device__ __forceinline__ long long tick() {
   return PROF ? clock64() : 0ll;
@@ -150,19 +173,22 @@ __device__ __forceinline__ void softmax_pair_sync() {
 }
 
 // PROF = true compiles in the cycle counters written to Params::prof.
-template <bool PROF>
+template <bool PROF, Kind KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vt, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* ring = smem;                                     // [kRing][64 KB]
-  Shared* sh = reinterpret_cast<Shared*>(ring + kRing * kSlotBytes);
+  using G = Geometry<KIND>;
+  constexpr int kRing = G::kRing;
+  constexpr int kSlotBytes = G::kSlotBytes;
+  uint8_t* ring = smem;                                     // [kRing][kSlotBytes]
+  Shared* sh = reinterpret_cast<Shared*>(ring + kRingBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int d_chunks = (p.d + 31) / 32;
+  const int d_chunks = (p.d + G::kChunkElems - 1) / G::kChunkElems;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRing; ++s) {
@@ -200,11 +226,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       // Q K^T of tile t for a K tile (signalled on s_full[t & 1]), P V of tile t for
       // a V tile (pv_done[t & 1]); t counts this CTA's key tiles.  The producer
       // remembers who occupies each slot and waits for that event before reuse.  It
-      // meets every event once and in order, and the next-but-one event on the same
-      // barrier needs a tile this producer has not loaded yet, so a parity wait is
-      // never two phases behind.
-      uint64_t* occupant_bar[kRing] = {nullptr, nullptr, nullptr};
-      uint32_t occupant_parity[kRing] = {0, 0, 0};
+      // meets every event once and in order, and with three slots the next-but-one
+      // event on the same barrier needs a tile this producer has not loaded yet, so
+      // a parity wait is never two phases behind (a deeper ring would break that).
+      uint64_t* occupant_bar[kRing] = {};
+      uint32_t occupant_parity[kRing] = {};
       long long tile_k = 0, tile_v = 0;       // tile counters of the next K / V load
       auto acquire = [&](int code) {
         if (!occupant_bar[slot]) return;
@@ -218,7 +244,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
         for (int c = 0; c < d_chunks; ++c)
-          tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * 32, j * kBKV, b);
+          tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kChunkElems,
+                      j * kBKV, b);
         occupant_bar[slot] = &sh->s_full[tile_k & 1];
         occupant_parity[slot] = static_cast<uint32_t>((tile_k >> 1) & 1);
         ++tile_k;
@@ -228,9 +255,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         acquire(202);
         if (!ok) return;
         uint8_t* dst = ring + slot * kSlotBytes;
-        mbar_arrive_expect_tx(&sh->kv_full[slot], 4 * kChunkBytes);
-        for (int c = 0; c < 4; ++c)
-          tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot], j * kBKV + c * 32, 0, b);
+        mbar_arrive_expect_tx(&sh->kv_full[slot], G::kTileChunks * kChunkBytes);
+        for (int c = 0; c < G::kTileChunks; ++c)
+          tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot],
+                      j * kBKV + c * G::kChunkElems, 0, b);
         occupant_bar[slot] = &sh->pv_done[tile_v & 1];
         occupant_parity[slot] = static_cast<uint32_t>((tile_v >> 1) & 1);
         ++tile_v;
@@ -251,10 +279,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc(Kind::TF32, kBQ, kBKV);
+      const uint32_t idesc_qk = make_idesc(KIND, kBQ, kBKV);
       const uint32_t n_pv = static_cast<uint32_t>((p.dv + 15) / 16 * 16);
-      const uint32_t idesc_pv = make_idesc(Kind::TF32, kBQ, n_pv);
-      const int k_steps = (p.d + 7) / 8;
+      const uint32_t idesc_pv = make_idesc(KIND, kBQ, n_pv);
+      const int k_steps = (p.d + G::kStepElems - 1) / G::kStepElems;
       int slot = 0;
       uint32_t phase = 0;
       const uint32_t ring_addr = smem_u32(ring);
@@ -277,11 +305,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
         const uint32_t q_tmem = tmem_base + kTmemQ;
 #pragma unroll
-        for (int ks = 0; ks < 16; ++ks) {
+        for (int ks = 0; ks < G::kSteps; ++ks) {
           if (ks < k_steps)
-            mma_ts<Kind::TF32>(d_tmem, q_tmem + ks * 8,
-                               k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
-                               ks != 0 ? 1u : 0u);
+            mma_ts<KIND>(d_tmem, q_tmem + ks * 8,
+                         k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
+                         ks != 0 ? 1u : 0u);
         }
         mma_commit(&sh->s_full[buf]);          // S ready, and the K tile's slot is free
         issue_qk_cycles += tick<PROF>() - ti;
@@ -301,15 +329,21 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
         const uint32_t d_tmem = tmem_base + kTmemO;
         const uint32_t p_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
+        // Keys 64h..64h+63 of P sit at the start of softmax half h's 64 columns:
+        // 64 columns of fp32 (TF32) or 32 columns of packed bf16 pairs.
+        auto p_col = [&](int ks) -> uint32_t {
+          constexpr int kHalfSteps = G::kSteps / 2;
+          return p_tmem + static_cast<uint32_t>((ks / kHalfSteps) * 64 + (ks % kHalfSteps) * 8);
+        };
         if (first_of_piece) {
-          mma_ts<Kind::TF32>(d_tmem, p_tmem, v_desc, idesc_pv, 0u);
+          mma_ts<KIND>(d_tmem, p_col(0), v_desc, idesc_pv, 0u);
         } else {
-          mma_ts<Kind::TF32>(d_tmem, p_tmem, v_desc, idesc_pv, 1u);
+          mma_ts<KIND>(d_tmem, p_col(0), v_desc, idesc_pv, 1u);
         }
 #pragma unroll
-        for (int ks = 1; ks < kBKV / 8; ++ks)
-          mma_ts<Kind::TF32>(d_tmem, p_tmem + ks * 8,
-                             v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
+        for (int ks = 1; ks < G::kSteps; ++ks)
+          mma_ts<KIND>(d_tmem, p_col(ks),
+                       v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
         mma_commit(&sh->pv_done[buf]);         // O updated, and the V tile's slot is free
         issue_pv_cycles += tick<PROF>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
@@ -368,27 +402,44 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       const float* qrow = p.q + (static_cast<size_t>(b) * p.nq + row) * p.d;
       const bool live = row < p.nq;
       const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
+      // This thread's 64 features [64h, 64h+64) of its row, rounded to the operand type.
+      auto load4 = [&](int col) {
+        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (live && vec && col + 4 <= p.d) {
+          x = *reinterpret_cast<const float4*>(qrow + col);
+        } else if (live) {
+          if (col + 0 < p.d) x.x = qrow[col + 0];
+          if (col + 1 < p.d) x.y = qrow[col + 1];
+          if (col + 2 < p.d) x.z = qrow[col + 2];
+          if (col + 3 < p.d) x.w = qrow[col + 3];
+        }
+        return x;
+      };
+      if (KIND == Kind::TF32) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = h * 64 + c * 32;
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = h * 64 + c * 32;
+          uint32_t v[32];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float4 x = load4(col0 + e);
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
+          }
+          tmem_st_32x32(tmem_base + lane_bits + kTmemQ + col0, v);
+        }
+      } else {
+        // bf16 pairs, two features per column: features [64h, 64h+64) -> columns [32h, 32h+32).
         uint32_t v[32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (live && vec && col0 + e + 4 <= p.d) {
-            x = *reinterpret_cast<const float4*>(qrow + col0 + e);
-          } else if (live) {
-            if (col0 + e + 0 < p.d) x.x = qrow[col0 + e + 0];
-            if (col0 + e + 1 < p.d) x.y = qrow[col0 + e + 1];
-            if (col0 + e + 2 < p.d) x.z = qrow[col0 + e + 2];
-            if (col0 + e + 3 < p.d) x.w = qrow[col0 + e + 3];
-          }
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
+        for (int e = 0; e < 32; e += 2) {
+          const float4 x = load4(h * 64 + 2 * e);
+          v[e + 0] = pack_bf16(x.x, x.y);
+          v[e + 1] = pack_bf16(x.z, x.w);
         }
-        tmem_st_32x32(tmem_base + lane_bits + kTmemQ + col0, v);
+        tmem_st_32x32(tmem_base + lane_bits + kTmemQ + h * 32, v);
       }
       tmem_wait_st();
       tc_fence_before_sync();
@@ -480,8 +531,19 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         s1[c] = __float_as_uint(e1);
       }
       l += sum0 + sum1;
-      tmem_st_32x32(s_tmem, s0);
-      tmem_st_32x32(s_tmem + 32, s1);
+      if (KIND == Kind::TF32) {
+        tmem_st_32x32(s_tmem, s0);
+        tmem_st_32x32(s_tmem + 32, s1);
+      } else {
+        // Pack this half's 64 probabilities as 32 bf16 pairs over the start of its own S columns.
+        uint32_t packed[32];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          packed[c] = pack_bf16(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1]));
+          packed[16 + c] = pack_bf16(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1]));
+        }
+        tmem_st_32x32(s_tmem, packed);
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -663,23 +725,26 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
   return static_cast<size_t>(2) * ctas * kBQ * (dv + 2);
 }
 
-int attention_tcgen05(const float* q, const float* k, const float* vt, float* o, size_t batch,
-                      size_t nq, size_t nk, size_t d, size_t dv, size_t nk_pitch, float* partials,
-                      cudaStream_t s) {
+int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
+                      size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
+                      bool bf16, float* partials, cudaStream_t s) {
   if (batch == 0 || nq == 0) return 0;
   if (nk == 0) return fail("ib_attention: no keys");
   if (nq >= (1u << 30) || nk >= (1u << 30) || batch >= (1u << 20))
     return fail("ib_attention: shape too large");
   if (d % 4 != 0 || d < 4 || d > 128 || dv < 1 || dv > 128)
     return fail("ib_attention: head dimensions outside the fused kernel's range");
-  const int smem_bytes = 1024 + kRing * kSlotBytes + static_cast<int>(sizeof(Shared)) + 64;
+  const int smem_bytes = 1024 + kRingBytes + static_cast<int>(sizeof(Shared)) + 64;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_tf32_kernel<false>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(attention_tf32_kernel<true>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t err = cudaSuccess;
+    const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<false, Kind::TF32>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Kind::TF32>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Kind::BF16>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Kind::BF16>)};
+    for (const void* fn : variants)
+      if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess)
       return fail(std::string("ib_attention: cannot reserve shared memory: ") +
                   cudaGetErrorString(err));
@@ -714,14 +779,28 @@ int attention_tcgen05(const float* q, const float* k, const float* vt, float* o,
   p.prof = g_attention_profile;
 
   CUtensorMap map_k, map_vt;
-  if (int rc = make_tensor_map_f32(&map_k, k, batch, nk, d, d, nk * d, kBKV)) return rc;
-  if (int rc = make_tensor_map_f32(&map_vt, vt, batch, dv, nk, nk_pitch, dv * nk_pitch, 128))
-    return rc;
+  if (bf16) {
+    if (int rc = make_tensor_map_bf16(&map_k, k, batch, nk, d, d_pitch, nk * d_pitch, kBKV)) return rc;
+    if (int rc = make_tensor_map_bf16(&map_vt, vt, batch, dv, nk, nk_pitch, dv * nk_pitch, 128))
+      return rc;
+  } else {
+    if (int rc = make_tensor_map_f32(&map_k, static_cast<const float*>(k), batch, nk, d, d_pitch,
+                                     nk * d_pitch, kBKV))
+      return rc;
+    if (int rc = make_tensor_map_f32(&map_vt, static_cast<const float*>(vt), batch, dv, nk, nk_pitch,
+                                     dv * nk_pitch, 128))
+      return rc;
+  }
 
-  if (p.prof)
-    attention_tf32_kernel<true><<<static_cast<unsigned>(ctas), kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+  const unsigned grid = static_cast<unsigned>(ctas);
+  if (bf16 && p.prof)
+    attention_tf32_kernel<true, Kind::BF16><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+  else if (bf16)
+    attention_tf32_kernel<false, Kind::BF16><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+  else if (p.prof)
+    attention_tf32_kernel<true, Kind::TF32><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
   else
-    attention_tf32_kernel<false><<<static_cast<unsigned>(ctas), kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+    attention_tf32_kernel<false, Kind::TF32><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
   if (int rc = check_launch("ib_attention (tcgen05 tf32)")) return rc;
   // Tail row tiles shared by several CTA ranges exist unless the ranges fall on tile boundaries.
   if (tail_units > 0 && !(p.iters_rem == 0 && p.iters_base % p.kv_tiles == 0)) {

@@ -231,7 +231,72 @@ convert_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ ou
   }
 }
 
+// bf16 operand preparation for attention, one launch: blockIdx.y = 0 converts K
+// ([rows][d] -> [rows][d_pitch]), blockIdx.y = 1 writes V^T ([nk][dv] -> [dv][nk_pitch])
+// through 64x64 shared-memory tiles.  Pad columns are written as zero.
+struct PrepareBf16Args {
+  const float* k; __nv_bfloat16* k16; size_t k_rows, d, d_pitch;
+  const float* v; __nv_bfloat16* vt16; size_t batch, nk, dv, nk_pitch;
+};
+
+__global__ void __launch_bounds__(256)
+prepare_attention_bf16_kernel(PrepareBf16Args a) {
+  __shared__ float tile[64][65];
+  if (blockIdx.y == 0) {
+    const size_t pairs = a.d_pitch / 2, total = a.k_rows * pairs;
+    const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
+      const size_t r = i / pairs, c = (i - r * pairs) * 2;
+      const float x = c < a.d ? a.k[r * a.d + c] : 0.0f;
+      const float y = c + 1 < a.d ? a.k[r * a.d + c + 1] : 0.0f;
+      reinterpret_cast<__nv_bfloat162*>(a.k16 + r * a.d_pitch)[c / 2] = __floats2bfloat162_rn(x, y);
+    }
+    return;
+  }
+  const size_t tiles_k = (a.nk_pitch + 63) / 64, tiles_d = (a.dv + 63) / 64;
+  const size_t total = a.batch * tiles_k * tiles_d;
+  for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const size_t b = t / (tiles_k * tiles_d);
+    const size_t rem = t - b * tiles_k * tiles_d;
+    const size_t k0 = (rem / tiles_d) * 64, d0 = (rem % tiles_d) * 64;
+    const float* src = a.v + b * a.nk * a.dv;
+    __nv_bfloat16* dst = a.vt16 + b * a.dv * a.nk_pitch;
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+      const int r = e >> 6, c = e & 63;
+      float x = 0.0f;
+      if (k0 + r < a.nk && d0 + c < a.dv) x = src[(k0 + r) * a.dv + d0 + c];
+      tile[r][c] = x;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+      const int c = e >> 5, r = (e & 31) * 2;             // c: feature, r: key pair
+      if (d0 + c < a.dv && k0 + r < a.nk_pitch)
+        reinterpret_cast<__nv_bfloat162*>(dst + (d0 + c) * a.nk_pitch + k0)[r / 2] =
+            __floats2bfloat162_rn(tile[r][c], tile[r + 1][c]);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
+
+int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
+                                    size_t batch, size_t nk, size_t d, size_t dv, size_t d_pitch,
+                                    size_t nk_pitch, bool v_kmajor, cudaStream_t s) {
+  if (v_kmajor) {
+    // V already [dv][nk]: both operands are plain row conversions.
+    if (int rc = convert_bf16_rows(k, k16, batch * nk, d, d_pitch, s)) return rc;
+    return convert_bf16_rows(v, vt16, batch * dv, nk, nk_pitch, s);
+  }
+  PrepareBf16Args a{k, static_cast<__nv_bfloat16*>(k16), batch * nk, d, d_pitch,
+                    v, static_cast<__nv_bfloat16*>(vt16), batch, nk, dv, nk_pitch};
+  const size_t most = std::max(batch * nk * d_pitch / 2 / 256 + 1,
+                               batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64));
+  const size_t cap = static_cast<size_t>(kNumSMs) * 8;
+  dim3 grid(static_cast<unsigned>(std::min(most, cap)), 2);
+  prepare_attention_bf16_kernel<<<grid, 256, 0, s>>>(a);
+  return check_launch("prepare_attention_operands_bf16");
+}
 
 int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,
                       cudaStream_t s) {

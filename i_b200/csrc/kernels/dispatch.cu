@@ -131,9 +131,16 @@ extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t n
   using namespace ib;
   const double flop = 4.0 * batch * nq * nk * d;
   if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
-    // TF32-rounded copy of K, V^T (rounded), and the KV-split partials.
-    size_t bytes = carve_bytes(batch * nk * d);
-    bytes += carve_bytes(batch * dv * round_up(nk, 4));
+    // Rounded copy of K, V^T (rounded), and the KV-split partials; bf16 copies
+    // are half the size, with pitches rounded up to 8 elements.
+    size_t bytes;
+    if (precision == IB_PRECISION_BF16) {
+      bytes = carve_bytes((batch * nk * round_up(d, 8) + 1) / 2);
+      bytes += carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2);
+    } else {
+      bytes = carve_bytes(batch * nk * d);
+      bytes += carve_bytes(batch * dv * round_up(nk, 4));
+    }
     bytes += carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
     return bytes;
   }
@@ -167,8 +174,21 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
     // to nearest into workspace copies (V transposed to [dv][keys] on the way,
     // the K-major layout the second contraction needs); the kernel rounds Q
     // itself while moving it into tensor memory.
-    const size_t pitch = round_up(nk, 4);
     const char* small = "ib_attention: workspace too small (see ib_attention_workspace_bytes)";
+    if (precision == IB_PRECISION_BF16) {
+      // Opt-in: bf16 operands (round to nearest even), fp32 scores, sums and outputs.
+      const size_t d_pitch = round_up(d, 8), nk_pitch = round_up(nk, 8);
+      float* k16 = ws.take((batch * nk * d_pitch + 1) / 2);
+      float* vt16 = ws.take((batch * dv * nk_pitch + 1) / 2);
+      float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
+      if (!k16 || !vt16 || !partials) return fail(small);
+      if (int rc = prepare_attention_operands_bf16(k, k16, v, vt16, batch, nk, d, dv, d_pitch,
+                                                   nk_pitch, v_kmajor != 0, s))
+        return rc;
+      return attention_tcgen05(q, k16, vt16, o, batch, nq, nk, d, dv, d_pitch, nk_pitch, true,
+                               partials, s);
+    }
+    const size_t pitch = round_up(nk, 4);
     float* kr = ws.take(batch * nk * d);
     float* vt = ws.take(batch * dv * pitch);
     if (!kr || !vt) return fail(small);
@@ -189,7 +209,7 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
     }
     float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
     if (!partials) return fail(small);
-    return attention_tcgen05(q, kr, vt, o, batch, nq, nk, d, dv, pitch, partials, s);
+    return attention_tcgen05(q, kr, vt, o, batch, nq, nk, d, dv, d, pitch, false, partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);

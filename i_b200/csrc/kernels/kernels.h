@@ -64,9 +64,16 @@ int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size
 // Floats of scratch for the partial results of row tiles shared between CTAs.
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv,
                                         int* ctas_out);
-int attention_tcgen05(const float* q, const float* k, const float* vt, float* o, size_t batch,
-                      size_t nq, size_t nk, size_t d, size_t dv, size_t nk_pitch, float* partials,
-                      cudaStream_t s);
+// With bf16 = true, k and vt hold bf16 ([b][nk][d_pitch] and [b][dv][nk_pitch], pitches multiples
+// of 8) and the contractions run as kind::f16.
+int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
+                      size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
+                      bool bf16, float* partials, cudaStream_t s);
+// bf16 operand preparation: k16[b][r][d_pitch] = bf16(k), vt16[b][c][nk_pitch] = bf16(v^T);
+// pad columns are zeroed.
+int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
+                                    size_t batch, size_t nk, size_t d, size_t dv, size_t d_pitch,
+                                    size_t nk_pitch, bool v_kmajor, cudaStream_t s);
 
 void set_attention_profile(unsigned long long* device_counters);
 void set_reserved_sms(int n);

@@ -302,7 +302,7 @@ def run_attention(lib, torch, q, k, v, precision, v_kmajor=False):
 
 
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "attention_*.npz"))))
-@pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32)])
+@pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32), (BF16, TOL_BF16)])
 def test_attention_golden(lib, torch, path, precision, tol):
     g = np.load(path)
     got = run_attention(lib, torch, g["q"], g["k"], g["v"], precision)
@@ -322,16 +322,33 @@ def test_attention_tf32_shapes(lib, oracle, torch, nq, nk, d, dv):
     assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= TOL_TF32
 
 
+@pytest.mark.parametrize("nq,nk,d,dv", [
+    (256, 128, 64, 64), (512, 512, 128, 128), (300, 200, 40, 24), (129, 65, 8, 100),
+    (1000, 3000, 128, 128),
+])
+def test_attention_bf16_shapes(lib, oracle, torch, nq, nk, d, dv):
+    q = rand((nq, d), 15) * np.float32(d ** -0.5)
+    k, v = rand((nk, d), 16), rand((nk, dv), 17)
+    got = run_attention(lib, torch, q, k, v, BF16)
+    assert not np.isnan(got).any()
+    err = max_rel_to_peak(got, oracle.attention_fused(q, k, v))
+    assert 1e-5 < err <= TOL_BF16          # bf16 arithmetic, within the opt-in bound
+
+
 def test_attention_tf32_batched_and_transposed_v(lib, oracle, torch):
     q = rand((3, 260, 64), 18) * np.float32(0.125)
     k, v = rand((3, 333, 64), 19), rand((3, 333, 48), 20)
     got = run_attention(lib, torch, q, k, v, TF32)
-    got_t = run_attention(lib, torch, q, k, np.ascontiguousarray(v.transpose(0, 2, 1)), TF32,
-                          v_kmajor=True)
+    vt = np.ascontiguousarray(v.transpose(0, 2, 1))
+    got_t = run_attention(lib, torch, q, k, vt, TF32, v_kmajor=True)
+    got_b = run_attention(lib, torch, q, k, v, BF16)
+    got_bt = run_attention(lib, torch, q, k, vt, BF16, v_kmajor=True)
     for i in range(3):
         ref = oracle.attention_fused(q[i], k[i], v[i])
         assert max_rel_to_peak(got[i], ref) <= TOL_TF32
         assert max_rel_to_peak(got_t[i], ref) <= TOL_TF32
+        assert max_rel_to_peak(got_b[i], ref) <= TOL_BF16
+        assert max_rel_to_peak(got_bt[i], ref) <= TOL_BF16
 
 
 def test_attention_large_scores_stay_finite(lib, oracle, torch):
