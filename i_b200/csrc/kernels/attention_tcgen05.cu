@@ -42,6 +42,7 @@
 // partial O with its (m, l); a small second kernel merges the pieces.
 // Roofline: tensor-bound, 4*Nq*Nk*d FLOP per head.
 #include <atomic>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -213,11 +214,18 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_slot;
   AbortState* abort = &sh->abort;
+  // The merge kernel that follows may be scheduled from now on (it waits for this
+  // grid to finish before it reads anything).
+  trigger_dependent_launch();
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_vt);
+      // K and V^T come from the preparation kernel before this one in the stream;
+      // this thread is the only one that reads them (Q, read by the softmax warps,
+      // is an input of the call and older than that kernel).
+      grid_dependency_wait();
       int slot = 0;
       bool ok = true;
       long long waited = 0;
@@ -267,8 +275,21 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       // Per piece, consumption order is K(0), then per tile K(j+1) before V(j).
       PieceCursor cursor = pieces_begin(p);
       Piece pc;
+      const bool q_prefetchable = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
       while (ok && next_piece(p, cursor, pc)) {
         b = pc.unit / p.q_tiles;
+        {
+          // Pull the Q rows of the piece after this one into L2 while this one runs.
+          PieceCursor ahead = cursor;
+          Piece nx;
+          if (q_prefetchable && next_piece(p, ahead, nx) && nx.unit != pc.unit) {
+            const int nb = nx.unit / p.q_tiles;
+            const long long row0 = static_cast<long long>(nx.unit - nb * p.q_tiles) * kBQ;
+            const long long rows = min(static_cast<long long>(kBQ), p.nq - row0);
+            prefetch_l2_bulk(p.q + (static_cast<size_t>(nb) * p.nq + row0) * p.d,
+                             static_cast<uint32_t>(rows * p.d * 4));
+          }
+        }
         load_k(pc.kv_lo);
         for (int jj = 0; ok && jj < pc.n_kv; ++jj) {
           if (jj + 1 < pc.n_kv) load_k(pc.kv_lo + jj + 1);
@@ -640,6 +661,8 @@ __device__ __forceinline__ int cta_of(const CombineArgs& a, long long it) {
 __global__ void __launch_bounds__(256)
 attention_combine_kernel(const CombineArgs a) {
   constexpr int kRowsPerCta = 16;
+  grid_dependency_wait();                   // every CTA, before any exit: the pieces come from the
+                                            // attention kernel this one may have been launched under
   const int tail_unit = blockIdx.x / (kBQ / kRowsPerCta);
   const int row0 = (blockIdx.x % (kBQ / kRowsPerCta)) * kRowsPerCta;
   const int unit = a.first_tail_unit + tail_unit;
@@ -700,6 +723,12 @@ int choose_ctas(long long units, long long kv_tiles, int sms) {
 
 // SMs the persistent kernel leaves free (for a communication kernel running next to it).
 std::atomic<int> g_reserved_sms{0};
+
+// I_B200_DEPENDENT_LAUNCH=0 launches the kernels of a call strictly one after another.
+const bool g_dependent_launch = [] {
+  const char* v = std::getenv("I_B200_DEPENDENT_LAUNCH");
+  return !(v && v[0] == '0');
+}();
 
 int device_sms() {
   int sms = kNumSMs;
@@ -792,22 +821,42 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
       return rc;
   }
 
-  const unsigned grid = static_cast<unsigned>(ctas);
+  // Both launches carry the programmatic-serialization attribute: the attention
+  // kernel's set-up and its Q load run under the tail of the preparation kernel,
+  // and the merge kernel's launch latency under the attention kernel.
+  cudaLaunchAttribute overlap{};
+  overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  overlap.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = s;
+  cfg.attrs = &overlap;
+  cfg.numAttrs = g_dependent_launch ? 1 : 0;
+  cudaError_t launched;
   if (bf16 && p.prof)
-    attention_tf32_kernel<true, Kind::BF16><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Kind::BF16>, map_k, map_vt, p);
   else if (bf16)
-    attention_tf32_kernel<false, Kind::BF16><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Kind::BF16>, map_k, map_vt, p);
   else if (p.prof)
-    attention_tf32_kernel<true, Kind::TF32><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Kind::TF32>, map_k, map_vt, p);
   else
-    attention_tf32_kernel<false, Kind::TF32><<<grid, kThreads, smem_bytes, s>>>(map_k, map_vt, p);
-  if (int rc = check_launch("ib_attention (tcgen05 tf32)")) return rc;
+    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Kind::TF32>, map_k, map_vt, p);
+  if (launched != cudaSuccess)
+    return fail(std::string("ib_attention (tcgen05): launch failed: ") + cudaGetErrorString(launched));
+  count_launch();
   // Tail row tiles shared by several CTA ranges exist unless the ranges fall on tile boundaries.
   if (tail_units > 0 && !(p.iters_rem == 0 && p.iters_base % p.kv_tiles == 0)) {
     CombineArgs a{p.part_o, p.part_m, p.part_l, o, p.nq, p.dv, p.q_tiles, p.kv_tiles, ctas,
                   p.full_waves * ctas, p.iters_base, p.iters_rem};
-    attention_combine_kernel<<<static_cast<unsigned>(tail_units * 8), 256, 0, s>>>(a);
-    return check_launch("ib_attention (combine)");
+    cfg.gridDim = dim3(static_cast<unsigned>(tail_units * 8));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    launched = cudaLaunchKernelEx(&cfg, attention_combine_kernel, a);
+    if (launched != cudaSuccess)
+      return fail(std::string("ib_attention (combine): launch failed: ") + cudaGetErrorString(launched));
+    count_launch();
   }
   return 0;
 }

@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "sm100.cuh"
 
 namespace ib {
 namespace {
@@ -154,6 +155,9 @@ struct PrepareArgs {
 __global__ void __launch_bounds__(256)
 prepare_attention_kernel(PrepareArgs a) {
   __shared__ float tile[64][65];
+  // The attention kernel may be scheduled once every CTA of this grid has started;
+  // it waits for this grid's completion before it reads K or V^T.
+  sm100::trigger_dependent_launch();
   if (blockIdx.y < 2) {
     const float* in = blockIdx.y == 0 ? a.q : a.k;
     float* out = blockIdx.y == 0 ? a.qr : a.kr;
@@ -242,6 +246,7 @@ struct PrepareBf16Args {
 __global__ void __launch_bounds__(256)
 prepare_attention_bf16_kernel(PrepareBf16Args a) {
   __shared__ float tile[64][65];
+  sm100::trigger_dependent_launch();       // see prepare_attention_kernel
   if (blockIdx.y == 0) {
     const size_t pairs = a.d_pitch / 2, total = a.k_rows * pairs;
     const size_t stride = static_cast<size_t>(gridDim.x) * 256;

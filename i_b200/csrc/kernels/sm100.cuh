@@ -105,6 +105,27 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, A
   return ok != 0;
 }
 
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it in the stream is still running.  It must
+// execute grid_dependency_wait() before it touches anything that kernel wrote;
+// the earlier kernel lets it start early with trigger_dependent_launch() (all of
+// its CTAs must have executed that, or exited).  Without the attribute both are
+// no-ops.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void trigger_dependent_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Hint: bring [ptr, ptr + bytes) into L2 (16-byte aligned, multiple of 16 bytes).
+__device__ __forceinline__ void prefetch_l2_bulk(const void* ptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(ptr)),
+               "r"(bytes)
+               : "memory");
+}
+
 // ---- TMA ------------------------------------------------------------------
 
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
