@@ -31,16 +31,6 @@ bool fuse_always() {
   return env && std::string(env) == "always";
 }
 
-bool supported(Op op) {
-  switch (op) {
-    case Op::Add: case Op::Mul: case Op::Sub: case Op::Div:
-    case Op::Max: case Op::Min: case Op::Pow: case Op::Log:
-      return true;
-    default:
-      return false;
-  }
-}
-
 bool is_iota(const std::vector<size_t>& v, size_t n) {
   if (v.size() != n) return false;
   for (size_t i = 0; i < n; ++i)
@@ -94,9 +84,6 @@ std::optional<std::string> basic_steps(Builder& b) {
   b.alive.assign(g.nodes.size(), true);
   for (size_t n = 0; n < g.nodes.size(); ++n) {
     const Node& node = g.nodes[n].inner;
-    if (!supported(node.op))
-      return lower_error(std::string("operator `") + op_name(node.op) +
-                         "` is outside the B200 target's hot path (supported: + * - / > < ^ $)");
     for (size_t i = 0; i < node.inputs.size(); ++i)
       if (g.nodes[n].inputs[i].is_input && node.compute_sites[i])
         return lower_error("node " + std::to_string(n) + " input " + std::to_string(i) +

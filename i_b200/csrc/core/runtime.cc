@@ -69,7 +69,17 @@ int op_code(Op op) {
     case Op::Max: return IB_OP_MAX;
     case Op::Min: return IB_OP_MIN;
     case Op::Pow: return IB_OP_POW;
-    default: return IB_OP_LOG;
+    case Op::Log: return IB_OP_LOG;
+    case Op::Gt: return IB_OP_GT;
+    case Op::Ge: return IB_OP_GE;
+    case Op::Lt: return IB_OP_LT;
+    case Op::Le: return IB_OP_LE;
+    case Op::Eq: return IB_OP_EQ;
+    case Op::Ne: return IB_OP_NE;
+    case Op::And: return IB_OP_AND;
+    case Op::Or: return IB_OP_OR;
+    case Op::Xor: return IB_OP_XOR;
+    default: return IB_OP_NOT;
   }
 }
 

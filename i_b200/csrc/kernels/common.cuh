@@ -74,6 +74,15 @@ __device__ __forceinline__ float apply_binary(int op, float a, float b) {
     case IB_OP_MAX: return fmaxf(a, b);
     case IB_OP_MIN: return fminf(a, b);
     case IB_OP_POW: return powf(a, b);
+    case IB_OP_GT: return a > b ? 1.0f : 0.0f;
+    case IB_OP_GE: return a >= b ? 1.0f : 0.0f;
+    case IB_OP_LT: return a < b ? 1.0f : 0.0f;
+    case IB_OP_LE: return a <= b ? 1.0f : 0.0f;
+    case IB_OP_EQ: return a == b ? 1.0f : 0.0f;
+    case IB_OP_NE: return a != b ? 1.0f : 0.0f;
+    case IB_OP_AND: return (a != 0.0f && b != 0.0f) ? 1.0f : 0.0f;
+    case IB_OP_OR: return (a != 0.0f || b != 0.0f) ? 1.0f : 0.0f;
+    case IB_OP_XOR: return ((a != 0.0f) != (b != 0.0f)) ? 1.0f : 0.0f;
     default: return logf(a);  // IB_OP_LOG: the C backend drops the second operand
   }
 }
@@ -87,6 +96,16 @@ __device__ __forceinline__ float apply_unary(int op, float x) {
     case IB_OP_MAX: return fmaxf(0.0f, x);
     case IB_OP_MIN: return fminf(0.0f, x);
     case IB_OP_POW: return exp_e32_fast(x);
+    case IB_OP_GT: return x > 0.0f ? 1.0f : 0.0f;
+    case IB_OP_GE: return x >= 0.0f ? 1.0f : 0.0f;
+    case IB_OP_LT: return x < 0.0f ? 1.0f : 0.0f;
+    case IB_OP_LE: return x <= 0.0f ? 1.0f : 0.0f;
+    case IB_OP_EQ: return x == 0.0f ? 1.0f : 0.0f;
+    case IB_OP_NE: return x != 0.0f ? 1.0f : 0.0f;
+    case IB_OP_AND:
+    case IB_OP_OR:
+    case IB_OP_XOR: return x;
+    case IB_OP_NOT: return x == 0.0f ? 1.0f : 0.0f;
     default: return logf(x);
   }
 }
@@ -96,6 +115,9 @@ __device__ __forceinline__ float reduce_identity(int op) {
     case IB_OP_ADD: return 0.0f;
     case IB_OP_MUL: return 1.0f;
     case IB_OP_MAX: return -CUDART_INF_F;
+    case IB_OP_AND: return 1.0f;
+    case IB_OP_OR:
+    case IB_OP_XOR: return 0.0f;
     default: return CUDART_INF_F;  // IB_OP_MIN
   }
 }
@@ -105,7 +127,10 @@ __device__ __forceinline__ float fold(float a, float b) {
   if (OP == IB_OP_ADD) return a + b;
   if (OP == IB_OP_MUL) return a * b;
   if (OP == IB_OP_MAX) return fmaxf(a, b);
-  return fminf(a, b);
+  if (OP == IB_OP_MIN) return fminf(a, b);
+  // Logic folds work on truth values; every element passes through at least one
+  // fold with the identity, so results are always 0 or 1 as in the serial form.
+  return apply_binary(OP, a, b);
 }
 
 template <int OP>

@@ -211,6 +211,16 @@ int launch_strided(const float* a, const float* b, float* y, size_t n, const Str
     case IB_OP_MIN: return CALL(IB_OP_MIN);                        \
     case IB_OP_POW: return CALL(IB_OP_POW);                        \
     case IB_OP_LOG: return CALL(IB_OP_LOG);                        \
+    case IB_OP_GT: return CALL(IB_OP_GT);                          \
+    case IB_OP_GE: return CALL(IB_OP_GE);                          \
+    case IB_OP_LT: return CALL(IB_OP_LT);                          \
+    case IB_OP_LE: return CALL(IB_OP_LE);                          \
+    case IB_OP_EQ: return CALL(IB_OP_EQ);                          \
+    case IB_OP_NE: return CALL(IB_OP_NE);                          \
+    case IB_OP_AND: return CALL(IB_OP_AND);                        \
+    case IB_OP_OR: return CALL(IB_OP_OR);                          \
+    case IB_OP_XOR: return CALL(IB_OP_XOR);                        \
+    case IB_OP_NOT: return CALL(IB_OP_NOT);                        \
     default: return ib::fail("unknown operator code");             \
   }
 
@@ -227,6 +237,7 @@ extern "C" int ib_map_binary(int op, int mode, const float* a, const float* b, f
                              size_t rows, size_t cols, void* stream) {
   if (rows == 0 || cols == 0) return 0;
   if (!a || !b || !y) return ib::fail("ib_map_binary: null pointer");
+  if (op == IB_OP_NOT) return ib::fail("ib_map_binary: operator `!!` has one operand");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define CALL(OP) ib::dispatch_mode<OP>(mode, a, b, y, rows, cols, s)
   IB_DISPATCH_OP(op, CALL)
@@ -237,6 +248,7 @@ extern "C" int ib_map_strided(int op, const float* a, const float* b, float* y, 
                               const size_t* extent, const ptrdiff_t* stride_a,
                               const ptrdiff_t* stride_b, void* stream) {
   if (rank < 0 || rank > IB_MAX_RANK) return ib::fail("ib_map_strided: rank out of range");
+  if (b && op == IB_OP_NOT) return ib::fail("ib_map_strided: operator `!!` has one operand");
   if (!a || !y || (rank > 0 && (!extent || !stride_a)) || (b && rank > 0 && !stride_b))
     return ib::fail("ib_map_strided: null pointer");
   ib::StridedArgs args{};

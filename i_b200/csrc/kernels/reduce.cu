@@ -1,4 +1,4 @@
-// Row reductions `+ * > <` over the last axis, and a general strided fold.
+// Row reductions `+ * > < && || ^^` over the last axis, and a general strided fold.
 //
 // Identities and accumulate form follow the reference
 // (compiler/src/lower/exec_plan_to_module.rs:592-603, 354-367): the fold starts
@@ -153,7 +153,10 @@ int launch_strided(const float* x, float* y, size_t n_out, size_t n_red, const F
     case IB_OP_MUL: return CALL(IB_OP_MUL);                                    \
     case IB_OP_MAX: return CALL(IB_OP_MAX);                                    \
     case IB_OP_MIN: return CALL(IB_OP_MIN);                                    \
-    default: return ib::fail("operator is not reducible (only + * > < fold)"); \
+    case IB_OP_AND: return CALL(IB_OP_AND);                                    \
+    case IB_OP_OR: return CALL(IB_OP_OR);                                      \
+    case IB_OP_XOR: return CALL(IB_OP_XOR);                                    \
+    default: return ib::fail("operator is not reducible (only + * > < && || ^^ fold)"); \
   }
 
 extern "C" int ib_reduce_rows(int op, const float* x, float* y, size_t rows, size_t cols,

@@ -19,7 +19,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "libi_oracle.so")
 _REF = os.path.join(_HERE, "_ref", "libref_flashattn.so")
 
-OPS = {"+": 0, "*": 1, "-": 2, "/": 3, ">": 4, "<": 5, "^": 6, "$": 7}
+OPS = {"+": 0, "*": 1, "-": 2, "/": 3, ">": 4, "<": 5, "^": 6, "$": 7,
+       ">>": 8, ">=": 9, "<<": 10, "<=": 11, "==": 12, "!=": 13,
+       "&&": 14, "||": 15, "^^": 16, "!!": 17}
 
 _fp = ctypes.POINTER(ctypes.c_float)
 _sz = ctypes.c_size_t

@@ -36,7 +36,11 @@
 
 enum {
   IO_ADD = 0, IO_MUL = 1, IO_SUB = 2, IO_DIV = 3,
-  IO_MAX = 4, IO_MIN = 5, IO_POW = 6, IO_LOG = 7
+  IO_MAX = 4, IO_MIN = 5, IO_POW = 6, IO_LOG = 7,
+  /* comparisons and logic: C operators on floats, the int result stored as 0.0f / 1.0f
+   * (compiler/src/backends/c/expr.rs:136-146, xor at :331-339) */
+  IO_GT = 8, IO_GE = 9, IO_LT = 10, IO_LE = 11, IO_EQ = 12, IO_NE = 13,
+  IO_AND = 14, IO_OR = 15, IO_XOR = 16, IO_NOT = 17
 };
 
 static inline size_t io_ceil_div(size_t n, size_t f) { return (n + f - 1) / f; }
@@ -51,6 +55,15 @@ static inline float io_binary(int op, float a, float b) {
     case IO_MIN: return fminf(a, b);
     case IO_POW: return powf(a, b);
     case IO_LOG: return logf(a); /* second operand dropped by the C backend */
+    case IO_GT: return (float)(a > b);
+    case IO_GE: return (float)(a >= b);
+    case IO_LT: return (float)(a < b);
+    case IO_LE: return (float)(a <= b);
+    case IO_EQ: return (float)(a == b);
+    case IO_NE: return (float)(a != b);
+    case IO_AND: return (float)(a && b);
+    case IO_OR: return (float)(a || b);
+    case IO_XOR: return (float)(((a) != 0.0f) != ((b) != 0.0f));
   }
   return NAN;
 }
@@ -64,6 +77,16 @@ static inline float io_unary(int op, float x) {
     case IO_MIN: return fminf(0.0f, x);
     case IO_POW: return powf(IO_E, x);
     case IO_LOG: return logf(x);
+    /* unary forms, compiler/src/lower/exec_plan_to_module.rs:613-637: comparisons
+     * compare with 0.0f, and / or / xor copy their operand, not is `!x` */
+    case IO_GT: return (float)(x > 0.0f);
+    case IO_GE: return (float)(x >= 0.0f);
+    case IO_LT: return (float)(x < 0.0f);
+    case IO_LE: return (float)(x <= 0.0f);
+    case IO_EQ: return (float)(x == 0.0f);
+    case IO_NE: return (float)(x != 0.0f);
+    case IO_AND: case IO_OR: case IO_XOR: return x;
+    case IO_NOT: return (float)(!x);
   }
   return NAN;
 }
@@ -74,6 +97,8 @@ static inline float io_identity(int op) {
     case IO_MUL: return 1.0f;
     case IO_MAX: return -INFINITY;
     case IO_MIN: return INFINITY;
+    case IO_AND: return 1.0f;   /* exec_plan_to_module.rs:592-603 */
+    case IO_OR: case IO_XOR: return 0.0f;
   }
   return NAN;
 }

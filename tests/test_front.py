@@ -137,11 +137,22 @@ def test_graph_input_cannot_be_staged(ilang):
     assert "node 0 input 0 is a graph input with a compute site" in str(info.value)
 
 
-def test_ops_outside_the_hot_path_are_errors(ilang):
-    for src in (">>ij~ij", "ij==ij~ij", "!!ij~ij", "&&ij~i"):
+def test_comparisons_and_logic_compile(ilang):
+    # compiler/src/front/parser.rs:270-279, 374-413: every operator token in unary and binary form.
+    for tok in (">>", ">=", "<<", "<=", "==", "!=", "&&", "||", "^^"):
+        for src in (tok + "ij~ij", "ij" + tok + "ij~ij", "ij" + tok + "j~ij"):
+            assert "ib_map" in ilang.i(src)._code()
+    assert "ib_map" in ilang.i("!!ij~ij")._code()
+    for tok in ("&&", "||", "^^"):
+        assert "ib_reduce" in ilang.i(tok + "ij~i")._code()
+
+
+def test_not_and_comparisons_do_not_reduce(ilang):
+    # compiler/src/check/component.rs:407-412
+    for src, name in ((">>ij~i", "Gt"), ("==ij~i", "Eq"), ("!!ij~i", "Not")):
         with pytest.raises(RuntimeError) as info:
             ilang.i(src)._compile()
-        assert "outside the B200 target's hot path" in str(info.value)
+        assert name in str(info.value)
 
 
 # ---- wiring ---------------------------------------------------------------

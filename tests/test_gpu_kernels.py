@@ -108,6 +108,68 @@ def test_map_strided_transpose(lib, oracle, torch):
     assert np.array_equal(y.cpu().numpy(), -x.T)
 
 
+LOGIC_BINARY = [">>", ">=", "<<", "<=", "==", "!=", "&&", "||", "^^"]
+
+
+def logic_values(shape, seed):
+    """Mostly small integers (so equal and zero operands are common), some NaN, inf and -0."""
+    rng = np.random.default_rng(seed)
+    x = rng.integers(-2, 3, size=shape).astype(np.float32)
+    special = rng.random(shape)
+    x[special < 0.03] = np.nan
+    x[(special >= 0.03) & (special < 0.05)] = np.inf
+    x[(special >= 0.05) & (special < 0.07)] = -0.0
+    return x
+
+
+@pytest.mark.parametrize("op", LOGIC_BINARY + ["!!"])
+@pytest.mark.parametrize("n", [1, 1024, 100003])
+def test_map_unary_comparisons_and_logic(lib, oracle, torch, op, n):
+    x = logic_values((n,), 11)
+    d = dev(torch, x)
+    y = torch.empty_like(d)
+    ok(lib, lib.ib_map_unary(oracle.OPS[op], d.data_ptr(), y.data_ptr(), n, None))
+    assert np.array_equal(y.cpu().numpy(), oracle.map_unary(op, x), equal_nan=True)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("op", LOGIC_BINARY)
+def test_map_binary_comparisons_and_logic(lib, oracle, torch, mode, op):
+    rows, cols = 37, 52 if mode % 2 == 0 else 51
+    full = logic_values((rows, cols), 12)
+    row_v, col_v = logic_values((rows,), 13), logic_values((cols,), 14)
+    a = full if mode in (0, 1, 3) else (row_v if mode == 2 else col_v)
+    b = logic_values((rows, cols), 15) if mode in (0, 2, 4) else (row_v if mode == 1 else col_v)
+    da, db = dev(torch, a), dev(torch, b)
+    y = torch.empty(rows, cols, device="cuda")
+    ok(lib, lib.ib_map_binary(oracle.OPS[op], mode, da.data_ptr(), db.data_ptr(), y.data_ptr(),
+                              rows, cols, None))
+    assert np.array_equal(y.cpu().numpy(), oracle.map_binary(op, a, b, mode))
+
+
+def test_map_binary_rejects_not(lib, oracle, torch):
+    x = torch.zeros(4, device="cuda")
+    assert lib.ib_map_binary(oracle.OPS["!!"], 0, x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 4,
+                             None) == -1
+    assert "one operand" in last_error(lib)
+
+
+@pytest.mark.parametrize("op", ["&&", "||", "^^"])
+@pytest.mark.parametrize("shape", [(16, 8), (100, 257), (7, 5000), (3, 4096), (5, 1), (4, 0)])
+def test_reduce_rows_logic(lib, oracle, torch, op, shape):
+    rng = np.random.default_rng(16)
+    x = logic_values(shape, 17)
+    # rows that are all true, all false, and mixed
+    x[rng.random(shape) < (0.9 if op == "&&" else 0.0)] = 3.0
+    if op == "||":
+        x[rng.random(shape) < 0.98] = 0.0
+    d = dev(torch, x) if x.size else torch.empty(shape, device="cuda")
+    y = torch.empty(shape[0], device="cuda")
+    ptr = d.data_ptr() if x.size else None
+    ok(lib, lib.ib_reduce_rows(oracle.OPS[op], ptr, y.data_ptr(), shape[0], shape[1], None))
+    assert np.array_equal(y.cpu().numpy(), oracle.reduce_rows(op, x))
+
+
 # ---- reductions -----------------------------------------------------------
 
 @pytest.mark.parametrize("op", list("+*><"))

@@ -60,6 +60,27 @@ def test_mlp_intent(ilang):
     np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
 
 
+def test_comparison_and_logic_components(ilang):
+    # Operators of compiler/src/front/parser.rs:270-279 through whole components: a causal-style
+    # mask built from comparisons, a column-wise "any", and not-of-a-reduction.
+    i = ilang.i
+    x = rand((33, 20), 1)
+    x[x < -1.0] = 0.0
+    thr = rand((20,), 2)
+    mask = i("ij>>j~ij").exec_numpy(x, thr)                       # 1 where x > thr[j]
+    assert np.array_equal(mask, (x > thr[None, :]).astype(np.float32))
+    sel = i("ij*ij~ij").exec_numpy(mask, x)                       # select by mask
+    assert np.array_equal(sel, np.where(x > thr[None, :], x, 0.0).astype(np.float32))
+    any_col = i("||ij~j").exec_numpy(x)
+    assert np.array_equal(any_col, (x != 0).any(axis=0).astype(np.float32))
+    none_row = (i("||ij~i") >> i("!!i~i")).exec_numpy(x)
+    assert np.array_equal(none_row, (~(x != 0).any(axis=1)).astype(np.float32))
+    parity = i("^^ij~i").exec_numpy(x)
+    assert np.array_equal(parity, ((x != 0).sum(axis=1) % 2).astype(np.float32))
+    both = i("ij&&ij~ij").exec_numpy(x, mask)
+    assert np.array_equal(both, ((x != 0) & (mask != 0)).astype(np.float32))
+
+
 @pytest.mark.parametrize("src,fn", [(">ij~i", np.max), ("<ij~i", np.min), ("+ij~i", np.sum)])
 def test_row_reductions(ilang, src, fn):
     # test.py:103-128

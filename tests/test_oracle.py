@@ -87,6 +87,45 @@ def test_unary_defaults(oracle):
     np.testing.assert_allclose(oracle.map_unary("$", x[3:]), np.log(x[3:].astype(np.float64)), rtol=2e-7)
 
 
+LOGIC_VALUES = np.array([-2.0, -0.0, 0.0, 0.5, 3.0, np.nan, np.inf, -np.inf], dtype=np.float32)
+
+
+def test_comparisons_and_logic(oracle):
+    # C operators on floats, result stored as 0.0f / 1.0f (compiler/src/backends/c/expr.rs:136-146,
+    # xor :331-339); unary forms compiler/src/lower/exec_plan_to_module.rs:613-637.
+    a = np.repeat(LOGIC_VALUES, LOGIC_VALUES.size).reshape(LOGIC_VALUES.size, -1)
+    b = np.ascontiguousarray(a.T)
+    ta, tb = a != 0, b != 0                    # NaN is true
+    with np.errstate(invalid="ignore"):
+        expect = {">>": a > b, ">=": a >= b, "<<": a < b, "<=": a <= b, "==": a == b, "!=": a != b,
+                  "&&": ta & tb, "||": ta | tb, "^^": ta ^ tb}
+        for op, want in expect.items():
+            assert np.array_equal(oracle.map_binary(op, a, b), want.astype(np.float32)), op
+        x = LOGIC_VALUES
+        unary = {">>": x > 0, ">=": x >= 0, "<<": x < 0, "<=": x <= 0, "==": x == 0, "!=": x != 0,
+                 "!!": x == 0}
+        for op, want in unary.items():
+            assert np.array_equal(oracle.map_unary(op, x), want.astype(np.float32)), op
+    for op in ("&&", "||", "^^"):              # unary logic copies its operand
+        assert np.array_equal(oracle.map_unary(op, x), x, equal_nan=True), op
+
+
+def test_logic_reductions(oracle):
+    # identities 1, 0, 0 (exec_plan_to_module.rs:592-603); dst = dst OP x over ascending columns.
+    x = (rand((32, 9), 5) > 0.3).astype(np.float32) * rand((32, 9), 6)
+    t = x != 0
+    assert np.array_equal(oracle.reduce_rows("&&", x), t.all(axis=1).astype(np.float32))
+    assert np.array_equal(oracle.reduce_rows("||", x), t.any(axis=1).astype(np.float32))
+    assert np.array_equal(oracle.reduce_rows("^^", x), (t.sum(axis=1) % 2).astype(np.float32))
+    empty = np.zeros((3, 0), dtype=np.float32)
+    assert np.array_equal(oracle.reduce_rows("&&", empty), np.ones(3, np.float32))
+    assert np.array_equal(oracle.reduce_rows("||", empty), np.zeros(3, np.float32))
+    assert np.array_equal(oracle.reduce_rows("^^", empty), np.zeros(3, np.float32))
+    one = np.array([[2.5], [0.0]], dtype=np.float32)      # a single element still becomes 0 / 1
+    assert np.array_equal(oracle.reduce_rows("&&", one), np.array([1, 0], np.float32))
+    assert np.array_equal(oracle.reduce_rows("^^", one), np.array([1, 0], np.float32))
+
+
 def test_binary_log_drops_second_operand(oracle):
     # compiler/src/backends/c/expr.rs:136, 319-321.
     a = np.array([[1.0, 2.0], [3.0, 4.0]], dtype=np.float32)
