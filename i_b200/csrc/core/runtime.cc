@@ -533,6 +533,212 @@ cudaStream_t thread_stream() {
   return s;
 }
 
+// ---- host operands: copies overlapped with the kernels -----------------------
+//
+// A program that is one fused attention step, called with host buffers, spends
+// more time on the PCIe copies than in the kernel.  Query rows are independent
+// and so are heads (ilang-python/annotated-flashattn.c:92-127, 240-307), so the
+// call is cut into blocks and run as a three-stage pipeline on three streams:
+// upload block c+1 | attend block c | download block c-1.
+//   one head:  K and V go up first and are prepared once; blocks are ranges of
+//              query rows (ib_attention_prepare / ib_attention_run);
+//   many heads: blocks are ranges of heads, each a complete ib_attention.
+struct SideStreams {
+  cudaStream_t in = nullptr, out = nullptr;
+  std::vector<cudaEvent_t> events;
+  size_t used = 0;
+  cudaEvent_t event() {
+    if (used == events.size()) {
+      cudaEvent_t e = nullptr;
+      if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+      events.push_back(e);
+    }
+    return events[used++];
+  }
+};
+
+SideStreams* side_streams() {
+  thread_local std::map<int, SideStreams> per_device;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  SideStreams& s = per_device[dev];
+  if (!s.in && cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+  if (!s.out && cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking) != cudaSuccess)
+    return nullptr;
+  s.used = 0;
+  return &s;
+}
+
+size_t host_pipeline_blocks() {
+  static const size_t blocks = [] {
+    const char* v = std::getenv("I_B200_HOST_BLOCKS");     // 1 switches the pipeline off
+    long n = v ? std::atol(v) : 4;
+    return static_cast<size_t>(n < 1 ? 1 : (n > 64 ? 64 : n));
+  }();
+  return blocks;
+}
+
+constexpr size_t kPipelineMinBytes = 4u << 20;   // below this the copies are too short to split
+
+// Returns 1 when the call is not of this form (the caller takes the plain path),
+// 0 on success, -1 on error.  All pointers are host memory.
+int pipelined_host_attention(const i_program* program, const ShapeTable& shapes,
+                             const i_tensor* inputs, size_t input_count, i_tensor_mut* outputs,
+                             size_t output_count, cudaStream_t stream) {
+  const Plan& plan = program->plan;
+  if (plan.steps.size() != 1 || plan.steps[0].kind != StepKind::Attention) return 1;
+  if (output_count != 1 || plan.outputs.size() != 1 || plan.outputs[0].is_input) return 1;
+  const Step& step = plan.steps[0];
+  if (plan.outputs[0].index != step.out.buffer.index) return 1;
+  for (int a = 0; a < 3; ++a)
+    if (!step.in[a].buffer.is_input || step.in[a].buffer.index >= input_count) return 1;
+  const size_t iq = step.in[0].buffer.index, ik = step.in[1].buffer.index,
+               iv = step.in[2].buffer.index;
+  if (iq == ik || iq == iv || ik == iv) return 1;
+  AttentionDims dims;
+  Shape oshape;
+  std::string err;
+  if (!attention_dims(step, shapes, &dims, &oshape, &err)) return 1;   // reported by the plain path
+  const int precision = program->precision.load();
+  if (!ib_attention_uses_tensor_arm(dims.batch, dims.nq, dims.nk, dims.d, dims.dv, precision)) return 1;
+  const size_t q_floats = dims.nq * dims.d, k_floats = dims.nk * dims.d, v_floats = dims.nk * dims.dv,
+               o_floats = dims.nq * dims.dv;                           // per head
+  if (dims.batch * (q_floats + k_floats + v_floats + o_floats) * sizeof(float) < kPipelineMinBytes)
+    return 1;
+  size_t blocks = host_pipeline_blocks();
+  const bool by_rows = dims.batch == 1;
+  size_t rows_per_block = 0, heads_per_block = 0;
+  if (by_rows) {
+    const size_t tiles = (dims.nq + 127) / 128;
+    blocks = std::min(blocks, tiles / 8);                  // at least 1024 rows a block
+    if (blocks < 2) return 1;
+    rows_per_block = (tiles + blocks - 1) / blocks * 128;
+    blocks = (dims.nq + rows_per_block - 1) / rows_per_block;
+  } else {
+    blocks = std::min(blocks * 2, dims.batch);
+    if (blocks < 2) return 1;
+    heads_per_block = (dims.batch + blocks - 1) / blocks;
+    blocks = (dims.batch + heads_per_block - 1) / heads_per_block;
+  }
+  for (size_t i : {iq, ik, iv})
+    if (!inputs[i].data) {
+      set_error("input " + std::to_string(i) + " has null data");
+      return -1;
+    }
+  if (!outputs[0].data) {
+    set_error("output 0 has null data");
+    return -1;
+  }
+  SideStreams* side = side_streams();
+  if (!side) return 1;
+
+  const float* hq = inputs[iq].data;
+  const float* hk = inputs[ik].data;
+  const float* hv = inputs[iv].data;
+  float* ho = outputs[0].data;
+  DeviceBuffers dev;
+  dev.stream = stream;
+  float* dq = dev.alloc(dims.batch * q_floats * sizeof(float), &err);
+  float* dk = dev.alloc(dims.batch * k_floats * sizeof(float), &err);
+  float* dv = dev.alloc(dims.batch * v_floats * sizeof(float), &err);
+  float* dout = dev.alloc(dims.batch * o_floats * sizeof(float), &err);
+  const size_t block_heads = by_rows ? 1 : heads_per_block;
+  const size_t block_rows = by_rows ? rows_per_block : dims.nq;
+  const size_t prep_bytes =
+      by_rows ? ib_attention_prepare_bytes(1, dims.nk, dims.d, dims.dv, precision) : 0;
+  const size_t ws_bytes =
+      by_rows ? ib_attention_run_workspace_bytes(1, block_rows, dims.nk, dims.dv)
+              : ib_attention_workspace_bytes(block_heads, dims.nq, dims.nk, dims.d, dims.dv,
+                                             dims.v_kmajor, precision);
+  float* prepared = by_rows ? dev.alloc(prep_bytes, &err) : nullptr;
+  float* ws = dev.alloc(ws_bytes, &err);
+  int rc = 0;
+  if (!dq || !dk || !dv || !dout || !ws || (by_rows && !prepared)) {
+    set_error(err);
+    rc = -1;
+  }
+  auto ok = [&](cudaError_t e, const char* what) {
+    if (e == cudaSuccess || rc) return;
+    set_error(std::string(what) + ": " + cudaGetErrorString(e));
+    rc = -1;
+  };
+  auto signal = [&](cudaStream_t from, cudaStream_t to, const char* what) {
+    cudaEvent_t e = side->event();
+    if (!e) {
+      ok(cudaErrorMemoryAllocation, what);
+      return;
+    }
+    ok(cudaEventRecord(e, from), what);
+    ok(cudaStreamWaitEvent(to, e, 0), what);
+  };
+  const size_t f = sizeof(float);
+  if (rc == 0) {
+    // The buffers were allocated in `stream` order; the copy streams start after that point.
+    signal(stream, side->in, "ordering the upload stream");
+    signal(stream, side->out, "ordering the download stream");
+    if (by_rows) {
+      ok(cudaMemcpyAsync(dk, hk, k_floats * f, cudaMemcpyHostToDevice, side->in), "uploading K");
+      ok(cudaMemcpyAsync(dv, hv, v_floats * f, cudaMemcpyHostToDevice, side->in), "uploading V");
+      signal(side->in, stream, "ordering the preparation");
+      if (rc == 0)
+        rc = ib_attention_prepare(dk, dv, 1, dims.nk, dims.d, dims.dv, dims.v_kmajor, precision,
+                                  prepared, prep_bytes, stream);
+    }
+    for (size_t c = 0; rc == 0 && c < blocks; ++c) {
+      if (by_rows) {
+        const size_t r0 = c * block_rows, rows = std::min(block_rows, dims.nq - r0);
+        ok(cudaMemcpyAsync(dq + r0 * dims.d, hq + r0 * dims.d, rows * dims.d * f,
+                           cudaMemcpyHostToDevice, side->in), "uploading Q");
+        signal(side->in, stream, "ordering a query block");
+        if (rc == 0)
+          rc = ib_attention_run(dq + r0 * dims.d, prepared, dout + r0 * dims.dv, 1, rows, dims.nk,
+                                dims.d, dims.dv, precision, ws, ws_bytes, stream);
+        signal(stream, side->out, "ordering a download");
+        ok(cudaMemcpyAsync(ho + r0 * dims.dv, dout + r0 * dims.dv, rows * dims.dv * f,
+                           cudaMemcpyDeviceToHost, side->out), "downloading O");
+      } else {
+        const size_t h0 = c * block_heads, heads = std::min(block_heads, dims.batch - h0);
+        ok(cudaMemcpyAsync(dk + h0 * k_floats, hk + h0 * k_floats, heads * k_floats * f,
+                           cudaMemcpyHostToDevice, side->in), "uploading K");
+        ok(cudaMemcpyAsync(dv + h0 * v_floats, hv + h0 * v_floats, heads * v_floats * f,
+                           cudaMemcpyHostToDevice, side->in), "uploading V");
+        ok(cudaMemcpyAsync(dq + h0 * q_floats, hq + h0 * q_floats, heads * q_floats * f,
+                           cudaMemcpyHostToDevice, side->in), "uploading Q");
+        signal(side->in, stream, "ordering a block of heads");
+        if (rc == 0)
+          rc = ib_attention(dq + h0 * q_floats, dk + h0 * k_floats, dv + h0 * v_floats,
+                            dout + h0 * o_floats, heads, dims.nq, dims.nk, dims.d, dims.dv,
+                            dims.v_kmajor, precision, step.hint.col_split, ws, ws_bytes, stream);
+        signal(stream, side->out, "ordering a download");
+        ok(cudaMemcpyAsync(ho + h0 * o_floats, dout + h0 * o_floats, heads * o_floats * f,
+                           cudaMemcpyDeviceToHost, side->out), "downloading O");
+      }
+    }
+  }
+  // Join both copy streams into `stream` (also after an error: the buffers are
+  // freed in `stream` order and must outlive every copy already queued).
+  {
+    cudaEvent_t a = side->event(), b = side->event();
+    if (a && b) {
+      cudaEventRecord(a, side->in);
+      cudaEventRecord(b, side->out);
+      cudaStreamWaitEvent(stream, a, 0);
+      cudaStreamWaitEvent(stream, b, 0);
+    } else {
+      cudaStreamSynchronize(side->in);
+      cudaStreamSynchronize(side->out);
+    }
+  }
+  dev.release();
+  cudaError_t sync = cudaStreamSynchronize(stream);
+  if (rc == 0 && sync != cudaSuccess) {
+    set_error(std::string("CUDA error while running the program: ") + cudaGetErrorString(sync));
+    rc = -1;
+  }
+  if (rc == 0) rc = check_device_status("i_exec_into", stream);
+  return rc;
+}
+
 // Synchronous run accepting host and/or device pointers.
 int exec_any(const i_program* program, const i_tensor* inputs, size_t input_count,
              i_tensor_mut* outputs, size_t output_count) {
@@ -548,6 +754,16 @@ int exec_any(const i_program* program, const i_tensor* inputs, size_t input_coun
     return -1;
   }
   cudaStream_t stream = thread_stream();
+  {
+    bool all_host = true;
+    for (size_t i = 0; i < input_count; ++i) all_host = all_host && !is_device_pointer(inputs[i].data);
+    for (size_t o = 0; o < output_count; ++o) all_host = all_host && !is_device_pointer(outputs[o].data);
+    if (all_host) {
+      const int piped = pipelined_host_attention(program, shapes, inputs, input_count, outputs,
+                                                 output_count, stream);
+      if (piped <= 0) return piped;
+    }
+  }
   DeviceBuffers staging;
   staging.stream = stream;
   std::vector<const float*> in_ptrs(input_count);

@@ -756,7 +756,7 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      bool bf16, float* partials, cudaStream_t s) {
+                      bool bf16, bool follows_prepare, float* partials, cudaStream_t s) {
   if (batch == 0 || nq == 0) return 0;
   if (nk == 0) return fail("ib_attention: no keys");
   if (nq >= (1u << 30) || nk >= (1u << 30) || batch >= (1u << 20))
@@ -823,7 +823,9 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
 
   // Both launches carry the programmatic-serialization attribute: the attention
   // kernel's set-up and its Q load run under the tail of the preparation kernel,
-  // and the merge kernel's launch latency under the attention kernel.
+  // and the merge kernel's launch latency under the attention kernel.  The
+  // attention kernel reads Q before it waits for its predecessor, so it only gets
+  // the attribute when that predecessor is this library's preparation kernel.
   cudaLaunchAttribute overlap{};
   overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   overlap.val.programmaticStreamSerializationAllowed = 1;
@@ -833,7 +835,7 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = s;
   cfg.attrs = &overlap;
-  cfg.numAttrs = g_dependent_launch ? 1 : 0;
+  cfg.numAttrs = g_dependent_launch && follows_prepare ? 1 : 0;
   cudaError_t launched;
   if (bf16 && p.prof)
     launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Kind::BF16>, map_k, map_vt, p);
@@ -850,6 +852,7 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   if (tail_units > 0 && !(p.iters_rem == 0 && p.iters_base % p.kv_tiles == 0)) {
     CombineArgs a{p.part_o, p.part_m, p.part_l, o, p.nq, p.dv, p.q_tiles, p.kv_tiles, ctas,
                   p.full_waves * ctas, p.iters_base, p.iters_rem};
+    cfg.numAttrs = g_dependent_launch ? 1 : 0;
     cfg.gridDim = dim3(static_cast<unsigned>(tail_units * 8));
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = 0;

@@ -39,6 +39,61 @@ bool attention_shape_ok(size_t d, size_t dv) {
   return d % 4 == 0 && d >= 4 && d <= 128 && dv >= 1 && dv <= 128;
 }
 
+// The attention kernel's K and V operands: rounded (TF32) or converted (BF16)
+// copies, V transposed to [dv][keys].
+struct PreparedKV {
+  const void* k = nullptr;
+  const void* vt = nullptr;
+  size_t d_pitch = 0, nk_pitch = 0;
+  bool bf16 = false;
+};
+
+size_t prepared_kv_bytes(size_t batch, size_t nk, size_t d, size_t dv, bool bf16) {
+  if (bf16)
+    return carve_bytes((batch * nk * round_up(d, 8) + 1) / 2) +
+           carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2);
+  return carve_bytes(batch * nk * d) + carve_bytes(batch * dv * round_up(nk, 4));
+}
+
+// Carves the two copies out of `ws`; with `fill` it also launches the kernels that write them.
+int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t d, size_t dv,
+                bool v_kmajor, bool bf16, bool fill, Carver& ws, PreparedKV* out, cudaStream_t s) {
+  const char* small = "ib_attention: workspace too small (see the matching *_bytes function)";
+  out->bf16 = bf16;
+  if (bf16) {
+    // Opt-in: bf16 operands (round to nearest even), fp32 scores, sums and outputs.
+    out->d_pitch = round_up(d, 8);
+    out->nk_pitch = round_up(nk, 8);
+    float* k16 = ws.take((batch * nk * out->d_pitch + 1) / 2);
+    float* vt16 = ws.take((batch * dv * out->nk_pitch + 1) / 2);
+    if (!k16 || !vt16) return fail(small);
+    out->k = k16;
+    out->vt = vt16;
+    if (!fill) return 0;
+    return prepare_attention_operands_bf16(k, k16, v, vt16, batch, nk, d, dv, out->d_pitch,
+                                           out->nk_pitch, v_kmajor, s);
+  }
+  // The tensor core truncates fp32 operands to TF32.  K and V are first rounded
+  // to nearest into workspace copies (V transposed to [dv][keys] on the way,
+  // the K-major layout the second contraction needs); the kernel rounds Q
+  // itself while moving it into tensor memory.
+  out->d_pitch = d;
+  out->nk_pitch = round_up(nk, 4);
+  float* kr = ws.take(batch * nk * d);
+  float* vt = ws.take(batch * dv * out->nk_pitch);
+  if (!kr || !vt) return fail(small);
+  out->k = kr;
+  out->vt = vt;
+  if (!fill) return 0;
+  const bool aligned = (reinterpret_cast<uintptr_t>(k) & 15u) == 0;
+  if (!v_kmajor && aligned)
+    return prepare_attention_operands(nullptr, nullptr, 0, k, kr, batch * nk * d, v, vt, batch, nk,
+                                      dv, out->nk_pitch, s);
+  if (int rc = round_tf32_rows(k, kr, batch * nk, d, d, d, nullptr, nullptr, 0, 0, 0, 0, s)) return rc;
+  if (!v_kmajor) return transpose_batched(v, vt, batch, nk, dv, out->nk_pitch, true, s);
+  return round_tf32_rows(v, vt, batch * dv, nk, nk, out->nk_pitch, nullptr, nullptr, 0, 0, 0, 0, s);
+}
+
 }  // namespace
 }  // namespace ib
 
@@ -133,16 +188,8 @@ extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t n
   if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
     // Rounded copy of K, V^T (rounded), and the KV-split partials; bf16 copies
     // are half the size, with pitches rounded up to 8 elements.
-    size_t bytes;
-    if (precision == IB_PRECISION_BF16) {
-      bytes = carve_bytes((batch * nk * round_up(d, 8) + 1) / 2);
-      bytes += carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2);
-    } else {
-      bytes = carve_bytes(batch * nk * d);
-      bytes += carve_bytes(batch * dv * round_up(nk, 4));
-    }
-    bytes += carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
-    return bytes;
+    return prepared_kv_bytes(batch, nk, d, dv, precision == IB_PRECISION_BF16) +
+           carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
   }
   // Unfused: S = Q K^T, softmax in place, O = S V.
   size_t bytes = carve_bytes(batch * nq * nk);
@@ -170,46 +217,15 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
   const bool tensor = wants_tensor(precision, flop);
 
   if (tensor && attention_shape_ok(d, dv)) {
-    // The tensor core truncates fp32 operands to TF32.  K and V are first rounded
-    // to nearest into workspace copies (V transposed to [dv][keys] on the way,
-    // the K-major layout the second contraction needs); the kernel rounds Q
-    // itself while moving it into tensor memory.
-    const char* small = "ib_attention: workspace too small (see ib_attention_workspace_bytes)";
-    if (precision == IB_PRECISION_BF16) {
-      // Opt-in: bf16 operands (round to nearest even), fp32 scores, sums and outputs.
-      const size_t d_pitch = round_up(d, 8), nk_pitch = round_up(nk, 8);
-      float* k16 = ws.take((batch * nk * d_pitch + 1) / 2);
-      float* vt16 = ws.take((batch * dv * nk_pitch + 1) / 2);
-      float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
-      if (!k16 || !vt16 || !partials) return fail(small);
-      if (int rc = prepare_attention_operands_bf16(k, k16, v, vt16, batch, nk, d, dv, d_pitch,
-                                                   nk_pitch, v_kmajor != 0, s))
-        return rc;
-      return attention_tcgen05(q, k16, vt16, o, batch, nq, nk, d, dv, d_pitch, nk_pitch, true,
-                               partials, s);
-    }
-    const size_t pitch = round_up(nk, 4);
-    float* kr = ws.take(batch * nk * d);
-    float* vt = ws.take(batch * dv * pitch);
-    if (!kr || !vt) return fail(small);
-    const bool aligned = (reinterpret_cast<uintptr_t>(k) & 15u) == 0;
-    if (!v_kmajor && aligned) {
-      if (int rc = prepare_attention_operands(nullptr, nullptr, 0, k, kr, batch * nk * d, v, vt,
-                                              batch, nk, dv, pitch, s))
-        return rc;
-    } else {
-      if (int rc = round_tf32_rows(k, kr, batch * nk, d, d, d, nullptr, nullptr, 0, 0, 0, 0, s))
-        return rc;
-      if (!v_kmajor) {
-        if (int rc = transpose_batched(v, vt, batch, nk, dv, pitch, true, s)) return rc;
-      } else {
-        if (int rc = round_tf32_rows(v, vt, batch * dv, nk, nk, pitch, nullptr, nullptr, 0, 0, 0, 0, s))
-          return rc;
-      }
-    }
+    PreparedKV kv;
+    if (int rc = prepared_kv(k, v, batch, nk, d, dv, v_kmajor != 0, precision == IB_PRECISION_BF16,
+                             true, ws, &kv, s))
+      return rc;
     float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
-    if (!partials) return fail(small);
-    return attention_tcgen05(q, kr, vt, o, batch, nq, nk, d, dv, d, pitch, false, partials, s);
+    if (!partials)
+      return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
+    return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch,
+                             kv.bf16, true, partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);
@@ -220,6 +236,66 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
   uint8_t* rest = ws.base ? ws.base + ws.used : nullptr;
   return ib_contract(scores, v, o, batch, nq, dv, nk, 1, v_kmajor, sub, rest,
                      workspace_bytes - ws.used, stream);
+}
+
+// ---- two-phase form: prepare K and V once, run query blocks against them ----
+
+extern "C" size_t ib_attention_prepare_bytes(size_t batch, size_t nk, size_t d, size_t dv,
+                                             int precision) {
+  return ib::prepared_kv_bytes(batch, nk, d, dv, precision == IB_PRECISION_BF16);
+}
+
+extern "C" int ib_attention_prepare(const float* k, const float* v, size_t batch, size_t nk,
+                                    size_t d, size_t dv, int v_kmajor, int precision,
+                                    void* prepared, size_t prepared_bytes, void* stream) {
+  using namespace ib;
+  if (batch == 0) return 0;
+  if (!k || !v) return fail("ib_attention_prepare: null pointer");
+  if (nk == 0 || !attention_shape_ok(d, dv))
+    return fail("ib_attention_prepare: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
+  if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
+    return fail("ib_attention_prepare: the two-phase form exists for the tensor arms (auto, tf32, bf16)");
+  if (reinterpret_cast<uintptr_t>(prepared) & 255u)
+    return fail("ib_attention_prepare: buffer must be 256-byte aligned");
+  Carver ws(prepared, prepared_bytes);
+  PreparedKV kv;
+  return prepared_kv(k, v, batch, nk, d, dv, v_kmajor != 0, precision == IB_PRECISION_BF16, true, ws,
+                     &kv, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t ib_attention_run_workspace_bytes(size_t batch, size_t nq, size_t nk, size_t dv) {
+  return ib::carve_bytes(ib::attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
+}
+
+extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, size_t batch,
+                                size_t nq, size_t nk, size_t d, size_t dv, int precision,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace ib;
+  if (batch == 0 || nq == 0) return 0;
+  if (!q || !prepared || !o) return fail("ib_attention_run: null pointer");
+  if (nk == 0 || !attention_shape_ok(d, dv))
+    return fail("ib_attention_run: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
+  if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
+    return fail("ib_attention_run: the two-phase form exists for the tensor arms (auto, tf32, bf16)");
+  if ((reinterpret_cast<uintptr_t>(prepared) | reinterpret_cast<uintptr_t>(workspace)) & 255u)
+    return fail("ib_attention_run: buffers must be 256-byte aligned");
+  const bool bf16 = precision == IB_PRECISION_BF16;
+  // Same carving as ib_attention_prepare, without touching the contents.
+  Carver held(const_cast<void*>(prepared), prepared_kv_bytes(batch, nk, d, dv, bf16));
+  PreparedKV kv;
+  if (int rc = prepared_kv(nullptr, nullptr, batch, nk, d, dv, false, bf16, false, held, &kv, nullptr))
+    return rc;
+  Carver ws(workspace, workspace_bytes);
+  float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
+  if (!partials)
+    return fail("ib_attention_run: workspace too small (see ib_attention_run_workspace_bytes)");
+  return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch, bf16,
+                           false, partials, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ib_attention_uses_tensor_arm(size_t batch, size_t nq, size_t nk, size_t d, size_t dv,
+                                            int precision) {
+  return ib::wants_tensor(precision, 4.0 * batch * nq * nk * d) && ib::attention_shape_ok(d, dv);
 }
 
 extern "C" int i_b200_set_reserved_sms(int n) {

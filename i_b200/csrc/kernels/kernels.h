@@ -65,10 +65,11 @@ int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv,
                                         int* ctas_out);
 // With bf16 = true, k and vt hold bf16 ([b][nk][d_pitch] and [b][dv][nk_pitch], pitches multiples
-// of 8) and the contractions run as kind::f16.
+// of 8) and the contractions run as kind::f16.  follows_prepare: the kernel before this call in
+// the stream is the one that wrote k and vt (the launch may then overlap its tail).
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      bool bf16, float* partials, cudaStream_t s);
+                      bool bf16, bool follows_prepare, float* partials, cudaStream_t s);
 // bf16 operand preparation: k16[b][r][d_pitch] = bf16(k), vt16[b][c][nk_pitch] = bf16(v^T);
 // pad columns are zeroed.
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,

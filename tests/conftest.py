@@ -62,6 +62,16 @@ def lib(ilang):
     lib.ib_attention.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, ci, ci, sz, vp, sz, vp]
     lib.ib_attention_workspace_bytes.argtypes = [sz, sz, sz, sz, sz, ci, ci]
     lib.ib_attention_workspace_bytes.restype = sz
+    lib.ib_attention_prepare_bytes.argtypes = [sz, sz, sz, sz, ci]
+    lib.ib_attention_prepare_bytes.restype = sz
+    lib.ib_attention_prepare.argtypes = [vp, vp, sz, sz, sz, sz, ci, ci, vp, sz, vp]
+    lib.ib_attention_prepare.restype = ci
+    lib.ib_attention_run_workspace_bytes.argtypes = [sz, sz, sz, sz]
+    lib.ib_attention_run_workspace_bytes.restype = sz
+    lib.ib_attention_run.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, ci, vp, sz, vp]
+    lib.ib_attention_run.restype = ci
+    lib.ib_attention_uses_tensor_arm.argtypes = [sz, sz, sz, sz, sz, ci]
+    lib.ib_attention_uses_tensor_arm.restype = ci
     for name in ("ib_map_unary", "ib_map_binary", "ib_map_strided", "ib_reduce_rows",
                  "ib_reduce_strided", "ib_row_softmax", "ib_contract", "ib_attention"):
         getattr(lib, name).restype = ci

@@ -413,6 +413,48 @@ def test_attention_tf32_batched_and_transposed_v(lib, oracle, torch):
         assert max_rel_to_peak(got_bt[i], ref) <= TOL_BF16
 
 
+@pytest.mark.parametrize("precision,tol", [(TF32, TOL_TF32), (BF16, TOL_BF16)])
+@pytest.mark.parametrize("v_kmajor", [False, True])
+def test_attention_two_phase_matches_one_call(lib, oracle, torch, precision, tol, v_kmajor):
+    # K and V prepared once, query rows attended in ragged blocks: same rows as one ib_attention.
+    batch, nq, nk, d, dv = 2, 1000, 700, 64, 48
+    q = rand((batch, nq, d), 31) * np.float32(d ** -0.5)
+    k = rand((batch, nk, d), 32)
+    v = rand((batch, dv, nk) if v_kmajor else (batch, nk, dv), 33)
+    whole = run_attention(lib, torch, q, k, v, precision, v_kmajor=v_kmajor)
+    dk, dvv = dev(torch, k), dev(torch, v)
+    pb = lib.ib_attention_prepare_bytes(batch, nk, d, dv, precision)
+    prepared = torch.empty(pb, dtype=torch.uint8, device="cuda")
+    ok(lib, lib.ib_attention_prepare(dk.data_ptr(), dvv.data_ptr(), batch, nk, d, dv, int(v_kmajor),
+                                     precision, prepared.data_ptr(), pb, None))
+    got = np.empty_like(whole)
+    for r0, r1 in ((0, 1), (1, 300), (300, 1000)):
+        rows = r1 - r0
+        dq = dev(torch, np.ascontiguousarray(q[:, r0:r1]))
+        o = torch.full((batch, rows, dv), float("nan"), device="cuda")
+        wb = lib.ib_attention_run_workspace_bytes(batch, rows, nk, dv)
+        ws = torch.empty(max(wb, 16), dtype=torch.uint8, device="cuda")
+        ok(lib, lib.ib_attention_run(dq.data_ptr(), prepared.data_ptr(), o.data_ptr(), batch, rows,
+                                     nk, d, dv, precision, ws.data_ptr(), wb, None))
+        torch.cuda.synchronize()
+        got[:, r0:r1] = o.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert max_rel_to_peak(got, whole) <= 1e-5           # same operands, same arithmetic per row
+    for b in range(batch):
+        vb = np.ascontiguousarray(v[b].T) if v_kmajor else v[b]
+        assert max_rel_to_peak(got[b], oracle.attention_fused(q[b], k[b], vb)) <= tol
+
+
+def test_attention_two_phase_rejects_fp32_arm(lib, torch):
+    x = torch.zeros(1 << 16, device="cuda")
+    assert lib.ib_attention_prepare(x.data_ptr(), x.data_ptr(), 1, 64, 64, 64, 0, FP32,
+                                    x.data_ptr(), 1 << 18, None) == -1
+    assert "tensor arms" in last_error(lib)
+    assert lib.ib_attention_uses_tensor_arm(1, 16384, 16384, 128, 128, 0) == 1
+    assert lib.ib_attention_uses_tensor_arm(1, 16, 16, 128, 128, 0) == 0      # too small under AUTO
+    assert lib.ib_attention_uses_tensor_arm(1, 16384, 16384, 130, 128, TF32) == 0
+
+
 def test_attention_large_scores_stay_finite(lib, oracle, torch):
     # Unscaled Q: scores of magnitude ~ sqrt(d) * 4, the running maximum moves a lot.
     q, k, v = rand((256, 128), 21) * 3, rand((1024, 128), 22), rand((1024, 128), 23)

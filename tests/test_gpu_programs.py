@@ -109,6 +109,51 @@ def test_config1_through_the_front_end(ilang, oracle):
     assert max_rel_to_peak(attn.exec_numpy(q, k, v), ref) <= 5e-3       # fused tcgen05 kernel
 
 
+def batched_readme_attention(ilang):
+    """README attention with a leading head axis: one invocation for all heads."""
+    i, I = ilang.i, ilang.I
+    mm_t = i("hik*hjk~hijk | i:16,j:16 | hjii'j'k") >> i("+hijk~hij | i:16,j:16 | hjii'j'k0")
+    row_max_shift = (I & i(">hij~hi | i:16,j:16 | hji0i'j'")) >> i("hij-hi~hij | i:16,j:16 | hji01i'j'")
+    exp = i("^hij~hij | i:16,j:16 | hji0i'j'")
+    row_normalize = (I & i("+hij~hi | i:16,j:16 | hji0i'j'")) >> i("hij/hi~hij | i:16,j:16 | hji01i'j'")
+    mm = i("hij*hjk~hikj | i:16,j:16 | hji0i'kj'") >> i("+hikj~hik | i:16,j:16 | hjii'kj'0")
+    return mm_t >> row_max_shift >> exp >> row_normalize >> mm
+
+
+def test_host_buffers_one_head_pipelined_by_query_rows(ilang, oracle):
+    # Large enough that i_exec_into overlaps its copies with the kernels, block by block of
+    # query rows (ragged last block: 8100 rows).  Rows are checked against the reference's
+    # emitted C where it was built, else the restated oracle.
+    nq, nk, d = 8100, 2048, 128
+    q = rand((nq, d), 41) * np.float32(d ** -0.5)
+    k, v = rand((nk, d), 42), rand((nk, d), 43)
+    attn = readme_attention(ilang)
+    launches = ilang.launch_count()
+    got = attn.exec_numpy(q, k, v)
+    assert ilang.launch_count() - launches >= 5          # one preparation, several row blocks
+    assert got.shape == (nq, d) and not np.isnan(got).any()
+    rows = np.r_[0:64, 2000:2064, 4090:4110, nq - 36:nq]
+    ref = oracle.attention_fused(q[rows], k, v)
+    assert max_rel_to_peak(got[rows], ref) <= 5e-3
+    assert max_rel_to_peak(got, np_attention(q, k, v)) <= 5e-3
+    out = np.full((nq, d), np.nan, dtype=np.float32)      # same through `into`
+    attn.into(out, q, k, v)
+    assert np.array_equal(out, got)
+
+
+def test_host_buffers_many_heads_pipelined_by_heads(ilang, oracle):
+    heads, n, d = 20, 512, 64                              # blocks of 3 heads, the last of 2
+    q = rand((heads, n, d), 44) * np.float32(d ** -0.5)
+    k, v = rand((heads, n, d), 45), rand((heads, n, d), 46)
+    attn = batched_readme_attention(ilang)
+    assert "attention" in attn._code()
+    got = attn.exec_numpy(q, k, v)
+    assert got.shape == (heads, n, d) and not np.isnan(got).any()
+    assert max_rel_to_peak(got, np_attention(q, k, v)) <= 5e-3
+    for h in (0, 7, 19):
+        assert max_rel_to_peak(got[h], oracle.attention_fused(q[h], k[h], v[h])) <= 5e-3
+
+
 def test_softmax_component_config2_slice(ilang, oracle):
     i, I = ilang.i, ilang.I
     sm = ((I & i(">ij~i | i:16,j:16 | jii'j'")) >> i("ij-i~ij | i:16,j:16 | 1jii'j'")) \
