@@ -102,3 +102,15 @@ int check_device_status(const char* what, cudaStream_t) {
 }
 
 }  // namespace ib
+
+// Undocumented hook for kernel development: returns and clears the code a bounded
+// device-side wait left for the current device, 0 if none.
+extern "C" int ib_debug_take_device_status(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= ib::kMaxDevices) return 0;
+  std::lock_guard<std::mutex> lock(ib::g_status_mutex);
+  if (!ib::g_status_host[dev]) return 0;
+  const int code = *static_cast<volatile int*>(ib::g_status_host[dev]);
+  *static_cast<volatile int*>(ib::g_status_host[dev]) = 0;
+  return code;
+}
