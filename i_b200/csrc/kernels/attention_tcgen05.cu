@@ -405,6 +405,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     const int dv_chunks = (p.dv + 31) / 32;
     long long it = 0;                         // key tiles consumed so far by this CTA
     long long wait_s = 0;
+    long long c_load = 0, c_max = 0, c_sync = 0, c_exp = 0, c_store = 0;   // PROF: cycles per phase
     const long long t_start = tick<PROF>();
     bool dead = false;                        // a wait gave up; keep hitting the barriers only
 
@@ -483,11 +484,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         wait_s += tick<PROF>() - t0;
       }
       float mx = -CUDART_INF_F;
+      long long tp = tick<PROF>();
       if (!dead) {
         tc_fence_after_sync();
         tmem_ld_32x32(s_tmem, s0);
         tmem_ld_32x32(s_tmem + 32, s1);
         tmem_wait_ld();
+        c_load += tick<PROF>() - tp;
+        tp = tick<PROF>();
         const int col0 = (kv_lo + jj) * kBKV + h * 64;
         if (col0 + 64 > p.nk) {
 #pragma unroll
@@ -509,7 +513,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       } else {
         sh->give_up = 1;
       }
+      c_max += tick<PROF>() - tp;
+      tp = tick<PROF>();
       softmax_pair_sync();
+      c_sync += tick<PROF>() - tp;
+      tp = tick<PROF>();
       if (sh->give_up) break;                 // uniform: every writer wrote before the barrier
       mx = fmaxf(mx, sh->half_max[buf][h ^ 1][r]);
 
@@ -552,6 +560,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         s1[c] = __float_as_uint(e1);
       }
       l += sum0 + sum1;
+      c_exp += tick<PROF>() - tp;
+      tp = tick<PROF>();
       if (KIND == Kind::TF32) {
         tmem_st_32x32(s_tmem, s0);
         tmem_st_32x32(s_tmem + 32, s1);
@@ -569,6 +579,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->p_full[buf]);
+      c_store += tick<PROF>() - tp;
     }
 
     // ---- epilogue: total row sum, normalise, store columns [64h, 64h+64) of O ----
@@ -620,8 +631,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     tc_fence_before_sync();
     it += n_kv;
     }  // pieces
-    if (PROF && p.prof && quad == 0 && lane == 0 && h == 0)
+    if (PROF && p.prof && quad == 0 && lane == 0 && h == 0) {
       p.prof[blockIdx.x * 16 + 7] = tick<PROF>() - t_start - wait_s;
+      p.prof[blockIdx.x * 16 + 9] = c_load;
+      p.prof[blockIdx.x * 16 + 10] = c_max;
+      p.prof[blockIdx.x * 16 + 11] = c_sync;
+      p.prof[blockIdx.x * 16 + 12] = c_exp;
+      p.prof[blockIdx.x * 16 + 13] = c_store;
+    }
   }
 
   tc_fence_before_sync();
