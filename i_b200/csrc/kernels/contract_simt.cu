@@ -220,18 +220,33 @@ prepare_attention_kernel(PrepareArgs a) {
   }
 }
 
+__device__ __forceinline__ uint2 pack4_bf16(float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 __global__ void __launch_bounds__(256)
 convert_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t rows,
                     size_t cols, size_t out_pitch) {
-  // One thread per pair of output columns.
-  const size_t pairs = out_pitch / 2;
-  const size_t total = rows * pairs;
+  // Four output columns per thread: a 16-byte load and an 8-byte store (out_pitch is a
+  // multiple of 8, so every row starts 16-byte aligned).
+  const size_t quads = out_pitch / 4;
+  const size_t total = rows * quads;
   const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+  const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
   for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
-    const size_t r = i / pairs, c = (i - r * pairs) * 2;
-    const float x = c < cols ? in[r * cols + c] : 0.0f;
-    const float y = c + 1 < cols ? in[r * cols + c + 1] : 0.0f;
-    reinterpret_cast<__nv_bfloat162*>(out + r * out_pitch)[c / 2] = __floats2bfloat162_rn(x, y);
+    const size_t r = i / quads, c = (i - r * quads) * 4;
+    float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float* src = in + r * cols + c;
+    if (vec && c + 4 <= cols) {
+      x = __ldcs(reinterpret_cast<const float4*>(src));
+    } else {
+      if (c + 0 < cols) x.x = src[0];
+      if (c + 1 < cols) x.y = src[1];
+      if (c + 2 < cols) x.z = src[2];
+      if (c + 3 < cols) x.w = src[3];
+    }
+    *reinterpret_cast<uint2*>(out + r * out_pitch + c) = pack4_bf16(x.x, x.y, x.z, x.w);
   }
 }
 
@@ -248,36 +263,60 @@ prepare_attention_bf16_kernel(PrepareBf16Args a) {
   __shared__ float tile[64][65];
   sm100::trigger_dependent_launch();       // see prepare_attention_kernel
   if (blockIdx.y == 0) {
-    const size_t pairs = a.d_pitch / 2, total = a.k_rows * pairs;
+    // Four columns per thread: one 16-byte load, one 8-byte store (d_pitch is a multiple of 8).
+    const size_t quads = a.d_pitch / 4, total = a.k_rows * quads;
     const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+    const bool vec = a.d % 4 == 0 && (reinterpret_cast<uintptr_t>(a.k) & 15u) == 0;
     for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
-      const size_t r = i / pairs, c = (i - r * pairs) * 2;
-      const float x = c < a.d ? a.k[r * a.d + c] : 0.0f;
-      const float y = c + 1 < a.d ? a.k[r * a.d + c + 1] : 0.0f;
-      reinterpret_cast<__nv_bfloat162*>(a.k16 + r * a.d_pitch)[c / 2] = __floats2bfloat162_rn(x, y);
+      const size_t r = i / quads, c = (i - r * quads) * 4;
+      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      const float* src = a.k + r * a.d + c;
+      if (vec && c + 4 <= a.d) {
+        x = __ldcs(reinterpret_cast<const float4*>(src));
+      } else {
+        if (c + 0 < a.d) x.x = src[0];
+        if (c + 1 < a.d) x.y = src[1];
+        if (c + 2 < a.d) x.z = src[2];
+        if (c + 3 < a.d) x.w = src[3];
+      }
+      *reinterpret_cast<uint2*>(a.k16 + r * a.d_pitch + c) = pack4_bf16(x.x, x.y, x.z, x.w);
     }
     return;
   }
   const size_t tiles_k = (a.nk_pitch + 63) / 64, tiles_d = (a.dv + 63) / 64;
   const size_t total = a.batch * tiles_k * tiles_d;
+  const bool vec_in = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
   for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
     const size_t b = t / (tiles_k * tiles_d);
     const size_t rem = t - b * tiles_k * tiles_d;
     const size_t k0 = (rem / tiles_d) * 64, d0 = (rem % tiles_d) * 64;
     const float* src = a.v + b * a.nk * a.dv;
     __nv_bfloat16* dst = a.vt16 + b * a.dv * a.nk_pitch;
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-      const int r = e >> 6, c = e & 63;
-      float x = 0.0f;
-      if (k0 + r < a.nk && d0 + c < a.dv) x = src[(k0 + r) * a.dv + d0 + c];
-      tile[r][c] = x;
+    // 64 keys x 64 features in: 16 float4 per key row.
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int r = e >> 4, c = (e & 15) * 4;           // r: key, c: feature (contiguous in V)
+      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (k0 + r < a.nk) {
+        const float* row = src + (k0 + r) * a.dv + d0 + c;
+        if (vec_in && d0 + c + 4 <= a.dv) {
+          x = __ldcs(reinterpret_cast<const float4*>(row));
+        } else {
+          if (d0 + c + 0 < a.dv) x.x = row[0];
+          if (d0 + c + 1 < a.dv) x.y = row[1];
+          if (d0 + c + 2 < a.dv) x.z = row[2];
+          if (d0 + c + 3 < a.dv) x.w = row[3];
+        }
+      }
+      tile[r][c + 0] = x.x; tile[r][c + 1] = x.y; tile[r][c + 2] = x.z; tile[r][c + 3] = x.w;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < 64 * 32; e += 256) {
-      const int c = e >> 5, r = (e & 31) * 2;             // c: feature, r: key pair
+    // 64 features x 64 keys out: 16 groups of 4 keys (8 bytes) per feature row; keys past nk
+    // (up to the pitch) are written as the zeros the load left in the tile.
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int c = e >> 4, r = (e & 15) * 4;           // c: feature, r: first key of the group
       if (d0 + c < a.dv && k0 + r < a.nk_pitch)
-        reinterpret_cast<__nv_bfloat162*>(dst + (d0 + c) * a.nk_pitch + k0)[r / 2] =
-            __floats2bfloat162_rn(tile[r][c], tile[r + 1][c]);
+        *reinterpret_cast<uint2*>(dst + (d0 + c) * a.nk_pitch + k0 + r) =
+            pack4_bf16(tile[r][c], tile[r + 1][c], tile[r + 2][c], tile[r + 3][c]);
     }
     __syncthreads();
   }
@@ -295,7 +334,7 @@ int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, v
   }
   PrepareBf16Args a{k, static_cast<__nv_bfloat16*>(k16), batch * nk, d, d_pitch,
                     v, static_cast<__nv_bfloat16*>(vt16), batch, nk, dv, nk_pitch};
-  const size_t most = std::max(batch * nk * d_pitch / 2 / 256 + 1,
+  const size_t most = std::max(batch * nk * d_pitch / 4 / 256 + 1,
                                batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64));
   const size_t cap = static_cast<size_t>(kNumSMs) * 8;
   dim3 grid(static_cast<unsigned>(std::min(most, cap)), 2);
@@ -306,7 +345,7 @@ int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, v
 int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,
                       cudaStream_t s) {
   if (rows == 0 || cols == 0) return 0;
-  size_t blocks = (rows * (out_pitch / 2) + 255) / 256;
+  size_t blocks = (rows * (out_pitch / 4) + 255) / 256;
   if (blocks > static_cast<size_t>(kNumSMs) * 16) blocks = static_cast<size_t>(kNumSMs) * 16;
   convert_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
       in, static_cast<__nv_bfloat16*>(out), rows, cols, out_pitch);
