@@ -1,4 +1,6 @@
-// Pointwise maps: memory-bound, 128-bit vectorised, grid sized in SM multiples.
+// Pointwise maps: memory-bound, 128-bit vectorised, eight 16-byte loads in flight per thread and
+// one block per 32 KB of input (measured on B200 at 8192 x 8192: 6.0-6.1 TB/s against 5.5-5.8 for four
+// loads per thread on a grid capped at 16 blocks per SM; a plain device copy by torch runs at 6.07).
 //
 // Scalar semantics follow the reference's lowering
 // (compiler/src/lower/exec_plan_to_module.rs:605-640 for unary defaults,
@@ -11,11 +13,17 @@ namespace ib {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kVecPerThread = 4;  // float4 loads in flight per thread
+#ifndef IB_MAP_VEC
+#define IB_MAP_VEC 8
+#endif
+#ifndef IB_MAP_CAP
+#define IB_MAP_CAP 65536
+#endif
+constexpr int kVecPerThread = IB_MAP_VEC;  // float4 loads in flight per thread
 
 inline int grid_for(size_t work_items, size_t per_block) {
   size_t blocks = (work_items + per_block - 1) / per_block;
-  size_t cap = static_cast<size_t>(kNumSMs) * 16;
+  size_t cap = static_cast<size_t>(kNumSMs) * IB_MAP_CAP;
   if (blocks > cap) blocks = cap;
   if (blocks == 0) blocks = 1;
   return static_cast<int>(blocks);

@@ -5,14 +5,23 @@
 // from the op's identity and applies dst = op(dst, x).  The reference folds in
 // ascending column order on one thread; here a row is folded as a tree across
 // lanes, which is exact for max/min and differs from the sequential float sum
-// only by rounding.  Algorithmic traffic: rows*cols*4 + rows*4 bytes.
+// only by rounding.  Algorithmic traffic: rows*cols*4 + rows*4 bytes.  Eight 16-byte loads in
+// flight per thread and one CTA per row (no cap on the grid) measured 5.6-5.85 TB/s on B200 against
+// 5.2 for two loads per thread on a grid capped at 16 CTAs per SM.
 #include "common.cuh"
 
 namespace ib {
 namespace {
 
+#ifndef IB_RED_UNROLL
+#define IB_RED_UNROLL 8
+#endif
+#ifndef IB_RED_CAP
+#define IB_RED_CAP 65536
+#endif
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+constexpr int kUnroll = IB_RED_UNROLL;   // 16-byte loads in flight per thread in the one-row-per-CTA kernel
 
 // One warp per row: rows of up to a few thousand columns.
 template <int OP>
@@ -28,7 +37,17 @@ reduce_rows_warp(const float* __restrict__ x, float* __restrict__ y, size_t rows
     if (vec) {
       const float4* row4 = reinterpret_cast<const float4*>(row);
       const size_t nvec = cols / 4;
-      for (size_t i = lane; i < nvec; i += 32) {
+      constexpr int kWarpUnroll = 4;          // 16-byte loads in flight per lane
+      size_t i = lane;
+      for (; i + (kWarpUnroll - 1) * 32 < nvec; i += kWarpUnroll * 32) {
+        float4 v[kWarpUnroll];
+#pragma unroll
+        for (int u = 0; u < kWarpUnroll; ++u) v[u] = __ldcs(row4 + i + u * 32);
+#pragma unroll
+        for (int u = 0; u < kWarpUnroll; ++u)
+          acc = fold<OP>(acc, fold<OP>(fold<OP>(v[u].x, v[u].y), fold<OP>(v[u].z, v[u].w)));
+      }
+      for (; i < nvec; i += 32) {
         float4 v = __ldcs(row4 + i);
         acc = fold<OP>(acc, fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
       }
@@ -48,25 +67,32 @@ reduce_rows_block(const float* __restrict__ x, float* __restrict__ y, size_t row
   __shared__ float partial[kWarps];
   for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const float* row = x + r * cols;
-    float acc0 = reduce_identity(OP), acc1 = acc0;
+    float accs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) accs[u] = reduce_identity(OP);
     if (vec) {
       const float4* row4 = reinterpret_cast<const float4*>(row);
       const size_t nvec = cols / 4;
       size_t i = threadIdx.x;
-      for (; i + kThreads < nvec; i += 2 * kThreads) {
-        float4 v = __ldcs(row4 + i);
-        float4 w = __ldcs(row4 + i + kThreads);
-        acc0 = fold<OP>(acc0, fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
-        acc1 = fold<OP>(acc1, fold<OP>(fold<OP>(w.x, w.y), fold<OP>(w.z, w.w)));
+      for (; i + (kUnroll - 1) * kThreads < nvec; i += kUnroll * kThreads) {
+        float4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = __ldcs(row4 + i + u * kThreads);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          accs[u] = fold<OP>(accs[u], fold<OP>(fold<OP>(v[u].x, v[u].y), fold<OP>(v[u].z, v[u].w)));
       }
-      if (i < nvec) {
-        float4 v = __ldcs(row4 + i);
-        acc0 = fold<OP>(acc0, fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
+      for (; i < nvec; i += kThreads) {
+        const float4 v = __ldcs(row4 + i);
+        accs[0] = fold<OP>(accs[0], fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
       }
     } else {
-      for (size_t i = threadIdx.x; i < cols; i += kThreads) acc0 = fold<OP>(acc0, row[i]);
+      for (size_t i = threadIdx.x; i < cols; i += kThreads) accs[0] = fold<OP>(accs[0], row[i]);
     }
-    float acc = warp_fold<OP>(fold<OP>(acc0, acc1));
+    float acc0 = accs[0];
+#pragma unroll
+    for (int u = 1; u < kUnroll; ++u) acc0 = fold<OP>(acc0, accs[u]);
+    float acc = warp_fold<OP>(acc0);
     if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
     __syncthreads();
     if (threadIdx.x < 32) {
@@ -123,11 +149,11 @@ int launch_rows(const float* x, float* y, size_t rows, size_t cols, cudaStream_t
   const bool vec = cols % 4 == 0 && aligned16(x);
   if (cols <= 2048) {
     size_t blocks = (rows + kWarps - 1) / kWarps;
-    size_t cap = static_cast<size_t>(kNumSMs) * 16;
+    size_t cap = static_cast<size_t>(kNumSMs) * IB_RED_CAP;
     reduce_rows_warp<OP><<<static_cast<int>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
         x, y, rows, cols, vec);
   } else {
-    size_t cap = static_cast<size_t>(kNumSMs) * 16;
+    size_t cap = static_cast<size_t>(kNumSMs) * IB_RED_CAP;
     reduce_rows_block<OP><<<static_cast<int>(rows < cap ? rows : cap), kThreads, 0, s>>>(
         x, y, rows, cols, vec);
   }
@@ -138,7 +164,7 @@ template <int OP>
 int launch_strided(const float* x, float* y, size_t n_out, size_t n_red, const FoldArgs& args,
                    cudaStream_t s) {
   size_t blocks = (n_out + kWarps - 1) / kWarps;
-  size_t cap = static_cast<size_t>(kNumSMs) * 16;
+  size_t cap = static_cast<size_t>(kNumSMs) * IB_RED_CAP;
   reduce_strided<OP><<<static_cast<int>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
       x, y, n_out, n_red, args);
   return check_launch("ib_reduce_strided");
