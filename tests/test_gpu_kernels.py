@@ -231,7 +231,8 @@ def test_reduce_rejects_non_reducible(lib, oracle, torch):
 # ---- row softmax ----------------------------------------------------------
 
 @pytest.mark.parametrize("shape", [(64, 16), (100, 257), (33, 1000), (5, 1023), (16, 4096),
-                                   (8, 8192), (3, 16384), (2, 20001), (1, 1)])
+                                   (8, 8192), (3, 16384), (2, 20001), (1, 1), (5, 12000), (3, 20000),
+                                   (2, 32768), (2, 40000)])
 def test_row_softmax(lib, oracle, torch, shape):
     x = 2.0 * rand(shape, 10)                        # N(0, 4) like BASELINE config 2
     d = dev(torch, x)
@@ -382,6 +383,26 @@ def test_attention_tf32_shapes(lib, oracle, torch, nq, nk, d, dv):
     got = run_attention(lib, torch, q, k, v, TF32)
     assert not np.isnan(got).any()
     assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= TOL_TF32
+
+
+def test_attention_tf32_random_shapes(lib, oracle, torch):
+    # Seeded sweep over ragged shapes (rows, keys, both head dimensions, heads): every way a row
+    # tile, a key tile or a feature chunk can be partial, and every split of the work over CTAs
+    # that small and medium problems produce.  Each head is checked against the oracle.
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        batch = int(rng.integers(1, 4))
+        nq = int(rng.integers(1, 700))
+        nk = int(rng.integers(1, 900))
+        d = 4 * int(rng.integers(1, 33))
+        dv = int(rng.integers(1, 129))
+        q = rand((batch, nq, d), 100 + case) * np.float32(d ** -0.5)
+        k, v = rand((batch, nk, d), 200 + case), rand((batch, nk, dv), 300 + case)
+        got = run_attention(lib, torch, q, k, v, TF32)
+        assert not np.isnan(got).any(), (batch, nq, nk, d, dv)
+        for b in range(batch):
+            err = max_rel_to_peak(got[b], oracle.attention_fused(q[b], k[b], v[b]))
+            assert err <= TOL_TF32, (batch, nq, nk, d, dv, b, err)
 
 
 @pytest.mark.parametrize("nq,nk,d,dv", [
