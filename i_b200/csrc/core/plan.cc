@@ -327,6 +327,104 @@ void fuse_attention(Builder& b) {
   }
 }
 
+// Attention written with the normalisation deferred: E = exp(S) or exp(S - rowmax S),
+// O = (E V) / rowsum E — `mm_t >> exp >> (mm & row_sum) >> row_div`, the form the reference's
+// tests build in compiler/src/lower/stage_to_kernel_program.rs:2705-2780.  It is the same
+// function of Q, K, V as the README chain wherever exp(S) is finite, and the fused kernel
+// subtracts the running maximum in any case, so it also stays finite where the unshifted
+// form would overflow.  The schedule gate is the one of fuse_attention.
+void fuse_deferred_attention(Builder& b) {
+  auto is_exp = [](const Step& s) {
+    return s.kind == StepKind::Map && s.op == Op::Pow && s.in.size() == 1 &&
+           is_iota(s.in[0].index, s.rank) && is_iota(s.out.index, s.rank);
+  };
+  auto reads = [](const Access& a, size_t node) { return !a.buffer.is_input && a.buffer.index == node; };
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n] || b.steps[n].kind != StepKind::Contract) continue;
+    const Step& qk = b.steps[n];
+    const ContractForm& f1 = qk.form;
+    if (!f1.has_m || !f1.has_n || !f1.a_kmajor || !f1.b_kmajor || f1.swap_out) continue;
+    const size_t s_node = qk.out.buffer.index;
+    if (b.is_output[s_node]) continue;
+    std::vector<size_t> group = qk.nodes;
+    std::vector<size_t> slots = {n};
+    // exp directly on S, or on S - rowmax S.
+    std::vector<size_t> rd = b.readers(s_node);
+    size_t i_exp;
+    if (rd.size() == 1 && is_exp(b.steps[rd[0]])) {
+      i_exp = rd[0];
+    } else if (rd.size() == 2) {
+      size_t i_max = rd[0], i_sub = rd[1];
+      if (!is_row_reduce(b.steps[i_max], Op::Max)) std::swap(i_max, i_sub);
+      const Step& mx = b.steps[i_max];
+      const Step& sub = b.steps[i_sub];
+      if (!is_row_reduce(mx, Op::Max) || !is_row_broadcast(sub, Op::Sub)) continue;
+      const size_t m_node = mx.out.buffer.index;
+      if (!reads(mx.in[0], s_node) || !reads(sub.in[0], s_node) || !reads(sub.in[1], m_node)) continue;
+      if (b.is_output[m_node] || b.readers(m_node).size() != 1) continue;
+      const size_t y_node = sub.out.buffer.index;
+      auto r_exp = b.sole_reader(y_node);
+      if (!r_exp || !is_exp(b.steps[*r_exp])) continue;
+      i_exp = *r_exp;
+      slots.push_back(i_max);
+      slots.push_back(i_sub);
+      group.insert(group.end(), mx.nodes.begin(), mx.nodes.end());
+      group.insert(group.end(), sub.nodes.begin(), sub.nodes.end());
+    } else {
+      continue;
+    }
+    const Step& ex = b.steps[i_exp];
+    if (ex.rank != f1.n_batch + 2) continue;
+    const size_t e_node = ex.out.buffer.index;
+    if (b.is_output[e_node]) continue;
+    // E feeds the second contraction and the row sum.
+    rd = b.readers(e_node);
+    if (rd.size() != 2) continue;
+    size_t i_pv = rd[0], i_sum = rd[1];
+    if (b.steps[i_pv].kind != StepKind::Contract) std::swap(i_pv, i_sum);
+    const Step& pv = b.steps[i_pv];
+    const Step& sum = b.steps[i_sum];
+    if (pv.kind != StepKind::Contract || !is_row_reduce(sum, Op::Add)) continue;
+    if (!reads(pv.in[0], e_node) || !reads(sum.in[0], e_node)) continue;
+    const ContractForm& f2 = pv.form;
+    if (!f2.has_m || !f2.has_n || !f2.a_kmajor || f2.swap_out || f2.n_batch != f1.n_batch) continue;
+    const size_t o_node = pv.out.buffer.index, l_node = sum.out.buffer.index;
+    if (b.is_output[o_node] || b.is_output[l_node]) continue;
+    auto r_div = b.sole_reader(o_node);
+    auto r_div2 = b.sole_reader(l_node);
+    if (!r_div || !r_div2 || *r_div != *r_div2) continue;
+    const Step& dv = b.steps[*r_div];
+    if (!is_row_broadcast(dv, Op::Div) || !reads(dv.in[0], o_node) || !reads(dv.in[1], l_node)) continue;
+    if (dv.rank != f1.n_batch + 2) continue;
+    const Node& pv_mul = b.g.nodes[pv.nodes[0]].inner;
+    const bool e_staged = pv_mul.compute_sites[0] && !pv_mul.compute_sites[0]->root;
+    if (!e_staged && !fuse_always()) continue;
+
+    Step fused;
+    fused.kind = StepKind::Attention;
+    fused.op = Op::Add;
+    fused.rank = qk.rank;
+    fused.in = {qk.in[0], qk.in[1], pv.in[1]};
+    fused.out = dv.out;
+    fused.form = f1;
+    fused.form2 = f2;
+    fused.hint = qk.hint;
+    fused.hint.staged = true;
+    group.insert(group.end(), ex.nodes.begin(), ex.nodes.end());
+    group.insert(group.end(), pv.nodes.begin(), pv.nodes.end());
+    group.insert(group.end(), sum.nodes.begin(), sum.nodes.end());
+    group.insert(group.end(), dv.nodes.begin(), dv.nodes.end());
+    fused.nodes = group;
+    slots.push_back(i_exp);
+    slots.push_back(i_pv);
+    slots.push_back(i_sum);
+    const size_t slot = *r_div;
+    for (size_t dead : slots) b.alive[dead] = false;
+    b.steps[slot] = std::move(fused);
+    b.alive[slot] = true;
+  }
+}
+
 const char* kind_name(StepKind k) {
   switch (k) {
     case StepKind::Map: return "map";
@@ -435,6 +533,7 @@ Result<Plan> make_plan(const Graph& g) {
   fuse_contractions(b);
   fuse_softmax(b);
   fuse_attention(b);
+  fuse_deferred_attention(b);
 
   Plan plan;
   plan.n_inputs = g.n_inputs;

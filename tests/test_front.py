@@ -245,6 +245,29 @@ def test_fused_schedule_is_one_attention_kernel(ilang):
     assert steps_of(readme_attention(ilang)) == ["attention"]
 
 
+def deferred_attention(ilang, shift=False, staged=True):
+    """Attention with the division deferred: exp, then (E V) and rowsum(E), then the division —
+    the formulation of compiler/src/lower/stage_to_kernel_program.rs:2705-2780 (same strings)."""
+    i, I = ilang.i, ilang.I
+    mm_t = i("ik*jk~ijk|i:2,j:2|iji'j'k") >> i("+ijk~ij|i:2,j:2|iji'j'k0")
+    exp = i("^ij~ij|i:2,j:2|iji'j'0")
+    mm = i("ik*kj~ijk|i:2,k:2|ik0i'jk'" if staged else "ik*kj~ijk|i:2,k:2|iki'jk'") \
+        >> i("+ijk~ij|i:2,k:2|iki'jk'0")
+    row_sum = i("+ij~i|i:2,j:2|ij0i'j'")
+    row_div = i("ij/i~ij|i:2|i01i'j")
+    chain = mm_t
+    if shift:
+        chain = chain >> ((I & i(">ij~i|i:2,j:2|ij0i'j'")) >> i("ij-i~ij|i:2,j:2|ij01i'j'"))
+    return chain >> exp >> (mm & row_sum) >> row_div
+
+
+def test_deferred_normalisation_is_one_attention_kernel(ilang):
+    assert steps_of(deferred_attention(ilang)) == ["attention"]
+    assert steps_of(deferred_attention(ilang, shift=True)) == ["attention"]
+    # Without a staged producer in the second contraction nothing fuses across it.
+    assert "attention" not in steps_of(deferred_attention(ilang, staged=False))
+
+
 def test_naive_schedule_keeps_three_kernels(ilang):
     # ilang-python/flash-attn.py:57-65: no staging of P => intermediates stay.
     assert steps_of(naive_attention(ilang)) == ["contract", "row_softmax", "contract"]

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from conftest import max_rel_elementwise, max_rel_to_peak
-from test_front import naive_attention, readme_attention
+from test_front import deferred_attention, naive_attention, readme_attention
 
 pytestmark = pytest.mark.gpu
 
@@ -107,6 +107,27 @@ def test_config1_through_the_front_end(ilang, oracle):
     assert max_rel_to_peak(attn.exec_numpy(q, k, v), ref) <= 2e-5       # auto -> fp32 arm
     attn.set_precision("tf32")
     assert max_rel_to_peak(attn.exec_numpy(q, k, v), ref) <= 5e-3       # fused tcgen05 kernel
+
+
+@pytest.mark.parametrize("shift", [False, True])
+def test_deferred_normalisation_attention(ilang, shift):
+    # exp >> (mm & row_sum) >> row_div (stage_to_kernel_program.rs:2705-2780), fused and unfused.
+    q = rand((300, 64), 51) * np.float32(64 ** -0.5)
+    k, v = rand((500, 64), 52), rand((500, 48), 53)
+    ref = np_attention(q, k, v)
+    for staged in (True, False):
+        attn = deferred_attention(ilang, shift=shift, staged=staged)
+        np.testing.assert_allclose(attn.exec_numpy(q, k, v), ref, rtol=3e-4, atol=5e-5)   # fp32 arm
+        attn.set_precision("tf32")
+        assert max_rel_to_peak(attn.exec_numpy(q, k, v), ref) <= 5e-3
+    # Logits beyond exp's range (|S| up to ~150): the fused step works relative to the row maximum,
+    # so the unshifted form stays finite too.  Exact arm for the values, tensor arm for finiteness
+    # (TF32 rounding of logits this large moves the probabilities themselves).
+    big = deferred_attention(ilang, shift=False)
+    qb = q * np.float32(40.0)
+    assert max_rel_to_peak(big.exec_numpy(qb, k, v), np_attention(qb, k, v)) <= 1e-4
+    big.set_precision("tf32")
+    assert np.isfinite(big.exec_numpy(qb, k, v)).all()
 
 
 def batched_readme_attention(ilang):
