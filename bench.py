@@ -284,6 +284,13 @@ def secondary_metrics(torch, ilang, peaks):
     aflop = 4.0 * SEQ * SEQ * DIM
     ms = timed(lambda: lib.ib_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, SEQ,
                                         SEQ, DIM, DIM, 0, 3, 0, ws.data_ptr(), wsb, stream), 10, flush)
+    wsb2 = lib.ib_attention_workspace_bytes(1, SEQ, SEQ, DIM, DIM, 0, 2)
+    ws2 = torch.empty(wsb2, dtype=torch.uint8, device="cuda")
+    ms2 = timed(lambda: lib.ib_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, SEQ,
+                                         SEQ, DIM, DIM, 0, 2, 0, ws2.data_ptr(), wsb2, stream), 10, flush)
+    out["attention_16384_d128_tf32_both_contractions"] = {
+        "tflops": aflop / ms2 / 1e9, "ms": ms2,
+        "frac_tf32_peak": aflop / ms2 / 1e9 / (peaks["bf16_tflops"] / 2)}
     out["attention_16384_d128_bf16_optin"] = {
         "tflops": aflop / ms / 1e9, "ms": ms, "frac_bf16_peak": aflop / ms / 1e9 / peaks["bf16_tflops"],
         "note": "includes the fp32->bf16 conversion of K and V; bound by ex2, not by the tensor pipe"}
@@ -312,7 +319,9 @@ def run_gpu_arm(args):
     peaks = load_peaks()
     heads = args.heads
     batched = heads > 1
-    attn = readme_attention(ilang, batched=batched).set_precision("tf32")
+    # "auto" is what a caller gets without asking: for attention of this size the TF32 x fp16
+    # arm (Q K^T on TF32 operands, P V on fp16 operands with the same 10-bit mantissa).
+    attn = readme_attention(ilang, batched=batched).set_precision(args.precision)
     flop_per_step = heads * FLOP_PER_HEAD
 
     def shaped(t):
@@ -473,12 +482,30 @@ def run_gpu_arm(args):
     parity = float(np.abs(got[rows] - ref).max() / np.abs(ref).max())
 
     tf32_peak = peaks["bf16_tflops"] / 2.0
+    f16_peak = peaks["bf16_tflops"]            # fp16 and bf16 issue at the same rate
+    mixed = args.precision in ("auto", "tf32_f16")
+    if args.precision == "bf16":
+        arm_peak, arm_dtype = f16_peak, "bf16"
+        arm_text = "tcgen05 kind::f16 on bf16 operands, fp32 accumulate"
+        peak_text = "%s bf16_tflops %.1f" % (peaks["source"], peaks["bf16_tflops"])
+    elif mixed:
+        # Half of the FLOPs (Q K^T) run at the TF32 rate, half (P V) at the 16-bit rate.
+        arm_peak, arm_dtype = 2.0 / (1.0 / tf32_peak + 1.0 / f16_peak), "tf32+f16"
+        arm_text = ("S = Q K^T: tcgen05 kind::tf32; O += P V: kind::f16 on fp16 operands (10-bit "
+                    "mantissa like TF32, V scaled per head by a power of two); fp32 accumulate")
+        peak_text = ("%s bf16_tflops %.1f: half the FLOPs at the TF32 rate (bf16 / 2), half at the "
+                     "16-bit rate -> harmonic mean" % (peaks["source"], peaks["bf16_tflops"]))
+    else:
+        arm_peak, arm_dtype = tf32_peak, "tf32"
+        arm_text = "tcgen05 kind::tf32 for both contractions, fp32 accumulate"
+        peak_text = ("%s bf16_tflops %.1f / 2 (TF32 MMA issues at half the bf16 rate)"
+                     % (peaks["source"], peaks["bf16_tflops"]))
     achieved = flop_per_step / ms_per_step / 1e9
     traffic = ATTENTION_DRAM_BYTES_PER_LAUNCH if (heads == 1 and SEQ == 16384) else None
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": arm_dtype, "data": "synthetic",
         "config": {"workload": WORKLOAD if (heads == 1 and SEQ == 16384) else
                    "%d heads x seq %d x d %d per rank per step (batched README attention)"
                    % (heads, SEQ, DIM),
@@ -487,12 +514,12 @@ def run_gpu_arm(args):
                          % (rotation, rotation * set_bytes // 2 ** 20),
                    "multi_gpu": "one head per rank per step; output assembly: " + gather_mode,
                    "gathered_output_verified": gather_ok,
-                   "precision": "tcgen05 kind::tf32, fp32 accumulate",
+                   "precision": arm_text,
                    "parity_max_rel_to_peak_vs_oracle": parity},
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                     "frac": achieved / tf32_peak, "traffic": traffic,
-                     "peak_source": "%s bf16_tflops %.1f / 2 (TF32 MMA issues at half the bf16 rate)"
-                                    % (peaks["source"], peaks["bf16_tflops"]),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": arm_peak, "unit": "TFLOP/s",
+                     "frac": achieved / arm_peak, "traffic": traffic,
+                     "peak_source": peak_text,
+                     "frac_of_tf32_peak": achieved / tf32_peak,
                      "frac_of_bf16_peak": achieved / peaks["bf16_tflops"],
                      "note": "achieved = 4*Nq*Nk*d FLOP / average step time on one rank; a step "
                              "launches the operand-preparation, attention and merge kernels"},
@@ -529,6 +556,8 @@ def main():
                     help="output assembly at N > 1: copy-engine peer writes or NCCL all-gather")
     ap.add_argument("--reserve-sms", type=int, default=20,
                     help="SMs left free for NCCL kernels when the NCCL gather is used")
+    ap.add_argument("--precision", default="auto", choices=["auto", "tf32", "bf16", "tf32_f16"],
+                    help="arithmetic of the fused attention kernel (default: the library's own choice)")
     ap.add_argument("--heads", type=int, default=1,
                     help="heads per rank per step (default 1 = BASELINE config 4)")
     ap.add_argument("--seq", type=int, default=16384, help="sequence length (default 16384)")

@@ -59,20 +59,31 @@ constexpr int kThreads = 384;
 constexpr int kChunkBytes = 128 * 128;     // 128 rows of 128 bytes: 32 fp32 or 64 bf16 per row
 constexpr int kMaxRing = 3;
 
-// Per operand type: a K or V^T tile of 128 keys is 4 chunks (TF32) or 2 (BF16);
-// the ring always has three slots (the producer's slot-reuse waits rely on that
-// distance, see there).  One MMA consumes 32 bytes of
-// every operand row (8 TF32 or 16 BF16 along K) and 8 tensor-memory columns of
-// its A operand (bf16 pairs are packed two to a column), so a 128-deep
-// contraction is 16 or 8 instructions.
-template <Kind KIND>
+// Arithmetic of the two contractions.  MIXED runs S = Q K^T on TF32 operands and O += P V on
+// fp16 ones: fp16 has TF32's 10-bit mantissa, P lies in [0, 1], and V is scaled per head by a
+// power of two into fp16's range, so the result has TF32 accuracy while the second contraction
+// issues half as many MMAs.
+enum class Arm { TF32, BF16, MIXED };
+
+// Per contraction: a tile of 128 keys is 4 chunks of 32 fp32 or 2 chunks of 64 16-bit
+// elements; the ring always has three slots (the producer's slot-reuse waits rely on that
+// distance, see there).  One MMA consumes 32 bytes of every operand row (8 fp32 or 16 16-bit
+// values along K) and 8 tensor-memory columns of its A operand (16-bit pairs are packed two to
+// a column), so a 128-deep contraction is 16 or 8 instructions.
+template <Arm ARM>
 struct Geometry {
-  static constexpr int kChunkElems = KIND == Kind::TF32 ? 32 : 64;
-  static constexpr int kTileChunks = 128 / kChunkElems;            // 4 or 2
-  static constexpr int kSlotBytes = kTileChunks * kChunkBytes;     // 64 KB or 32 KB
+  static constexpr bool kQkHalf = ARM == Arm::BF16;               // Q, K are 16-bit
+  static constexpr bool kPvHalf = ARM != Arm::TF32;               // P, V are 16-bit
+  static constexpr Fmt kQkFmt = kQkHalf ? Fmt::BF16 : Fmt::TF32;
+  static constexpr Fmt kPvFmt = ARM == Arm::TF32 ? Fmt::TF32 : (ARM == Arm::BF16 ? Fmt::BF16 : Fmt::F16);
+  static constexpr int kQkChunkElems = kQkHalf ? 64 : 32;
+  static constexpr int kQkStepElems = kQkHalf ? 16 : 8;           // K per MMA
+  static constexpr int kQkSteps = 128 / kQkStepElems;             // 16 or 8
+  static constexpr int kPvChunkElems = kPvHalf ? 64 : 32;
+  static constexpr int kPvTileChunks = 128 / kPvChunkElems;       // 4 or 2
+  static constexpr int kPvSteps = kPvHalf ? 8 : 16;
+  static constexpr int kSlotBytes = (kQkHalf && kPvHalf ? 2 : 4) * kChunkBytes;   // 32 KB or 64 KB
   static constexpr int kRing = 3;
-  static constexpr int kStepElems = KIND == Kind::TF32 ? 8 : 16;   // K per MMA
-  static constexpr int kSteps = 128 / kStepElems;                  // 16 or 8
 };
 constexpr int kRingBytes = 3 * 4 * kChunkBytes;
 constexpr uint32_t kTmemCols = 512;
@@ -91,6 +102,7 @@ struct Params {
   int full_waves;         // whole row tiles every CTA takes before the tail
   long long iters_base;   // tail (row tile, key tile) pairs per CTA: CTA g takes iters_base, plus
   int iters_rem;          // one more when g < iters_rem
+  const float* v_scale;   // mixed arm: V^T holds V / v_scale[head] (a power of two); else null
   float* o;            // [batch][nq][dv]
   float* part_o;       // [2 * ctas][128][dv]: slot 2g + (0: first piece, 1: last piece of CTA g)
   float* part_m;       // [2 * ctas][128]
@@ -164,6 +176,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return out;
 }
 
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  uint32_t out;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+
 template <bool PROF>
 __device__ __forceinline__ long long tick() {
   return PROF ? clock64() : 0ll;
@@ -174,14 +192,14 @@ __device__ __forceinline__ void softmax_pair_sync() {
 }
 
 // PROF = true compiles in the cycle counters written to Params::prof.
-template <bool PROF, Kind KIND>
+template <bool PROF, Arm ARM>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vt, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  using G = Geometry<KIND>;
+  using G = Geometry<ARM>;
   constexpr int kRing = G::kRing;
   constexpr int kSlotBytes = G::kSlotBytes;
   uint8_t* ring = smem;                                     // [kRing][kSlotBytes]
@@ -189,7 +207,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int d_chunks = (p.d + G::kChunkElems - 1) / G::kChunkElems;
+  const int d_chunks = (p.d + G::kQkChunkElems - 1) / G::kQkChunkElems;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRing; ++s) {
@@ -252,7 +270,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         uint8_t* dst = ring + slot * kSlotBytes;
         mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
         for (int c = 0; c < d_chunks; ++c)
-          tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kChunkElems,
+          tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kQkChunkElems,
                       j * kBKV, b);
         occupant_bar[slot] = &sh->s_full[tile_k & 1];
         occupant_parity[slot] = static_cast<uint32_t>((tile_k >> 1) & 1);
@@ -263,10 +281,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         acquire(202);
         if (!ok) return;
         uint8_t* dst = ring + slot * kSlotBytes;
-        mbar_arrive_expect_tx(&sh->kv_full[slot], G::kTileChunks * kChunkBytes);
-        for (int c = 0; c < G::kTileChunks; ++c)
+        mbar_arrive_expect_tx(&sh->kv_full[slot], G::kPvTileChunks * kChunkBytes);
+        for (int c = 0; c < G::kPvTileChunks; ++c)
           tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot],
-                      j * kBKV + c * G::kChunkElems, 0, b);
+                      j * kBKV + c * G::kPvChunkElems, 0, b);
         occupant_bar[slot] = &sh->pv_done[tile_v & 1];
         occupant_parity[slot] = static_cast<uint32_t>((tile_v >> 1) & 1);
         ++tile_v;
@@ -300,10 +318,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc(KIND, kBQ, kBKV);
+      const uint32_t idesc_qk = make_idesc_fmt(G::kQkFmt, kBQ, kBKV);
       const uint32_t n_pv = static_cast<uint32_t>((p.dv + 15) / 16 * 16);
-      const uint32_t idesc_pv = make_idesc(KIND, kBQ, n_pv);
-      const int k_steps = (p.d + G::kStepElems - 1) / G::kStepElems;
+      const uint32_t idesc_pv = make_idesc_fmt(G::kPvFmt, kBQ, n_pv);
+      const int k_steps = (p.d + G::kQkStepElems - 1) / G::kQkStepElems;
       int slot = 0;
       uint32_t phase = 0;
       const uint32_t ring_addr = smem_u32(ring);
@@ -326,9 +344,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
         const uint32_t q_tmem = tmem_base + kTmemQ;
 #pragma unroll
-        for (int ks = 0; ks < G::kSteps; ++ks) {
+        for (int ks = 0; ks < G::kQkSteps; ++ks) {
           if (ks < k_steps)
-            mma_ts<KIND>(d_tmem, q_tmem + ks * 8,
+            mma_ts_w<G::kQkHalf>(d_tmem, q_tmem + ks * 8,
                          k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
                          ks != 0 ? 1u : 0u);
         }
@@ -353,17 +371,17 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         // Keys 64h..64h+63 of P sit at the start of softmax half h's 64 columns:
         // 64 columns of fp32 (TF32) or 32 columns of packed bf16 pairs.
         auto p_col = [&](int ks) -> uint32_t {
-          constexpr int kHalfSteps = G::kSteps / 2;
+          constexpr int kHalfSteps = G::kPvSteps / 2;
           return p_tmem + static_cast<uint32_t>((ks / kHalfSteps) * 64 + (ks % kHalfSteps) * 8);
         };
         if (first_of_piece) {
-          mma_ts<KIND>(d_tmem, p_col(0), v_desc, idesc_pv, 0u);
+          mma_ts_w<G::kPvHalf>(d_tmem, p_col(0), v_desc, idesc_pv, 0u);
         } else {
-          mma_ts<KIND>(d_tmem, p_col(0), v_desc, idesc_pv, 1u);
+          mma_ts_w<G::kPvHalf>(d_tmem, p_col(0), v_desc, idesc_pv, 1u);
         }
 #pragma unroll
-        for (int ks = 1; ks < G::kSteps; ++ks)
-          mma_ts<KIND>(d_tmem, p_col(ks),
+        for (int ks = 1; ks < G::kPvSteps; ++ks)
+          mma_ts_w<G::kPvHalf>(d_tmem, p_col(ks),
                        v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
         mma_commit(&sh->pv_done[buf]);         // O updated, and the V tile's slot is free
         issue_pv_cycles += tick<PROF>() - ti;
@@ -437,7 +455,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         return x;
       };
-      if (KIND == Kind::TF32) {
+      if (!G::kQkHalf) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int col0 = h * 64 + c * 32;
@@ -562,16 +580,22 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       l += sum0 + sum1;
       c_exp += tick<PROF>() - tp;
       tp = tick<PROF>();
-      if (KIND == Kind::TF32) {
+      if (!G::kPvHalf) {
         tmem_st_32x32(s_tmem, s0);
         tmem_st_32x32(s_tmem + 32, s1);
       } else {
-        // Pack this half's 64 probabilities as 32 bf16 pairs over the start of its own S columns.
+        // Pack this half's 64 probabilities as 32 pairs of 16-bit values (bf16, or fp16 in the
+        // mixed arm) over the start of its own S columns.
         uint32_t packed[32];
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          packed[c] = pack_bf16(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1]));
-          packed[16 + c] = pack_bf16(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1]));
+          if (G::kPvFmt == Fmt::BF16) {
+            packed[c] = pack_bf16(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1]));
+            packed[16 + c] = pack_bf16(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1]));
+          } else {
+            packed[c] = pack_f16(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1]));
+            packed[16 + c] = pack_f16(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1]));
+          }
         }
         tmem_st_32x32(s_tmem, packed);
       }
@@ -593,7 +617,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     if (!sh->give_up) {
       tc_fence_after_sync();
       const float l_total = l + sh->half_sum[h ^ 1][r];
-      const float inv = 1.0f / l_total;
+      const float inv = (p.v_scale ? p.v_scale[b] : 1.0f) / l_total;
       float* dst;
       if (whole) {
         dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
@@ -773,7 +797,9 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      bool bf16, bool follows_prepare, float* partials, cudaStream_t s) {
+                      AttentionArm arm, const float* v_scale, bool follows_prepare, float* partials,
+                      cudaStream_t s) {
+  const bool bf16 = arm == AttentionArm::BF16, mixed = arm == AttentionArm::MIXED;
   if (batch == 0 || nq == 0) return 0;
   if (nk == 0) return fail("ib_attention: no keys");
   if (nq >= (1u << 30) || nk >= (1u << 30) || batch >= (1u << 20))
@@ -784,10 +810,12 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaSuccess;
-    const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<false, Kind::TF32>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Kind::TF32>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Kind::BF16>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Kind::BF16>)};
+    const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::TF32>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::TF32>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::BF16>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::BF16>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::MIXED>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::MIXED>)};
     for (const void* fn : variants)
       if (err == cudaSuccess)
         err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -816,6 +844,7 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   p.iters_base = tail_iters / ctas;
   p.iters_rem = static_cast<int>(tail_iters % ctas);
   p.o = o;
+  p.v_scale = mixed ? v_scale : nullptr;
   const size_t slots_rows = static_cast<size_t>(2) * ctas * kBQ;
   p.part_o = partials;
   p.part_m = partials + slots_rows * dv;
@@ -824,15 +853,21 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   if (!p.status) return fail("ib_attention: cannot allocate the device status word");
   p.prof = g_attention_profile;
 
+  // K: fp32 (TF32-rounded) unless the whole call is bf16; V^T: fp32 only in the pure TF32 arm
+  // (the 16-bit tensor map serves fp16 as well as bf16: TMA moves the bytes and fills zeros).
+  const size_t k_pitch = bf16 ? d_pitch : d;
   CUtensorMap map_k, map_vt;
   if (bf16) {
-    if (int rc = make_tensor_map_bf16(&map_k, k, batch, nk, d, d_pitch, nk * d_pitch, kBKV)) return rc;
+    if (int rc = make_tensor_map_bf16(&map_k, k, batch, nk, d, k_pitch, nk * k_pitch, kBKV)) return rc;
+  } else {
+    if (int rc = make_tensor_map_f32(&map_k, static_cast<const float*>(k), batch, nk, d, k_pitch,
+                                     nk * k_pitch, kBKV))
+      return rc;
+  }
+  if (bf16 || mixed) {
     if (int rc = make_tensor_map_bf16(&map_vt, vt, batch, dv, nk, nk_pitch, dv * nk_pitch, 128))
       return rc;
   } else {
-    if (int rc = make_tensor_map_f32(&map_k, static_cast<const float*>(k), batch, nk, d, d_pitch,
-                                     nk * d_pitch, kBKV))
-      return rc;
     if (int rc = make_tensor_map_f32(&map_vt, static_cast<const float*>(vt), batch, dv, nk, nk_pitch,
                                      dv * nk_pitch, 128))
       return rc;
@@ -854,14 +889,16 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   cfg.attrs = &overlap;
   cfg.numAttrs = g_dependent_launch && follows_prepare ? 1 : 0;
   cudaError_t launched;
-  if (bf16 && p.prof)
-    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Kind::BF16>, map_k, map_vt, p);
-  else if (bf16)
-    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Kind::BF16>, map_k, map_vt, p);
-  else if (p.prof)
-    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Kind::TF32>, map_k, map_vt, p);
+  const bool prof = p.prof != nullptr;
+  if (bf16)
+    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::BF16>, map_k, map_vt, p)
+                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::BF16>, map_k, map_vt, p);
+  else if (mixed)
+    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::MIXED>, map_k, map_vt, p)
+                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::MIXED>, map_k, map_vt, p);
   else
-    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Kind::TF32>, map_k, map_vt, p);
+    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::TF32>, map_k, map_vt, p)
+                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::TF32>, map_k, map_vt, p);
   if (launched != cudaSuccess)
     return fail(std::string("ib_attention (tcgen05): launch failed: ") + cudaGetErrorString(launched));
   count_launch();

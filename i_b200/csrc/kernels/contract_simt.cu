@@ -10,6 +10,7 @@
 // ib::transpose_batched rewrites [b][r][c] as [b][c][r]; the tensor path uses
 // it to give tcgen05 K-major operands.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 
@@ -322,6 +323,169 @@ prepare_attention_bf16_kernel(PrepareBf16Args a) {
   }
 }
 
+// ---- mixed arm: K rounded to TF32, V^T as fp16 scaled per head into fp16's range ----
+
+// Largest |v| of each head, in kAbsmaxBlocks partial maxima per head (no atomics, nothing to clear).
+__global__ void __launch_bounds__(256)
+absmax_heads_kernel(const float* __restrict__ v, float* __restrict__ block_max, size_t per_head) {
+  __shared__ float warp_max[8];
+  // blockIdx.x = head, blockIdx.y = slice of the head
+  const float* base = v + static_cast<size_t>(blockIdx.x) * per_head;
+  float m = 0.0f;
+  const bool vec = per_head % 4 == 0 && (reinterpret_cast<uintptr_t>(base) & 15u) == 0;
+  const size_t stride = static_cast<size_t>(gridDim.y) * 256;
+  if (vec) {
+    const float4* b4 = reinterpret_cast<const float4*>(base);
+    for (size_t i = static_cast<size_t>(blockIdx.y) * 256 + threadIdx.x; i < per_head / 4; i += stride) {
+      const float4 x = b4[i];                  // plain load: the conversion pass reads V again
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+    }
+  } else {
+    for (size_t i = static_cast<size_t>(blockIdx.y) * 256 + threadIdx.x; i < per_head; i += stride)
+      m = fmaxf(m, fabsf(base[i]));
+  }
+  m = warp_fold<IB_OP_MAX>(m);
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+    block_max[static_cast<size_t>(blockIdx.x) * gridDim.y + blockIdx.y] = m;
+  }
+}
+
+// The power of two that brings a head's largest magnitude into [2^14, 2^15): large values fit
+// fp16 (which holds up to 65504) and small ones keep their mantissa instead of falling into
+// fp16's subnormals.  1 for an all-zero head or one holding inf / NaN (which then propagate as
+// they would anyway).
+__device__ __forceinline__ float f16_scale_for(float absmax) {
+  if (!(absmax > 0.0f) || !(absmax < CUDART_INF_F)) return 1.0f;
+  int e;
+  frexpf(absmax, &e);                          // absmax = f * 2^e, f in [0.5, 1)
+  return ldexpf(1.0f, max(e - 15, -120));      // absmax / scale = f * 2^15
+}
+
+// Every thread returns the scale of head b (reduces that head's partial maxima).
+__device__ __forceinline__ float head_scale(const float* block_max, size_t b, float* scratch) {
+  float m = threadIdx.x < kAbsmaxBlocks ? block_max[b * kAbsmaxBlocks + threadIdx.x] : 0.0f;
+  m = warp_fold<IB_OP_MAX>(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  float all = scratch[0];
+  for (int w = 1; w < 8; ++w) all = fmaxf(all, scratch[w]);
+  return f16_scale_for(all);
+}
+
+__device__ __forceinline__ uint2 pack4_f16(float a, float b, float c, float d) {
+  const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+struct PrepareMixedArgs {
+  const float* k; float* kr; size_t k_elems;
+  const float* v; __half* vt16; float* scale; const float* block_max;
+  size_t batch, nk, dv, nk_pitch;
+  int v_kmajor;
+};
+
+// blockIdx.y = 0 rounds K to TF32; blockIdx.y = 1 writes fp16(V^T / scale[head]) — through 64x64
+// shared-memory tiles when V is [keys][dv], as plain rows when it is already [dv][keys].
+__global__ void __launch_bounds__(256)
+prepare_attention_mixed_kernel(PrepareMixedArgs a) {
+  __shared__ float tile[64][65];
+  __shared__ float scratch[8];
+  sm100::trigger_dependent_launch();       // see prepare_attention_kernel
+  if (blockIdx.y == 0) {
+    const size_t n4 = a.k_elems / 4;          // d is a multiple of 4
+    const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+    const bool vec = (reinterpret_cast<uintptr_t>(a.k) & 15u) == 0;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n4; i += stride) {
+      float4 x;
+      if (vec) {
+        x = __ldcs(reinterpret_cast<const float4*>(a.k) + i);
+      } else {
+        x = make_float4(a.k[4 * i], a.k[4 * i + 1], a.k[4 * i + 2], a.k[4 * i + 3]);
+      }
+      x.x = round_tf32(x.x); x.y = round_tf32(x.y); x.z = round_tf32(x.z); x.w = round_tf32(x.w);
+      reinterpret_cast<float4*>(a.kr)[i] = x;
+    }
+    return;
+  }
+  if (a.v_kmajor) {
+    // Rows [batch * dv][nk] -> [batch * dv][nk_pitch], one row per block at a time.
+    const size_t quads = a.nk_pitch / 4;
+    const bool vec = a.nk % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
+    size_t scaled_for = static_cast<size_t>(-1);
+    float inv = 1.0f;
+    for (size_t row = blockIdx.x; row < a.batch * a.dv; row += gridDim.x) {
+      const size_t b = row / a.dv;
+      if (b != scaled_for) {
+        inv = 1.0f / head_scale(a.block_max, b, scratch);
+        scaled_for = b;
+      }
+      if (row == b * a.dv && threadIdx.x == 0) a.scale[b] = 1.0f / inv;
+      for (size_t q = threadIdx.x; q < quads; q += 256) {
+        const size_t c = q * 4;
+        const float* src = a.v + row * a.nk + c;
+        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (vec && c + 4 <= a.nk) {
+          x = __ldcs(reinterpret_cast<const float4*>(src));
+        } else {
+          if (c + 0 < a.nk) x.x = src[0];
+          if (c + 1 < a.nk) x.y = src[1];
+          if (c + 2 < a.nk) x.z = src[2];
+          if (c + 3 < a.nk) x.w = src[3];
+        }
+        *reinterpret_cast<uint2*>(a.vt16 + row * a.nk_pitch + c) =
+            pack4_f16(x.x * inv, x.y * inv, x.z * inv, x.w * inv);
+      }
+    }
+    return;
+  }
+  const size_t tiles_k = (a.nk_pitch + 63) / 64, tiles_d = (a.dv + 63) / 64;
+  const size_t total = a.batch * tiles_k * tiles_d;
+  const bool vec_in = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
+  size_t scaled_for = static_cast<size_t>(-1);
+  float inv = 1.0f;
+  for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const size_t b = t / (tiles_k * tiles_d);
+    const size_t rem = t - b * tiles_k * tiles_d;
+    if (b != scaled_for) {
+      inv = 1.0f / head_scale(a.block_max, b, scratch);
+      scaled_for = b;
+    }
+    if (rem == 0 && threadIdx.x == 0) a.scale[b] = 1.0f / inv;   // the block with the head's first tile
+    const size_t k0 = (rem / tiles_d) * 64, d0 = (rem % tiles_d) * 64;
+    const float* src = a.v + b * a.nk * a.dv;
+    __half* dst = a.vt16 + b * a.dv * a.nk_pitch;
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int r = e >> 4, c = (e & 15) * 4;           // r: key, c: feature (contiguous in V)
+      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (k0 + r < a.nk) {
+        const float* row = src + (k0 + r) * a.dv + d0 + c;
+        if (vec_in && d0 + c + 4 <= a.dv) {
+          x = __ldcs(reinterpret_cast<const float4*>(row));
+        } else {
+          if (d0 + c + 0 < a.dv) x.x = row[0];
+          if (d0 + c + 1 < a.dv) x.y = row[1];
+          if (d0 + c + 2 < a.dv) x.z = row[2];
+          if (d0 + c + 3 < a.dv) x.w = row[3];
+        }
+      }
+      tile[r][c + 0] = x.x * inv; tile[r][c + 1] = x.y * inv;
+      tile[r][c + 2] = x.z * inv; tile[r][c + 3] = x.w * inv;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int c = e >> 4, r = (e & 15) * 4;           // c: feature, r: first key of the group
+      if (d0 + c < a.dv && k0 + r < a.nk_pitch)
+        *reinterpret_cast<uint2*>(dst + (d0 + c) * a.nk_pitch + k0 + r) =
+            pack4_f16(tile[r][c], tile[r + 1][c], tile[r + 2][c], tile[r + 3][c]);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
 
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
@@ -340,6 +504,23 @@ int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, v
   dim3 grid(static_cast<unsigned>(std::min(most, cap)), 2);
   prepare_attention_bf16_kernel<<<grid, 256, 0, s>>>(a);
   return check_launch("prepare_attention_operands_bf16");
+}
+
+int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, void* vt16,
+                                     float* scale, float* block_max, size_t batch, size_t nk,
+                                     size_t d, size_t dv, size_t nk_pitch, bool v_kmajor,
+                                     cudaStream_t s) {
+  dim3 agrid(static_cast<unsigned>(batch), kAbsmaxBlocks);
+  absmax_heads_kernel<<<agrid, 256, 0, s>>>(v, block_max, nk * dv);
+  if (int rc = check_launch("absmax_heads")) return rc;
+  PrepareMixedArgs a{k, kr, batch * nk * d, v, static_cast<__half*>(vt16), scale, block_max,
+                     batch, nk, dv, nk_pitch, v_kmajor ? 1 : 0};
+  const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64);
+  const size_t most = std::max(batch * nk * d / 4 / 256 + 1, v_blocks);
+  const size_t cap = static_cast<size_t>(kNumSMs) * 8;
+  dim3 grid(static_cast<unsigned>(std::min(most, cap)), 2);
+  prepare_attention_mixed_kernel<<<grid, 256, 0, s>>>(a);
+  return check_launch("prepare_attention_operands_mixed");
 }
 
 int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,

@@ -39,28 +39,42 @@ bool attention_shape_ok(size_t d, size_t dv) {
   return d % 4 == 0 && d >= 4 && d <= 128 && dv >= 1 && dv <= 128;
 }
 
-// The attention kernel's K and V operands: rounded (TF32) or converted (BF16)
-// copies, V transposed to [dv][keys].
+// Which arithmetic the fused attention kernel uses for a precision request: AUTO and
+// TF32_F16 take the mixed arm (TF32 for Q K^T, fp16 with TF32's mantissa for P V), TF32 the
+// pure TF32 arm, BF16 the bf16 arm.
+AttentionArm attention_arm(int precision) {
+  if (precision == IB_PRECISION_BF16) return AttentionArm::BF16;
+  if (precision == IB_PRECISION_TF32) return AttentionArm::TF32;
+  return AttentionArm::MIXED;
+}
+
+// The attention kernel's K and V operands: rounded (TF32), converted (BF16) or mixed copies,
+// V transposed to [dv][keys]; the mixed arm also keeps one scale per head.
 struct PreparedKV {
   const void* k = nullptr;
   const void* vt = nullptr;
+  const float* v_scale = nullptr;
   size_t d_pitch = 0, nk_pitch = 0;
-  bool bf16 = false;
+  AttentionArm arm = AttentionArm::TF32;
 };
 
-size_t prepared_kv_bytes(size_t batch, size_t nk, size_t d, size_t dv, bool bf16) {
-  if (bf16)
+size_t prepared_kv_bytes(size_t batch, size_t nk, size_t d, size_t dv, AttentionArm arm) {
+  if (arm == AttentionArm::BF16)
     return carve_bytes((batch * nk * round_up(d, 8) + 1) / 2) +
            carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2);
+  if (arm == AttentionArm::MIXED)
+    return carve_bytes(batch * nk * d) + carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2) +
+           carve_bytes(batch) + carve_bytes(batch * kAbsmaxBlocks);
   return carve_bytes(batch * nk * d) + carve_bytes(batch * dv * round_up(nk, 4));
 }
 
-// Carves the two copies out of `ws`; with `fill` it also launches the kernels that write them.
+// Carves the copies out of `ws`; with `fill` it also launches the kernels that write them.
 int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t d, size_t dv,
-                bool v_kmajor, bool bf16, bool fill, Carver& ws, PreparedKV* out, cudaStream_t s) {
+                bool v_kmajor, AttentionArm arm, bool fill, Carver& ws, PreparedKV* out,
+                cudaStream_t s) {
   const char* small = "ib_attention: workspace too small (see the matching *_bytes function)";
-  out->bf16 = bf16;
-  if (bf16) {
+  out->arm = arm;
+  if (arm == AttentionArm::BF16) {
     // Opt-in: bf16 operands (round to nearest even), fp32 scores, sums and outputs.
     out->d_pitch = round_up(d, 8);
     out->nk_pitch = round_up(nk, 8);
@@ -73,10 +87,27 @@ int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t 
     return prepare_attention_operands_bf16(k, k16, v, vt16, batch, nk, d, dv, out->d_pitch,
                                            out->nk_pitch, v_kmajor, s);
   }
-  // The tensor core truncates fp32 operands to TF32.  K and V are first rounded
-  // to nearest into workspace copies (V transposed to [dv][keys] on the way,
-  // the K-major layout the second contraction needs); the kernel rounds Q
-  // itself while moving it into tensor memory.
+  if (arm == AttentionArm::MIXED) {
+    // K rounded to TF32; V^T as fp16 of V / scale[head], the scale a power of two that brings
+    // the head's largest magnitude into [2^14, 2^15).
+    out->d_pitch = d;
+    out->nk_pitch = round_up(nk, 8);
+    float* kr = ws.take(batch * nk * d);
+    float* vt16 = ws.take((batch * dv * out->nk_pitch + 1) / 2);
+    float* scale = ws.take(batch);
+    float* block_max = ws.take(batch * kAbsmaxBlocks);
+    if (!kr || !vt16 || !scale || !block_max) return fail(small);
+    out->k = kr;
+    out->vt = vt16;
+    out->v_scale = scale;
+    if (!fill) return 0;
+    return prepare_attention_operands_mixed(k, kr, v, vt16, scale, block_max, batch, nk, d, dv,
+                                            out->nk_pitch, v_kmajor, s);
+  }
+  // Pure TF32.  The tensor core truncates fp32 operands to TF32, so K and V are first rounded
+  // to nearest into workspace copies (V transposed to [dv][keys] on the way, the K-major
+  // layout the second contraction needs); the kernel rounds Q itself while moving it into
+  // tensor memory.
   out->d_pitch = d;
   out->nk_pitch = round_up(nk, 4);
   float* kr = ws.take(batch * nk * d);
@@ -100,6 +131,7 @@ int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t 
 extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, size_t k,
                                               int a_kmajor, int b_kmajor, int precision) {
   using namespace ib;
+  if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
   const double flop = 2.0 * batch * m * n * k;
   if (!wants_tensor(precision, flop)) return 0;
   if (precision == IB_PRECISION_BF16) {
@@ -123,8 +155,9 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
   using namespace ib;
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!a || !b || !c) return fail("ib_contract: null pointer");
-  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_TF32_F16)
     return fail("ib_contract: unknown precision");
+  if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (k == 0) {
     cudaError_t err = cudaMemsetAsync(c, 0, batch * m * n * sizeof(float), s);
@@ -188,7 +221,7 @@ extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t n
   if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
     // Rounded copy of K, V^T (rounded), and the KV-split partials; bf16 copies
     // are half the size, with pitches rounded up to 8 elements.
-    return prepared_kv_bytes(batch, nk, d, dv, precision == IB_PRECISION_BF16) +
+    return prepared_kv_bytes(batch, nk, d, dv, attention_arm(precision)) +
            carve_bytes(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
   }
   // Unfused: S = Q K^T, softmax in place, O = S V.
@@ -207,7 +240,7 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
   if (batch == 0 || nq == 0 || dv == 0) return 0;
   if (!q || !k || !v || !o) return fail("ib_attention: null pointer");
   if (nk == 0 || d == 0) return fail("ib_attention: empty key or feature axis");
-  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_TF32_F16)
     return fail("ib_attention: unknown precision");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (reinterpret_cast<uintptr_t>(workspace) & 255u)
@@ -218,14 +251,14 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
 
   if (tensor && attention_shape_ok(d, dv)) {
     PreparedKV kv;
-    if (int rc = prepared_kv(k, v, batch, nk, d, dv, v_kmajor != 0, precision == IB_PRECISION_BF16,
-                             true, ws, &kv, s))
+    if (int rc = prepared_kv(k, v, batch, nk, d, dv, v_kmajor != 0, attention_arm(precision), true,
+                             ws, &kv, s))
       return rc;
     float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
     if (!partials)
       return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
     return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch,
-                             kv.bf16, true, partials, s);
+                             kv.arm, kv.v_scale, true, partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);
@@ -242,7 +275,7 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
 
 extern "C" size_t ib_attention_prepare_bytes(size_t batch, size_t nk, size_t d, size_t dv,
                                              int precision) {
-  return ib::prepared_kv_bytes(batch, nk, d, dv, precision == IB_PRECISION_BF16);
+  return ib::prepared_kv_bytes(batch, nk, d, dv, ib::attention_arm(precision));
 }
 
 extern "C" int ib_attention_prepare(const float* k, const float* v, size_t batch, size_t nk,
@@ -253,14 +286,15 @@ extern "C" int ib_attention_prepare(const float* k, const float* v, size_t batch
   if (!k || !v) return fail("ib_attention_prepare: null pointer");
   if (nk == 0 || !attention_shape_ok(d, dv))
     return fail("ib_attention_prepare: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
-  if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
-    return fail("ib_attention_prepare: the two-phase form exists for the tensor arms (auto, tf32, bf16)");
+  if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO ||
+      precision > IB_PRECISION_TF32_F16)
+    return fail("ib_attention_prepare: the two-phase form exists for the tensor arms (auto, tf32, bf16, tf32_f16)");
   if (reinterpret_cast<uintptr_t>(prepared) & 255u)
     return fail("ib_attention_prepare: buffer must be 256-byte aligned");
   Carver ws(prepared, prepared_bytes);
   PreparedKV kv;
-  return prepared_kv(k, v, batch, nk, d, dv, v_kmajor != 0, precision == IB_PRECISION_BF16, true, ws,
-                     &kv, static_cast<cudaStream_t>(stream));
+  return prepared_kv(k, v, batch, nk, d, dv, v_kmajor != 0, attention_arm(precision), true, ws, &kv,
+                     static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t ib_attention_run_workspace_bytes(size_t batch, size_t nq, size_t nk, size_t dv) {
@@ -275,22 +309,23 @@ extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, 
   if (!q || !prepared || !o) return fail("ib_attention_run: null pointer");
   if (nk == 0 || !attention_shape_ok(d, dv))
     return fail("ib_attention_run: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
-  if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO || precision > IB_PRECISION_BF16)
-    return fail("ib_attention_run: the two-phase form exists for the tensor arms (auto, tf32, bf16)");
+  if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO ||
+      precision > IB_PRECISION_TF32_F16)
+    return fail("ib_attention_run: the two-phase form exists for the tensor arms (auto, tf32, bf16, tf32_f16)");
   if ((reinterpret_cast<uintptr_t>(prepared) | reinterpret_cast<uintptr_t>(workspace)) & 255u)
     return fail("ib_attention_run: buffers must be 256-byte aligned");
-  const bool bf16 = precision == IB_PRECISION_BF16;
+  const AttentionArm arm = attention_arm(precision);
   // Same carving as ib_attention_prepare, without touching the contents.
-  Carver held(const_cast<void*>(prepared), prepared_kv_bytes(batch, nk, d, dv, bf16));
+  Carver held(const_cast<void*>(prepared), prepared_kv_bytes(batch, nk, d, dv, arm));
   PreparedKV kv;
-  if (int rc = prepared_kv(nullptr, nullptr, batch, nk, d, dv, false, bf16, false, held, &kv, nullptr))
+  if (int rc = prepared_kv(nullptr, nullptr, batch, nk, d, dv, false, arm, false, held, &kv, nullptr))
     return rc;
   Carver ws(workspace, workspace_bytes);
   float* partials = ws.take(attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
   if (!partials)
     return fail("ib_attention_run: workspace too small (see ib_attention_run_workspace_bytes)");
-  return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch, bf16,
-                           false, partials, static_cast<cudaStream_t>(stream));
+  return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch, kv.arm,
+                           kv.v_scale, false, partials, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ib_attention_uses_tensor_arm(size_t batch, size_t nq, size_t nk, size_t d, size_t dv,

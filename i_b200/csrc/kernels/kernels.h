@@ -64,12 +64,24 @@ int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size
 // Floats of scratch for the partial results of row tiles shared between CTAs.
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv,
                                         int* ctas_out);
-// With bf16 = true, k and vt hold bf16 ([b][nk][d_pitch] and [b][dv][nk_pitch], pitches multiples
-// of 8) and the contractions run as kind::f16.  follows_prepare: the kernel before this call in
-// the stream is the one that wrote k and vt (the launch may then overlap its tail).
+// Operand types: TF32 — k, vt fp32 rounded to TF32 ([b][nk][d], [b][dv][nk_pitch], pitch % 4 == 0);
+// BF16 — both bf16 ([b][nk][d_pitch], [b][dv][nk_pitch], pitches % 8 == 0), kind::f16 MMAs;
+// MIXED — k as in TF32, vt fp16 holding V / v_scale[head] (nk_pitch % 8 == 0): S = Q K^T in TF32,
+// O += P V in fp16 (same 10-bit mantissa).  follows_prepare: the kernel before this call in the
+// stream is the one that wrote k and vt (the launch may then overlap its tail).
+enum class AttentionArm { TF32, BF16, MIXED };
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      bool bf16, bool follows_prepare, float* partials, cudaStream_t s);
+                      AttentionArm arm, const float* v_scale, bool follows_prepare, float* partials,
+                      cudaStream_t s);
+// Mixed-arm operand preparation: kr = K rounded to TF32; vt16[b][c][nk_pitch] = fp16(V^T / scale[b])
+// with scale[b] the power of two that brings the head's largest |V| into [2^14, 2^15); block_max
+// is scratch of batch * kAbsmaxBlocks floats.
+constexpr int kAbsmaxBlocks = 64;
+int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, void* vt16,
+                                     float* scale, float* block_max, size_t batch, size_t nk,
+                                     size_t d, size_t dv, size_t nk_pitch, bool v_kmajor,
+                                     cudaStream_t s);
 // bf16 operand preparation: k16[b][r][d_pitch] = bf16(k), vt16[b][c][nk_pitch] = bf16(v^T);
 // pad columns are zeroed.
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,

@@ -231,6 +231,13 @@ __host__ __device__ constexpr uint32_t make_idesc(Kind kind, uint32_t m, uint32_
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// Operand element formats of the instruction descriptor (A and B take the same one here).
+enum class Fmt : uint32_t { F16 = 0, BF16 = 1, TF32 = 2 };
+__host__ __device__ constexpr uint32_t make_idesc_fmt(Fmt fmt, uint32_t m, uint32_t n) {
+  const uint32_t f = static_cast<uint32_t>(fmt);
+  return (1u << 4) | (f << 7) | (f << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
 // 64-bit shared-memory matrix descriptor for a K-major operand stored as rows
 // of 128 bytes with the 128-byte swizzle (what a TMA box of 128 bytes x rows
 // with CU_TENSOR_MAP_SWIZZLE_128B writes):
@@ -296,6 +303,14 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+
+// The same with the instruction kind chosen by the operand width: 16-bit operands (fp16 or
+// bf16, told apart by the descriptor's format field) issue as kind::f16, fp32 ones as kind::tf32.
+template <bool HALF>
+__device__ __forceinline__ void mma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  mma_ts<HALF ? Kind::BF16 : Kind::TF32>(d_tmem, a_tmem, b_desc, idesc, accumulate);
 }
 
 // Makes `bar` receive one arrival when all MMAs issued so far by this thread

@@ -18,7 +18,7 @@ from conftest import last_error, max_rel_elementwise, max_rel_to_peak
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-FP32, TF32, BF16 = 1, 2, 3
+FP32, TF32, BF16, TF32_F16 = 1, 2, 3, 4
 TOL_MAP = 1e-5
 TOL_FP32 = 1e-5
 TOL_TF32 = 5e-3
@@ -365,7 +365,8 @@ def run_attention(lib, torch, q, k, v, precision, v_kmajor=False):
 
 
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "attention_*.npz"))))
-@pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32), (BF16, TOL_BF16)])
+@pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32), (BF16, TOL_BF16),
+                                           (TF32_F16, TOL_TF32)])
 def test_attention_golden(lib, torch, path, precision, tol):
     g = np.load(path)
     got = run_attention(lib, torch, g["q"], g["k"], g["v"], precision)
@@ -406,6 +407,39 @@ def test_attention_tf32_random_shapes(lib, oracle, torch):
 
 
 @pytest.mark.parametrize("nq,nk,d,dv", [
+    (256, 64, 64, 64), (512, 512, 128, 128), (300, 200, 40, 24), (1, 1, 4, 1), (129, 65, 8, 100),
+    (1000, 3000, 128, 128), (64, 4096, 32, 16),
+])
+def test_attention_tf32_f16_shapes(lib, oracle, torch, nq, nk, d, dv):
+    # S = Q K^T in TF32, O += P V in fp16 (same mantissa): held to the TF32 bound.
+    q = rand((nq, d), 15) * np.float32(d ** -0.5)
+    k, v = rand((nk, d), 16), rand((nk, dv), 17)
+    got = run_attention(lib, torch, q, k, v, TF32_F16)
+    assert not np.isnan(got).any()
+    assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= TOL_TF32
+
+
+@pytest.mark.parametrize("scale", [1e-30, 1e-6, 1.0, 3.0e4, 7.0e4, 1e9, 1e30])
+@pytest.mark.parametrize("v_kmajor", [False, True])
+def test_attention_tf32_f16_value_range(lib, oracle, torch, scale, v_kmajor):
+    # V is scaled per head by a power of two so that its largest magnitude sits just under 2^15:
+    # magnitudes far outside fp16's range (6e-5 .. 65504) in either direction must come out as
+    # accurately as ordinary ones, and heads with different magnitudes must not affect each other.
+    nq, nk, d, dv = 200, 333, 64, 40
+    q = rand((2, nq, d), 61) * np.float32(d ** -0.5)
+    k = rand((2, nk, d), 62)
+    v = rand((2, nk, dv), 63)
+    v[0] *= np.float32(scale)
+    v[0, 5, 3] = np.float32(scale) * 20           # one outlier sets the head's scale
+    ref = [oracle.attention_fused(q[b], k[b], v[b]) for b in range(2)]
+    vin = np.ascontiguousarray(np.swapaxes(v, 1, 2)) if v_kmajor else v
+    got = run_attention(lib, torch, q, k, vin, TF32_F16, v_kmajor=v_kmajor)
+    assert np.isfinite(got).all()
+    for b in range(2):
+        assert max_rel_to_peak(got[b], ref[b]) <= TOL_TF32, (b, scale)
+
+
+@pytest.mark.parametrize("nq,nk,d,dv", [
     (256, 128, 64, 64), (512, 512, 128, 128), (300, 200, 40, 24), (129, 65, 8, 100),
     (1000, 3000, 128, 128),
 ])
@@ -434,7 +468,7 @@ def test_attention_tf32_batched_and_transposed_v(lib, oracle, torch):
         assert max_rel_to_peak(got_bt[i], ref) <= TOL_BF16
 
 
-@pytest.mark.parametrize("precision,tol", [(TF32, TOL_TF32), (BF16, TOL_BF16)])
+@pytest.mark.parametrize("precision,tol", [(TF32, TOL_TF32), (BF16, TOL_BF16), (TF32_F16, TOL_TF32)])
 @pytest.mark.parametrize("v_kmajor", [False, True])
 def test_attention_two_phase_matches_one_call(lib, oracle, torch, precision, tol, v_kmajor):
     # K and V prepared once, query rows attended in ragged blocks: same rows as one ib_attention.
