@@ -329,6 +329,9 @@ prepare_attention_bf16_kernel(PrepareBf16Args a) {
 __global__ void __launch_bounds__(256)
 absmax_heads_kernel(const float* __restrict__ v, float* __restrict__ block_max, size_t per_head) {
   __shared__ float warp_max[8];
+  // The conversion kernel behind this one may start now: its K half does not need these maxima,
+  // its V half waits for this grid before it reads them.
+  sm100::trigger_dependent_launch();
   // blockIdx.x = head, blockIdx.y = slice of the head
   const float* base = v + static_cast<size_t>(blockIdx.x) * per_head;
   float m = 0.0f;
@@ -411,6 +414,7 @@ prepare_attention_mixed_kernel(PrepareMixedArgs a) {
     }
     return;
   }
+  sm100::grid_dependency_wait();           // the per-head maxima come from the kernel before this one
   if (a.v_kmajor) {
     // Rows [batch * dv][nk] -> [batch * dv][nk_pitch], one row per block at a time.
     const size_t quads = a.nk_pitch / 4;
@@ -518,9 +522,20 @@ int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, 
   const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64);
   const size_t most = std::max(batch * nk * d / 4 / 256 + 1, v_blocks);
   const size_t cap = static_cast<size_t>(kNumSMs) * 8;
-  dim3 grid(static_cast<unsigned>(std::min(most, cap)), 2);
-  prepare_attention_mixed_kernel<<<grid, 256, 0, s>>>(a);
-  return check_launch("prepare_attention_operands_mixed");
+  // Launched so that it may overlap the maxima kernel (see the wait in its V half).
+  cudaLaunchAttribute overlap{};
+  overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  overlap.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(std::min(most, cap)), 2);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cfg.attrs = &overlap;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, prepare_attention_mixed_kernel, a) != cudaSuccess)
+    return fail(std::string("prepare_attention_operands_mixed: ") + cudaGetErrorString(cudaGetLastError()));
+  count_launch();
+  return 0;
 }
 
 int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,

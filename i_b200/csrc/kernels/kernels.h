@@ -77,7 +77,7 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
 // Mixed-arm operand preparation: kr = K rounded to TF32; vt16[b][c][nk_pitch] = fp16(V^T / scale[b])
 // with scale[b] the power of two that brings the head's largest |V| into [2^14, 2^15); block_max
 // is scratch of batch * kAbsmaxBlocks floats.
-constexpr int kAbsmaxBlocks = 64;
+constexpr int kAbsmaxBlocks = 256;   // partial maxima per head (= threads of the block that folds them)
 int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, void* vt16,
                                      float* scale, float* block_max, size_t batch, size_t nk,
                                      size_t d, size_t dv, size_t nk_pitch, bool v_kmajor,
