@@ -42,7 +42,7 @@ WORKLOAD = "config4: single-head fused i-attention, seq_q=seq_kv=16384, d=128, f
 ROTATION = 8          # distinct input sets: 8 x 32 MiB = 256 MiB > 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention_tf32_kernel launch on this
 # workload, from the ncu capture summarised in profiles/attention_tf32_kernel_seq16384_d128.md.
-ATTENTION_DRAM_BYTES_PER_LAUNCH = 25242112
+ATTENTION_DRAM_BYTES_PER_LAUNCH = {"tf32+f16": 21210624, "tf32": 25411584}
 
 
 def load_peaks():
@@ -501,7 +501,7 @@ def run_gpu_arm(args):
         peak_text = ("%s bf16_tflops %.1f / 2 (TF32 MMA issues at half the bf16 rate)"
                      % (peaks["source"], peaks["bf16_tflops"]))
     achieved = flop_per_step / ms_per_step / 1e9
-    traffic = ATTENTION_DRAM_BYTES_PER_LAUNCH if (heads == 1 and SEQ == 16384) else None
+    traffic = ATTENTION_DRAM_BYTES_PER_LAUNCH.get(arm_dtype) if (heads == 1 and SEQ == 16384) else None
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
