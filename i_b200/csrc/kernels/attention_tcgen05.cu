@@ -182,6 +182,12 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   return out;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+
 // Two fp16 exponentials (2^x) in one special-function instruction.
 __device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
   uint32_t y;
@@ -544,13 +550,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
             if (col0 + 32 + c >= p.nk) s1[c] = __float_as_uint(-CUDART_INF_F);
           }
         }
+        // Three-operand maximum: 32 instructions for the 64 values instead of 64.
         float mx0 = -CUDART_INF_F, mx1 = mx0, mx2 = mx0, mx3 = mx0;
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
-          mx1 = fmaxf(mx1, __uint_as_float(s0[c + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(s1[c]));
-          mx3 = fmaxf(mx3, __uint_as_float(s1[c + 1]));
+        for (int c = 0; c < 32; c += 4) {
+          mx0 = max3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(s0[c + 2]), __uint_as_float(s0[c + 3]));
+          mx2 = max3(mx2, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+          mx3 = max3(mx3, __uint_as_float(s1[c + 2]), __uint_as_float(s1[c + 3]));
         }
         mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         sh->half_max[buf][h][r] = mx;
