@@ -252,3 +252,19 @@ def test_concurrent_exec_from_threads(ilang, oracle):
         outs = list(pool.map(sm.exec_numpy, xs))
     for x, o in zip(xs, outs):
         assert max_rel_elementwise(o, oracle.row_softmax(x)) <= 1e-5
+
+
+def test_concurrent_pipelined_attention_from_threads(ilang):
+    # Several host threads run the copy/compute pipeline of host-buffer attention at once (each
+    # thread has its own three streams); results must not mix.
+    from concurrent.futures import ThreadPoolExecutor
+    attn = readme_attention(ilang)
+    cases = []
+    for s in range(6):
+        q = rand((4096, 128), 70 + s) * np.float32(128 ** -0.5)
+        cases.append((q, rand((2048, 128), 80 + s), rand((2048, 128), 90 + s)))
+    with ThreadPoolExecutor(3) as pool:
+        outs = list(pool.map(lambda c: attn.exec_numpy(*c), cases))
+    for (q, k, v), o in zip(cases, outs):
+        assert max_rel_to_peak(o, np_attention(q, k, v)) <= 5e-3
+
