@@ -29,9 +29,12 @@
 //               partial row sum until the end.  O is rescaled in tensor memory
 //               only when the maximum grows by more than 2^8.
 // Tensor memory (512 columns): Q 128 | S buffer 0 128 | S buffer 1 128 | O 128.
-// Q is loaded from global memory by the softmax threads, rounded to TF32 and
-// stored to tensor memory once.  K/V rows past the end are zero-filled by TMA
-// and masked to -inf; query rows past the end are computed and not stored.
+// Q is loaded from global memory by the softmax threads, rounded to the operand
+// type and stored to tensor memory once per row tile: for the first row tile of a
+// CTA at kernel start, for every later one as soon as the last Q K^T of the row
+// tile before has been consumed, i.e. before that row tile's O is read out, so
+// the next Q K^T overlaps the read-out.  K/V rows past the end are zero-filled by
+// TMA and masked to -inf; query rows past the end are computed and not stored.
 //
 // Work is balanced over the SMs.  CTA g of G first takes whole row tiles
 // g, g+G, g+2G, ... (neighbouring CTAs then stream the same head's K/V at the
@@ -114,6 +117,7 @@ struct Params {
 struct Shared {
   uint64_t kv_full[kMaxRing];
   uint64_t q_ready;
+  uint64_t o_free;           // the epilogue of a piece has read O
   uint64_t s_full[2];
   uint64_t p_full[2];
   uint64_t pv_done[2];       // [KV tile parity]: see the note at its wait
@@ -246,6 +250,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       mbar_init(&sh->kv_full[s], 1);
     }
     mbar_init(&sh->q_ready, 8);            // one arrival per softmax warp
+    mbar_init(&sh->o_free, 8);
     for (int u = 0; u < 2; ++u) {
       mbar_init(&sh->s_full[u], 1);
       mbar_init(&sh->p_full[u], 8);
@@ -387,10 +392,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
       // O += P[buf] V from the V^T tile in the current slot (A = P in tensor memory).
-      auto issue_pv = [&](long long t, bool first_of_piece) {
+      auto issue_pv = [&](long long t, bool first_of_piece, int piece) {
         const int buf = static_cast<int>(t & 1);
         long long t0 = tick<PROF>();
         if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) return;
+        // The first P V of a piece overwrites O: the piece before must have read it out.
+        if (first_of_piece && piece > 0 &&
+            !(ok = mbar_wait(&sh->o_free, static_cast<uint32_t>((piece - 1) & 1), abort, p.status, 210)))
+          return;
         wait_v += tick<PROF>() - t0;
         t0 = tick<PROF>();
         if (!(ok = mbar_wait(&sh->p_full[buf], (t >> 1) & 1, abort, p.status, 206))) return;
@@ -424,7 +433,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       Piece pc;
       for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
         const int n_kv = pc.n_kv;
-        // Q of this piece is in tensor memory (and the previous piece's O has been read).
+        // Q of this piece is in tensor memory.
         const long long tq = tick<PROF>();
         if (!(ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 203))) break;
         wait_q += tick<PROF>() - tq;
@@ -432,7 +441,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         issue_qk(static_cast<int>(it & 1));
         for (int jj = 0; ok && jj < n_kv; ++jj) {
           if (jj + 1 < n_kv) issue_qk(static_cast<int>((it + jj + 1) & 1));
-          if (ok) issue_pv(it + jj, jj == 0);
+          if (ok) issue_pv(it + jj, jj == 0, piece);
         }
         it += n_kv;
       }
@@ -459,19 +468,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     const long long t_start = tick<PROF>();
     bool dead = false;                        // a wait gave up; keep hitting the barriers only
 
-    PieceCursor cursor = pieces_begin(p);
-    Piece pc;
-    while (next_piece(p, cursor, pc)) {
-    const int kv_lo = pc.kv_lo, n_kv = pc.n_kv;
-    const int b = pc.unit / p.q_tiles;
-    const int qt = pc.unit - b * p.q_tiles;
-    const long long row = static_cast<long long>(qt) * kBQ + r;
-    const bool whole = pc.whole;
-    const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
-
-    // ---- Q: global -> TF32 (nearest) -> tensor memory, columns [64h, 64h+64) ----
-    {
-      const float* qrow = p.q + (static_cast<size_t>(b) * p.nq + row) * p.d;
+    // Q of one row tile: global -> operand type (nearest) -> tensor memory, this thread's 64
+    // features [64h, 64h+64) of its row; then one arrival per warp on q_ready.
+    auto stage_q = [&](int head, int q_tile) {
+      const long long row = static_cast<long long>(q_tile) * kBQ + r;
+      const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
       const bool live = row < p.nq;
       const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
       // This thread's 64 features [64h, 64h+64) of its row, rounded to the operand type.
@@ -517,7 +518,21 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->q_ready);
-    }
+    };
+
+    PieceCursor cursor = pieces_begin(p);
+    Piece pc;
+    bool first_piece = true;
+    while (next_piece(p, cursor, pc)) {
+    const int kv_lo = pc.kv_lo, n_kv = pc.n_kv;
+    const int b = pc.unit / p.q_tiles;
+    const int qt = pc.unit - b * p.q_tiles;
+    const long long row = static_cast<long long>(qt) * kBQ + r;
+    const bool whole = pc.whole;
+    const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
+
+    if (first_piece) stage_q(b, qt);        // later pieces: staged at the end of the piece before
+    first_piece = false;
 
     float m_used = -CUDART_INF_F;             // running maximum, log2 domain
     float l = 0.0f;                           // this half's share of the row sum
@@ -673,6 +688,18 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       c_store += tick<PROF>() - tp;
     }
 
+    // ---- Q of the next piece, before this one's epilogue: every Q K^T of this piece has
+    // completed (its S was read above), so Q's columns are free, and the MMA warp can run
+    // the next piece's first Q K^T while O is being read out below.
+    {
+      PieceCursor ahead = cursor;
+      Piece nx;
+      if (!dead && next_piece(p, ahead, nx)) {
+        const int nb = nx.unit / p.q_tiles;
+        stage_q(nb, nx.unit - nb * p.q_tiles);
+      }
+    }
+
     // ---- epilogue: total row sum, normalise, store columns [64h, 64h+64) of O ----
     if (!sh->give_up && !dead) {
       const long long last = it + n_kv - 1;
@@ -717,9 +744,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       }
     }
     if (sh->give_up) break;
-    // The epilogue's reads of O must land before the next piece's P V overwrites it;
-    // they are ordered before this thread's next arrival on q_ready.
+    // The epilogue's reads of O are complete (tcgen05.wait::ld above): the next piece's first
+    // P V may overwrite it.
     tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sh->o_free);
     it += n_kv;
     }  // pieces
     if (PROF && p.prof && quad == 0 && lane == 0 && h == 0) {
