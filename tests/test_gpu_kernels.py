@@ -439,6 +439,25 @@ def test_attention_tf32_f16_value_range(lib, oracle, torch, scale, v_kmajor):
         assert max_rel_to_peak(got[b], ref[b]) <= TOL_TF32, (b, scale)
 
 
+@pytest.mark.parametrize("v_kmajor", [False, True])
+def test_attention_tf32_f16_columns_of_different_magnitude(lib, oracle, torch, v_kmajor):
+    # The fp16 scaling of V is one power of two per head, chosen from the head's largest magnitude;
+    # fp16 then keeps full precision for values down to 2^-29 of that.  Columns whose magnitudes
+    # differ by six decades must each come out within the TF32 bound of their own peak.
+    nq, nk, d, dv = 300, 500, 64, 37
+    q = rand((nq, d), 64) * np.float32(d ** -0.5)
+    k, v = rand((nk, d), 65), rand((nk, dv), 66)
+    mags = np.float32(10.0) ** np.linspace(-3, 3, dv).astype(np.float32)
+    v = v * mags[None, :]
+    ref = oracle.attention_fused(q, k, v)
+    vin = np.ascontiguousarray(v.T) if v_kmajor else v
+    got = run_attention(lib, torch, q, k, vin, TF32_F16, v_kmajor=v_kmajor)
+    assert np.isfinite(got).all()
+    for c in range(dv):
+        err = np.abs(got[:, c] - ref[:, c]).max() / np.abs(ref[:, c]).max()
+        assert err <= TOL_TF32, (c, float(mags[c]), float(err))
+
+
 @pytest.mark.parametrize("nq,nk,d,dv", [
     (256, 128, 64, 64), (512, 512, 128, 128), (300, 200, 40, 24), (129, 65, 8, 100),
     (1000, 3000, 128, 128),
