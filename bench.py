@@ -529,6 +529,24 @@ def run_gpu_arm(args):
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }
+    if world == 1 and mixed:
+        # The same steps with both contractions on TF32 operands, for comparison in the same run.
+        pure = readme_attention(ilang, batched=batched).set_precision("tf32")
+        for s2 in range(3):
+            pure.into(outs[s2 % 2], *sets[s2 % rotation])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(main)
+        for s2 in range(args.steps):
+            pure.into(outs[s2 % 2], *sets[s2 % rotation])
+        b.record(main)
+        torch.cuda.synchronize()
+        pure_ms = a.elapsed_time(b) / args.steps
+        pure_tf = flop_per_step / pure_ms / 1e9
+        line["tf32_both_contractions"] = {
+            "value": pure_tf, "unit": "TFLOP/s", "ms_per_step": pure_ms,
+            "frac_of_tf32_peak": pure_tf / tf32_peak,
+            "note": "same workload and loop with --precision tf32 (Q K^T and P V both kind::tf32)"}
     if world == 1:
         res = cpu_reference_sample(256)        # ~20 s of CPU work over all cores
         line["cpu_baseline"] = {"value": res["flop"] / res["times"][0] / 1e12, "unit": "TFLOP/s",
