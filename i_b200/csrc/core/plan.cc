@@ -425,9 +425,91 @@ void fuse_deferred_attention(Builder& b) {
   }
 }
 
+// Consecutive pointwise maps over one index space become one pass: `ij-i~ij` then `^ij~ij` then
+// `ij/i~ij` reads its operands once and writes once instead of moving two full-size
+// intermediates through memory, which is what the reference's staged loops do for such chains
+// (compiler/src/lower/node_to_stage.rs:621-674: a producer whose axes align with the consumer's
+// prefix is computed inside the consumer's loops).  Fused here whatever the schedule says: the
+// arithmetic per element is the same.  A link is fused when the earlier map has a single reader,
+// both write the full index space in order, and every other operand is the full tensor, one value
+// per row (all axes but the last), one value per column (the last axis) or a scalar.
+constexpr size_t kMaxChainOps = 8, kMaxChainOperands = 4;
+
+bool chain_operand_ok(const Access& a, size_t rank) {
+  if (is_iota(a.index, rank)) return true;                        // full
+  if (rank >= 1 && is_iota(a.index, rank - 1)) return true;       // per row (or scalar when rank 1)
+  if (a.index.empty()) return true;                               // scalar
+  return rank >= 2 && a.index.size() == 1 && a.index[0] == rank - 1;   // per column
+}
+
+void fuse_map_chains(Builder& b) {
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n]) continue;
+    const Step& first = b.steps[n];
+    if (first.kind != StepKind::Map && first.kind != StepKind::MapChain) continue;
+    if (first.rank == 0 || !is_iota(first.out.index, first.rank)) continue;
+    const size_t a_node = first.out.buffer.index;
+    auto reader = b.sole_reader(a_node);
+    if (!reader) continue;
+    const Step& next = b.steps[*reader];
+    if (next.kind != StepKind::Map || next.rank != first.rank || !is_iota(next.out.index, next.rank))
+      continue;
+    // The link: `next` reads the earlier result element for element, exactly once.
+    int link = -1, links = 0;
+    for (size_t i = 0; i < next.in.size(); ++i)
+      if (!next.in[i].buffer.is_input && next.in[i].buffer.index == a_node) {
+        link = static_cast<int>(i);
+        ++links;
+      }
+    if (links != 1 || !is_iota(next.in[link].index, next.rank)) continue;
+    bool ok = true;
+    for (const Access& acc : first.in) ok = ok && chain_operand_ok(acc, first.rank);
+    for (size_t i = 0; i < next.in.size(); ++i)
+      if (static_cast<int>(i) != link) ok = ok && chain_operand_ok(next.in[i], next.rank);
+    if (!ok) continue;
+
+    Step fused;
+    fused.kind = StepKind::MapChain;
+    fused.op = next.op;
+    fused.rank = first.rank;
+    fused.out = next.out;
+    fused.hint = next.hint;
+    fused.nodes = first.nodes;
+    fused.nodes.insert(fused.nodes.end(), next.nodes.begin(), next.nodes.end());
+    fused.in = first.in;
+    if (first.kind == StepKind::MapChain) {
+      fused.chain = first.chain;
+    } else {
+      ChainOp op0;
+      op0.op = first.op;
+      op0.lhs = 0;
+      op0.rhs = first.in.size() == 2 ? 1 : kChainNone;
+      fused.chain = {op0};
+    }
+    auto operand = [&](size_t i) -> int {
+      if (static_cast<int>(i) == link) return kChainPrev;
+      for (size_t e = 0; e < fused.in.size(); ++e)
+        if (fused.in[e].buffer == next.in[i].buffer && fused.in[e].index == next.in[i].index)
+          return static_cast<int>(e);
+      fused.in.push_back(next.in[i]);
+      return static_cast<int>(fused.in.size() - 1);
+    };
+    ChainOp op1;
+    op1.op = next.op;
+    op1.lhs = operand(0);
+    op1.rhs = next.in.size() == 2 ? operand(1) : kChainNone;
+    fused.chain.push_back(op1);
+    if (fused.chain.size() > kMaxChainOps || fused.in.size() > kMaxChainOperands) continue;
+    const size_t slot = *reader;
+    b.alive[n] = false;
+    b.steps[slot] = std::move(fused);
+  }
+}
+
 const char* kind_name(StepKind k) {
   switch (k) {
     case StepKind::Map: return "map";
+    case StepKind::MapChain: return "map_chain";
     case StepKind::Reduce: return "reduce";
     case StepKind::Contract: return "contract";
     case StepKind::RowSoftmax: return "row_softmax";
@@ -483,6 +565,20 @@ std::string Plan::describe() const {
       case StepKind::Map:
         os << "    kernel: ib_map\n";
         break;
+      case StepKind::MapChain: {
+        os << "    kernel: ib_map_chain (one pass):";
+        auto name = [&](int code) -> std::string {
+          if (code == kChainPrev) return "_";
+          return buffer_name(s.in[code].buffer);
+        };
+        for (const ChainOp& c : s.chain) {
+          os << "  ";
+          if (c.rhs == kChainNone) os << op_token(c.op) << name(c.lhs);
+          else os << name(c.lhs) << op_token(c.op) << name(c.rhs);
+        }
+        os << "\n";
+        break;
+      }
     }
     if (s.kind == StepKind::Attention || s.kind == StepKind::Contract) {
       const size_t row_tile = 128, col_tile = s.kind == StepKind::Attention ? 128 : 256;
@@ -534,6 +630,7 @@ Result<Plan> make_plan(const Graph& g) {
   fuse_softmax(b);
   fuse_attention(b);
   fuse_deferred_attention(b);
+  fuse_map_chains(b);
 
   Plan plan;
   plan.n_inputs = g.n_inputs;

@@ -18,6 +18,7 @@ namespace ib {
 
 enum class StepKind {
   Map,          // pointwise unary or binary, any broadcast / permutation
+  MapChain,     // several pointwise operators applied in sequence in one pass
   Reduce,       // fold over the axes missing from the output
   Contract,     // Mul node + Add-reduce node = batched GEMM
   RowSoftmax,   // max, shift, exp, sum, divide over the last axis
@@ -48,6 +49,15 @@ struct ScheduleHint {
   bool staged = false;         // producers are staged into the consumer's loops
 };
 
+// One operator of a MapChain.  Operand codes: kChainNone (unary form), kChainPrev (the result of
+// the operator before it), or an index into Step::in.
+constexpr int kChainNone = -1;
+constexpr int kChainPrev = -2;
+struct ChainOp {
+  Op op = Op::Add;
+  int lhs = kChainNone, rhs = kChainNone;
+};
+
 struct Step {
   StepKind kind = StepKind::Map;
   Op op = Op::Add;
@@ -58,6 +68,7 @@ struct Step {
   ContractForm form2;
   ScheduleHint hint;
   std::vector<size_t> nodes;       // graph nodes folded into this step
+  std::vector<ChainOp> chain;      // MapChain: the operators in order
 };
 
 struct Plan {

@@ -349,6 +349,30 @@ int run_map(const Step& step, const ShapeTable& shapes, const std::vector<size_t
                         pb ? sb.data() : nullptr, stream);
 }
 
+int run_map_chain(const Step& step, DeviceBuffers& dev, float* out, const Shape& oshape) {
+  const size_t cols = oshape.empty() ? 1 : oshape.back();
+  const size_t rows = cols ? product(oshape) / cols : 0;
+  std::vector<const float*> operands;
+  std::vector<int> modes;
+  for (const Access& acc : step.in) {
+    operands.push_back(dev.get(acc.buffer));
+    int mode = 3;                                              // scalar
+    if (acc.index.size() == step.rank) mode = 0;               // the planner admits only these forms
+    else if (step.rank >= 2 && acc.index.size() == 1 && acc.index[0] == step.rank - 1) mode = 2;
+    else if (!acc.index.empty()) mode = 1;
+    modes.push_back(mode);
+  }
+  std::vector<int> ops;
+  for (const ChainOp& c : step.chain) {
+    ops.push_back(op_code(c.op));
+    ops.push_back(c.lhs == kChainPrev ? IB_CHAIN_PREV : c.lhs);
+    ops.push_back(c.rhs == kChainPrev ? IB_CHAIN_PREV : c.rhs == kChainNone ? IB_CHAIN_NONE : c.rhs);
+  }
+  return ib_map_chain(static_cast<int>(step.chain.size()), ops.data(),
+                      static_cast<int>(operands.size()), operands.data(), modes.data(), out, rows,
+                      cols, dev.stream);
+}
+
 int run_reduce(const Step& step, const ShapeTable& shapes, const std::vector<size_t>& extent,
                DeviceBuffers& dev, float* out, const Shape& oshape) {
   const int op = op_code(step.op);
@@ -469,6 +493,7 @@ int run_plan(const i_program* program, const ShapeTable& shapes, const float* co
     }
     switch (step.kind) {
       case StepKind::Map: rc = run_map(step, shapes, extent, dev, out, oshape); break;
+      case StepKind::MapChain: rc = run_map_chain(step, dev, out, oshape); break;
       case StepKind::Reduce: rc = run_reduce(step, shapes, extent, dev, out, oshape); break;
       case StepKind::Contract: rc = run_contract(step, extent, dev, out, precision, &err); break;
       case StepKind::RowSoftmax: {

@@ -206,6 +206,201 @@ int launch_strided(const float* a, const float* b, float* y, size_t n, const Str
   return check_launch("ib_map_strided");
 }
 
+
+// ---- chains of pointwise operators in one pass ------------------------------------------
+//
+// `ij-i~ij` then `^ij~ij` then `ij/i~ij` as three launches moves two full-size intermediates
+// through memory; here each element is read once, run through the operator list in registers and
+// written once.  The operator list is data, not a template: every operator is a warp-uniform switch
+// costing a few instructions per element, well inside what a memory-bound pass has to spare.
+// Algorithmic traffic: the operands at their own sizes plus the result, once.
+#ifndef IB_CHAIN_BLOCKS
+#define IB_CHAIN_BLOCKS 4
+#endif
+#ifndef IB_CHAIN_VEC
+#define IB_CHAIN_VEC 4
+#endif
+constexpr int kChainVec = IB_CHAIN_VEC;    // float4 results per thread and step
+
+struct ChainArgs {
+  int n_ops, n_operands;
+  int op[IB_MAX_CHAIN_OPS], lhs[IB_MAX_CHAIN_OPS], rhs[IB_MAX_CHAIN_OPS];
+  const float* operand[IB_MAX_CHAIN_OPERANDS];
+  int mode[IB_MAX_CHAIN_OPERANDS];   // 0 [r][c], 1 [r], 2 [c], 3 scalar
+  bool needs_rc;                     // some operand is per row or per column
+  // Row of vector i is umulhi(i, div_mul) >> div_shift (i when a row is one vector wide): exact for
+  // i < 2^31 with div_mul = ceil(2^(31+L) / cvec), L = ceil(log2 cvec), div_shift = L - 1.
+  unsigned cvec, div_mul, div_shift;
+};
+
+// One operand for all of a thread's vectors; the addressing mode is decided once, outside the
+// unrolled loads, so the loads of one operator issue back to back.
+__device__ __forceinline__ void chain_fetch_all(const ChainArgs& a, int code,
+                                                float4 (&dst)[kChainVec], size_t base, size_t nvec) {
+  const float* p = a.operand[code];
+  const int mode = a.mode[code];
+  if (mode == 0) {
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) {
+      size_t i = base + static_cast<size_t>(u) * kThreads;
+      if (i < nvec) dst[u] = __ldcs(reinterpret_cast<const float4*>(p) + i);
+    }
+  } else if (mode == 3) {
+    float s = __ldg(p);
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) dst[u] = make_float4(s, s, s, s);
+  } else {
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) {
+      size_t i = base + static_cast<size_t>(u) * kThreads;
+      if (i < nvec) {
+        unsigned row = a.cvec == 1 ? static_cast<unsigned>(i)
+                                   : __umulhi(static_cast<unsigned>(i), a.div_mul) >> a.div_shift;
+        if (mode == 1) {
+          float s = __ldg(p + row);
+          dst[u] = make_float4(s, s, s, s);
+        } else {
+          unsigned col = (static_cast<unsigned>(i) - row * a.cvec) * 4u;
+          dst[u] = __ldg(reinterpret_cast<const float4*>(p + col));
+        }
+      }
+    }
+  }
+}
+
+// Operators run one after another, so a full-size operand first touched by the third operator
+// would add a trip to memory to the thread's critical path.  Its addresses are known up front: ask
+// the L2 for them at once (measured on `ij+j`, `>ij`, `ij*ij` at 8192 x 8192: 154 us with, 169
+// without).  The same for per-row and per-column vectors measured slower, to L1 or L2, from every
+// lane or from one lane per line (`ij-i`, `^ij`: 187 us against 131-145), so those are left to the
+// loads themselves.
+__device__ __forceinline__ void chain_prefetch_all(const ChainArgs& a, int code, size_t base,
+                                                   size_t nvec) {
+  if (a.mode[code] != 0) return;
+  const float4* p = reinterpret_cast<const float4*>(a.operand[code]);
+#pragma unroll
+  for (int u = 0; u < kChainVec; ++u) {
+    size_t i = base + static_cast<size_t>(u) * kThreads;
+    if (i < nvec) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + i));
+  }
+}
+
+// acc = f(acc, t) over the sixteen elements a thread holds.
+template <class F>
+__device__ __forceinline__ void chain_apply_all(float4 (&acc)[kChainVec],
+                                                const float4 (&t)[kChainVec], F f) {
+#pragma unroll
+  for (int u = 0; u < kChainVec; ++u) {
+    acc[u].x = f(acc[u].x, t[u].x);
+    acc[u].y = f(acc[u].y, t[u].y);
+    acc[u].z = f(acc[u].z, t[u].z);
+    acc[u].w = f(acc[u].w, t[u].w);
+  }
+}
+
+__device__ __forceinline__ float chain_fetch(const ChainArgs& a, int code, float prev, size_t e,
+                                             size_t r, size_t c) {
+  if (code == IB_CHAIN_PREV) return prev;
+  const float* p = a.operand[code];
+  switch (a.mode[code]) {
+    case 0: return p[e];
+    case 1: return __ldg(p + r);
+    case 2: return __ldg(p + c);
+    default: return __ldg(p);
+  }
+}
+
+// cols % 4 == 0, every full or per-column operand 16-byte aligned, under 2^32 elements.  A thread
+// holds sixteen elements of the running result and, per operator, sixteen of the other operand;
+// the operator is decided once per step for all of them: one warp-uniform branch per operator,
+// straight-line arithmetic behind it.  Registers stay under 64 so that four blocks share an SM.
+#define IB_CHAIN_CASE(OP)                                                                        \
+  case OP:                                                                                       \
+    if (form == 0)                                                                               \
+      chain_apply_all(acc, t, [](float p, float) { return apply_unary(OP, p); });                \
+    else if (form == 1)                                                                          \
+      chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, p, q); });          \
+    else                                                                                         \
+      chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, q, p); });          \
+    break;
+
+__global__ void __launch_bounds__(kThreads, IB_CHAIN_BLOCKS)
+map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, size_t nvec) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads * kChainVec;
+  for (size_t base = static_cast<size_t>(blockIdx.x) * kThreads * kChainVec + threadIdx.x;
+       base < nvec; base += stride) {
+    float4 acc[kChainVec], t[kChainVec];
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) acc[u] = t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    chain_fetch_all(a, a.lhs[0], acc, base, nvec);
+    for (int e = 0; e < a.n_operands; ++e)
+      if (e != a.lhs[0]) chain_prefetch_all(a, e, base, nvec);
+    for (int k = 0; k < a.n_ops; ++k) {
+      // Every operator after the first takes the running result on at least one side (the host
+      // checks): form 0 op(acc), 1 op(acc, other), 2 op(other, acc).
+      const int lc = a.lhs[k], rc = a.rhs[k];
+      const bool acc_left = k == 0 || lc == IB_CHAIN_PREV;
+      const int form = rc == IB_CHAIN_NONE ? 0 : (acc_left ? 1 : 2);
+      const int other = acc_left ? rc : lc;
+      if (form != 0) {
+        if (other == IB_CHAIN_PREV) {
+#pragma unroll
+          for (int u = 0; u < kChainVec; ++u) t[u] = acc[u];
+        } else {
+          chain_fetch_all(a, other, t, base, nvec);
+        }
+      }
+      switch (a.op[k]) {
+        IB_CHAIN_CASE(IB_OP_ADD)
+        IB_CHAIN_CASE(IB_OP_MUL)
+        IB_CHAIN_CASE(IB_OP_SUB)
+        IB_CHAIN_CASE(IB_OP_DIV)
+        IB_CHAIN_CASE(IB_OP_MAX)
+        IB_CHAIN_CASE(IB_OP_MIN)
+        IB_CHAIN_CASE(IB_OP_POW)
+        IB_CHAIN_CASE(IB_OP_LOG)
+        IB_CHAIN_CASE(IB_OP_GT)
+        IB_CHAIN_CASE(IB_OP_GE)
+        IB_CHAIN_CASE(IB_OP_LT)
+        IB_CHAIN_CASE(IB_OP_LE)
+        IB_CHAIN_CASE(IB_OP_EQ)
+        IB_CHAIN_CASE(IB_OP_NE)
+        IB_CHAIN_CASE(IB_OP_AND)
+        IB_CHAIN_CASE(IB_OP_OR)
+        IB_CHAIN_CASE(IB_OP_XOR)
+        IB_CHAIN_CASE(IB_OP_NOT)
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) {
+      size_t i = base + static_cast<size_t>(u) * kThreads;
+      if (i < nvec) __stcs(y + i, acc[u]);
+    }
+  }
+}
+#undef IB_CHAIN_CASE
+
+__global__ void __launch_bounds__(kThreads)
+map_chain_scalar(const __grid_constant__ ChainArgs a, float* __restrict__ y, size_t n,
+                 size_t cols) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t e = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; e < n; e += stride) {
+    size_t r = 0, c = 0;
+    if (a.needs_rc) {
+      r = e / cols;
+      c = e - r * cols;
+    }
+    float acc = 0.0f;
+    for (int k = 0; k < a.n_ops; ++k) {
+      float l = chain_fetch(a, a.lhs[k], acc, e, r, c);
+      if (a.rhs[k] != IB_CHAIN_NONE)
+        acc = apply_binary(a.op[k], l, chain_fetch(a, a.rhs[k], acc, e, r, c));
+      else
+        acc = apply_unary(a.op[k], l);
+    }
+    y[e] = acc;
+  }
+}
 }  // namespace
 }  // namespace ib
 
@@ -273,4 +468,62 @@ extern "C" int ib_map_strided(int op, const float* a, const float* b, float* y, 
 #define CALL(OP) ib::launch_strided<OP>(a, b, y, n, args, s)
   IB_DISPATCH_OP(op, CALL)
 #undef CALL
+}
+
+extern "C" int ib_map_chain(int n_ops, const int* ops, int n_operands, const float* const* operands,
+                            const int* modes, float* y, size_t rows, size_t cols, void* stream) {
+  if (n_ops < 1 || n_ops > IB_MAX_CHAIN_OPS) return ib::fail("ib_map_chain: 1 to 8 operators");
+  if (n_operands < 1 || n_operands > IB_MAX_CHAIN_OPERANDS)
+    return ib::fail("ib_map_chain: 1 to 4 operands");
+  if (!ops || !operands || !modes) return ib::fail("ib_map_chain: null pointer");
+  if (rows == 0 || cols == 0) return 0;
+  if (!y) return ib::fail("ib_map_chain: null pointer");
+  ib::ChainArgs args{};
+  args.n_ops = n_ops;
+  args.n_operands = n_operands;
+  bool vec = cols % 4 == 0 && ib::aligned16(y) && rows * cols <= 0xffffffffull;
+  for (int e = 0; e < n_operands; ++e) {
+    if (!operands[e]) return ib::fail("ib_map_chain: null pointer");
+    if (modes[e] < 0 || modes[e] > 3) return ib::fail("ib_map_chain: operand mode must be 0..3");
+    args.operand[e] = operands[e];
+    args.mode[e] = modes[e];
+    if (modes[e] == 1 || modes[e] == 2) args.needs_rc = true;
+    if ((modes[e] == 0 || modes[e] == 2) && !ib::aligned16(operands[e])) vec = false;
+  }
+  for (int k = 0; k < n_ops; ++k) {
+    const int op = ops[3 * k], lhs = ops[3 * k + 1], rhs = ops[3 * k + 2];
+    if (op < IB_OP_ADD || op > IB_OP_NOT) return ib::fail("unknown operator code");
+    auto valid = [&](int code, bool may_be_none) {
+      if (code == IB_CHAIN_NONE) return may_be_none;
+      if (code == IB_CHAIN_PREV) return k > 0;
+      return code >= 0 && code < n_operands;
+    };
+    if (!valid(lhs, false) || !valid(rhs, true))
+      return ib::fail("ib_map_chain: operand code out of range");
+    if (op == IB_OP_NOT && rhs != IB_CHAIN_NONE)
+      return ib::fail("ib_map_chain: operator `!!` has one operand");
+    if (k > 0 && lhs != IB_CHAIN_PREV && rhs != IB_CHAIN_PREV)
+      return ib::fail("ib_map_chain: an operator after the first must take the previous result");
+    args.op[k] = op;
+    args.lhs[k] = lhs;
+    args.rhs[k] = rhs;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t n = rows * cols;
+  if (vec) {
+    const size_t nvec = n / 4;
+    args.cvec = static_cast<unsigned>(cols / 4);
+    if (args.cvec > 1) {
+      unsigned log2_ceil = 0;
+      while ((1ull << log2_ceil) < args.cvec) ++log2_ceil;
+      const unsigned long long two_p = 1ull << (31 + log2_ceil);
+      args.div_mul = static_cast<unsigned>((two_p + args.cvec - 1) / args.cvec);
+      args.div_shift = log2_ceil - 1;
+    }
+    ib::map_chain_vec<<<ib::grid_for(nvec, ib::kThreads * ib::kChainVec), ib::kThreads, 0, s>>>(
+        args, reinterpret_cast<float4*>(y), nvec);
+  } else {
+    ib::map_chain_scalar<<<ib::grid_for(n, ib::kThreads), ib::kThreads, 0, s>>>(args, y, n, cols);
+  }
+  return ib::check_launch("ib_map_chain");
 }

@@ -305,6 +305,31 @@ def test_softmax_alone(ilang):
     assert sm.output_shapes(np.zeros((5, 9), np.float32)) == [(5, 9)]
 
 
+def test_pointwise_chains_are_one_kernel(ilang):
+    i, I = ilang.i, ilang.I
+    bias_relu_gate = i("ij+j~ij") >> i(">ij~ij") >> i("ij*ij~ij")
+    assert steps_of(bias_relu_gate) == ["map_chain"]
+    assert "in0+in1  >_  _*in2" in bias_relu_gate._code()
+    assert bias_relu_gate.output_shapes(*(np.zeros(s, np.float32) for s in ((6, 8), (8,), (6, 8)))) == [(6, 8)]
+    assert steps_of(i("bij-bi~bij") >> i("^bij~bij") >> i("bij/bi~bij")) == ["map_chain"]
+    assert steps_of(i(".*i~i") >> i("-i~i")) == ["map_chain"]         # scalar operand, rank 1
+    # An intermediate that is also an output stays a kernel of its own.
+    assert steps_of(i("ij+j~ij") >> (I & i(">ij~ij"))) == ["map", "map"]
+    # So does a map that permutes or broadcasts along a leading axis only.
+    assert steps_of(i("ij+j~ij") >> i("ij~ji")) == ["map", "map"]
+    assert steps_of(i("bij*b~bij") >> i("^bij~bij")) == ["map", "map"]
+    # The reading map may take the earlier result on either side, but only once.
+    assert steps_of(i("^ij~ij") >> (I & I) >> i("ij*ij~ij")) == ["map", "map"]
+    # Nine operators: the ninth starts a new kernel.
+    long = i("-i~i")
+    for _ in range(8):
+        long = long >> i("-i~i")
+    assert steps_of(long) == ["map_chain", "map"]
+    # Softmax still wins over the generic chain.
+    sm = ((I & i(">ij~i")) >> i("ij-i~ij")) >> i("^ij~ij") >> ((I & i("+ij~i")) >> i("ij/i~ij"))
+    assert steps_of(sm) == ["row_softmax"]
+
+
 def test_output_shapes_follow_inputs(ilang):
     attn = readme_attention(ilang)
     q, k, v = (np.zeros(s, np.float32) for s in ((100, 40), (77, 40), (77, 24)))

@@ -97,6 +97,95 @@ def test_map_binary_modes(lib, oracle, torch, mode, op):
     assert max_rel_elementwise(y.cpu().numpy(), ref) <= TOL_MAP
 
 
+NONE, PREV = -1, -2
+
+
+def run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=False):
+    """ops: (token, lhs, rhs) with lhs/rhs an operand index, PREV or NONE.  Returns (got, ref):
+    the kernel's result and the same operators applied one at a time by the oracle."""
+    devs = []
+    for a in operands:
+        if misalign:                                   # 4-byte aligned only
+            buf = torch.zeros(a.size + 1, device="cuda")
+            buf[1:] = dev(torch, a).reshape(-1)
+            devs.append(buf[1:])
+        else:
+            devs.append(dev(torch, a))
+    y = torch.empty(rows * cols + 1, device="cuda")[1 if misalign else 0:][:rows * cols]
+    flat = (ctypes.c_int * (3 * len(ops)))(*[v for tok, l, r in ops for v in (oracle.OPS[tok], l, r)])
+    ptrs = (ctypes.c_void_p * len(devs))(*[d.data_ptr() for d in devs])
+    md = (ctypes.c_int * len(modes))(*modes)
+    ok(lib, lib.ib_map_chain(len(ops), flat, len(devs), ptrs, md, y.data_ptr(), rows, cols, None))
+
+    def full(code, prev):
+        if code == PREV:
+            return prev
+        a, m = operands[code], modes[code]
+        shaped = {0: lambda: a.reshape(rows, cols), 1: lambda: a.reshape(rows, 1),
+                  2: lambda: a.reshape(1, cols), 3: lambda: a.reshape(1, 1)}[m]()
+        return np.ascontiguousarray(np.broadcast_to(shaped, (rows, cols)))
+    prev = None
+    for tok, l, r in ops:
+        prev = (oracle.map_unary(tok, full(l, prev)) if r == NONE
+                else oracle.map_binary(tok, full(l, prev), full(r, prev)))
+    return y.cpu().numpy().reshape(rows, cols), prev
+
+
+@pytest.mark.parametrize("rows,cols,misalign", [(37, 52, False), (37, 51, False), (64, 128, True),
+                                                (1, 100003, False), (300, 4, False)])
+def test_map_chain_softmax_like(lib, oracle, torch, rows, cols, misalign):
+    # (x - m[r]) -> exp -> / s[r] -> * g[c] -> + scalar: every operand mode in one chain.
+    x, m = rand((rows, cols), 1), rand((rows,), 2)
+    s_, g, c0 = np.abs(rand((rows,), 3)) + 0.5, rand((cols,), 4), rand((1,), 5)
+    ops = [("-", 0, 1), ("^", PREV, NONE), ("/", PREV, 2), ("*", 3, PREV), ("+", PREV, 4)]
+    # Five operands is one too many for one call: fold the scalar in a second chain.
+    got, ref = run_chain(lib, oracle, torch, ops[:4], [x, m, s_, g], [0, 1, 1, 2], rows, cols, misalign)
+    assert max_rel_elementwise(got, ref) <= TOL_MAP
+    got2, ref2 = run_chain(lib, oracle, torch, [("+", 0, 1), ("-", PREV, NONE)], [ref, c0], [0, 3],
+                           rows, cols, misalign)
+    assert np.array_equal(got2, ref2)
+
+
+def test_map_chain_exact_ops_and_reuse(lib, oracle, torch):
+    # Select by a comparison: (x > t[c]) * x, then clamp at a per-row ceiling; x appears twice.
+    rows, cols = 129, 260
+    x, t, hi = rand((rows, cols), 6), rand((cols,), 7), np.abs(rand((rows,), 8))
+    ops = [(">>", 0, 1), ("*", PREV, 0), ("<", PREV, 2), ("!!", PREV, NONE)]
+    got, ref = run_chain(lib, oracle, torch, ops[:3], [x, t, hi], [0, 2, 1], rows, cols)
+    assert np.array_equal(got, ref)
+    assert np.array_equal(ref, np.minimum(np.where(x > t[None, :], x, 0.0), hi[:, None]).astype(np.float32))
+    got, ref = run_chain(lib, oracle, torch, ops, [x, t, hi], [0, 2, 1], rows, cols)
+    assert np.array_equal(got, ref)
+
+
+def test_map_chain_larger_than_l2(lib, oracle, torch):
+    rows, cols = 4096, 8192 + 4
+    x, b = rand((rows, cols), 9), rand((cols,), 10)
+    got, ref = run_chain(lib, oracle, torch, [("+", 0, 1), (">", PREV, NONE), ("*", PREV, PREV)],
+                         [x, b], [0, 2], rows, cols)
+    assert np.array_equal(got, ref)
+
+
+def test_map_chain_rejects_bad_programs(lib, oracle, torch):
+    x = dev(torch, rand((4, 4), 1))
+    y = torch.empty_like(x)
+    ptrs = (ctypes.c_void_p * 1)(x.data_ptr())
+    md = (ctypes.c_int * 1)(0)
+
+    def call(triples, n_operands=1, modes=md):
+        flat = (ctypes.c_int * len(triples))(*triples)
+        return lib.ib_map_chain(len(triples) // 3, flat, n_operands, ptrs, modes, y.data_ptr(), 4, 4, None)
+    add = oracle.OPS["+"]
+    assert call([add, PREV, NONE]) != 0 and "operand code" in last_error(lib)     # nothing before the first
+    assert call([add, 0, 1]) != 0                                                  # operand 1 does not exist
+    assert call([add, NONE, 0]) != 0                                               # lhs is mandatory
+    assert call([99, 0, NONE]) != 0 and "unknown operator" in last_error(lib)
+    assert call([oracle.OPS["!!"], 0, 0]) != 0 and "one operand" in last_error(lib)
+    assert call([add, 0, NONE] * 9) != 0                                           # nine operators
+    assert call([add, 0, NONE], modes=(ctypes.c_int * 1)(4)) != 0
+    assert call([add, 0, NONE]) == 0
+
+
 def test_map_strided_transpose(lib, oracle, torch):
     x = rand((19, 33), 7)
     d = dev(torch, x)

@@ -81,6 +81,30 @@ def test_comparison_and_logic_components(ilang):
     assert np.array_equal(both, ((x != 0) & (mask != 0)).astype(np.float32))
 
 
+def test_pointwise_chain_components(ilang, oracle):
+    # Consecutive maps over one index space run as one kernel; results are those of the maps one
+    # after another (each rounded to fp32), which is what the oracle computes here.
+    i = ilang.i
+    x, b, g = rand((130, 72), 1), rand((72,), 2), rand((130, 72), 3)
+    f = i("ij+j~ij") >> i(">ij~ij") >> i("ij*ij~ij")
+    assert "map_chain" in f._code()
+    ref = oracle.map_binary("*", oracle.map_unary(">", oracle.map_binary("+", x, b, 3)), g)
+    assert np.array_equal(f.exec_numpy(x, b, g), ref)
+    # Batched, per-row operands (the two halves of a softmax whose statistics come from elsewhere).
+    y, m, l = rand((3, 50, 41), 4), rand((3, 50), 5), np.abs(rand((3, 50), 6)) + 0.5
+    h = i("bij-bi~bij") >> i("^bij~bij") >> i("bij/bi~bij")
+    ref = oracle.map_binary("/", oracle.map_unary("^", oracle.map_binary("-", y, m, 1)), l, 1)
+    got = h.exec_numpy(y, m, l)
+    assert got.shape == (3, 50, 41) and max_rel_elementwise(got, ref) <= 1e-5
+    # Rank 1 with a scalar, and a chain feeding a reduction.
+    two = np.array(2.0, dtype=np.float32)
+    v = rand((1000,), 7)
+    assert np.array_equal((i(".*i~i") >> i("-i~i")).exec_numpy(two, v), -(2 * v))
+    norm = i("ij*ij~ij") >> i("-ij~ij") >> i("+ij~i")
+    ref = oracle.reduce_rows("+", oracle.map_unary("-", oracle.map_binary("*", x, x)))
+    assert max_rel_elementwise(norm.exec_numpy(x, x), ref) <= 1e-5
+
+
 @pytest.mark.parametrize("src,fn", [(">ij~i", np.max), ("<ij~i", np.min), ("+ij~i", np.sum)])
 def test_row_reductions(ilang, src, fn):
     # test.py:103-128
