@@ -250,7 +250,23 @@ def secondary_metrics(torch, ilang, peaks):
     ms = timed(lambda: lib.ib_reduce_rows(0, x.data_ptr(), r.data_ptr(), 8192, 8192, stream), 10, flush)
     out["reduce_sum_rows_8192x8192"] = {"gbs": rbytes / ms / 1e6, "ms": ms,
                                         "frac_hbm": rbytes / ms / 1e6 / peaks["hbm_gbs"]}
-    del x, y
+    # Three pointwise operators in one pass (`ij+j`, `>ij`, `ij*ij`): two full-size operands and a
+    # per-column vector in, one result out.
+    import ctypes
+    gate = torch.randn(8192, 8192, device="cuda", generator=g)
+    bias = torch.randn(8192, device="cuda", generator=g)
+    ops = (ctypes.c_int * 9)(0, 0, 1, 4, -2, -1, 1, -2, 2)      # add(x, bias); max(0, _); mul(_, gate)
+    ptrs = (ctypes.c_void_p * 3)(x.data_ptr(), bias.data_ptr(), gate.data_ptr())
+    modes = (ctypes.c_int * 3)(0, 2, 0)
+    lib.ib_map_chain.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int),
+                                 ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p]
+    lib.ib_map_chain.restype = ctypes.c_int
+    cbytes = 3.0 * x.numel() * 4 + 8192 * 4
+    ms = timed(lambda: lib.ib_map_chain(3, ops, 3, ptrs, modes, y.data_ptr(), 8192, 8192, stream), 10, flush)
+    out["map_chain_bias_relu_gate_8192x8192"] = {"gbs": cbytes / ms / 1e6, "ms": ms,
+                                                 "frac_hbm": cbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del x, y, gate
     g.manual_seed(2)
     a = 2 * torch.rand(8192, 4096, device="cuda", generator=g) - 1
     b = 2 * torch.rand(8192, 4096, device="cuda", generator=g) - 1

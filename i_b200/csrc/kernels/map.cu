@@ -236,13 +236,13 @@ struct ChainArgs {
 // One operand for all of a thread's vectors; the addressing mode is decided once, outside the
 // unrolled loads, so the loads of one operator issue back to back.
 __device__ __forceinline__ void chain_fetch_all(const ChainArgs& a, int code,
-                                                float4 (&dst)[kChainVec], size_t base, size_t nvec) {
+                                                float4 (&dst)[kChainVec], unsigned base, unsigned nvec) {
   const float* p = a.operand[code];
   const int mode = a.mode[code];
   if (mode == 0) {
 #pragma unroll
     for (int u = 0; u < kChainVec; ++u) {
-      size_t i = base + static_cast<size_t>(u) * kThreads;
+      unsigned i = base + u * kThreads;
       if (i < nvec) dst[u] = __ldcs(reinterpret_cast<const float4*>(p) + i);
     }
   } else if (mode == 3) {
@@ -252,15 +252,15 @@ __device__ __forceinline__ void chain_fetch_all(const ChainArgs& a, int code,
   } else {
 #pragma unroll
     for (int u = 0; u < kChainVec; ++u) {
-      size_t i = base + static_cast<size_t>(u) * kThreads;
+      unsigned i = base + u * kThreads;
       if (i < nvec) {
-        unsigned row = a.cvec == 1 ? static_cast<unsigned>(i)
-                                   : __umulhi(static_cast<unsigned>(i), a.div_mul) >> a.div_shift;
+        unsigned row = a.cvec == 1 ? i
+                                   : __umulhi(i, a.div_mul) >> a.div_shift;
         if (mode == 1) {
           float s = __ldg(p + row);
           dst[u] = make_float4(s, s, s, s);
         } else {
-          unsigned col = (static_cast<unsigned>(i) - row * a.cvec) * 4u;
+          unsigned col = (i - row * a.cvec) * 4u;
           dst[u] = __ldg(reinterpret_cast<const float4*>(p + col));
         }
       }
@@ -274,13 +274,13 @@ __device__ __forceinline__ void chain_fetch_all(const ChainArgs& a, int code,
 // without).  The same for per-row and per-column vectors measured slower, to L1 or L2, from every
 // lane or from one lane per line (`ij-i`, `^ij`: 187 us against 131-145), so those are left to the
 // loads themselves.
-__device__ __forceinline__ void chain_prefetch_all(const ChainArgs& a, int code, size_t base,
-                                                   size_t nvec) {
+__device__ __forceinline__ void chain_prefetch_all(const ChainArgs& a, int code, unsigned base,
+                                                   unsigned nvec) {
   if (a.mode[code] != 0) return;
   const float4* p = reinterpret_cast<const float4*>(a.operand[code]);
 #pragma unroll
   for (int u = 0; u < kChainVec; ++u) {
-    size_t i = base + static_cast<size_t>(u) * kThreads;
+    unsigned i = base + u * kThreads;
     if (i < nvec) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + i));
   }
 }
@@ -314,21 +314,20 @@ __device__ __forceinline__ float chain_fetch(const ChainArgs& a, int code, float
 // holds sixteen elements of the running result and, per operator, sixteen of the other operand;
 // the operator is decided once per step for all of them: one warp-uniform branch per operator,
 // straight-line arithmetic behind it.  Registers stay under 64 so that four blocks share an SM.
-#define IB_CHAIN_CASE(OP)                                                                        \
-  case OP:                                                                                       \
-    if (form == 0)                                                                               \
-      chain_apply_all(acc, t, [](float p, float) { return apply_unary(OP, p); });                \
-    else if (form == 1)                                                                          \
-      chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, p, q); });          \
-    else                                                                                         \
-      chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, q, p); });          \
+#define IB_CHAIN_CASE(OP)                                                                  \
+  case OP:                                                                                 \
+    if (unary)                                                                             \
+      chain_apply_all(acc, t, [](float p, float) { return apply_unary(OP, p); });          \
+    else                                                                                   \
+      chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, p, q); });    \
     break;
 
 __global__ void __launch_bounds__(kThreads, IB_CHAIN_BLOCKS)
-map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, size_t nvec) {
-  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads * kChainVec;
-  for (size_t base = static_cast<size_t>(blockIdx.x) * kThreads * kChainVec + threadIdx.x;
-       base < nvec; base += stride) {
+map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, unsigned nvec) {
+  // Under 2^30 vectors and at most one block per kThreads * kChainVec of them: 32-bit indexes.
+  const unsigned stride = gridDim.x * kThreads * kChainVec;
+  for (unsigned base = blockIdx.x * kThreads * kChainVec + threadIdx.x; base < nvec;
+       base += stride) {
     float4 acc[kChainVec], t[kChainVec];
 #pragma unroll
     for (int u = 0; u < kChainVec; ++u) acc[u] = t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -337,17 +336,26 @@ map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, size_
       if (e != a.lhs[0]) chain_prefetch_all(a, e, base, nvec);
     for (int k = 0; k < a.n_ops; ++k) {
       // Every operator after the first takes the running result on at least one side (the host
-      // checks): form 0 op(acc), 1 op(acc, other), 2 op(other, acc).
+      // checks).  With the running result on the right, the two sets of registers change places
+      // first, so that each operator exists once as op(acc) and once as op(acc, other).
       const int lc = a.lhs[k], rc = a.rhs[k];
+      const bool unary = rc == IB_CHAIN_NONE;
       const bool acc_left = k == 0 || lc == IB_CHAIN_PREV;
-      const int form = rc == IB_CHAIN_NONE ? 0 : (acc_left ? 1 : 2);
       const int other = acc_left ? rc : lc;
-      if (form != 0) {
+      if (!unary) {
         if (other == IB_CHAIN_PREV) {
 #pragma unroll
           for (int u = 0; u < kChainVec; ++u) t[u] = acc[u];
         } else {
           chain_fetch_all(a, other, t, base, nvec);
+        }
+        if (!acc_left) {
+#pragma unroll
+          for (int u = 0; u < kChainVec; ++u) {
+            float4 keep = acc[u];
+            acc[u] = t[u];
+            t[u] = keep;
+          }
         }
       }
       switch (a.op[k]) {
@@ -373,7 +381,7 @@ map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, size_
     }
 #pragma unroll
     for (int u = 0; u < kChainVec; ++u) {
-      size_t i = base + static_cast<size_t>(u) * kThreads;
+      unsigned i = base + u * kThreads;
       if (i < nvec) __stcs(y + i, acc[u]);
     }
   }
@@ -521,7 +529,7 @@ extern "C" int ib_map_chain(int n_ops, const int* ops, int n_operands, const flo
       args.div_shift = log2_ceil - 1;
     }
     ib::map_chain_vec<<<ib::grid_for(nvec, ib::kThreads * ib::kChainVec), ib::kThreads, 0, s>>>(
-        args, reinterpret_cast<float4*>(y), nvec);
+        args, reinterpret_cast<float4*>(y), static_cast<unsigned>(nvec));
   } else {
     ib::map_chain_scalar<<<ib::grid_for(n, ib::kThreads), ib::kThreads, 0, s>>>(args, y, n, cols);
   }
