@@ -166,6 +166,37 @@ def test_map_chain_larger_than_l2(lib, oracle, torch):
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_map_chain_random_programs(lib, oracle, torch, seed):
+    # Random operator lists over random shapes and operand modes.  Every operator used here is
+    # exactly rounded on both sides, so the results must agree bit for bit (NaN and inf included:
+    # differences and quotients of random values produce them).
+    rng = np.random.default_rng(1000 + seed)
+    rows = int(rng.choice([1, 3, 17, 64, 257]))
+    cols = int(rng.choice([1, 4, 5, 60, 128, 1001, 4096]))
+    n_operands = int(rng.integers(1, 5))
+    modes = [0] + [int(rng.integers(0, 4)) for _ in range(n_operands - 1)]
+    rng.shuffle(modes)
+    if 0 not in modes:
+        modes[0] = 0
+    shape = {0: (rows, cols), 1: (rows,), 2: (cols,), 3: (1,)}
+    operands = [rng.choice([-2.0, -1.0, 0.0, 0.5, 1.0, 3.0], size=shape[m]).astype(np.float32)
+                + (rng.standard_normal(shape[m]).astype(np.float32) if rng.random() < 0.7 else 0)
+                for m in modes]
+    binary = ["+", "*", "-", "/", ">", "<", ">>", ">=", "<<", "<=", "==", "!=", "&&", "||", "^^"]
+    unary = ["-", "/", ">", "<", "!!", ">>", "=="]
+    ops = []
+    for k in range(int(rng.integers(1, 9))):
+        if rng.random() < 0.3:
+            ops.append((str(rng.choice(unary)), PREV if k else int(rng.integers(n_operands)), NONE))
+            continue
+        other = int(rng.integers(n_operands)) if rng.random() < 0.85 or k == 0 else PREV
+        mine = PREV if k else int(rng.integers(n_operands))
+        ops.append((str(rng.choice(binary)),) + ((mine, other) if rng.random() < 0.6 or k == 0 else (other, mine)))
+    got, ref = run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=bool(seed % 5 == 4))
+    assert np.array_equal(got, ref, equal_nan=True), (ops, modes, rows, cols)
+
+
 def test_map_chain_rejects_bad_programs(lib, oracle, torch):
     x = dev(torch, rand((4, 4), 1))
     y = torch.empty_like(x)
