@@ -506,10 +506,54 @@ void fuse_map_chains(Builder& b) {
   }
 }
 
+// A row fold whose operand is a pointwise map or chain with no other reader: the operand is
+// computed inside the fold (`ij-i~ij`, `^ij~ij`, `+ij~i`), so the full-size intermediate is never
+// written.  Only folds of the last axis alone, which is the split the chain's per-row and
+// per-column operands are defined against.
+void fuse_chain_reductions(Builder& b) {
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n]) continue;
+    const Step& m = b.steps[n];
+    if (m.kind != StepKind::Map && m.kind != StepKind::MapChain) continue;
+    if (m.rank == 0 || !is_iota(m.out.index, m.rank)) continue;
+    auto reader = b.sole_reader(m.out.buffer.index);
+    if (!reader) continue;
+    const Step& red = b.steps[*reader];
+    if (red.kind != StepKind::Reduce || red.rank != m.rank || red.in.size() != 1) continue;
+    if (!is_iota(red.in[0].index, red.rank) || !is_iota(red.out.index, red.rank - 1)) continue;
+    bool ok = true;
+    for (const Access& acc : m.in) ok = ok && chain_operand_ok(acc, m.rank);
+    if (!ok || m.in.size() > kMaxChainOperands) continue;
+
+    Step fused;
+    fused.kind = StepKind::ChainReduce;
+    fused.op = red.op;
+    fused.rank = m.rank;
+    fused.in = m.in;
+    fused.out = red.out;
+    fused.hint = red.hint;
+    fused.nodes = m.nodes;
+    fused.nodes.insert(fused.nodes.end(), red.nodes.begin(), red.nodes.end());
+    if (m.kind == StepKind::MapChain) {
+      fused.chain = m.chain;
+    } else {
+      ChainOp op0;
+      op0.op = m.op;
+      op0.lhs = 0;
+      op0.rhs = m.in.size() == 2 ? 1 : kChainNone;
+      fused.chain = {op0};
+    }
+    const size_t slot = *reader;
+    b.alive[n] = false;
+    b.steps[slot] = std::move(fused);
+  }
+}
+
 const char* kind_name(StepKind k) {
   switch (k) {
     case StepKind::Map: return "map";
     case StepKind::MapChain: return "map_chain";
+    case StepKind::ChainReduce: return "chain_reduce";
     case StepKind::Reduce: return "reduce";
     case StepKind::Contract: return "contract";
     case StepKind::RowSoftmax: return "row_softmax";
@@ -565,8 +609,12 @@ std::string Plan::describe() const {
       case StepKind::Map:
         os << "    kernel: ib_map\n";
         break;
-      case StepKind::MapChain: {
-        os << "    kernel: ib_map_chain (one pass):";
+      case StepKind::MapChain:
+      case StepKind::ChainReduce: {
+        if (s.kind == StepKind::MapChain)
+          os << "    kernel: ib_map_chain (one pass):";
+        else
+          os << "    kernel: ib_reduce_rows_chain (fold `" << op_token(s.op) << "` of, in one pass):";
         auto name = [&](int code) -> std::string {
           if (code == kChainPrev) return "_";
           return buffer_name(s.in[code].buffer);
@@ -631,6 +679,7 @@ Result<Plan> make_plan(const Graph& g) {
   fuse_attention(b);
   fuse_deferred_attention(b);
   fuse_map_chains(b);
+  fuse_chain_reductions(b);
 
   Plan plan;
   plan.n_inputs = g.n_inputs;

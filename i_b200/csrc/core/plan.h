@@ -19,6 +19,7 @@ namespace ib {
 enum class StepKind {
   Map,          // pointwise unary or binary, any broadcast / permutation
   MapChain,     // several pointwise operators applied in sequence in one pass
+  ChainReduce,  // the same, folded along the last axis instead of stored (Step::op is the fold)
   Reduce,       // fold over the axes missing from the output
   Contract,     // Mul node + Add-reduce node = batched GEMM
   RowSoftmax,   // max, shift, exp, sum, divide over the last axis

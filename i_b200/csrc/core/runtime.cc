@@ -349,9 +349,21 @@ int run_map(const Step& step, const ShapeTable& shapes, const std::vector<size_t
                         pb ? sb.data() : nullptr, stream);
 }
 
-int run_map_chain(const Step& step, DeviceBuffers& dev, float* out, const Shape& oshape) {
-  const size_t cols = oshape.empty() ? 1 : oshape.back();
-  const size_t rows = cols ? product(oshape) / cols : 0;
+// MapChain: `oshape` is the result's shape.  ChainReduce: the result is one value per row and the
+// column count comes from an operand that carries the folded (last) axis.
+int run_map_chain(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev, float* out,
+                  const Shape& oshape) {
+  size_t rows, cols;
+  if (step.kind == StepKind::ChainReduce) {
+    rows = product(oshape);
+    cols = 1;
+    for (const Access& acc : step.in)
+      if (!acc.index.empty() && acc.index.back() == step.rank - 1)
+        cols = shapes.get(acc.buffer)->back();
+  } else {
+    cols = oshape.empty() ? 1 : oshape.back();
+    rows = cols ? product(oshape) / cols : 0;
+  }
   std::vector<const float*> operands;
   std::vector<int> modes;
   for (const Access& acc : step.in) {
@@ -368,6 +380,10 @@ int run_map_chain(const Step& step, DeviceBuffers& dev, float* out, const Shape&
     ops.push_back(c.lhs == kChainPrev ? IB_CHAIN_PREV : c.lhs);
     ops.push_back(c.rhs == kChainPrev ? IB_CHAIN_PREV : c.rhs == kChainNone ? IB_CHAIN_NONE : c.rhs);
   }
+  if (step.kind == StepKind::ChainReduce)
+    return ib_reduce_rows_chain(op_code(step.op), static_cast<int>(step.chain.size()), ops.data(),
+                                static_cast<int>(operands.size()), operands.data(), modes.data(),
+                                out, rows, cols, dev.stream);
   return ib_map_chain(static_cast<int>(step.chain.size()), ops.data(),
                       static_cast<int>(operands.size()), operands.data(), modes.data(), out, rows,
                       cols, dev.stream);
@@ -493,7 +509,8 @@ int run_plan(const i_program* program, const ShapeTable& shapes, const float* co
     }
     switch (step.kind) {
       case StepKind::Map: rc = run_map(step, shapes, extent, dev, out, oshape); break;
-      case StepKind::MapChain: rc = run_map_chain(step, dev, out, oshape); break;
+      case StepKind::MapChain:
+      case StepKind::ChainReduce: rc = run_map_chain(step, shapes, dev, out, oshape); break;
       case StepKind::Reduce: rc = run_reduce(step, shapes, extent, dev, out, oshape); break;
       case StepKind::Contract: rc = run_contract(step, extent, dev, out, precision, &err); break;
       case StepKind::RowSoftmax: {

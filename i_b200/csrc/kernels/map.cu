@@ -310,10 +310,10 @@ __device__ __forceinline__ float chain_fetch(const ChainArgs& a, int code, float
   }
 }
 
-// cols % 4 == 0, every full or per-column operand 16-byte aligned, under 2^32 elements.  A thread
-// holds sixteen elements of the running result and, per operator, sixteen of the other operand;
-// the operator is decided once per step for all of them: one warp-uniform branch per operator,
-// straight-line arithmetic behind it.  Registers stay under 64 so that four blocks share an SM.
+// The operator list over the sixteen elements a thread holds.  A thread keeps the running result
+// and, per operator, the other operand; the operator is decided once per step for all sixteen:
+// one warp-uniform branch per operator, straight-line arithmetic behind it.  `fetch(code, dst)`
+// loads operand `code` for the thread's vectors.
 #define IB_CHAIN_CASE(OP)                                                                  \
   case OP:                                                                                 \
     if (unary)                                                                             \
@@ -322,63 +322,75 @@ __device__ __forceinline__ float chain_fetch(const ChainArgs& a, int code, float
       chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, p, q); });    \
     break;
 
+template <class Fetch>
+__device__ __forceinline__ void chain_run(const ChainArgs& a, float4 (&acc)[kChainVec],
+                                          Fetch fetch) {
+  float4 t[kChainVec];
+#pragma unroll
+  for (int u = 0; u < kChainVec; ++u) acc[u] = t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  fetch(a.lhs[0], acc);
+  for (int k = 0; k < a.n_ops; ++k) {
+    // Every operator after the first takes the running result on at least one side (the host
+    // checks).  With the running result on the right, the two sets of registers change places
+    // first, so that each operator exists once as op(acc) and once as op(acc, other).
+    const int lc = a.lhs[k], rc = a.rhs[k];
+    const bool unary = rc == IB_CHAIN_NONE;
+    const bool acc_left = k == 0 || lc == IB_CHAIN_PREV;
+    const int other = acc_left ? rc : lc;
+    if (!unary) {
+      if (other == IB_CHAIN_PREV) {
+#pragma unroll
+        for (int u = 0; u < kChainVec; ++u) t[u] = acc[u];
+      } else {
+        fetch(other, t);
+      }
+      if (!acc_left) {
+#pragma unroll
+        for (int u = 0; u < kChainVec; ++u) {
+          float4 keep = acc[u];
+          acc[u] = t[u];
+          t[u] = keep;
+        }
+      }
+    }
+    switch (a.op[k]) {
+      IB_CHAIN_CASE(IB_OP_ADD)
+      IB_CHAIN_CASE(IB_OP_MUL)
+      IB_CHAIN_CASE(IB_OP_SUB)
+      IB_CHAIN_CASE(IB_OP_DIV)
+      IB_CHAIN_CASE(IB_OP_MAX)
+      IB_CHAIN_CASE(IB_OP_MIN)
+      IB_CHAIN_CASE(IB_OP_POW)
+      IB_CHAIN_CASE(IB_OP_LOG)
+      IB_CHAIN_CASE(IB_OP_GT)
+      IB_CHAIN_CASE(IB_OP_GE)
+      IB_CHAIN_CASE(IB_OP_LT)
+      IB_CHAIN_CASE(IB_OP_LE)
+      IB_CHAIN_CASE(IB_OP_EQ)
+      IB_CHAIN_CASE(IB_OP_NE)
+      IB_CHAIN_CASE(IB_OP_AND)
+      IB_CHAIN_CASE(IB_OP_OR)
+      IB_CHAIN_CASE(IB_OP_XOR)
+      IB_CHAIN_CASE(IB_OP_NOT)
+    }
+  }
+}
+#undef IB_CHAIN_CASE
+
+// cols % 4 == 0, every full or per-column operand 16-byte aligned, under 2^32 elements.  64
+// registers, so that four blocks share an SM.
 __global__ void __launch_bounds__(kThreads, IB_CHAIN_BLOCKS)
 map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, unsigned nvec) {
   // Under 2^30 vectors and at most one block per kThreads * kChainVec of them: 32-bit indexes.
   const unsigned stride = gridDim.x * kThreads * kChainVec;
   for (unsigned base = blockIdx.x * kThreads * kChainVec + threadIdx.x; base < nvec;
        base += stride) {
-    float4 acc[kChainVec], t[kChainVec];
-#pragma unroll
-    for (int u = 0; u < kChainVec; ++u) acc[u] = t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    chain_fetch_all(a, a.lhs[0], acc, base, nvec);
     for (int e = 0; e < a.n_operands; ++e)
       if (e != a.lhs[0]) chain_prefetch_all(a, e, base, nvec);
-    for (int k = 0; k < a.n_ops; ++k) {
-      // Every operator after the first takes the running result on at least one side (the host
-      // checks).  With the running result on the right, the two sets of registers change places
-      // first, so that each operator exists once as op(acc) and once as op(acc, other).
-      const int lc = a.lhs[k], rc = a.rhs[k];
-      const bool unary = rc == IB_CHAIN_NONE;
-      const bool acc_left = k == 0 || lc == IB_CHAIN_PREV;
-      const int other = acc_left ? rc : lc;
-      if (!unary) {
-        if (other == IB_CHAIN_PREV) {
-#pragma unroll
-          for (int u = 0; u < kChainVec; ++u) t[u] = acc[u];
-        } else {
-          chain_fetch_all(a, other, t, base, nvec);
-        }
-        if (!acc_left) {
-#pragma unroll
-          for (int u = 0; u < kChainVec; ++u) {
-            float4 keep = acc[u];
-            acc[u] = t[u];
-            t[u] = keep;
-          }
-        }
-      }
-      switch (a.op[k]) {
-        IB_CHAIN_CASE(IB_OP_ADD)
-        IB_CHAIN_CASE(IB_OP_MUL)
-        IB_CHAIN_CASE(IB_OP_SUB)
-        IB_CHAIN_CASE(IB_OP_DIV)
-        IB_CHAIN_CASE(IB_OP_MAX)
-        IB_CHAIN_CASE(IB_OP_MIN)
-        IB_CHAIN_CASE(IB_OP_POW)
-        IB_CHAIN_CASE(IB_OP_LOG)
-        IB_CHAIN_CASE(IB_OP_GT)
-        IB_CHAIN_CASE(IB_OP_GE)
-        IB_CHAIN_CASE(IB_OP_LT)
-        IB_CHAIN_CASE(IB_OP_LE)
-        IB_CHAIN_CASE(IB_OP_EQ)
-        IB_CHAIN_CASE(IB_OP_NE)
-        IB_CHAIN_CASE(IB_OP_AND)
-        IB_CHAIN_CASE(IB_OP_OR)
-        IB_CHAIN_CASE(IB_OP_XOR)
-        IB_CHAIN_CASE(IB_OP_NOT)
-      }
-    }
+    float4 acc[kChainVec];
+    chain_run(a, acc, [&](int code, float4 (&dst)[kChainVec]) {
+      chain_fetch_all(a, code, dst, base, nvec);
+    });
 #pragma unroll
     for (int u = 0; u < kChainVec; ++u) {
       unsigned i = base + u * kThreads;
@@ -386,7 +398,91 @@ map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, unsig
     }
   }
 }
-#undef IB_CHAIN_CASE
+
+// ---- a chain of pointwise operators folded along the rows it produces ----------------------
+//
+// `ij-i~ij`, `^ij~ij`, `+ij~i` (a softmax's denominator), `ij*ij~ij`-style squares under a sum, a
+// mask under an "any": the full-size intermediate never exists.  TPR threads share a row (a warp
+// for short rows, the block for long ones); each runs the chain on its vectors and folds them.
+// Algorithmic traffic: the operands at their own sizes plus one value per row.
+template <int OP, int TPR>
+__global__ void __launch_bounds__(kThreads, IB_CHAIN_BLOCKS)
+reduce_chain_vec(const __grid_constant__ ChainArgs a, float* __restrict__ y, unsigned rows,
+                 unsigned cvec) {
+  constexpr int kRowsPerBlock = kThreads / TPR;
+  __shared__ float partial[kThreads / 32];
+  const unsigned j = threadIdx.x % TPR;
+  for (unsigned r0 = blockIdx.x * kRowsPerBlock; r0 < rows; r0 += gridDim.x * kRowsPerBlock) {
+    const unsigned r = r0 + threadIdx.x / TPR;
+    const bool live = r < rows;
+    float folded = reduce_identity(OP);
+    for (unsigned cv = j; live && cv < cvec; cv += TPR * kChainVec) {
+      float4 acc[kChainVec];
+      chain_run(a, acc, [&](int code, float4 (&dst)[kChainVec]) {
+        const float* p = a.operand[code];
+        const int mode = a.mode[code];
+        if (mode == 1 || mode == 3) {
+          const float s = __ldg(mode == 1 ? p + r : p);
+#pragma unroll
+          for (int u = 0; u < kChainVec; ++u) dst[u] = make_float4(s, s, s, s);
+        } else {
+          const float4* p4 = reinterpret_cast<const float4*>(p) +
+                             (mode == 0 ? static_cast<size_t>(r) * cvec : 0);
+#pragma unroll
+          for (int u = 0; u < kChainVec; ++u) {
+            const unsigned c = cv + u * TPR;
+            if (c < cvec) dst[u] = mode == 0 ? __ldcs(p4 + c) : __ldg(p4 + c);
+          }
+        }
+      });
+#pragma unroll
+      for (int u = 0; u < kChainVec; ++u)
+        if (cv + u * TPR < cvec)
+          folded = fold<OP>(folded, fold<OP>(fold<OP>(acc[u].x, acc[u].y), fold<OP>(acc[u].z, acc[u].w)));
+    }
+    folded = warp_fold<OP>(folded);
+    if (TPR == 32) {
+      if (j == 0 && live) y[r] = folded;
+    } else {
+      if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = folded;
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float v = threadIdx.x < kThreads / 32 ? partial[threadIdx.x] : reduce_identity(OP);
+        v = warp_fold<OP>(v);
+        if (threadIdx.x == 0 && live) y[r] = v;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Any shape and alignment: one warp per row, one element per lane and step.
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+reduce_chain_scalar(const __grid_constant__ ChainArgs a, float* __restrict__ y, size_t rows,
+                    size_t cols) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps_total = static_cast<size_t>(gridDim.x) * (kThreads / 32);
+  for (size_t r = static_cast<size_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); r < rows;
+       r += warps_total) {
+    float folded = reduce_identity(OP);
+    for (size_t c = lane; c < cols; c += 32) {
+      const size_t e = r * cols + c;
+      float acc = 0.0f;
+      for (int k = 0; k < a.n_ops; ++k) {
+        float l = chain_fetch(a, a.lhs[k], acc, e, r, c);
+        if (a.rhs[k] != IB_CHAIN_NONE)
+          acc = apply_binary(a.op[k], l, chain_fetch(a, a.rhs[k], acc, e, r, c));
+        else
+          acc = apply_unary(a.op[k], l);
+      }
+      folded = fold<OP>(folded, acc);
+    }
+    folded = warp_fold<OP>(folded);
+    if (lane == 0) y[r] = folded;
+  }
+}
+
 
 __global__ void __launch_bounds__(kThreads)
 map_chain_scalar(const __grid_constant__ ChainArgs a, float* __restrict__ y, size_t n,
@@ -478,44 +574,77 @@ extern "C" int ib_map_strided(int op, const float* a, const float* b, float* y, 
 #undef CALL
 }
 
-extern "C" int ib_map_chain(int n_ops, const int* ops, int n_operands, const float* const* operands,
-                            const int* modes, float* y, size_t rows, size_t cols, void* stream) {
-  if (n_ops < 1 || n_ops > IB_MAX_CHAIN_OPS) return ib::fail("ib_map_chain: 1 to 8 operators");
-  if (n_operands < 1 || n_operands > IB_MAX_CHAIN_OPERANDS)
-    return ib::fail("ib_map_chain: 1 to 4 operands");
-  if (!ops || !operands || !modes) return ib::fail("ib_map_chain: null pointer");
-  if (rows == 0 || cols == 0) return 0;
-  if (!y) return ib::fail("ib_map_chain: null pointer");
-  ib::ChainArgs args{};
-  args.n_ops = n_ops;
-  args.n_operands = n_operands;
-  bool vec = cols % 4 == 0 && ib::aligned16(y) && rows * cols <= 0xffffffffull;
+namespace ib {
+namespace {
+
+// Checks an operator list and fills the kernel's argument block; `vec` says whether the operands
+// allow the 16-byte paths (the caller adds its own conditions on the result).
+int chain_args(const char* who, int n_ops, const int* ops, int n_operands,
+               const float* const* operands, const int* modes, ChainArgs* args, bool* vec) {
+  const std::string name(who);
+  if (n_ops < 1 || n_ops > IB_MAX_CHAIN_OPS) return fail(name + ": 1 to 8 operators");
+  if (n_operands < 1 || n_operands > IB_MAX_CHAIN_OPERANDS) return fail(name + ": 1 to 4 operands");
+  if (!ops || !operands || !modes) return fail(name + ": null pointer");
+  args->n_ops = n_ops;
+  args->n_operands = n_operands;
   for (int e = 0; e < n_operands; ++e) {
-    if (!operands[e]) return ib::fail("ib_map_chain: null pointer");
-    if (modes[e] < 0 || modes[e] > 3) return ib::fail("ib_map_chain: operand mode must be 0..3");
-    args.operand[e] = operands[e];
-    args.mode[e] = modes[e];
-    if (modes[e] == 1 || modes[e] == 2) args.needs_rc = true;
-    if ((modes[e] == 0 || modes[e] == 2) && !ib::aligned16(operands[e])) vec = false;
+    if (!operands[e]) return fail(name + ": null pointer");
+    if (modes[e] < 0 || modes[e] > 3) return fail(name + ": operand mode must be 0..3");
+    args->operand[e] = operands[e];
+    args->mode[e] = modes[e];
+    if (modes[e] == 1 || modes[e] == 2) args->needs_rc = true;
+    if ((modes[e] == 0 || modes[e] == 2) && !aligned16(operands[e])) *vec = false;
   }
   for (int k = 0; k < n_ops; ++k) {
     const int op = ops[3 * k], lhs = ops[3 * k + 1], rhs = ops[3 * k + 2];
-    if (op < IB_OP_ADD || op > IB_OP_NOT) return ib::fail("unknown operator code");
+    if (op < IB_OP_ADD || op > IB_OP_NOT) return fail("unknown operator code");
     auto valid = [&](int code, bool may_be_none) {
       if (code == IB_CHAIN_NONE) return may_be_none;
       if (code == IB_CHAIN_PREV) return k > 0;
       return code >= 0 && code < n_operands;
     };
-    if (!valid(lhs, false) || !valid(rhs, true))
-      return ib::fail("ib_map_chain: operand code out of range");
+    if (!valid(lhs, false) || !valid(rhs, true)) return fail(name + ": operand code out of range");
     if (op == IB_OP_NOT && rhs != IB_CHAIN_NONE)
-      return ib::fail("ib_map_chain: operator `!!` has one operand");
+      return fail(name + ": operator `!!` has one operand");
     if (k > 0 && lhs != IB_CHAIN_PREV && rhs != IB_CHAIN_PREV)
-      return ib::fail("ib_map_chain: an operator after the first must take the previous result");
-    args.op[k] = op;
-    args.lhs[k] = lhs;
-    args.rhs[k] = rhs;
+      return fail(name + ": an operator after the first must take the previous result");
+    args->op[k] = op;
+    args->lhs[k] = lhs;
+    args->rhs[k] = rhs;
   }
+  return 0;
+}
+
+template <int OP>
+int launch_reduce_chain(const ChainArgs& args, bool vec, float* y, size_t rows, size_t cols,
+                        cudaStream_t s) {
+  const size_t cap = static_cast<size_t>(kNumSMs) * IB_MAP_CAP;
+  if (vec && cols >= 4096) {
+    reduce_chain_vec<OP, kThreads><<<static_cast<int>(rows < cap ? rows : cap), kThreads, 0, s>>>(
+        args, y, static_cast<unsigned>(rows), static_cast<unsigned>(cols / 4));
+  } else if (vec) {
+    const size_t blocks = (rows + kThreads / 32 - 1) / (kThreads / 32);
+    reduce_chain_vec<OP, 32><<<static_cast<int>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
+        args, y, static_cast<unsigned>(rows), static_cast<unsigned>(cols / 4));
+  } else {
+    const size_t blocks = (rows + kThreads / 32 - 1) / (kThreads / 32);
+    reduce_chain_scalar<OP><<<static_cast<int>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
+        args, y, rows, cols);
+  }
+  return check_launch("ib_reduce_rows_chain");
+}
+
+}  // namespace
+}  // namespace ib
+
+extern "C" int ib_map_chain(int n_ops, const int* ops, int n_operands, const float* const* operands,
+                            const int* modes, float* y, size_t rows, size_t cols, void* stream) {
+  ib::ChainArgs args{};
+  bool vec = cols % 4 == 0 && ib::aligned16(y) && rows * cols <= 0xffffffffull;
+  if (int rc = ib::chain_args("ib_map_chain", n_ops, ops, n_operands, operands, modes, &args, &vec))
+    return rc;
+  if (rows == 0 || cols == 0) return 0;
+  if (!y) return ib::fail("ib_map_chain: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t n = rows * cols;
   if (vec) {
@@ -534,4 +663,29 @@ extern "C" int ib_map_chain(int n_ops, const int* ops, int n_operands, const flo
     ib::map_chain_scalar<<<ib::grid_for(n, ib::kThreads), ib::kThreads, 0, s>>>(args, y, n, cols);
   }
   return ib::check_launch("ib_map_chain");
+}
+
+extern "C" int ib_reduce_rows_chain(int fold_op, int n_ops, const int* ops, int n_operands,
+                                    const float* const* operands, const int* modes, float* y,
+                                    size_t rows, size_t cols, void* stream) {
+  ib::ChainArgs args{};
+  bool vec = cols % 4 == 0 && cols > 0 && rows <= 0xffffffffull && rows * cols <= 0xffffffffull;
+  if (int rc = ib::chain_args("ib_reduce_rows_chain", n_ops, ops, n_operands, operands, modes, &args,
+                              &vec))
+    return rc;
+  if (rows == 0) return 0;
+  if (!y) return ib::fail("ib_reduce_rows_chain: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CALL(OP) ib::launch_reduce_chain<OP>(args, vec, y, rows, cols, s)
+  switch (fold_op) {
+    case IB_OP_ADD: return CALL(IB_OP_ADD);
+    case IB_OP_MUL: return CALL(IB_OP_MUL);
+    case IB_OP_MAX: return CALL(IB_OP_MAX);
+    case IB_OP_MIN: return CALL(IB_OP_MIN);
+    case IB_OP_AND: return CALL(IB_OP_AND);
+    case IB_OP_OR: return CALL(IB_OP_OR);
+    case IB_OP_XOR: return CALL(IB_OP_XOR);
+    default: return ib::fail("operator is not reducible (only + * > < && || ^^ fold)");
+  }
+#undef CALL
 }

@@ -56,6 +56,8 @@ def lib(ilang):
     lib.ib_map_chain.argtypes = [ci, ctypes.POINTER(ci), ci, ctypes.POINTER(vp), ctypes.POINTER(ci),
                                  vp, sz, sz, vp]
     lib.ib_reduce_rows.argtypes = [ci, vp, vp, sz, sz, vp]
+    lib.ib_reduce_rows_chain.argtypes = [ci, ci, ctypes.POINTER(ci), ci, ctypes.POINTER(vp),
+                                         ctypes.POINTER(ci), vp, sz, sz, vp]
     lib.ib_reduce_strided.argtypes = [ci, vp, vp, ci, ps, pd, ci, ps, pd, vp]
     lib.ib_row_softmax.argtypes = [vp, vp, sz, sz, vp]
     lib.ib_contract.argtypes = [vp, vp, vp, sz, sz, sz, sz, ci, ci, ci, vp, sz, vp]
@@ -75,6 +77,7 @@ def lib(ilang):
     lib.ib_attention_uses_tensor_arm.argtypes = [sz, sz, sz, sz, sz, ci]
     lib.ib_attention_uses_tensor_arm.restype = ci
     for name in ("ib_map_unary", "ib_map_binary", "ib_map_strided", "ib_map_chain", "ib_reduce_rows",
+                 "ib_reduce_rows_chain",
                  "ib_reduce_strided", "ib_row_softmax", "ib_contract", "ib_attention"):
         getattr(lib, name).restype = ci
     return lib

@@ -330,6 +330,23 @@ def test_pointwise_chains_are_one_kernel(ilang):
     assert steps_of(sm) == ["row_softmax"]
 
 
+def test_pointwise_chain_under_a_row_fold_is_one_kernel(ilang):
+    i, I = ilang.i, ilang.I
+    denom = i("ij-i~ij") >> i("^ij~ij") >> i("+ij~i")
+    assert steps_of(denom) == ["chain_reduce"]
+    assert "fold `+` of" in denom._code() and "in0-in1  ^_" in denom._code()
+    assert denom.output_shapes(np.zeros((6, 8), np.float32), np.zeros((6,), np.float32)) == [(6,)]
+    assert steps_of(i("ij>>j~ij") >> i("||ij~i")) == ["chain_reduce"]
+    assert steps_of(i("^bij~bij") >> i(">bij~bi")) == ["chain_reduce"]
+    assert steps_of(i("-i~i") >> i("+i~.")) == ["chain_reduce"]
+    # A product under a sum is still a contraction, a fold of another axis a plain fold.
+    assert steps_of(i("ij*ij~ij") >> i("+ij~i")) == ["contract"]
+    assert steps_of(i("^ij~ij") >> i("+ij~j")) == ["map", "reduce"]
+    assert steps_of(i("^bij~bij") >> i("+bij~b")) == ["map", "reduce"]
+    # The pointwise result is needed elsewhere: it is stored, and folded separately.
+    assert steps_of(i("^ij~ij") >> (I & i("+ij~i"))) == ["map", "reduce"]
+
+
 def test_output_shapes_follow_inputs(ilang):
     attn = readme_attention(ilang)
     q, k, v = (np.zeros(s, np.float32) for s in ((100, 40), (77, 40), (77, 24)))

@@ -100,9 +100,10 @@ def test_map_binary_modes(lib, oracle, torch, mode, op):
 NONE, PREV = -1, -2
 
 
-def run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=False):
+def run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=False, fold=None):
     """ops: (token, lhs, rhs) with lhs/rhs an operand index, PREV or NONE.  Returns (got, ref):
-    the kernel's result and the same operators applied one at a time by the oracle."""
+    the kernel's result and the same operators applied one at a time by the oracle; with `fold`
+    (an operator token) both are folded along each row."""
     devs = []
     for a in operands:
         if misalign:                                   # 4-byte aligned only
@@ -111,11 +112,16 @@ def run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=Fal
             devs.append(buf[1:])
         else:
             devs.append(dev(torch, a))
-    y = torch.empty(rows * cols + 1, device="cuda")[1 if misalign else 0:][:rows * cols]
+    n_out = rows if fold else rows * cols
+    y = torch.empty(n_out + 1, device="cuda")[1 if misalign else 0:][:n_out]
     flat = (ctypes.c_int * (3 * len(ops)))(*[v for tok, l, r in ops for v in (oracle.OPS[tok], l, r)])
     ptrs = (ctypes.c_void_p * len(devs))(*[d.data_ptr() for d in devs])
     md = (ctypes.c_int * len(modes))(*modes)
-    ok(lib, lib.ib_map_chain(len(ops), flat, len(devs), ptrs, md, y.data_ptr(), rows, cols, None))
+    if fold:
+        ok(lib, lib.ib_reduce_rows_chain(oracle.OPS[fold], len(ops), flat, len(devs), ptrs, md,
+                                         y.data_ptr(), rows, cols, None))
+    else:
+        ok(lib, lib.ib_map_chain(len(ops), flat, len(devs), ptrs, md, y.data_ptr(), rows, cols, None))
 
     def full(code, prev):
         if code == PREV:
@@ -128,6 +134,8 @@ def run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=Fal
     for tok, l, r in ops:
         prev = (oracle.map_unary(tok, full(l, prev)) if r == NONE
                 else oracle.map_binary(tok, full(l, prev), full(r, prev)))
+    if fold:
+        return y.cpu().numpy(), oracle.reduce_rows(fold, prev)
     return y.cpu().numpy().reshape(rows, cols), prev
 
 
@@ -195,6 +203,56 @@ def test_map_chain_random_programs(lib, oracle, torch, seed):
         ops.append((str(rng.choice(binary)),) + ((mine, other) if rng.random() < 0.6 or k == 0 else (other, mine)))
     got, ref = run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, misalign=bool(seed % 5 == 4))
     assert np.array_equal(got, ref, equal_nan=True), (ops, modes, rows, cols)
+
+
+@pytest.mark.parametrize("rows,cols,misalign", [(37, 52, False), (37, 51, False), (9, 8192, False),
+                                                (5, 4096 + 4, True), (300, 4, False), (2, 20000, False),
+                                                (1, 1, False), (1000, 128, False)])
+def test_reduce_rows_chain_softmax_denominator(lib, oracle, torch, rows, cols, misalign):
+    # sum_c exp(x[r][c] - m[r]) and max_c (x[r][c] - m[r]) * g[c]: warp-per-row, block-per-row and
+    # element-wise paths.
+    x, m, g = rand((rows, cols), 1), rand((rows,), 2) + 2.0, rand((cols,), 3)
+    got, ref = run_chain(lib, oracle, torch, [("-", 0, 1), ("^", PREV, NONE)], [x, m], [0, 1], rows, cols,
+                         misalign, fold="+")
+    assert max_rel_elementwise(got, ref) <= TOL_MAP
+    got, ref = run_chain(lib, oracle, torch, [("-", 0, 1), ("*", 2, PREV)], [x, m, g], [0, 1, 2], rows, cols,
+                         misalign, fold=">")
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("fold", ["+", "*", ">", "<", "&&", "||", "^^"])
+def test_reduce_rows_chain_every_fold(lib, oracle, torch, fold):
+    rows, cols = 67, 1028
+    x, t = rand((rows, cols), 4), rand((cols,), 5)
+    if fold == "*":
+        ops, operands, modes = [("*", 0, 1), ("+", PREV, 2)], [x, np.float32([0.01]), np.float32([1.0])], [0, 3, 3]
+    elif fold in ("&&", "||", "^^"):
+        x[3] = 5.0                                     # a row that is above every threshold
+        x[4] = -5.0                                    # and one below
+        ops, operands, modes = [(">>", 0, 1)], [x, t], [0, 2]
+    else:
+        ops, operands, modes = [("-", 0, 1), ("*", PREV, PREV)], [x, t], [0, 2]
+    got, ref = run_chain(lib, oracle, torch, ops, operands, modes, rows, cols, fold=fold)
+    if fold in "+*":
+        assert max_rel_elementwise(got, ref) <= TOL_MAP
+    else:
+        assert np.array_equal(got, ref)
+
+
+def test_reduce_rows_chain_rejects_bad_calls(lib, oracle, torch):
+    x = dev(torch, rand((4, 4), 1))
+    y = torch.empty(4, device="cuda")
+    ptrs = (ctypes.c_void_p * 1)(x.data_ptr())
+    md = (ctypes.c_int * 1)(0)
+    one = (ctypes.c_int * 3)(oracle.OPS["-"], 0, NONE)
+    assert lib.ib_reduce_rows_chain(oracle.OPS["-"], 1, one, 1, ptrs, md, y.data_ptr(), 4, 4, None) != 0
+    assert "not reducible" in last_error(lib)
+    bad = (ctypes.c_int * 3)(oracle.OPS["-"], PREV, NONE)
+    assert lib.ib_reduce_rows_chain(oracle.OPS["+"], 1, bad, 1, ptrs, md, y.data_ptr(), 4, 4, None) != 0
+    ok(lib, lib.ib_reduce_rows_chain(oracle.OPS["+"], 1, one, 1, ptrs, md, y.data_ptr(), 4, 4, None))
+    # No columns: every row is the fold's identity.
+    ok(lib, lib.ib_reduce_rows_chain(oracle.OPS[">"], 1, one, 1, ptrs, md, y.data_ptr(), 4, 0, None))
+    assert np.all(np.isneginf(y.cpu().numpy()))
 
 
 def test_map_chain_rejects_bad_programs(lib, oracle, torch):

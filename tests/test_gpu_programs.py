@@ -105,6 +105,28 @@ def test_pointwise_chain_components(ilang, oracle):
     assert max_rel_elementwise(norm.exec_numpy(x, x), ref) <= 1e-5
 
 
+def test_chain_reduction_components(ilang, oracle):
+    i, I = ilang.i, ilang.I
+    x, m = rand((70, 130), 1), rand((70,), 2) + 2.0
+    denom = i("ij-i~ij") >> i("^ij~ij") >> i("+ij~i")
+    assert "chain_reduce" in denom._code()
+    ref = oracle.reduce_rows("+", oracle.map_unary("^", oracle.map_binary("-", x, m, 1)))
+    assert max_rel_elementwise(denom.exec_numpy(x, m), ref) <= 1e-5
+    # log-sum-exp with the maximum taken by the program itself: fan-out, two folds, two chains.
+    lse = (I & i(">ij~i")) >> (i("ij-i~ij") >> i("^ij~ij") >> i("+ij~i") >> i("$i~i"))
+    got = lse.exec_numpy(x)
+    want = np.log(np.exp(x.astype(np.float64) - x.max(axis=1, keepdims=True)).sum(axis=1))
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+    # Batched "any above the column's threshold", exact.
+    y, t = rand((3, 40, 33), 3), rand((33,), 4) + 1.5
+    any_above = i("bij>>j~bij") >> i("||bij~bi")
+    assert np.array_equal(any_above.exec_numpy(y, t), (y > t).any(axis=2).astype(np.float32))
+    # Rank 1 to a scalar.
+    v = rand((1000,), 5)
+    got = (i("-i~i") >> i(">i~.")).exec_numpy(v)
+    assert got.shape == () and got == np.max(-v)
+
+
 @pytest.mark.parametrize("src,fn", [(">ij~i", np.max), ("<ij~i", np.min), ("+ij~i", np.sum)])
 def test_row_reductions(ilang, src, fn):
     # test.py:103-128
