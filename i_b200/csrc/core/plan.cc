@@ -289,6 +289,28 @@ void fuse_attention(Builder& b) {
     if (!f1.has_m || !f1.has_n || !f1.a_kmajor || !f1.b_kmajor || f1.swap_out) continue;
     const size_t s_node = qk.out.buffer.index;
     auto r_sm = b.sole_reader(s_node);
+    // Optionally one scalar on the logits between the contraction and the softmax
+    // (`.*ik~ik`, `ik*.~ik`, `ik/.~ik`): carried as a fourth operand of the fused step.
+    std::optional<size_t> scale_slot;
+    Access scale_operand;
+    bool scale_divides = false;
+    if (r_sm && b.steps[*r_sm].kind == StepKind::Map && b.steps[*r_sm].in.size() == 2) {
+      const Step& sc = b.steps[*r_sm];
+      const bool s_first = !sc.in[0].buffer.is_input && sc.in[0].buffer.index == s_node;
+      const Access& s_side = sc.in[s_first ? 0 : 1];
+      const Access& c_side = sc.in[s_first ? 1 : 0];
+      const bool shape_ok = sc.rank == qk.out.index.size() && is_iota(sc.out.index, sc.rank) &&
+                            is_iota(s_side.index, sc.rank) && c_side.index.empty() &&
+                            !s_side.buffer.is_input && s_side.buffer.index == s_node &&
+                            !(!c_side.buffer.is_input && c_side.buffer.index == s_node);
+      const bool op_ok = sc.op == Op::Mul || (sc.op == Op::Div && s_first);
+      if (shape_ok && op_ok) {
+        scale_slot = *r_sm;
+        scale_operand = c_side;
+        scale_divides = sc.op == Op::Div;
+        r_sm = b.sole_reader(sc.out.buffer.index);
+      }
+    }
     if (!r_sm || b.steps[*r_sm].kind != StepKind::RowSoftmax) continue;
     const Step& sm = b.steps[*r_sm];
     if (sm.rank != f1.n_batch + 2) continue;
@@ -312,16 +334,24 @@ void fuse_attention(Builder& b) {
     fused.op = Op::Add;
     fused.rank = qk.rank;
     fused.in = {qk.in[0], qk.in[1], pv.in[1]};
+    if (scale_slot) {
+      fused.in.push_back(scale_operand);
+      fused.op = scale_divides ? Op::Div : Op::Mul;     // how the fourth operand meets the logits
+    }
     fused.out = pv.out;
     fused.form = f1;
     fused.form2 = f2;
     fused.hint = sm.hint;
     fused.hint.staged = pv.hint.staged || sm.hint.staged;
     fused.nodes = qk.nodes;
+    if (scale_slot)
+      fused.nodes.insert(fused.nodes.end(), b.steps[*scale_slot].nodes.begin(),
+                         b.steps[*scale_slot].nodes.end());
     fused.nodes.insert(fused.nodes.end(), sm.nodes.begin(), sm.nodes.end());
     fused.nodes.insert(fused.nodes.end(), pv.nodes.begin(), pv.nodes.end());
     const size_t slot = *r_pv, sm_slot = *r_sm;
     b.alive[n] = false;
+    if (scale_slot) b.alive[*scale_slot] = false;
     b.alive[sm_slot] = false;
     b.steps[slot] = std::move(fused);
   }
@@ -601,7 +631,10 @@ std::string Plan::describe() const {
       case StepKind::Attention:
         os << "    kernel: ib_attention (fused online softmax, both contractions on tcgen05, S/P/O "
               "in TMEM); batch axes "
-           << s.form.n_batch << ", V " << (s.form2.b_kmajor ? "[dv,j]" : "[j,dv]") << "\n";
+           << s.form.n_batch << ", V " << (s.form2.b_kmajor ? "[dv,j]" : "[j,dv]");
+        if (s.in.size() == 4)
+          os << ", logits " << (s.op == Op::Div ? "/ " : "* ") << buffer_name(s.in[3].buffer);
+        os << "\n";
         break;
       case StepKind::Reduce:
         os << "    kernel: ib_reduce\n";

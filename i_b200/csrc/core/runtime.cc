@@ -161,6 +161,13 @@ bool attention_dims(const Step& step, const ShapeTable& shapes, AttentionDims* o
       *err = "attention batch axes differ between operands";
       return false;
     }
+  if (step.in.size() == 4) {
+    const Shape* c = shapes.get(step.in[3].buffer);
+    if (!c || !c->empty()) {
+      *err = "the scale on the attention logits must be a scalar";
+      return false;
+    }
+  }
   out->batch = product(*q, 0, nb);
   out->nq = (*q)[nb];
   out->d = (*q)[nb + 1];
@@ -463,10 +470,11 @@ int run_attention(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev
     set_error(*err);
     return -1;
   }
-  return ib_attention(dev.get(step.in[0].buffer), dev.get(step.in[1].buffer),
-                      dev.get(step.in[2].buffer), out, dims.batch, dims.nq, dims.nk, dims.d,
-                      dims.dv, dims.v_kmajor, precision, step.hint.col_split, ws, ws_bytes,
-                      dev.stream);
+  const float* scale = step.in.size() == 4 ? dev.get(step.in[3].buffer) : nullptr;
+  return ib_attention_scaled(dev.get(step.in[0].buffer), dev.get(step.in[1].buffer),
+                             dev.get(step.in[2].buffer), out, dims.batch, dims.nq, dims.nk, dims.d,
+                             dims.dv, dims.v_kmajor, precision, step.hint.col_split, scale,
+                             step.op == Op::Div, ws, ws_bytes, dev.stream);
 }
 
 // Runs the plan on device pointers.  `outputs[i]` receives graph output i.
@@ -632,6 +640,7 @@ int pipelined_host_attention(const i_program* program, const ShapeTable& shapes,
   if (plan.steps.size() != 1 || plan.steps[0].kind != StepKind::Attention) return 1;
   if (output_count != 1 || plan.outputs.size() != 1 || plan.outputs[0].is_input) return 1;
   const Step& step = plan.steps[0];
+  if (step.in.size() != 3) return 1;                   // scaled logits: the plain path
   if (plan.outputs[0].index != step.out.buffer.index) return 1;
   for (int a = 0; a < 3; ++a)
     if (!step.in[a].buffer.is_input || step.in[a].buffer.index >= input_count) return 1;

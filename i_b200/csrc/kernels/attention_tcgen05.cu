@@ -112,6 +112,8 @@ struct Params {
   long long iters_base;   // tail (row tile, key tile) pairs per CTA: CTA g takes iters_base, plus
   int iters_rem;          // one more when g < iters_rem
   const float* v_scale;   // mixed arm: V^T holds V / v_scale[head] (a power of two); else null
+  const float* logit_scale;   // one value on the device, or null: the logits are S * it (S / it when
+  int logit_divide;           // logit_divide), applied to Q as it is staged
   float* o;            // [batch][nq][dv]
   float* part_o;       // [2 * ctas][128][dv]: slot 2g + (0: first piece, 1: last piece of CTA g)
   float* part_m;       // [2 * ctas][128]
@@ -481,6 +483,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
       const bool live = row < p.nq;
       const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
+      // A scale on the logits is a scale on Q: (c q) . k = c (q . k).  Read here, once per row
+      // tile, rather than held in a register across the key loop.
+      float qs = 1.0f;
+      if (p.logit_scale) {
+        qs = __ldg(p.logit_scale);
+        if (p.logit_divide) qs = 1.0f / qs;
+      }
       // This thread's 64 features [64h, 64h+64) of its row, rounded to the operand type.
       auto load4 = [&](int col) {
         float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -492,6 +501,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
           if (col + 2 < p.d) x.z = qrow[col + 2];
           if (col + 3 < p.d) x.w = qrow[col + 3];
         }
+        x.x *= qs; x.y *= qs; x.z *= qs; x.w *= qs;
         return x;
       };
       if (!G::kQkHalf) {
@@ -899,8 +909,8 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      AttentionArm arm, const float* v_scale, bool follows_prepare, float* partials,
-                      cudaStream_t s) {
+                      AttentionArm arm, const float* v_scale, const float* logit_scale,
+                      bool logit_divide, bool follows_prepare, float* partials, cudaStream_t s) {
   const bool bf16 = arm == AttentionArm::BF16, mixed = arm == AttentionArm::MIXED;
   if (batch == 0 || nq == 0) return 0;
   if (nk == 0) return fail("ib_attention: no keys");
@@ -947,6 +957,8 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   p.iters_rem = static_cast<int>(tail_iters % ctas);
   p.o = o;
   p.v_scale = mixed ? v_scale : nullptr;
+  p.logit_scale = logit_scale;
+  p.logit_divide = logit_divide ? 1 : 0;
   const size_t slots_rows = static_cast<size_t>(2) * ctas * kBQ;
   p.part_o = partials;
   p.part_m = partials + slots_rows * dv;

@@ -231,10 +231,11 @@ extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t n
   return bytes;
 }
 
-extern "C" int ib_attention(const float* q, const float* k, const float* v, float* o, size_t batch,
-                            size_t nq, size_t nk, size_t d, size_t dv, int v_kmajor, int precision,
-                            size_t kv_tile, void* workspace, size_t workspace_bytes,
-                            void* stream) {
+extern "C" int ib_attention_scaled(const float* q, const float* k, const float* v, float* o,
+                                   size_t batch, size_t nq, size_t nk, size_t d, size_t dv,
+                                   int v_kmajor, int precision, size_t kv_tile,
+                                   const float* logit_scale, int logit_divide, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
   using namespace ib;
   (void)kv_tile;
   if (batch == 0 || nq == 0 || dv == 0) return 0;
@@ -258,17 +259,30 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
     if (!partials)
       return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
     return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch,
-                             kv.arm, kv.v_scale, true, partials, s);
+                             kv.arm, kv.v_scale, logit_scale, logit_divide != 0, true, partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);
   if (!scores) return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
   const int sub = tensor ? IB_PRECISION_TF32 : IB_PRECISION_FP32;
   if (int rc = ib_contract(q, k, scores, batch, nq, nk, d, 1, 1, sub, nullptr, 0, stream)) return rc;
+  // The scale as the component states it: each logit times (or over) the scalar, in place.
+  if (logit_scale)
+    if (int rc = ib_map_binary(logit_divide ? IB_OP_DIV : IB_OP_MUL, 1, scores, logit_scale, scores,
+                               1, batch * nq * nk, stream))
+      return rc;
   if (int rc = ib_row_softmax(scores, scores, batch * nq, nk, stream)) return rc;
   uint8_t* rest = ws.base ? ws.base + ws.used : nullptr;
   return ib_contract(scores, v, o, batch, nq, dv, nk, 1, v_kmajor, sub, rest,
                      workspace_bytes - ws.used, stream);
+}
+
+extern "C" int ib_attention(const float* q, const float* k, const float* v, float* o, size_t batch,
+                            size_t nq, size_t nk, size_t d, size_t dv, int v_kmajor, int precision,
+                            size_t kv_tile, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  return ib_attention_scaled(q, k, v, o, batch, nq, nk, d, dv, v_kmajor, precision, kv_tile, nullptr,
+                             0, workspace, workspace_bytes, stream);
 }
 
 // ---- two-phase form: prepare K and V once, run query blocks against them ----
@@ -325,7 +339,8 @@ extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, 
   if (!partials)
     return fail("ib_attention_run: workspace too small (see ib_attention_run_workspace_bytes)");
   return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch, kv.arm,
-                           kv.v_scale, false, partials, static_cast<cudaStream_t>(stream));
+                           kv.v_scale, nullptr, false, false, partials,
+                           static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ib_attention_uses_tensor_arm(size_t batch, size_t nq, size_t nk, size_t d, size_t dv,

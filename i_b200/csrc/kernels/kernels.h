@@ -68,12 +68,13 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 // BF16 — both bf16 ([b][nk][d_pitch], [b][dv][nk_pitch], pitches % 8 == 0), kind::f16 MMAs;
 // MIXED — k as in TF32, vt fp16 holding V / v_scale[head] (nk_pitch % 8 == 0): S = Q K^T in TF32,
 // O += P V in fp16 (same 10-bit mantissa).  follows_prepare: the kernel before this call in the
-// stream is the one that wrote k and vt (the launch may then overlap its tail).
+// stream is the one that wrote k and vt (the launch may then overlap its tail).  logit_scale: one
+// float on the device, or null; the logits are S * it, or S / it with logit_divide.
 enum class AttentionArm { TF32, BF16, MIXED };
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      AttentionArm arm, const float* v_scale, bool follows_prepare, float* partials,
-                      cudaStream_t s);
+                      AttentionArm arm, const float* v_scale, const float* logit_scale,
+                      bool logit_divide, bool follows_prepare, float* partials, cudaStream_t s);
 // Mixed-arm operand preparation: kr = K rounded to TF32; vt16[b][c][nk_pitch] = fp16(V^T / scale[b])
 // with scale[b] the power of two that brings the head's largest |V| into [2^14, 2^15); block_max
 // is scratch of batch * kAbsmaxBlocks floats.

@@ -227,6 +227,8 @@ def _view_of(x, writable):
         import numpy as np
     except ImportError:  # pragma: no cover
         np = None
+    if np is not None and isinstance(x, np.generic) and not writable:
+        x = np.asarray(x, dtype=np.float32)             # a NumPy scalar is a rank-0 tensor
     if np is not None and isinstance(x, np.ndarray):
         arr = x
         if arr.dtype != np.float32 or not arr.flags.c_contiguous:

@@ -64,6 +64,8 @@ def lib(ilang):
     lib.ib_contract_workspace_bytes.argtypes = [sz, sz, sz, sz, ci, ci, ci]
     lib.ib_contract_workspace_bytes.restype = sz
     lib.ib_attention.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, ci, ci, sz, vp, sz, vp]
+    lib.ib_attention_scaled.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, ci, ci, sz, vp, ci, vp, sz, vp]
+    lib.ib_attention_scaled.restype = ci
     lib.ib_attention_workspace_bytes.argtypes = [sz, sz, sz, sz, sz, ci, ci]
     lib.ib_attention_workspace_bytes.restype = sz
     lib.ib_attention_prepare_bytes.argtypes = [sz, sz, sz, sz, ci]

@@ -261,6 +261,37 @@ def deferred_attention(ilang, shift=False, staged=True):
     return chain >> exp >> (mm & row_sum) >> row_div
 
 
+def scaled_attention(ilang, kind="mul_right", batched=False):
+    """README attention with one scalar on the logits: (q, k, c, v), or (c, q, k, v) for mul_left
+    and rdiv.  `batched` puts two leading axes on every tensor."""
+    i, I = ilang.i, ilang.I
+    b = "bh" if batched else ""
+    mm_t = i(f"{b}ik*{b}jk~{b}ijk | i:16,j:16 | {b}jii'j'k") >> i(f"+{b}ijk~{b}ij | i:16,j:16 | {b}jii'j'k0")
+    scale = {"mul_left": f".*{b}ij~{b}ij", "mul_right": f"{b}ij*.~{b}ij", "div": f"{b}ij/.~{b}ij",
+             "rdiv": f"./{b}ij~{b}ij"}[kind]
+    logits = ((I | mm_t) if kind in ("mul_left", "rdiv") else (mm_t | I)) >> i(scale)
+    row_max_shift = (I & i(f">{b}ij~{b}i | i:16,j:16 | {b}ji0i'j'")) >> i(f"{b}ij-{b}i~{b}ij | i:16,j:16 | {b}ji01i'j'")
+    exp = i(f"^{b}ij~{b}ij | i:16,j:16 | {b}ji0i'j'")
+    row_normalize = (I & i(f"+{b}ij~{b}i | i:16,j:16 | {b}ji0i'j'")) >> i(f"{b}ij/{b}i~{b}ij | i:16,j:16 | {b}ji01i'j'")
+    mm = i(f"{b}ij*{b}jk~{b}ikj | i:16,j:16 | {b}ji0i'kj'") >> i(f"+{b}ikj~{b}ik | i:16,j:16 | {b}jii'kj'0")
+    return logits >> row_max_shift >> exp >> row_normalize >> mm
+
+
+def test_scaled_logits_stay_one_attention_kernel(ilang):
+    for kind, text in (("mul_right", "logits * in2"), ("mul_left", "logits * in0"), ("div", "logits / in2")):
+        attn = scaled_attention(ilang, kind)
+        assert steps_of(attn) == ["attention"], kind
+        assert text in attn._code()
+    assert steps_of(scaled_attention(ilang, "div", batched=True)) == ["attention"]
+    # A scalar over the logits is not a scale on them.
+    assert steps_of(scaled_attention(ilang, "rdiv")) == ["contract", "map", "row_softmax", "contract"]
+    attn = scaled_attention(ilang)
+    q, k, v = (np.zeros(s, np.float32) for s in ((100, 40), (77, 40), (77, 24)))
+    assert attn.output_shapes(q, k, np.float32(0.5), v) == [(100, 24)]
+    with pytest.raises(RuntimeError, match="scalar"):
+        attn.output_shapes(q, k, np.zeros((3,), np.float32), v)
+
+
 def test_deferred_normalisation_is_one_attention_kernel(ilang):
     assert steps_of(deferred_attention(ilang)) == ["attention"]
     assert steps_of(deferred_attention(ilang, shift=True)) == ["attention"]

@@ -597,6 +597,31 @@ def test_attention_tf32_f16_shapes(lib, oracle, torch, nq, nk, d, dv):
     assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= TOL_TF32
 
 
+@pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32), (BF16, TOL_BF16),
+                                           (TF32_F16, TOL_TF32)])
+@pytest.mark.parametrize("c,divide", [(0.125, False), (8.0, True), (-0.25, False), (-5.0, True)])
+@pytest.mark.parametrize("nq,nk,d,dv", [(300, 517, 64, 40), (2, 130, 128, 128)])
+def test_attention_scaled_logits(lib, oracle, torch, precision, tol, c, divide, nq, nk, d, dv):
+    # softmax(c Q K^T) V or softmax(Q K^T / c) V against the oracle's chain with the scale applied
+    # to the scores (a negative scale turns the row maximum into the row minimum).
+    q, k, v = rand((2, nq, d), 71), rand((2, nk, d), 72), rand((2, nk, dv), 73)
+    dq, dk, dvv = dev(torch, q), dev(torch, k), dev(torch, v)
+    dc = dev(torch, np.float32([c]))
+    o = torch.full((2, nq, dv), float("nan"), device="cuda")
+    ws_bytes = lib.ib_attention_workspace_bytes(2, nq, nk, d, dv, 0, precision)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    ok(lib, lib.ib_attention_scaled(dq.data_ptr(), dk.data_ptr(), dvv.data_ptr(), o.data_ptr(), 2, nq,
+                                    nk, d, dv, 0, precision, 0, dc.data_ptr(), int(divide),
+                                    ws.data_ptr(), ws_bytes, None))
+    got = o.cpu().numpy()
+    assert not np.isnan(got).any()
+    for b in range(2):
+        s_ = oracle.contract(q[b], k[b])
+        s_ = oracle.map_binary("/" if divide else "*", s_, np.full_like(s_, c))
+        ref = oracle.contract(oracle.row_softmax(s_), v[b], b_kmajor=False)
+        assert max_rel_to_peak(got[b], ref) <= tol
+
+
 @pytest.mark.parametrize("scale", [1e-30, 1e-6, 1.0, 3.0e4, 7.0e4, 1e9, 1e30])
 @pytest.mark.parametrize("v_kmajor", [False, True])
 def test_attention_tf32_f16_value_range(lib, oracle, torch, scale, v_kmajor):

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from conftest import max_rel_elementwise, max_rel_to_peak
-from test_front import deferred_attention, naive_attention, readme_attention
+from test_front import deferred_attention, naive_attention, readme_attention, scaled_attention
 
 pytestmark = pytest.mark.gpu
 
@@ -174,6 +174,32 @@ def test_deferred_normalisation_attention(ilang, shift):
     assert max_rel_to_peak(big.exec_numpy(qb, k, v), np_attention(qb, k, v)) <= 1e-4
     big.set_precision("tf32")
     assert np.isfinite(big.exec_numpy(qb, k, v)).all()
+
+
+@pytest.mark.parametrize("kind", ["mul_right", "mul_left", "div"])
+def test_scaled_dot_product_attention(ilang, kind):
+    # The 1/sqrt(d) of scaled-dot-product attention written into the component: one fused kernel,
+    # on the tensor arm (large case) and on the exact arm (small case).
+    attn = scaled_attention(ilang, kind)
+    assert "step 0: attention" in attn._code()
+    for (nq, nk, d, dv), tol in (((700, 900, 64, 64), 5e-3), ((40, 50, 16, 8), 1e-5)):
+        q, k, v = rand((nq, d), 1), rand((nk, d), 2), rand((nk, dv), 3)
+        c = np.float32(d ** 0.5 if kind == "div" else d ** -0.5)
+        args = (c, q, k, v) if kind == "mul_left" else (q, k, c, v)
+        attn.set_precision("auto" if tol > 1e-4 else "fp32")
+        got = attn.exec_numpy(*args)
+        ref = np_attention(q * np.float32(d ** -0.5), k, v)
+        assert max_rel_to_peak(got, ref) <= tol
+
+
+def test_scaled_attention_batched_on_device(ilang):
+    import torch
+    attn = scaled_attention(ilang, "div", batched=True)
+    q, k, v = rand((2, 3, 260, 64), 4), rand((2, 3, 300, 64), 5), rand((2, 3, 300, 32), 6)
+    c = torch.tensor(8.0, device="cuda")
+    got = attn.exec_torch(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), c,
+                          torch.from_numpy(v).cuda()).cpu().numpy()
+    assert max_rel_to_peak(got, np_attention(q / 8.0, k, v)) <= 5e-3
 
 
 def batched_readme_attention(ilang):
