@@ -91,6 +91,7 @@ int default_precision() {
   if (v == "tf32") return IB_PRECISION_TF32;
   if (v == "bf16") return IB_PRECISION_BF16;
   if (v == "tf32_f16") return IB_PRECISION_TF32_F16;
+  if (v == "f16") return IB_PRECISION_F16;
   return IB_PRECISION_AUTO;
 }
 
@@ -1097,7 +1098,7 @@ void i_string_free(char* s) { std::free(s); }
 
 int i_b200_program_set_precision(i_program* program, int precision) {
   if (!program) return ib::set_error("null program"), -1;
-  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_TF32_F16)
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_F16)
     return ib::set_error("unknown precision"), -1;
   program->precision.store(precision);
   return 0;

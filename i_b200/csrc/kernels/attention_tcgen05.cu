@@ -71,8 +71,11 @@ constexpr int kMaxRing = 3;
 // Arithmetic of the two contractions.  MIXED runs S = Q K^T on TF32 operands and O += P V on
 // fp16 ones: fp16 has TF32's 10-bit mantissa, P lies in [0, 1], and V is scaled per head by a
 // power of two into fp16's range, so the result has TF32 accuracy while the second contraction
-// issues half as many MMAs.
-enum class Arm { TF32, BF16, MIXED };
+// issues half as many MMAs.  F16 does the same for S = Q K^T: Q is scaled per query row and K per
+// tile of 128 keys by powers of two into fp16's range (the scales return, exactly, in the
+// multiplier that takes S to the exponent), so both contractions issue half as many MMAs on
+// operands of TF32's precision.
+enum class Arm { TF32, BF16, MIXED, F16 };
 
 // Per contraction: a tile of 128 keys is 4 chunks of 32 fp32 or 2 chunks of 64 16-bit
 // elements; the ring always has three slots (the producer's slot-reuse waits rely on that
@@ -81,9 +84,10 @@ enum class Arm { TF32, BF16, MIXED };
 // a column), so a 128-deep contraction is 16 or 8 instructions.
 template <Arm ARM>
 struct Geometry {
-  static constexpr bool kQkHalf = ARM == Arm::BF16;               // Q, K are 16-bit
+  static constexpr bool kQkHalf = ARM == Arm::BF16 || ARM == Arm::F16;   // Q, K are 16-bit
   static constexpr bool kPvHalf = ARM != Arm::TF32;               // P, V are 16-bit
-  static constexpr Fmt kQkFmt = kQkHalf ? Fmt::BF16 : Fmt::TF32;
+  static constexpr bool kScaledQk = ARM == Arm::F16;              // Q rows and K tiles carry scales
+  static constexpr Fmt kQkFmt = ARM == Arm::BF16 ? Fmt::BF16 : (ARM == Arm::F16 ? Fmt::F16 : Fmt::TF32);
   static constexpr Fmt kPvFmt = ARM == Arm::TF32 ? Fmt::TF32 : (ARM == Arm::BF16 ? Fmt::BF16 : Fmt::F16);
   static constexpr int kQkChunkElems = kQkHalf ? 64 : 32;
   static constexpr int kQkStepElems = kQkHalf ? 16 : 8;           // K per MMA
@@ -112,6 +116,7 @@ struct Params {
   long long iters_base;   // tail (row tile, key tile) pairs per CTA: CTA g takes iters_base, plus
   int iters_rem;          // one more when g < iters_rem
   const float* v_scale;   // mixed arm: V^T holds V / v_scale[head] (a power of two); else null
+  const float* k_tile_scale;  // fp16 arm: K holds K / k_tile_scale[head][key tile] (powers of two)
   const float* logit_scale;   // one value on the device, or null: the logits are S * it (S / it when
   int logit_divide;           // logit_divide), applied to Q as it is staged
   float* o;            // [batch][nq][dv]
@@ -186,6 +191,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t out;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
   return out;
+}
+
+// The power of two that brings a largest magnitude into [2^14, 2^15) (1 for zero, inf or NaN):
+// what fp16 operands are stored over so that large values fit and small ones keep their mantissa.
+__device__ __forceinline__ float f16_range_scale(float absmax) {
+  if (!(absmax > 0.0f) || !(absmax < CUDART_INF_F)) return 1.0f;
+  int e;
+  frexpf(absmax, &e);                          // absmax = f * 2^e, f in [0.5, 1)
+  return ldexpf(1.0f, max(e - 15, -120));
 }
 
 __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
@@ -475,10 +489,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     long long c_load = 0, c_max = 0, c_sync = 0, c_exp = 0, c_store = 0;   // PROF: cycles per phase
     const long long t_start = tick<PROF>();
     bool dead = false;                        // a wait gave up; keep hitting the barriers only
+    float row_mul = kLog2E32;                 // S of this thread's row -> exponent units (see stage_q)
 
     // Q of one row tile: global -> operand type (nearest) -> tensor memory, this thread's 64
     // features [64h, 64h+64) of its row; then one arrival per warp on q_ready.
-    auto stage_q = [&](int head, int q_tile) {
+    // Returns the factor that takes this row's S to the exponent's units, K's tile scale aside:
+    // log2(e), times the row's own power of two where Q is stored scaled.
+    auto stage_q = [&](int head, int q_tile) -> float {
+      float row_mul = kLog2E32;
       const long long row = static_cast<long long>(q_tile) * kBQ + r;
       const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
       const bool live = row < p.nq;
@@ -520,13 +538,48 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
           tmem_st_32x32(tmem_base + lane_bits + kTmemQ + col0, v);
         }
       } else {
-        // bf16 pairs, two features per column: features [64h, 64h+64) -> columns [32h, 32h+32).
+        // 16-bit pairs, two features per column: features [64h, 64h+64) -> columns [32h, 32h+32).
+        // The whole row's largest magnitude decides the power of two that brings the row into
+        // [2^14, 2^15); the other half of the row is read for that alone (once per row tile,
+        // from L2, eight loads at a time), then this thread's own 64 features, all in flight
+        // together.
+        float m = 0.0f;
+        if (G::kScaledQk) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            float4 other[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) other[e] = load4((h ^ 1) * 64 + half * 32 + 4 * e);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              m = fmaxf(m, fmaxf(fmaxf(fabsf(other[e].x), fabsf(other[e].y)),
+                                 fmaxf(fabsf(other[e].z), fabsf(other[e].w))));
+          }
+        }
+        float4 own[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) own[e] = load4(h * 64 + 4 * e);
+        float inv = 1.0f;
+        if (G::kScaledQk) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(own[e].x), fabsf(own[e].y)),
+                               fmaxf(fabsf(own[e].z), fabsf(own[e].w))));
+          const float scale = f16_range_scale(m);
+          inv = 1.0f / scale;
+          row_mul = kLog2E32 * scale;
+        }
         uint32_t v[32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float4 x = load4(h * 64 + 2 * e);
-          v[e + 0] = pack_bf16(x.x, x.y);
-          v[e + 1] = pack_bf16(x.z, x.w);
+        for (int e = 0; e < 16; ++e) {
+          const float4 x = own[e];
+          if (G::kQkFmt == Fmt::F16) {
+            v[2 * e + 0] = pack_f16(x.x * inv, x.y * inv);
+            v[2 * e + 1] = pack_f16(x.z * inv, x.w * inv);
+          } else {
+            v[2 * e + 0] = pack_bf16(x.x, x.y);
+            v[2 * e + 1] = pack_bf16(x.z, x.w);
+          }
         }
         tmem_st_32x32(tmem_base + lane_bits + kTmemQ + h * 32, v);
       }
@@ -534,6 +587,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->q_ready);
+      return row_mul;
     };
 
     PieceCursor cursor = pieces_begin(p);
@@ -547,9 +601,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     const bool whole = pc.whole;
     const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
 
-    if (first_piece) stage_q(b, qt);        // later pieces: staged at the end of the piece before
+    if (first_piece) row_mul = stage_q(b, qt);   // later pieces: staged at the end of the piece before
     first_piece = false;
 
+    float ks_ahead = 1.0f;                    // fp16 arm: the next tile's K scale, read a tile early
     float m_used = -CUDART_INF_F;             // running maximum, log2 domain
     float l = 0.0f;                           // this half's share of the row sum
 
@@ -563,6 +618,16 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         const long long t0 = tick<PROF>();
         dead = !mbar_wait_warp(&sh->s_full[buf], (t >> 1) & 1, abort, p.status, 207);
         wait_s += tick<PROF>() - t0;
+      }
+      // S -> exponent units: log2(e), times the scales Q's row and K's tile were stored over.
+      // K's scales come from the preparation kernel; every read of them follows an S that was
+      // computed from its K, so the kernel has completed.
+      float mul = kLog2E32;
+      if (G::kScaledQk) {
+        const float* ks = p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + kv_lo + jj;
+        const float here = jj == 0 ? __ldg(ks) : ks_ahead;
+        if (jj + 1 < n_kv) ks_ahead = __ldg(ks + 1);
+        mul = row_mul * here;
       }
       float mx = -CUDART_INF_F;
       long long tp = tick<PROF>();
@@ -603,7 +668,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       if (sh->give_up) break;                 // uniform: every writer wrote before the barrier
       mx = fmaxf(mx, sh->half_max[buf][h ^ 1][r]);
 
-      const float m_new = fmaxf(m_used, mx * kLog2E32);
+      const float m_new = fmaxf(m_used, mx * mul);
       const bool grow = m_new > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow)) {
         const float factor = grow ? ex2_approx(m_used - m_new) : 1.0f;
@@ -646,10 +711,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int c = g8 * 8 + u * 2;
-            const uint32_t e0 = ex2_f16x2(pack_f16(fmaf(__uint_as_float(s0[c]), kLog2E32, -m_used),
-                                                   fmaf(__uint_as_float(s0[c + 1]), kLog2E32, -m_used)));
-            const uint32_t e1 = ex2_f16x2(pack_f16(fmaf(__uint_as_float(s1[c]), kLog2E32, -m_used),
-                                                   fmaf(__uint_as_float(s1[c + 1]), kLog2E32, -m_used)));
+            const uint32_t e0 = ex2_f16x2(pack_f16(fmaf(__uint_as_float(s0[c]), mul, -m_used),
+                                                   fmaf(__uint_as_float(s0[c + 1]), mul, -m_used)));
+            const uint32_t e1 = ex2_f16x2(pack_f16(fmaf(__uint_as_float(s1[c]), mul, -m_used),
+                                                   fmaf(__uint_as_float(s1[c + 1]), mul, -m_used)));
             packed[c / 2] = e0;
             packed[16 + c / 2] = e1;
             acc0 = add_f16x2(acc0, e0);
@@ -667,8 +732,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        float e0 = ex2_approx(fmaf(__uint_as_float(s0[c]), kLog2E32, -m_used));
-        float e1 = ex2_approx(fmaf(__uint_as_float(s1[c]), kLog2E32, -m_used));
+        float e0 = ex2_approx(fmaf(__uint_as_float(s0[c]), mul, -m_used));
+        float e1 = ex2_approx(fmaf(__uint_as_float(s1[c]), mul, -m_used));
         sum0 += e0;
         sum1 += e1;
         s0[c] = __float_as_uint(e0);
@@ -707,12 +772,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     // ---- Q of the next piece, before this one's epilogue: every Q K^T of this piece has
     // completed (its S was read above), so Q's columns are free, and the MMA warp can run
     // the next piece's first Q K^T while O is being read out below.
+    float next_row_mul = kLog2E32;
     {
       PieceCursor ahead = cursor;
       Piece nx;
       if (!dead && next_piece(p, ahead, nx)) {
         const int nb = nx.unit / p.q_tiles;
-        stage_q(nb, nx.unit - nb * p.q_tiles);
+        next_row_mul = stage_q(nb, nx.unit - nb * p.q_tiles);
       }
     }
 
@@ -766,6 +832,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncwarp();
     if (lane == 0) mbar_arrive(&sh->o_free);
     it += n_kv;
+    row_mul = next_row_mul;
     }  // pieces
     if (PROF && p.prof && quad == 0 && lane == 0 && h == 0) {
       p.prof[blockIdx.x * 16 + 7] = tick<PROF>() - t_start - wait_s;
@@ -909,9 +976,13 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      AttentionArm arm, const float* v_scale, const float* logit_scale,
-                      bool logit_divide, bool follows_prepare, float* partials, cudaStream_t s) {
-  const bool bf16 = arm == AttentionArm::BF16, mixed = arm == AttentionArm::MIXED;
+                      AttentionArm arm, const float* v_scale, const float* k_tile_scale,
+                      const float* logit_scale, bool logit_divide, bool follows_prepare,
+                      float* partials, cudaStream_t s) {
+  const bool f16 = arm == AttentionArm::F16;
+  const bool bf16 = arm == AttentionArm::BF16 || f16;      // K is 16-bit
+  const bool mixed = arm == AttentionArm::MIXED || f16;    // V^T is fp16 over per-head scales
+  if (f16 && (!k_tile_scale || !v_scale)) return fail("ib_attention: the fp16 arm needs its scales");
   if (batch == 0 || nq == 0) return 0;
   if (nk == 0) return fail("ib_attention: no keys");
   if (nq >= (1u << 30) || nk >= (1u << 30) || batch >= (1u << 20))
@@ -927,7 +998,9 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
                               reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::BF16>),
                               reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::BF16>),
                               reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::MIXED>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::MIXED>)};
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::MIXED>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::F16>),
+                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::F16>)};
     for (const void* fn : variants)
       if (err == cudaSuccess)
         err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -957,6 +1030,7 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   p.iters_rem = static_cast<int>(tail_iters % ctas);
   p.o = o;
   p.v_scale = mixed ? v_scale : nullptr;
+  p.k_tile_scale = f16 ? k_tile_scale : nullptr;
   p.logit_scale = logit_scale;
   p.logit_divide = logit_divide ? 1 : 0;
   const size_t slots_rows = static_cast<size_t>(2) * ctas * kBQ;
@@ -1004,7 +1078,10 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   cfg.numAttrs = g_dependent_launch && follows_prepare ? 1 : 0;
   cudaError_t launched;
   const bool prof = p.prof != nullptr;
-  if (bf16)
+  if (f16)
+    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::F16>, map_k, map_vt, p)
+                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::F16>, map_k, map_vt, p);
+  else if (bf16)
     launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::BF16>, map_k, map_vt, p)
                     : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::BF16>, map_k, map_vt, p);
   else if (mixed)

@@ -389,32 +389,15 @@ struct PrepareMixedArgs {
   const float* v; __half* vt16; float* scale; const float* block_max;
   size_t batch, nk, dv, nk_pitch;
   int v_kmajor;
+  // fp16 arm only: K as fp16 [batch][nk][d_pitch], each tile of 128 keys over its own power of two.
+  __half* k16; float* k_tile_scale; size_t d, d_pitch, kv_tiles;
 };
 
-// blockIdx.y = 0 rounds K to TF32; blockIdx.y = 1 writes fp16(V^T / scale[head]) — through 64x64
-// shared-memory tiles when V is [keys][dv], as plain rows when it is already [dv][keys].
-__global__ void __launch_bounds__(256)
-prepare_attention_mixed_kernel(PrepareMixedArgs a) {
-  __shared__ float tile[64][65];
-  __shared__ float scratch[8];
-  sm100::trigger_dependent_launch();       // see prepare_attention_kernel
-  if (blockIdx.y == 0) {
-    const size_t n4 = a.k_elems / 4;          // d is a multiple of 4
-    const size_t stride = static_cast<size_t>(gridDim.x) * 256;
-    const bool vec = (reinterpret_cast<uintptr_t>(a.k) & 15u) == 0;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n4; i += stride) {
-      float4 x;
-      if (vec) {
-        x = __ldcs(reinterpret_cast<const float4*>(a.k) + i);
-      } else {
-        x = make_float4(a.k[4 * i], a.k[4 * i + 1], a.k[4 * i + 2], a.k[4 * i + 3]);
-      }
-      x.x = round_tf32(x.x); x.y = round_tf32(x.y); x.z = round_tf32(x.z); x.w = round_tf32(x.w);
-      reinterpret_cast<float4*>(a.kr)[i] = x;
-    }
-    return;
-  }
-  sm100::grid_dependency_wait();           // the per-head maxima come from the kernel before this one
+// fp16(V^T / scale[head]) — through 64x64 shared-memory tiles when V is [keys][dv], as plain rows
+// when it is already [dv][keys].  The per-head maxima come from the kernel before this one.
+__device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (*tile)[65],
+                                              float* scratch) {
+  sm100::grid_dependency_wait();
   if (a.v_kmajor) {
     // Rows [batch * dv][nk] -> [batch * dv][nk_pitch], one row per block at a time.
     const size_t quads = a.nk_pitch / 4;
@@ -490,6 +473,104 @@ prepare_attention_mixed_kernel(PrepareMixedArgs a) {
   }
 }
 
+// blockIdx.y = 0 rounds K to TF32; blockIdx.y = 1 writes the fp16 V^T.
+__global__ void __launch_bounds__(256)
+prepare_attention_mixed_kernel(PrepareMixedArgs a) {
+  __shared__ float tile[64][65];
+  __shared__ float scratch[8];
+  sm100::trigger_dependent_launch();       // see prepare_attention_kernel
+  if (blockIdx.y == 0) {
+    const size_t n4 = a.k_elems / 4;          // d is a multiple of 4
+    const size_t stride = static_cast<size_t>(gridDim.x) * 256;
+    const bool vec = (reinterpret_cast<uintptr_t>(a.k) & 15u) == 0;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n4; i += stride) {
+      float4 x;
+      if (vec) {
+        x = __ldcs(reinterpret_cast<const float4*>(a.k) + i);
+      } else {
+        x = make_float4(a.k[4 * i], a.k[4 * i + 1], a.k[4 * i + 2], a.k[4 * i + 3]);
+      }
+      x.x = round_tf32(x.x); x.y = round_tf32(x.y); x.z = round_tf32(x.z); x.w = round_tf32(x.w);
+      reinterpret_cast<float4*>(a.kr)[i] = x;
+    }
+    return;
+  }
+  prepare_v_f16(a, tile, scratch);
+}
+
+// fp16 arm.  blockIdx.y = 0: K, one tile of 128 keys per block at a time: the tile is read once
+// twice (the second time from cache), its largest magnitude decides the power of two that brings it into
+// [2^14, 2^15), and fp16(K / that) is written with rows padded to d_pitch (pad columns zero).  An
+// outlier key therefore costs precision only to the 127 keys beside it.  blockIdx.y = 1: the fp16
+// V^T as in the mixed arm.
+template <bool FEW_TILES>
+__global__ void __launch_bounds__(256)
+prepare_attention_f16_kernel(PrepareMixedArgs a) {
+  __shared__ float tile[64][65];
+  __shared__ float scratch[8];
+  sm100::trigger_dependent_launch();       // see prepare_attention_kernel
+  if (blockIdx.y == 1) {
+    prepare_v_f16(a, tile, scratch);
+    return;
+  }
+  const size_t quads = a.d_pitch / 4;       // 4-column groups per (padded) key row, at most 32
+  const bool vec = (reinterpret_cast<uintptr_t>(a.k) & 15u) == 0;   // d is a multiple of 4
+  // With few tiles (one head of a few thousand keys) the blocks are too few to hide two rounds of
+  // loads each: a thread then keeps its share of the tile in registers (sixteen 16-byte loads in
+  // flight, 118 registers) and the second pass is free.  With many tiles that register count
+  // would hold the V half of this grid to two blocks per SM, and eight loads at a time at 64
+  // registers is the faster whole.
+  constexpr int kBatch = FEW_TILES ? 16 : 8;
+  for (size_t t = blockIdx.x; t < a.batch * a.kv_tiles; t += gridDim.x) {
+    const size_t b = t / a.kv_tiles, key0 = (t - b * a.kv_tiles) * 128;
+    const size_t keys = a.nk - key0 < 128 ? a.nk - key0 : 128;
+    const float* src = a.k + (b * a.nk + key0) * a.d;
+    __half* dst = a.k16 + (b * a.nk + key0) * a.d_pitch;
+    const size_t groups = keys * quads;
+    auto fetch = [&](size_t g) {
+      const size_t r = g / quads, c = (g - r * quads) * 4;
+      if (g >= groups || c >= a.d) return make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      const float* at = src + r * a.d + c;
+      return vec ? *reinterpret_cast<const float4*>(at) : make_float4(at[0], at[1], at[2], at[3]);
+    };
+    // Pass 1: the tile's largest magnitude.  Pass 2 reads the same 64 KB again, from cache, unless
+    // the thread's whole share (128 x 32 groups over 256 threads = 16) is still in registers.
+    float m = 0.0f;
+    float4 x[kBatch];
+    for (size_t g0 = threadIdx.x; g0 < groups; g0 += 256 * kBatch) {
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) x[u] = fetch(g0 + static_cast<size_t>(u) * 256);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[u].x), fabsf(x[u].y)), fmaxf(fabsf(x[u].z), fabsf(x[u].w))));
+    }
+    m = warp_fold<IB_OP_MAX>(m);
+    __syncthreads();                         // scratch may still be read from the tile before
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+    __syncthreads();
+    float all = scratch[0];
+    for (int w = 1; w < 8; ++w) all = fmaxf(all, scratch[w]);
+    const float scale = f16_scale_for(all);
+    const float inv = 1.0f / scale;
+    if (threadIdx.x == 0) a.k_tile_scale[t] = scale;
+    for (size_t g0 = threadIdx.x; g0 < groups; g0 += 256 * kBatch) {
+      if (!FEW_TILES) {
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) x[u] = fetch(g0 + static_cast<size_t>(u) * 256);
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const size_t g = g0 + static_cast<size_t>(u) * 256;
+        if (g < groups) {
+          const size_t r = g / quads, c = (g - r * quads) * 4;
+          *reinterpret_cast<uint2*>(dst + r * a.d_pitch + c) =
+              pack4_f16(x[u].x * inv, x[u].y * inv, x[u].z * inv, x[u].w * inv);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
@@ -518,7 +599,7 @@ int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, 
   absmax_heads_kernel<<<agrid, 256, 0, s>>>(v, block_max, nk * dv);
   if (int rc = check_launch("absmax_heads")) return rc;
   PrepareMixedArgs a{k, kr, batch * nk * d, v, static_cast<__half*>(vt16), scale, block_max,
-                     batch, nk, dv, nk_pitch, v_kmajor ? 1 : 0};
+                     batch, nk, dv, nk_pitch, v_kmajor ? 1 : 0, nullptr, nullptr, d, d, 0};
   const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64);
   const size_t most = std::max(batch * nk * d / 4 / 256 + 1, v_blocks);
   const size_t cap = static_cast<size_t>(kNumSMs) * 8;
@@ -534,6 +615,39 @@ int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, 
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, prepare_attention_mixed_kernel, a) != cudaSuccess)
     return fail(std::string("prepare_attention_operands_mixed: ") + cudaGetErrorString(cudaGetLastError()));
+  count_launch();
+  return 0;
+}
+
+int prepare_attention_operands_f16(const float* k, void* k16, float* k_tile_scale, const float* v,
+                                   void* vt16, float* v_scale, float* block_max, size_t batch,
+                                   size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
+                                   bool v_kmajor, cudaStream_t s) {
+  dim3 agrid(static_cast<unsigned>(batch), kAbsmaxBlocks);
+  absmax_heads_kernel<<<agrid, 256, 0, s>>>(v, block_max, nk * dv);
+  if (int rc = check_launch("absmax_heads")) return rc;
+  const size_t kv_tiles = (nk + 127) / 128;
+  PrepareMixedArgs a{k, nullptr, batch * nk * d, v, static_cast<__half*>(vt16), v_scale, block_max,
+                     batch, nk, dv, nk_pitch, v_kmajor ? 1 : 0,
+                     static_cast<__half*>(k16), k_tile_scale, d, d_pitch, kv_tiles};
+  const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64);
+  const size_t most = std::max(batch * kv_tiles, v_blocks);
+  const size_t cap = static_cast<size_t>(kNumSMs) * 8;
+  // Launched so that it may overlap the maxima kernel (see the wait in its V half).
+  cudaLaunchAttribute overlap{};
+  overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  overlap.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(std::min(most, cap)), 2);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cfg.attrs = &overlap;
+  cfg.numAttrs = 1;
+  const cudaError_t launched = batch * kv_tiles <= 512
+                                   ? cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a)
+                                   : cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<false>, a);
+  if (launched != cudaSuccess)
+    return fail(std::string("prepare_attention_operands_f16: ") + cudaGetErrorString(cudaGetLastError()));
   count_launch();
   return 0;
 }

@@ -45,6 +45,7 @@ bool attention_shape_ok(size_t d, size_t dv) {
 AttentionArm attention_arm(int precision) {
   if (precision == IB_PRECISION_BF16) return AttentionArm::BF16;
   if (precision == IB_PRECISION_TF32) return AttentionArm::TF32;
+  if (precision == IB_PRECISION_F16) return AttentionArm::F16;
   return AttentionArm::MIXED;
 }
 
@@ -54,6 +55,7 @@ struct PreparedKV {
   const void* k = nullptr;
   const void* vt = nullptr;
   const float* v_scale = nullptr;
+  const float* k_tile_scale = nullptr;
   size_t d_pitch = 0, nk_pitch = 0;
   AttentionArm arm = AttentionArm::TF32;
 };
@@ -62,6 +64,10 @@ size_t prepared_kv_bytes(size_t batch, size_t nk, size_t d, size_t dv, Attention
   if (arm == AttentionArm::BF16)
     return carve_bytes((batch * nk * round_up(d, 8) + 1) / 2) +
            carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2);
+  if (arm == AttentionArm::F16)
+    return carve_bytes((batch * nk * round_up(d, 8) + 1) / 2) +
+           carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2) + carve_bytes(batch) +
+           carve_bytes(batch * kAbsmaxBlocks) + carve_bytes(batch * ((nk + 127) / 128));
   if (arm == AttentionArm::MIXED)
     return carve_bytes(batch * nk * d) + carve_bytes((batch * dv * round_up(nk, 8) + 1) / 2) +
            carve_bytes(batch) + carve_bytes(batch * kAbsmaxBlocks);
@@ -86,6 +92,24 @@ int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t 
     if (!fill) return 0;
     return prepare_attention_operands_bf16(k, k16, v, vt16, batch, nk, d, dv, out->d_pitch,
                                            out->nk_pitch, v_kmajor, s);
+  }
+  if (arm == AttentionArm::F16) {
+    // Both operands fp16: K over one power of two per tile of 128 keys, V^T over one per head.
+    out->d_pitch = round_up(d, 8);
+    out->nk_pitch = round_up(nk, 8);
+    float* k16 = ws.take((batch * nk * out->d_pitch + 1) / 2);
+    float* vt16 = ws.take((batch * dv * out->nk_pitch + 1) / 2);
+    float* scale = ws.take(batch);
+    float* block_max = ws.take(batch * kAbsmaxBlocks);
+    float* k_tile_scale = ws.take(batch * ((nk + 127) / 128));
+    if (!k16 || !vt16 || !scale || !block_max || !k_tile_scale) return fail(small);
+    out->k = k16;
+    out->vt = vt16;
+    out->v_scale = scale;
+    out->k_tile_scale = k_tile_scale;
+    if (!fill) return 0;
+    return prepare_attention_operands_f16(k, k16, k_tile_scale, v, vt16, scale, block_max, batch, nk,
+                                          d, dv, out->d_pitch, out->nk_pitch, v_kmajor, s);
   }
   if (arm == AttentionArm::MIXED) {
     // K rounded to TF32; V^T as fp16 of V / scale[head], the scale a power of two that brings
@@ -131,7 +155,8 @@ int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t 
 extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, size_t k,
                                               int a_kmajor, int b_kmajor, int precision) {
   using namespace ib;
-  if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
+  if (precision == IB_PRECISION_TF32_F16 || precision == IB_PRECISION_F16)
+    precision = IB_PRECISION_TF32;   // attention-only distinctions
   const double flop = 2.0 * batch * m * n * k;
   if (!wants_tensor(precision, flop)) return 0;
   if (precision == IB_PRECISION_BF16) {
@@ -155,9 +180,10 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
   using namespace ib;
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!a || !b || !c) return fail("ib_contract: null pointer");
-  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_TF32_F16)
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_F16)
     return fail("ib_contract: unknown precision");
-  if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
+  if (precision == IB_PRECISION_TF32_F16 || precision == IB_PRECISION_F16)
+    precision = IB_PRECISION_TF32;   // attention-only distinctions
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (k == 0) {
     cudaError_t err = cudaMemsetAsync(c, 0, batch * m * n * sizeof(float), s);
@@ -241,7 +267,7 @@ extern "C" int ib_attention_scaled(const float* q, const float* k, const float* 
   if (batch == 0 || nq == 0 || dv == 0) return 0;
   if (!q || !k || !v || !o) return fail("ib_attention: null pointer");
   if (nk == 0 || d == 0) return fail("ib_attention: empty key or feature axis");
-  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_TF32_F16)
+  if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_F16)
     return fail("ib_attention: unknown precision");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (reinterpret_cast<uintptr_t>(workspace) & 255u)
@@ -259,7 +285,8 @@ extern "C" int ib_attention_scaled(const float* q, const float* k, const float* 
     if (!partials)
       return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
     return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch,
-                             kv.arm, kv.v_scale, logit_scale, logit_divide != 0, true, partials, s);
+                             kv.arm, kv.v_scale, kv.k_tile_scale, logit_scale, logit_divide != 0, true,
+                             partials, s);
   }
 
   float* scores = ws.take(batch * nq * nk);
@@ -301,8 +328,8 @@ extern "C" int ib_attention_prepare(const float* k, const float* v, size_t batch
   if (nk == 0 || !attention_shape_ok(d, dv))
     return fail("ib_attention_prepare: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
   if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO ||
-      precision > IB_PRECISION_TF32_F16)
-    return fail("ib_attention_prepare: the two-phase form exists for the tensor arms (auto, tf32, bf16, tf32_f16)");
+      precision > IB_PRECISION_F16)
+    return fail("ib_attention_prepare: the two-phase form exists for the tensor arms (auto, tf32, bf16, tf32_f16, f16)");
   if (reinterpret_cast<uintptr_t>(prepared) & 255u)
     return fail("ib_attention_prepare: buffer must be 256-byte aligned");
   Carver ws(prepared, prepared_bytes);
@@ -324,8 +351,8 @@ extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, 
   if (nk == 0 || !attention_shape_ok(d, dv))
     return fail("ib_attention_run: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
   if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO ||
-      precision > IB_PRECISION_TF32_F16)
-    return fail("ib_attention_run: the two-phase form exists for the tensor arms (auto, tf32, bf16, tf32_f16)");
+      precision > IB_PRECISION_F16)
+    return fail("ib_attention_run: the two-phase form exists for the tensor arms (auto, tf32, bf16, tf32_f16, f16)");
   if ((reinterpret_cast<uintptr_t>(prepared) | reinterpret_cast<uintptr_t>(workspace)) & 255u)
     return fail("ib_attention_run: buffers must be 256-byte aligned");
   const AttentionArm arm = attention_arm(precision);
@@ -339,7 +366,7 @@ extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, 
   if (!partials)
     return fail("ib_attention_run: workspace too small (see ib_attention_run_workspace_bytes)");
   return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch, kv.arm,
-                           kv.v_scale, nullptr, false, false, partials,
+                           kv.v_scale, kv.k_tile_scale, nullptr, false, false, partials,
                            static_cast<cudaStream_t>(stream));
 }
 

@@ -67,14 +67,16 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 // Operand types: TF32 — k, vt fp32 rounded to TF32 ([b][nk][d], [b][dv][nk_pitch], pitch % 4 == 0);
 // BF16 — both bf16 ([b][nk][d_pitch], [b][dv][nk_pitch], pitches % 8 == 0), kind::f16 MMAs;
 // MIXED — k as in TF32, vt fp16 holding V / v_scale[head] (nk_pitch % 8 == 0): S = Q K^T in TF32,
-// O += P V in fp16 (same 10-bit mantissa).  follows_prepare: the kernel before this call in the
+// O += P V in fp16 (same 10-bit mantissa); F16 — k fp16 holding K / k_tile_scale[head][key / 128]
+// ([b][nk][d_pitch], d_pitch % 8 == 0), vt as in MIXED: both contractions in fp16.  follows_prepare: the kernel before this call in the
 // stream is the one that wrote k and vt (the launch may then overlap its tail).  logit_scale: one
 // float on the device, or null; the logits are S * it, or S / it with logit_divide.
-enum class AttentionArm { TF32, BF16, MIXED };
+enum class AttentionArm { TF32, BF16, MIXED, F16 };
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
-                      AttentionArm arm, const float* v_scale, const float* logit_scale,
-                      bool logit_divide, bool follows_prepare, float* partials, cudaStream_t s);
+                      AttentionArm arm, const float* v_scale, const float* k_tile_scale,
+                      const float* logit_scale, bool logit_divide, bool follows_prepare,
+                      float* partials, cudaStream_t s);
 // Mixed-arm operand preparation: kr = K rounded to TF32; vt16[b][c][nk_pitch] = fp16(V^T / scale[b])
 // with scale[b] the power of two that brings the head's largest |V| into [2^14, 2^15); block_max
 // is scratch of batch * kAbsmaxBlocks floats.
@@ -85,6 +87,13 @@ int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, 
                                      cudaStream_t s);
 // bf16 operand preparation: k16[b][r][d_pitch] = bf16(k), vt16[b][c][nk_pitch] = bf16(v^T);
 // pad columns are zeroed.
+// fp16-arm operand preparation: k16[b][key][d_pitch] = fp16(K / k_tile_scale[b][key / 128]), every
+// tile of 128 keys over the power of two that brings its largest |K| into [2^14, 2^15); V as in
+// the mixed arm.
+int prepare_attention_operands_f16(const float* k, void* k16, float* k_tile_scale, const float* v,
+                                   void* vt16, float* v_scale, float* block_max, size_t batch,
+                                   size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
+                                   bool v_kmajor, cudaStream_t s);
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
                                     size_t batch, size_t nk, size_t d, size_t dv, size_t d_pitch,
                                     size_t nk_pitch, bool v_kmajor, cudaStream_t s);

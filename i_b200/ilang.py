@@ -13,7 +13,7 @@ Extensions, all additive:
     (the reference rejects non-CPU tensors, ilang.py:219-228, 376-385);
     `exec_torch` returns CUDA tensors when its inputs are CUDA tensors and the
     work is queued on torch's current stream without synchronising;
-  * `Component.set_precision("auto" | "fp32" | "tf32" | "bf16" | "tf32_f16")`.
+  * `Component.set_precision("auto" | "fp32" | "tf32" | "bf16" | "tf32_f16" | "f16")`.
 
 The library is found through ILANG_CORE_LIB (as in the reference, ilang.py:6-9)
 or in-tree at i_b200/lib/libi_core.so.  Nothing here computes on the CPU: with
@@ -25,7 +25,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 DEFAULT_LIB = os.path.join(_HERE, "lib", "libi_core.so")
 
-PRECISIONS = {"auto": 0, "fp32": 1, "tf32": 2, "bf16": 3, "tf32_f16": 4}
+PRECISIONS = {"auto": 0, "fp32": 1, "tf32": 2, "bf16": 3, "tf32_f16": 4, "f16": 5}
 
 
 class _CTensor(ctypes.Structure):

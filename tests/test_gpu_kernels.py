@@ -18,7 +18,7 @@ from conftest import last_error, max_rel_elementwise, max_rel_to_peak
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-FP32, TF32, BF16, TF32_F16 = 1, 2, 3, 4
+FP32, TF32, BF16, TF32_F16, F16 = 1, 2, 3, 4, 5
 TOL_MAP = 1e-5
 TOL_FP32 = 1e-5
 TOL_TF32 = 5e-3
@@ -544,7 +544,7 @@ def run_attention(lib, torch, q, k, v, precision, v_kmajor=False):
 
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "attention_*.npz"))))
 @pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32), (BF16, TOL_BF16),
-                                           (TF32_F16, TOL_TF32)])
+                                           (TF32_F16, TOL_TF32), (F16, TOL_TF32)])
 def test_attention_golden(lib, torch, path, precision, tol):
     g = np.load(path)
     got = run_attention(lib, torch, g["q"], g["k"], g["v"], precision)
@@ -588,17 +588,62 @@ def test_attention_tf32_random_shapes(lib, oracle, torch):
     (256, 64, 64, 64), (512, 512, 128, 128), (300, 200, 40, 24), (1, 1, 4, 1), (129, 65, 8, 100),
     (1000, 3000, 128, 128), (64, 4096, 32, 16),
 ])
-def test_attention_tf32_f16_shapes(lib, oracle, torch, nq, nk, d, dv):
-    # S = Q K^T in TF32, O += P V in fp16 (same mantissa): held to the TF32 bound.
+@pytest.mark.parametrize("precision", [TF32_F16, F16])
+def test_attention_tf32_f16_shapes(lib, oracle, torch, nq, nk, d, dv, precision):
+    # S = Q K^T in TF32 (or fp16 over per-row / per-tile scales), O += P V in fp16 (same
+    # mantissa): held to the TF32 bound.
     q = rand((nq, d), 15) * np.float32(d ** -0.5)
     k, v = rand((nk, d), 16), rand((nk, dv), 17)
-    got = run_attention(lib, torch, q, k, v, TF32_F16)
+    got = run_attention(lib, torch, q, k, v, precision)
     assert not np.isnan(got).any()
     assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= TOL_TF32
 
 
+def test_attention_f16_is_as_accurate_as_tf32(lib, oracle, torch):
+    # fp16 operands carry TF32's 10-bit mantissa: against an exact reference the fp16 arm's error
+    # must sit where the TF32 arm's does, not where bf16's (8 bits) does.
+    nq, nk, d, dv = 512, 2048, 128, 128
+    q = rand((nq, d), 81) * np.float32(d ** -0.5)
+    k, v = rand((nk, d), 82), rand((nk, dv), 83)
+    ref = oracle.attention_fused(q, k, v)
+    err = {name: max_rel_to_peak(run_attention(lib, torch, q, k, v, prec), ref)
+           for name, prec in (("tf32", TF32), ("f16", F16), ("bf16", BF16))}
+    assert err["f16"] <= 1.5 * err["tf32"] + 1e-5, err
+    assert err["f16"] < 0.5 * err["bf16"], err
+
+
+@pytest.mark.parametrize("q_mag,k_mag", [(1e-20, 1e20), (1e15, 1e-15), (3e4, 1.0), (1.0, 7e4), (1e-6, 1e6)])
+def test_attention_f16_operand_magnitudes(lib, oracle, torch, q_mag, k_mag):
+    # Q and K far outside fp16's range in opposite directions (their product stays O(1)): the
+    # per-row and per-tile powers of two must bring both into range and come back out exactly.
+    nq, nk, d, dv = 260, 700, 64, 40
+    q = rand((nq, d), 84) * np.float32(d ** -0.5) * np.float32(q_mag)
+    k, v = rand((nk, d), 85) * np.float32(k_mag), rand((nk, dv), 86)
+    got = run_attention(lib, torch, q, k, v, F16)
+    assert np.isfinite(got).all()
+    assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= TOL_TF32
+
+
+def test_attention_f16_rows_and_key_tiles_of_different_magnitude(lib, oracle, torch):
+    # Every query row has its own scale, every tile of 128 keys its own: rows six decades apart
+    # and key tiles three decades apart each keep full precision.  (Keys that large make the
+    # softmax pick single keys; the check is against the oracle on the same inputs.)
+    nq, nk, d, dv = 300, 1024, 64, 32
+    q = rand((nq, d), 87) * np.float32(d ** -0.5)
+    q *= (np.float32(10.0) ** np.linspace(-3, 3, nq).astype(np.float32))[:, None]
+    k, v = rand((nk, d), 88), rand((nk, dv), 89)
+    k[256:384] *= np.float32(1e-3)
+    k[512:640] *= np.float32(30.0)
+    q[:, :] /= np.float32(30.0)
+    got = run_attention(lib, torch, q, k, v, F16)
+    assert np.isfinite(got).all()
+    ref = oracle.attention_fused(q, k, v)
+    tf32 = run_attention(lib, torch, q, k, v, TF32)
+    assert max_rel_to_peak(got, ref) <= max(TOL_TF32, 1.5 * max_rel_to_peak(tf32, ref))
+
+
 @pytest.mark.parametrize("precision,tol", [(FP32, 2e-5), (TF32, TOL_TF32), (BF16, TOL_BF16),
-                                           (TF32_F16, TOL_TF32)])
+                                           (TF32_F16, TOL_TF32), (F16, TOL_TF32)])
 @pytest.mark.parametrize("c,divide", [(0.125, False), (8.0, True), (-0.25, False), (-5.0, True)])
 @pytest.mark.parametrize("nq,nk,d,dv", [(300, 517, 64, 40), (2, 130, 128, 128)])
 def test_attention_scaled_logits(lib, oracle, torch, precision, tol, c, divide, nq, nk, d, dv):
@@ -624,7 +669,8 @@ def test_attention_scaled_logits(lib, oracle, torch, precision, tol, c, divide, 
 
 @pytest.mark.parametrize("scale", [1e-30, 1e-6, 1.0, 3.0e4, 7.0e4, 1e9, 1e30])
 @pytest.mark.parametrize("v_kmajor", [False, True])
-def test_attention_tf32_f16_value_range(lib, oracle, torch, scale, v_kmajor):
+@pytest.mark.parametrize("precision", [TF32_F16, F16])
+def test_attention_tf32_f16_value_range(lib, oracle, torch, scale, v_kmajor, precision):
     # V is scaled per head by a power of two so that its largest magnitude sits just under 2^15:
     # magnitudes far outside fp16's range (6e-5 .. 65504) in either direction must come out as
     # accurately as ordinary ones, and heads with different magnitudes must not affect each other.
@@ -636,7 +682,7 @@ def test_attention_tf32_f16_value_range(lib, oracle, torch, scale, v_kmajor):
     v[0, 5, 3] = np.float32(scale) * 20           # one outlier sets the head's scale
     ref = [oracle.attention_fused(q[b], k[b], v[b]) for b in range(2)]
     vin = np.ascontiguousarray(np.swapaxes(v, 1, 2)) if v_kmajor else v
-    got = run_attention(lib, torch, q, k, vin, TF32_F16, v_kmajor=v_kmajor)
+    got = run_attention(lib, torch, q, k, vin, precision, v_kmajor=v_kmajor)
     assert np.isfinite(got).all()
     for b in range(2):
         assert max_rel_to_peak(got[b], ref[b]) <= TOL_TF32, (b, scale)
@@ -690,7 +736,8 @@ def test_attention_tf32_batched_and_transposed_v(lib, oracle, torch):
         assert max_rel_to_peak(got_bt[i], ref) <= TOL_BF16
 
 
-@pytest.mark.parametrize("precision,tol", [(TF32, TOL_TF32), (BF16, TOL_BF16), (TF32_F16, TOL_TF32)])
+@pytest.mark.parametrize("precision,tol", [(TF32, TOL_TF32), (BF16, TOL_BF16), (TF32_F16, TOL_TF32),
+                                           (F16, TOL_TF32)])
 @pytest.mark.parametrize("v_kmajor", [False, True])
 def test_attention_two_phase_matches_one_call(lib, oracle, torch, precision, tol, v_kmajor):
     # K and V prepared once, query rows attended in ragged blocks: same rows as one ib_attention.
