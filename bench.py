@@ -42,7 +42,7 @@ WORKLOAD = "config4: single-head fused i-attention, seq_q=seq_kv=16384, d=128, f
 ROTATION = 8          # distinct input sets: 8 x 32 MiB = 256 MiB > 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention_tf32_kernel launch on this
 # workload, from the ncu capture summarised in profiles/attention_tf32_kernel_seq16384_d128.md.
-ATTENTION_DRAM_BYTES_PER_LAUNCH = {"tf32+f16": 21210624, "tf32": 25411584}
+ATTENTION_DRAM_BYTES_PER_LAUNCH = {"tf32+f16": 21210624, "tf32": 25411584}   # "f16": after its capture
 
 
 def load_peaks():
@@ -499,11 +499,20 @@ def run_gpu_arm(args):
 
     tf32_peak = peaks["bf16_tflops"] / 2.0
     f16_peak = peaks["bf16_tflops"]            # fp16 and bf16 issue at the same rate
-    mixed = args.precision in ("auto", "tf32_f16")
+    f16_arm = args.precision in ("auto", "f16")
+    mixed = args.precision == "tf32_f16"
     if args.precision == "bf16":
         arm_peak, arm_dtype = f16_peak, "bf16"
         arm_text = "tcgen05 kind::f16 on bf16 operands, fp32 accumulate"
         peak_text = "%s bf16_tflops %.1f" % (peaks["source"], peaks["bf16_tflops"])
+    elif f16_arm:
+        arm_peak, arm_dtype = f16_peak, "f16"
+        arm_text = ("both contractions tcgen05 kind::f16 on fp16 operands (10-bit mantissa like TF32): "
+                    "Q per query row, K per 128-key tile and V per head stored over powers of two "
+                    "that bring them into fp16's range, scales restored exactly in fp32; fp32 "
+                    "accumulate, fp32 softmax statistics")
+        peak_text = ("%s bf16_tflops %.1f (fp16 and bf16 issue at the same rate)"
+                     % (peaks["source"], peaks["bf16_tflops"]))
     elif mixed:
         # Half of the FLOPs (Q K^T) run at the TF32 rate, half (P V) at the 16-bit rate.
         arm_peak, arm_dtype = 2.0 / (1.0 / tf32_peak + 1.0 / f16_peak), "tf32+f16"
@@ -545,24 +554,27 @@ def run_gpu_arm(args):
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }
-    if world == 1 and mixed:
-        # The same steps with both contractions on TF32 operands, for comparison in the same run.
-        pure = readme_attention(ilang, batched=batched).set_precision("tf32")
-        for s2 in range(3):
-            pure.into(outs[s2 % 2], *sets[s2 % rotation])
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(main)
-        for s2 in range(args.steps):
-            pure.into(outs[s2 % 2], *sets[s2 % rotation])
-        b.record(main)
-        torch.cuda.synchronize()
-        pure_ms = a.elapsed_time(b) / args.steps
-        pure_tf = flop_per_step / pure_ms / 1e9
-        line["tf32_both_contractions"] = {
-            "value": pure_tf, "unit": "TFLOP/s", "ms_per_step": pure_ms,
-            "frac_of_tf32_peak": pure_tf / tf32_peak,
-            "note": "same workload and loop with --precision tf32 (Q K^T and P V both kind::tf32)"}
+    if world == 1 and f16_arm:
+        # The same steps on the arms that keep TF32 operands, for comparison in the same run.
+        for key, prec, note in (
+                ("tf32_both_contractions", "tf32",
+                 "same workload and loop with --precision tf32 (Q K^T and P V both kind::tf32)"),
+                ("tf32_logits_f16_values", "tf32_f16",
+                 "same workload and loop with --precision tf32_f16 (Q K^T kind::tf32, P V kind::f16)")):
+            other = readme_attention(ilang, batched=batched).set_precision(prec)
+            for s2 in range(3):
+                other.into(outs[s2 % 2], *sets[s2 % rotation])
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(main)
+            for s2 in range(args.steps):
+                other.into(outs[s2 % 2], *sets[s2 % rotation])
+            b.record(main)
+            torch.cuda.synchronize()
+            other_ms = a.elapsed_time(b) / args.steps
+            other_tf = flop_per_step / other_ms / 1e9
+            line[key] = {"value": other_tf, "unit": "TFLOP/s", "ms_per_step": other_ms,
+                         "frac_of_tf32_peak": other_tf / tf32_peak, "note": note}
     if world == 1:
         res = cpu_reference_sample(256)        # ~20 s of CPU work over all cores
         line["cpu_baseline"] = {"value": res["flop"] / res["times"][0] / 1e12, "unit": "TFLOP/s",
@@ -590,7 +602,7 @@ def main():
                     help="output assembly at N > 1: copy-engine peer writes or NCCL all-gather")
     ap.add_argument("--reserve-sms", type=int, default=20,
                     help="SMs left free for NCCL kernels when the NCCL gather is used")
-    ap.add_argument("--precision", default="auto", choices=["auto", "tf32", "bf16", "tf32_f16"],
+    ap.add_argument("--precision", default="auto", choices=["auto", "tf32", "bf16", "tf32_f16", "f16"],
                     help="arithmetic of the fused attention kernel (default: the library's own choice)")
     ap.add_argument("--heads", type=int, default=1,
                     help="heads per rank per step (default 1 = BASELINE config 4)")

@@ -39,14 +39,15 @@ bool attention_shape_ok(size_t d, size_t dv) {
   return d % 4 == 0 && d >= 4 && d <= 128 && dv >= 1 && dv <= 128;
 }
 
-// Which arithmetic the fused attention kernel uses for a precision request: AUTO and
-// TF32_F16 take the mixed arm (TF32 for Q K^T, fp16 with TF32's mantissa for P V), TF32 the
-// pure TF32 arm, BF16 the bf16 arm.
+// Which arithmetic the fused attention kernel uses for a precision request: AUTO and F16 take the
+// fp16 arm (both contractions on fp16 operands scaled into range: TF32's mantissa, half the
+// tensor-core instructions), TF32_F16 the mixed arm (TF32 for Q K^T, fp16 for P V), TF32 the pure
+// TF32 arm, BF16 the bf16 arm.
 AttentionArm attention_arm(int precision) {
   if (precision == IB_PRECISION_BF16) return AttentionArm::BF16;
   if (precision == IB_PRECISION_TF32) return AttentionArm::TF32;
-  if (precision == IB_PRECISION_F16) return AttentionArm::F16;
-  return AttentionArm::MIXED;
+  if (precision == IB_PRECISION_TF32_F16) return AttentionArm::MIXED;
+  return AttentionArm::F16;
 }
 
 // The attention kernel's K and V operands: rounded (TF32), converted (BF16) or mixed copies,
