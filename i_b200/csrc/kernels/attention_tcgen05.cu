@@ -893,10 +893,49 @@ attention_combine_kernel(const CombineArgs a) {
   const int dv4 = (a.dv + 3) / 4;
   const bool vec = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.o) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(a.part_o) & 15u) == 0;
+  // A row tile is cut into at most kMaxPieces pieces when every CTA has at least half a row tile
+  // of work (the usual case); then a thread issues every load of its item at once instead of one
+  // dependent round trip to L2 per piece and quantity.
+  constexpr int kMaxPieces = 4;
+  const int pieces = g_last - g_first + 1;
+  int slots[kMaxPieces];
+#pragma unroll
+  for (int k = 0; k < kMaxPieces; ++k) {
+    const int g = min(g_first + k, g_last);
+    slots[k] = 2 * g + (range_start(a, g) >= lo ? 0 : 1);
+  }
   for (int i = threadIdx.x; i < kRowsPerCta * dv4; i += 256) {
     const int r = row0 + i / dv4, c = (i % dv4) * 4;
     const long long row = static_cast<long long>(qt) * kBQ + r;
     if (row >= a.nq) continue;
+    float* dst = a.o + (static_cast<size_t>(b) * a.nq + row) * a.dv + c;
+    if (vec && pieces <= kMaxPieces) {
+      float pm[kMaxPieces], pl[kMaxPieces];
+      float4 po[kMaxPieces];
+#pragma unroll
+      for (int k = 0; k < kMaxPieces; ++k) {
+        const size_t prow = static_cast<size_t>(slots[k]) * kBQ + r;
+        const bool live = k < pieces;
+        pm[k] = live ? a.part_m[prow] : -CUDART_INF_F;
+        pl[k] = live ? a.part_l[prow] : 0.0f;
+        po[k] = live ? *reinterpret_cast<const float4*>(a.part_o + prow * a.dv + c)
+                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+      float m = pm[0];
+#pragma unroll
+      for (int k = 1; k < kMaxPieces; ++k) m = fmaxf(m, pm[k]);
+      float wsum = 0.0f;
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int k = 0; k < kMaxPieces; ++k) {
+        const float w = k < pieces ? pl[k] * exp2f(pm[k] - m) : 0.0f;
+        wsum += w;
+        acc.x += w * po[k].x; acc.y += w * po[k].y; acc.z += w * po[k].z; acc.w += w * po[k].w;
+      }
+      const float inv = 1.0f / wsum;
+      *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      continue;
+    }
     float m = -CUDART_INF_F;
     for (int g = g_first; g <= g_last; ++g) {
       const int slot = 2 * g + (range_start(a, g) >= lo ? 0 : 1);
@@ -918,7 +957,6 @@ attention_combine_kernel(const CombineArgs a) {
       }
     }
     const float inv = 1.0f / wsum;
-    float* dst = a.o + (static_cast<size_t>(b) * a.nq + row) * a.dv + c;
     if (vec) {
       *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
     } else {
