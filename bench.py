@@ -42,7 +42,7 @@ WORKLOAD = "config4: single-head fused i-attention, seq_q=seq_kv=16384, d=128, f
 ROTATION = 8          # distinct input sets: 8 x 32 MiB = 256 MiB > 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention_tf32_kernel launch on this
 # workload, from the ncu capture summarised in profiles/attention_tf32_kernel_seq16384_d128.md.
-ATTENTION_DRAM_BYTES_PER_LAUNCH = {"tf32+f16": 21210624, "tf32": 25411584}   # "f16": after its capture
+ATTENTION_DRAM_BYTES_PER_LAUNCH = {"f16": 17051392, "tf32+f16": 21210624, "tf32": 25411584}
 
 
 def load_peaks():
