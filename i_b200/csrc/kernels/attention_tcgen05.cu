@@ -9,10 +9,12 @@
 // dividing once at the end is the same quantity.  exp is powf(2.71828175f, x)
 // in the reference; here it is 2^(x * log2(2.71828175)).
 //
-// Three instantiations (enum Arm): both contractions on TF32 operands; both on
-// bf16 operands; or, the default for large problems, S = Q K^T on TF32 operands
-// and O += P V on fp16 operands (same 10-bit mantissa, V scaled per head by a
-// power of two into fp16's range, P in [0, 1]).  With 16-bit P the softmax
+// Four instantiations (enum Arm): both contractions on TF32 operands; both on
+// bf16 operands; S = Q K^T on TF32 operands and O += P V on fp16 operands (same
+// 10-bit mantissa, V scaled per head by a power of two into fp16's range, P in
+// [0, 1]); or, the default for large problems, both on fp16 operands, with Q
+// scaled per row and K per tile of 128 keys as well and the scales multiplied
+// back into the factor that takes S to the exponent.  With 16-bit P the softmax
 // warps pack two probabilities per tensor-memory column.
 //
 // One CTA (384 threads) owns 128 query rows and walks the keys in tiles of 128:
