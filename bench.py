@@ -282,6 +282,17 @@ def secondary_metrics(torch, ilang, peaks):
     out["mm_t_8192x8192x4096_bf16_optin"] = {"tflops": flop / ms / 1e9, "ms": ms,
                                              "frac_bf16_peak": flop / ms / 1e9 / peaks["bf16_tflops"],
                                              "note": "includes the fp32->bf16 conversion of A and B"}
+    lib.ib_contract_workspace_bytes.restype = ctypes.c_size_t
+    lib.ib_contract_workspace_bytes.argtypes = [ctypes.c_size_t] * 4 + [ctypes.c_int] * 3
+    wsf_bytes = lib.ib_contract_workspace_bytes(1, 8192, 8192, 4096, 1, 1, 5)
+    wsf = torch.empty(wsf_bytes, dtype=torch.uint8, device="cuda")
+    ms = timed(lambda: lib.ib_contract(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, 8192, 8192, 4096,
+                                       1, 1, 5, wsf.data_ptr(), wsf_bytes, stream), 10, flush)
+    out["mm_t_8192x8192x4096_f16_scaled"] = {
+        "tflops": flop / ms / 1e9, "ms": ms, "frac_bf16_peak": flop / ms / 1e9 / peaks["bf16_tflops"],
+        "frac_tf32_peak": flop / ms / 1e9 / (peaks["bf16_tflops"] / 2),
+        "note": "fp16 operands over one power of two per row (TF32's mantissa), scales restored in the "
+                "epilogue; includes the conversion of A and B"}
     torch.backends.cuda.matmul.allow_tf32 = True
     ms = timed(lambda: torch.matmul(a, b.t(), out=c), 10, flush)
     out["cublas_tf32_8192x8192x4096"] = {"tflops": flop / ms / 1e9, "ms": ms}

@@ -571,6 +571,63 @@ prepare_attention_f16_kernel(PrepareMixedArgs a) {
   }
 }
 
+// fp16 operand of a contraction: one warp per row.  Pass 1 finds the row's largest magnitude, pass 2
+// (the row again, from cache) writes fp16(row / scale) with scale the power of two that brings that
+// magnitude into [2^14, 2^15), and the scale itself for the epilogue to multiply back.  Pad columns
+// up to the pitch are written as zero.
+__global__ void __launch_bounds__(256)
+convert_f16_rows_scaled_kernel(const float* __restrict__ in, __half* __restrict__ out,
+                               float* __restrict__ scale_out, size_t rows, size_t cols,
+                               size_t out_pitch) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps_total = static_cast<size_t>(gridDim.x) * 8;
+  const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
+  const size_t quads = out_pitch / 4;
+  for (size_t r = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); r < rows;
+       r += warps_total) {
+    const float* src = in + r * cols;
+    auto fetch = [&](size_t q) {
+      const size_t c = q * 4;
+      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (vec && c + 4 <= cols) {
+        x = *reinterpret_cast<const float4*>(src + c);
+      } else {
+        if (c + 0 < cols) x.x = src[c + 0];
+        if (c + 1 < cols) x.y = src[c + 1];
+        if (c + 2 < cols) x.z = src[c + 2];
+        if (c + 3 < cols) x.w = src[c + 3];
+      }
+      return x;
+    };
+    float m = 0.0f;
+    for (size_t q0 = lane; q0 < quads; q0 += 32 * 8) {
+      float4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        x[u] = q0 + u * 32 < quads ? fetch(q0 + u * 32) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[u].x), fabsf(x[u].y)), fmaxf(fabsf(x[u].z), fabsf(x[u].w))));
+    }
+    m = warp_fold<IB_OP_MAX>(m);
+    const float scale = f16_scale_for(m);
+    const float inv = 1.0f / scale;
+    if (lane == 0) scale_out[r] = scale;
+    __half* dst = out + r * out_pitch;
+    for (size_t q0 = lane; q0 < quads; q0 += 32 * 8) {
+      float4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        x[u] = q0 + u * 32 < quads ? fetch(q0 + u * 32) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (q0 + u * 32 < quads)
+          *reinterpret_cast<uint2*>(dst + (q0 + u * 32) * 4) =
+              pack4_f16(x[u].x * inv, x[u].y * inv, x[u].z * inv, x[u].w * inv);
+    }
+  }
+}
+
 }  // namespace
 
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
@@ -660,6 +717,16 @@ int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size
   convert_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
       in, static_cast<__nv_bfloat16*>(out), rows, cols, out_pitch);
   return check_launch("convert_bf16");
+}
+
+int convert_f16_rows_scaled(const float* in, void* out, float* scale, size_t rows, size_t cols,
+                            size_t out_pitch, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return 0;
+  size_t blocks = (rows + 7) / 8;
+  if (blocks > static_cast<size_t>(kNumSMs) * 64) blocks = static_cast<size_t>(kNumSMs) * 64;
+  convert_f16_rows_scaled_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+      in, static_cast<__half*>(out), scale, rows, cols, out_pitch);
+  return check_launch("convert_f16_rows_scaled");
 }
 
 int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const float* k,

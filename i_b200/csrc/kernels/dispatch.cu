@@ -156,10 +156,18 @@ int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t 
 extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, size_t k,
                                               int a_kmajor, int b_kmajor, int precision) {
   using namespace ib;
-  if (precision == IB_PRECISION_TF32_F16 || precision == IB_PRECISION_F16)
-    precision = IB_PRECISION_TF32;   // attention-only distinctions
+  if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
   const double flop = 2.0 * batch * m * n * k;
   if (!wants_tensor(precision, flop)) return 0;
+  if (precision == IB_PRECISION_F16) {
+    // fp16 copies of both operands plus one scale per row; fp32 transposes first when needed.
+    const size_t kp = round_up(k, 8);
+    size_t bytes = carve_bytes((batch * m * kp + 1) / 2) + carve_bytes((batch * n * kp + 1) / 2) +
+                   carve_bytes(batch * m) + carve_bytes(batch * n);
+    if (!a_kmajor) bytes += carve_bytes(batch * m * k);
+    if (!b_kmajor) bytes += carve_bytes(batch * n * k);
+    return bytes;
+  }
   if (precision == IB_PRECISION_BF16) {
     // bf16 copies of both operands ([rows][k rounded up to 8]); fp32 transposes first when needed.
     const size_t kp = round_up(k, 8);
@@ -183,14 +191,43 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
   if (!a || !b || !c) return fail("ib_contract: null pointer");
   if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_F16)
     return fail("ib_contract: unknown precision");
-  if (precision == IB_PRECISION_TF32_F16 || precision == IB_PRECISION_F16)
-    precision = IB_PRECISION_TF32;   // attention-only distinctions
+  if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (k == 0) {
     cudaError_t err = cudaMemsetAsync(c, 0, batch * m * n * sizeof(float), s);
     return err == cudaSuccess ? 0 : fail("ib_contract: memset failed");
   }
   const double flop = 2.0 * batch * m * n * k;
+  if (precision == IB_PRECISION_F16) {
+    // Both operands as fp16 over one power of two per row; the scales return in the epilogue.
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u)
+      return fail("ib_contract: workspace must be 256-byte aligned");
+    Carver ws(workspace, workspace_bytes);
+    const char* small = "ib_contract: workspace too small (see ib_contract_workspace_bytes)";
+    const size_t kp = round_up(k, 8);
+    float* a16 = ws.take((batch * m * kp + 1) / 2);
+    float* b16 = ws.take((batch * n * kp + 1) / 2);
+    float* a_scale = ws.take(batch * m);
+    float* b_scale = ws.take(batch * n);
+    if (!a16 || !b16 || !a_scale || !b_scale) return fail(small);
+    const float* ak = a;
+    const float* bk = b;
+    if (!a_kmajor) {
+      float* t = ws.take(batch * m * k);
+      if (!t) return fail(small);
+      if (int rc = transpose_batched(a, t, batch, k, m, k, false, s)) return rc;
+      ak = t;
+    }
+    if (!b_kmajor) {
+      float* t = ws.take(batch * n * k);
+      if (!t) return fail(small);
+      if (int rc = transpose_batched(b, t, batch, k, n, k, false, s)) return rc;
+      bk = t;
+    }
+    if (int rc = convert_f16_rows_scaled(ak, a16, a_scale, batch * m, k, kp, s)) return rc;
+    if (int rc = convert_f16_rows_scaled(bk, b16, b_scale, batch * n, k, kp, s)) return rc;
+    return gemm_tcgen05_f16(a16, b16, a_scale, b_scale, c, batch, m, n, k, kp, s);
+  }
   if (precision == IB_PRECISION_BF16) {
     if (reinterpret_cast<uintptr_t>(workspace) & 255u)
       return fail("ib_contract: workspace must be 256-byte aligned");

@@ -64,7 +64,9 @@ __device__ __forceinline__ TileCoord tile_coord(long long id, int tiles_m, int t
 template <int BN, Kind KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 float* __restrict__ c, int m, int n, int k, int batch, int* status) {
+                 float* __restrict__ c, int m, int n, int k, int batch, int* status,
+                 const float* __restrict__ row_scale, const float* __restrict__ col_scale,
+                 int f16_operands) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -131,7 +133,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(KIND, kBM, BN);
+      // The 16-bit instantiation serves bf16 and fp16 operands: only the descriptor differs.
+      const uint32_t idesc = KIND == Kind::BF16 && f16_operands ? make_idesc_fmt(Fmt::F16, kBM, BN)
+                                                                : make_idesc(KIND, kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -181,6 +185,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after_sync();
       const int row = t.m_tile * kBM + quad * 32 + lane;
       float* crow = c + (static_cast<size_t>(t.batch) * m + row) * n;
+      // fp16 operands stored over powers of two: C[i][j] = acc * row_scale[i] * col_scale[j], exact.
+      const float rs = row_scale && row < m ? row_scale[static_cast<size_t>(t.batch) * m + row] : 1.0f;
+      const float* cs = col_scale ? col_scale + static_cast<size_t>(t.batch) * n : nullptr;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
@@ -189,6 +196,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tmem_ld_32x32(taddr + chunk * 32, r);
         tmem_wait_ld();
         const int col0 = t.n_tile * BN + chunk * 32;
+        if (cs && row < m) {
+#pragma unroll
+          for (int v = 0; v < 32; ++v)
+            if (col0 + v < n) r[v] = __float_as_uint(__uint_as_float(r[v]) * rs * __ldg(cs + col0 + v));
+        }
         if (row < m) {
           if (vec_ok && col0 + 32 <= n) {
 #pragma unroll
@@ -221,7 +233,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 template <int BN, Kind KIND>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
-           size_t n, size_t k, cudaStream_t s) {
+           size_t n, size_t k, cudaStream_t s, const float* row_scale = nullptr,
+           const float* col_scale = nullptr, bool f16_operands = false) {
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tf32_kernel<BN, KIND>,
@@ -242,7 +255,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t 
   const int grid = static_cast<int>(tiles < static_cast<size_t>(sms) ? tiles : sms);
   gemm_tf32_kernel<BN, KIND><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
       map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-      static_cast<int>(batch), status);
+      static_cast<int>(batch), status, row_scale, col_scale, f16_operands ? 1 : 0);
   return check_launch("ib_contract (tcgen05 tf32)");
 }
 
@@ -282,6 +295,22 @@ int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, 
     return rc;
   return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s)
               : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s);
+}
+
+int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, const float* b_scale,
+                     float* c, size_t batch, size_t m, size_t n, size_t k, size_t k_pitch,
+                     cudaStream_t s) {
+  if (batch == 0 || m == 0 || n == 0) return 0;
+  if (k_pitch % 8 != 0 || k_pitch < k || !c || !a_scale || !b_scale || m >= (1u << 30) ||
+      n >= (1u << 30) || k >= (1u << 30) || batch >= (1u << 30))
+    return fail("ib_contract: shape not supported by the fp16 tensor-core arm");
+  const bool wide = n > 128;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_tensor_map_bf16(&map_a, a16, batch, m, k, k_pitch, m * k_pitch, kBM)) return rc;
+  if (int rc = make_tensor_map_bf16(&map_b, b16, batch, n, k, k_pitch, n * k_pitch, wide ? 256 : 128))
+    return rc;
+  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, a_scale, b_scale, true)
+              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, a_scale, b_scale, true);
 }
 
 }  // namespace ib

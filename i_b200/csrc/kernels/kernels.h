@@ -52,10 +52,20 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
                  size_t k, cudaStream_t s);
 // Same contraction with bf16 operands a16 / b16 ([b][rows][k_pitch] bf16, k_pitch a multiple of 8)
 // fed to tcgen05 kind::f16, fp32 accumulation.
+// The same on fp16 operands stored over one power of two per row (a16[b][i][:] = A / a_scale[b][i],
+// b16 likewise): the epilogue multiplies the two scales back, so the result carries TF32's rounding
+// at the 16-bit issue rate.
+int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, const float* b_scale,
+                     float* c, size_t batch, size_t m, size_t n, size_t k, size_t k_pitch,
+                     cudaStream_t s);
 int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
                       size_t k, size_t k_pitch, cudaStream_t s);
 // out[r][c] = bf16(in[r][c]) (round to nearest even) for a [rows][cols] fp32 array; `out_pitch` in
 // elements, columns cols..out_pitch-1 are zeroed.
+// fp16 rows over one power of two each: out[r][c] = fp16(in[r][c] / scale[r]), scale[r] bringing the
+// row's largest magnitude into [2^14, 2^15); out_pitch % 8 == 0, pad columns zero.
+int convert_f16_rows_scaled(const float* in, void* out, float* scale, size_t rows, size_t cols,
+                            size_t out_pitch, cudaStream_t s);
 int convert_bf16_rows(const float* in, void* out, size_t rows, size_t cols, size_t out_pitch,
                       cudaStream_t s);
 

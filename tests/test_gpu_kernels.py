@@ -497,6 +497,41 @@ def test_contract_bf16_arm(lib, oracle, torch, m, n, k, akm, bkm):
     assert err > 1e-6 or k < 8          # really bf16 arithmetic, not the fp32 arm
 
 
+@pytest.mark.parametrize("m,n,k,akm,bkm", [
+    (128, 128, 64, True, True), (256, 512, 256, True, True), (200, 300, 100, True, True),
+    (130, 70, 36, True, True), (3, 5, 7, True, True), (1, 1, 1, True, True),
+    (256, 256, 128, True, False), (96, 200, 64, False, False), (512, 1024, 512, True, True),
+])
+def test_contract_f16_arm(lib, oracle, torch, m, n, k, akm, bkm):
+    # fp16 operands over one power of two per row: TF32's mantissa, held to the TF32 bound.
+    rng = np.random.default_rng(2)
+    a = (2 * rng.random((m, k) if akm else (k, m), dtype=np.float32) - 1)
+    b = (2 * rng.random((n, k) if bkm else (k, n), dtype=np.float32) - 1)
+    got = run_contract(lib, torch, a, b, akm, bkm, F16)
+    assert not np.isnan(got).any()
+    assert max_rel_to_peak(got, oracle.contract(a, b, akm, bkm)) <= TOL_TF32
+
+
+def test_contract_f16_is_as_accurate_as_tf32_at_any_magnitude(lib, oracle, torch):
+    # Rows of A eight decades apart, B at 1e-20 (far below fp16's range), batched: every row of C
+    # must come out as accurately, relative to its own peak, as from the TF32 arm.
+    rng = np.random.default_rng(3)
+    batch, m, n, k = 2, 300, 260, 512
+    a = rng.standard_normal((batch, m, k), dtype=np.float32)
+    a *= (np.float32(10.0) ** np.linspace(-4, 4, m).astype(np.float32))[None, :, None]
+    b = rng.standard_normal((batch, n, k), dtype=np.float32) * np.float32(1e-20)
+    b[1] *= np.float32(1e25)
+    got = run_contract(lib, torch, a, b, True, True, F16, batch=batch)
+    tf32 = run_contract(lib, torch, a, b, True, True, TF32, batch=batch)
+    assert np.isfinite(got).all()
+    for i in range(batch):
+        ref = a[i].astype(np.float64) @ b[i].astype(np.float64).T
+        peak = np.abs(ref).max(axis=1)
+        err = (np.abs(got[i] - ref).max(axis=1) / peak).max()
+        err_tf32 = (np.abs(tf32[i] - ref).max(axis=1) / peak).max()
+        assert err <= TOL_TF32 and err <= 1.5 * err_tf32 + 1e-6, (i, err, err_tf32)
+
+
 def test_contract_tf32_batched(lib, oracle, torch):
     a, b = rand((3, 150, 64), 13), rand((3, 90, 64), 14)
     got = run_contract(lib, torch, a, b, True, True, TF32, batch=3)
