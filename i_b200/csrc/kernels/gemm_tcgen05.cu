@@ -197,9 +197,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tmem_wait_ld();
         const int col0 = t.n_tile * BN + chunk * 32;
         if (cs && row < m) {
+          if (vec_ok && col0 + 32 <= n && (reinterpret_cast<uintptr_t>(cs) & 15u) == 0) {
 #pragma unroll
-          for (int v = 0; v < 32; ++v)
-            if (col0 + v < n) r[v] = __float_as_uint(__uint_as_float(r[v]) * rs * __ldg(cs + col0 + v));
+            for (int v = 0; v < 8; ++v) {
+              const float4 w = __ldg(reinterpret_cast<const float4*>(cs + col0) + v);
+              r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) * rs * w.x);
+              r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) * rs * w.y);
+              r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) * rs * w.z);
+              r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) * rs * w.w);
+            }
+          } else {
+#pragma unroll
+            for (int v = 0; v < 32; ++v)
+              if (col0 + v < n)
+                r[v] = __float_as_uint(__uint_as_float(r[v]) * rs * __ldg(cs + col0 + v));
+          }
         }
         if (row < m) {
           if (vec_ok && col0 + 32 <= n) {

@@ -532,6 +532,28 @@ def test_contract_f16_is_as_accurate_as_tf32_at_any_magnitude(lib, oracle, torch
         assert err <= TOL_TF32 and err <= 1.5 * err_tf32 + 1e-6, (i, err, err_tf32)
 
 
+def test_contract_auto_large_deep_shape(lib, torch):
+    # Large enough for AUTO to take the fp16 arm (both extents >= 4096, depth >= 2048) when the
+    # caller brings the workspace ib_contract_workspace_bytes asks for; checked against float64 on
+    # the device (the CPU oracle would need minutes here), with and without that workspace.
+    m, n, k = 4096, 4224, 2048
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    a = torch.randn(m, k, device="cuda", generator=g) * 1e-3
+    b = torch.randn(n, k, device="cuda", generator=g) * 1e4
+    ref = a.double() @ b.double().t()
+    peak = ref.abs().max().item()
+    for with_ws in (True, False):
+        c = torch.full((m, n), float("nan"), device="cuda")
+        wb = lib.ib_contract_workspace_bytes(1, m, n, k, 1, 1, 0) if with_ws else 0
+        assert (wb > 0) == with_ws
+        ws = torch.empty(max(wb, 256), dtype=torch.uint8, device="cuda")
+        ok(lib, lib.ib_contract(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n, k, 1, 1, 0,
+                                ws.data_ptr() if with_ws else None, wb, None))
+        err = ((c.double() - ref).abs().max() / peak).item()
+        assert err <= TOL_TF32, (with_ws, err)
+
+
 def test_contract_tf32_batched(lib, oracle, torch):
     a, b = rand((3, 150, 64), 13), rand((3, 90, 64), 14)
     got = run_contract(lib, torch, a, b, True, True, TF32, batch=3)
