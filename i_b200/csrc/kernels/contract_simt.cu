@@ -325,7 +325,9 @@ prepare_attention_bf16_kernel(PrepareBf16Args a) {
 
 // ---- mixed arm: K rounded to TF32, V^T as fp16 scaled per head into fp16's range ----
 
-// Largest |v| of each head, in kAbsmaxBlocks partial maxima per head (no atomics, nothing to clear).
+// Largest |v| of each head, in kAbsmaxBlocks partial maxima per head (no atomics).  gridDim.y <=
+// kAbsmaxBlocks blocks share a head, each thread keeping eight 16-byte loads in flight; the slots of
+// the blocks a short head does not need are written as zero by its first block.
 __global__ void __launch_bounds__(256)
 absmax_heads_kernel(const float* __restrict__ v, float* __restrict__ block_max, size_t per_head) {
   __shared__ float warp_max[8];
@@ -339,9 +341,15 @@ absmax_heads_kernel(const float* __restrict__ v, float* __restrict__ block_max, 
   const size_t stride = static_cast<size_t>(gridDim.y) * 256;
   if (vec) {
     const float4* b4 = reinterpret_cast<const float4*>(base);
-    for (size_t i = static_cast<size_t>(blockIdx.y) * 256 + threadIdx.x; i < per_head / 4; i += stride) {
-      const float4 x = b4[i];                  // plain load: the conversion pass reads V again
-      m = fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+    const size_t n4 = per_head / 4;
+    for (size_t i0 = static_cast<size_t>(blockIdx.y) * 256 + threadIdx.x; i0 < n4; i0 += 8 * stride) {
+      float4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)   // plain loads: the conversion pass reads V again
+        x[u] = i0 + u * stride < n4 ? b4[i0 + u * stride] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[u].x), fabsf(x[u].y)), fmaxf(fabsf(x[u].z), fabsf(x[u].w))));
     }
   } else {
     for (size_t i = static_cast<size_t>(blockIdx.y) * 256 + threadIdx.x; i < per_head; i += stride)
@@ -350,10 +358,13 @@ absmax_heads_kernel(const float* __restrict__ v, float* __restrict__ block_max, 
   m = warp_fold<IB_OP_MAX>(m);
   if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
   __syncthreads();
+  float* slots = block_max + static_cast<size_t>(blockIdx.x) * kAbsmaxBlocks;
   if (threadIdx.x == 0) {
     for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
-    block_max[static_cast<size_t>(blockIdx.x) * gridDim.y + blockIdx.y] = m;
+    slots[blockIdx.y] = m;
   }
+  if (blockIdx.y == 0)
+    for (int i = gridDim.y + threadIdx.x; i < kAbsmaxBlocks; i += 256) slots[i] = 0.0f;
 }
 
 // The power of two that brings a head's largest magnitude into [2^14, 2^15): large values fit
@@ -505,11 +516,12 @@ prepare_attention_mixed_kernel(PrepareMixedArgs a) {
 // V^T as in the mixed arm.
 template <bool FEW_TILES>
 __global__ void __launch_bounds__(256)
-prepare_attention_f16_kernel(PrepareMixedArgs a) {
+prepare_attention_f16_kernel(PrepareMixedArgs a, int halves) {
   __shared__ float tile[64][65];
   __shared__ float scratch[8];
   sm100::trigger_dependent_launch();       // see prepare_attention_kernel
-  if (blockIdx.y == 1) {
+  // halves: 3 = this grid does both (blockIdx.y picks), 1 = K only, 2 = V only.
+  if ((halves == 3 ? blockIdx.y : halves - 1) == 1) {
     prepare_v_f16(a, tile, scratch);
     return;
   }
@@ -630,6 +642,16 @@ convert_f16_rows_scaled_kernel(const float* __restrict__ in, __half* __restrict_
 
 }  // namespace
 
+// Blocks that share a head in absmax_heads_kernel: one per 32 KB of the head (eight 16-byte loads
+// per thread), at most kAbsmaxBlocks.
+unsigned absmax_blocks_per_head(size_t per_head) {
+  const size_t per_block = 256 * 4 * 8;
+  size_t blocks = (per_head + per_block - 1) / per_block;
+  if (blocks < 1) blocks = 1;
+  if (blocks > static_cast<size_t>(kAbsmaxBlocks)) blocks = kAbsmaxBlocks;
+  return static_cast<unsigned>(blocks);
+}
+
 int prepare_attention_operands_bf16(const float* k, void* k16, const float* v, void* vt16,
                                     size_t batch, size_t nk, size_t d, size_t dv, size_t d_pitch,
                                     size_t nk_pitch, bool v_kmajor, cudaStream_t s) {
@@ -652,7 +674,7 @@ int prepare_attention_operands_mixed(const float* k, float* kr, const float* v, 
                                      float* scale, float* block_max, size_t batch, size_t nk,
                                      size_t d, size_t dv, size_t nk_pitch, bool v_kmajor,
                                      cudaStream_t s) {
-  dim3 agrid(static_cast<unsigned>(batch), kAbsmaxBlocks);
+  dim3 agrid(static_cast<unsigned>(batch), absmax_blocks_per_head(nk * dv));
   absmax_heads_kernel<<<agrid, 256, 0, s>>>(v, block_max, nk * dv);
   if (int rc = check_launch("absmax_heads")) return rc;
   PrepareMixedArgs a{k, kr, batch * nk * d, v, static_cast<__half*>(vt16), scale, block_max,
@@ -680,7 +702,7 @@ int prepare_attention_operands_f16(const float* k, void* k16, float* k_tile_scal
                                    void* vt16, float* v_scale, float* block_max, size_t batch,
                                    size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
                                    bool v_kmajor, cudaStream_t s) {
-  dim3 agrid(static_cast<unsigned>(batch), kAbsmaxBlocks);
+  dim3 agrid(static_cast<unsigned>(batch), absmax_blocks_per_head(nk * dv));
   absmax_heads_kernel<<<agrid, 256, 0, s>>>(v, block_max, nk * dv);
   if (int rc = check_launch("absmax_heads")) return rc;
   const size_t kv_tiles = (nk + 127) / 128;
@@ -688,21 +710,36 @@ int prepare_attention_operands_f16(const float* k, void* k16, float* k_tile_scal
                      batch, nk, dv, nk_pitch, v_kmajor ? 1 : 0,
                      static_cast<__half*>(k16), k_tile_scale, d, d_pitch, kv_tiles};
   const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64);
-  const size_t most = std::max(batch * kv_tiles, v_blocks);
   const size_t cap = static_cast<size_t>(kNumSMs) * 8;
-  // Launched so that it may overlap the maxima kernel (see the wait in its V half).
+  // Launched so that it may overlap the maxima kernel (see the wait in the V half).
   cudaLaunchAttribute overlap{};
   overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   overlap.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(std::min(most, cap)), 2);
   cfg.blockDim = dim3(256);
   cfg.stream = s;
   cfg.attrs = &overlap;
   cfg.numAttrs = 1;
-  const cudaError_t launched = batch * kv_tiles <= 512
-                                   ? cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a)
-                                   : cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<false>, a);
+  cudaError_t launched;
+  if (batch * kv_tiles <= 512) {
+    // Few tiles: one grid, both halves, K tiles held in registers.
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min(std::max(batch * kv_tiles, v_blocks), cap)), 2);
+    launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a, 3);
+  } else {
+    // Many tiles: V first (64 registers, four blocks per SM), then K with each tile held in
+    // registers (128 registers: in one grid with the V half it would halve that half's
+    // occupancy; with two passes per tile instead it measured 1.8x the bf16 conversion's time).
+    // The K launch carries no overlap attribute, so it starts when V^T is complete, and the
+    // attention kernel that waits for it thereby waits for both.
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min(v_blocks, cap)), 1);
+    launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<false>, a, 2);
+    if (launched == cudaSuccess) {
+      count_launch();
+      cfg.gridDim = dim3(static_cast<unsigned>(std::min(batch * kv_tiles, cap * 2)), 1);
+      cfg.numAttrs = 0;
+      launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a, 1);
+    }
+  }
   if (launched != cudaSuccess)
     return fail(std::string("prepare_attention_operands_f16: ") + cudaGetErrorString(cudaGetLastError()));
   count_launch();
