@@ -406,7 +406,101 @@ struct PrepareMixedArgs {
 
 // fp16(V^T / scale[head]) — through 64x64 shared-memory tiles when V is [keys][dv], as plain rows
 // when it is already [dv][keys].  The per-head maxima come from the kernel before this one.
-__device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (*tile)[65],
+__device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (*tile)[129],
+                                              float* scratch) {
+  sm100::grid_dependency_wait();
+  if (a.v_kmajor) {
+    // Rows [batch * dv][nk] -> [batch * dv][nk_pitch], one row per block at a time.
+    const size_t quads = a.nk_pitch / 4;
+    const bool vec = a.nk % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
+    size_t scaled_for = static_cast<size_t>(-1);
+    float inv = 1.0f;
+    for (size_t row = blockIdx.x; row < a.batch * a.dv; row += gridDim.x) {
+      const size_t b = row / a.dv;
+      if (b != scaled_for) {
+        inv = 1.0f / head_scale(a.block_max, b, scratch);
+        scaled_for = b;
+      }
+      if (row == b * a.dv && threadIdx.x == 0) a.scale[b] = 1.0f / inv;
+      for (size_t q = threadIdx.x; q < quads; q += 256) {
+        const size_t c = q * 4;
+        const float* src = a.v + row * a.nk + c;
+        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (vec && c + 4 <= a.nk) {
+          x = __ldcs(reinterpret_cast<const float4*>(src));
+        } else {
+          if (c + 0 < a.nk) x.x = src[0];
+          if (c + 1 < a.nk) x.y = src[1];
+          if (c + 2 < a.nk) x.z = src[2];
+          if (c + 3 < a.nk) x.w = src[3];
+        }
+        *reinterpret_cast<uint2*>(a.vt16 + row * a.nk_pitch + c) =
+            pack4_f16(x.x * inv, x.y * inv, x.z * inv, x.w * inv);
+      }
+    }
+    return;
+  }
+  // 64 keys x all dv features per step: eight 16-byte loads in flight per thread, one barrier pair
+  // per 32 KB instead of per 16 KB.
+  const size_t tiles_k = (a.nk_pitch + 63) / 64;
+  const size_t total = a.batch * tiles_k;
+  const bool vec_in = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
+  size_t scaled_for = static_cast<size_t>(-1);
+  float inv = 1.0f;
+  for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const size_t b = t / tiles_k;
+    const size_t k0 = (t - b * tiles_k) * 64;
+    if (b != scaled_for) {
+      inv = 1.0f / head_scale(a.block_max, b, scratch);
+      scaled_for = b;
+    }
+    if (k0 == 0 && threadIdx.x == 0) a.scale[b] = 1.0f / inv;   // the block with the head's first tile
+    const float* src = a.v + b * a.nk * a.dv;
+    __half* dst = a.vt16 + b * a.dv * a.nk_pitch;
+    float4 x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = threadIdx.x + u * 256;
+      const int r = e >> 5, c = (e & 31) * 4;           // r: key, c: feature (contiguous in V)
+      x[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (k0 + r < a.nk && static_cast<size_t>(c) < a.dv) {
+        const float* row = src + (k0 + r) * a.dv + c;
+        if (vec_in && static_cast<size_t>(c) + 4 <= a.dv) {
+          x[u] = __ldcs(reinterpret_cast<const float4*>(row));
+        } else {
+          x[u].x = row[0];
+          if (static_cast<size_t>(c) + 1 < a.dv) x[u].y = row[1];
+          if (static_cast<size_t>(c) + 2 < a.dv) x[u].z = row[2];
+          if (static_cast<size_t>(c) + 3 < a.dv) x[u].w = row[3];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = threadIdx.x + u * 256;
+      const int r = e >> 5, c = (e & 31) * 4;
+      tile[r][c + 0] = x[u].x * inv; tile[r][c + 1] = x[u].y * inv;
+      tile[r][c + 2] = x[u].z * inv; tile[r][c + 3] = x[u].w * inv;
+    }
+    __syncthreads();
+    // dv features x 64 keys out: 16 groups of 4 keys (8 bytes) per feature row; keys past nk (up
+    // to the pitch) are written as the zeros the load left in the tile.
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = threadIdx.x + u * 256;
+      const int c = e >> 4, r = (e & 15) * 4;           // c: feature, r: first key of the group
+      if (static_cast<size_t>(c) < a.dv && k0 + r < a.nk_pitch)
+        *reinterpret_cast<uint2*>(dst + c * a.nk_pitch + k0 + r) =
+            pack4_f16(tile[r][c], tile[r + 1][c], tile[r + 2][c], tile[r + 3][c]);
+    }
+    __syncthreads();
+  }
+}
+
+// The same in steps of 64 keys x 64 features (53 registers: for the grid whose other half is a plain
+// elementwise pass and lives on occupancy).  fp16(V^T / scale[head]) — through 64x64 shared-memory tiles when V is [keys][dv], as plain rows
+// when it is already [dv][keys].  The per-head maxima come from the kernel before this one.
+__device__ __forceinline__ void prepare_v_f16_by_quarters(const PrepareMixedArgs& a, float (*tile)[65],
                                               float* scratch) {
   sm100::grid_dependency_wait();
   if (a.v_kmajor) {
@@ -506,7 +600,7 @@ prepare_attention_mixed_kernel(PrepareMixedArgs a) {
     }
     return;
   }
-  prepare_v_f16(a, tile, scratch);
+  prepare_v_f16_by_quarters(a, tile, scratch);
 }
 
 // fp16 arm.  blockIdx.y = 0: K, one tile of 128 keys per block at a time: the tile is read once
@@ -517,7 +611,7 @@ prepare_attention_mixed_kernel(PrepareMixedArgs a) {
 template <bool FEW_TILES>
 __global__ void __launch_bounds__(256)
 prepare_attention_f16_kernel(PrepareMixedArgs a, int halves) {
-  __shared__ float tile[64][65];
+  __shared__ float tile[64][129];
   __shared__ float scratch[8];
   sm100::trigger_dependent_launch();       // see prepare_attention_kernel
   // halves: 3 = this grid does both (blockIdx.y picks), 1 = K only, 2 = V only.
@@ -709,7 +803,7 @@ int prepare_attention_operands_f16(const float* k, void* k16, float* k_tile_scal
   PrepareMixedArgs a{k, nullptr, batch * nk * d, v, static_cast<__half*>(vt16), v_scale, block_max,
                      batch, nk, dv, nk_pitch, v_kmajor ? 1 : 0,
                      static_cast<__half*>(k16), k_tile_scale, d, d_pitch, kv_tiles};
-  const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64) * ((dv + 63) / 64);
+  const size_t v_blocks = v_kmajor ? batch * dv : batch * ((nk_pitch + 63) / 64);
   const size_t cap = static_cast<size_t>(kNumSMs) * 8;
   // Launched so that it may overlap the maxima kernel (see the wait in the V half).
   cudaLaunchAttribute overlap{};
