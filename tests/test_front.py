@@ -440,6 +440,11 @@ def test_precision_switch(ilang):
     assert ilang.core().i_b200_program_precision(c._compile()) == 2
     c.set_precision("fp32")
     assert ilang.core().i_b200_program_precision(c._compile()) == 1
+    for name, code in (("bf16", 3), ("tf32_f16", 4), ("f16", 5), ("auto", 0)):
+        c.set_precision(name)
+        assert ilang.core().i_b200_program_precision(c._compile()) == code
+    with pytest.raises((ValueError, KeyError, RuntimeError)):
+        c.set_precision("fp64")
 
 
 @pytest.mark.skipif(not os.path.isdir(REFERENCE_PY), reason="reference checkout absent")
