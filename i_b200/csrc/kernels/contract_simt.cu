@@ -675,6 +675,9 @@ prepare_attention_f16_kernel(PrepareMixedArgs a, int halves) {
       }
     }
   }
+  // Launched on its own under the tail of the maxima kernel (many tiles): this grid then only
+  // completes once that one has, so that whoever waits for this grid has waited for both.
+  if (halves == 1) sm100::grid_dependency_wait();
 }
 
 // fp16 operand of a contraction: one warp per row.  Pass 1 finds the row's largest magnitude, pass 2
@@ -820,18 +823,17 @@ int prepare_attention_operands_f16(const float* k, void* k16, float* k_tile_scal
     cfg.gridDim = dim3(static_cast<unsigned>(std::min(std::max(batch * kv_tiles, v_blocks), cap)), 2);
     launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a, 3);
   } else {
-    // Many tiles: V first (64 registers, four blocks per SM), then K with each tile held in
-    // registers (128 registers: in one grid with the V half it would halve that half's
-    // occupancy; with two passes per tile instead it measured 1.8x the bf16 conversion's time).
-    // The K launch carries no overlap attribute, so it starts when V^T is complete, and the
-    // attention kernel that waits for it thereby waits for both.
-    cfg.gridDim = dim3(static_cast<unsigned>(std::min(v_blocks, cap)), 1);
-    launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<false>, a, 2);
+    // Many tiles: K with each tile held in registers (128 registers: in one grid with the V half
+    // it would halve that half's occupancy; with two passes per tile instead it measured 1.8x the
+    // bf16 conversion's time), running beside the maxima kernel, which it does not need but whose
+    // completion it waits for before it ends; then V, which waits for the K grid and so for the
+    // maxima.  The attention kernel that waits for the V grid thereby waits for all three.
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min(batch * kv_tiles, cap * 2)), 1);
+    launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a, 1);
     if (launched == cudaSuccess) {
       count_launch();
-      cfg.gridDim = dim3(static_cast<unsigned>(std::min(batch * kv_tiles, cap * 2)), 1);
-      cfg.numAttrs = 0;
-      launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<true>, a, 1);
+      cfg.gridDim = dim3(static_cast<unsigned>(std::min(v_blocks, cap)), 1);
+      launched = cudaLaunchKernelEx(&cfg, prepare_attention_f16_kernel<false>, a, 2);
     }
   }
   if (launched != cudaSuccess)
