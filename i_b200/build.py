@@ -23,6 +23,7 @@ SOURCES = [
     "core/validate.cc",
     "core/lower.cc",
     "core/plan.cc",
+    "core/schedule.cc",
     "core/runtime.cc",
     "kernels/map.cu",
     "kernels/reduce.cu",
@@ -69,38 +70,45 @@ def _headers():
     return out
 
 
-def _compile(src, headers, verbose):
-    obj = os.path.join(OBJ_DIR, src.replace("/", "_") + ".o")
+def _compile(src, headers, verbose, obj_dir=None, extra=()):
+    obj = os.path.join(obj_dir or OBJ_DIR, src.replace("/", "_") + ".o")
     path = os.path.join(CSRC, src)
     if _newer(obj, [path] + headers):
         return obj, ""
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-x", "cu", "-c", path, "-o", obj]
+    cmd = [_nvcc()] + NVCC_FLAGS + list(extra) + ["-x", "cu", "-c", path, "-o", obj]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, proc.stdout, proc.stderr))
     return obj, proc.stderr if verbose else ""
 
 
-def build(verbose=False, force=False):
-    """Compile what changed and link libi_core.so; returns its path."""
-    os.makedirs(OBJ_DIR, exist_ok=True)
+def build(verbose=False, force=False, out_dir=None, extra_flags=()):
+    """Compile what changed and link libi_core.so; returns its path.
+
+    `out_dir` and `extra_flags` build a variant beside the shipped library, e.g. one with the
+    attention kernels' cycle counters compiled in (`extra_flags=["-DIB_ATTN_PROFILE=1"]`).
+    """
+    out_dir = out_dir or OUT_DIR
+    obj_dir = os.path.join(out_dir, "obj")
+    lib = os.path.join(out_dir, "libi_core.so")
+    os.makedirs(obj_dir, exist_ok=True)
     headers = _headers()
     if force:
-        for f in os.listdir(OBJ_DIR):
-            os.remove(os.path.join(OBJ_DIR, f))
+        for f in os.listdir(obj_dir):
+            os.remove(os.path.join(obj_dir, f))
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
-        results = list(pool.map(lambda s: _compile(s, headers, verbose), SOURCES))
+        results = list(pool.map(lambda s: _compile(s, headers, verbose, obj_dir, extra_flags), SOURCES))
     objs = [o for o, _ in results]
     if verbose:
         for _, log in results:
             if log:
                 sys.stderr.write(log)
-    if not _newer(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", LIB] + objs + ["-lpthread", "-ldl", "-lrt"]
+    if not _newer(lib, objs):
+        cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", lib] + objs + ["-lpthread", "-ldl", "-lrt"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (proc.stdout, proc.stderr))
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":

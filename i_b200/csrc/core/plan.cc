@@ -707,6 +707,8 @@ std::string describe_graph(const Graph& g) {
 Result<Plan> make_plan(const Graph& g) {
   Builder b(g);
   if (auto err = basic_steps(b)) return Result<Plan>::failure(*err);
+  // Placements the reference's planner refuses are refused here too, before any kernel is chosen.
+  if (auto err = check_schedule(g)) return Result<Plan>::failure(lower_error(*err));
   fuse_contractions(b);
   fuse_softmax(b);
   fuse_attention(b);

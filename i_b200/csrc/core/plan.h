@@ -85,6 +85,11 @@ struct Plan {
 
 Result<Plan> make_plan(const Graph& g);
 
+// schedule.cc — the reference's message when its loop-nest planner would refuse the graph's
+// compute-at placements (mismatched splits between a staged producer and its consumer, an online
+// reduction whose correction no accumulator absorbs); nothing when it would accept them.
+std::optional<std::string> check_schedule(const Graph& g);
+
 // Text form of the wired graph: one line per node (op, index patterns, sources)
 // and the output list.  Printed by i_code ahead of the plan.
 std::string describe_graph(const Graph& g);

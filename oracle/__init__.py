@@ -107,6 +107,17 @@ def contract(a, b, a_kmajor=True, b_kmajor=True):
     return c
 
 
+def contract_rows(a_rows, b, threads=None):
+    """`contract` on slices of A's rows, one slice per task, on `threads` host cores (rows of C
+    are independent, and ctypes releases the GIL).  Returns the list of output slices in order."""
+    threads = threads or os.cpu_count() or 1
+    n = a_rows.shape[0]
+    cuts = np.linspace(0, n, min(threads, n) + 1).astype(int)
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        futs = [pool.submit(contract, a_rows[lo:hi], b) for lo, hi in zip(cuts[:-1], cuts[1:]) if hi > lo]
+        return [f.result() for f in futs]
+
+
 def row_softmax(x):
     x = _f32(x)
     rows = int(np.prod(x.shape[:-1]))

@@ -137,6 +137,82 @@ def test_graph_input_cannot_be_staged(ilang):
     assert "node 0 input 0 is a graph input with a compute site" in str(info.value)
 
 
+
+# ---- schedules the reference's planner refuses (csrc/core/schedule.cc) -----------------------------
+
+def compile_error(component):
+    with pytest.raises(RuntimeError) as info:
+        component._compile()
+    return str(info.value)
+
+
+def test_online_row_sum_without_downstream_accumulator_is_refused(ilang):
+    # compiler/src/lower/stage_to_kernel_program.rs:2410-2431, the component of that test: the row
+    # sum is consumed inside its own reduction loop by the division, and the division's result is
+    # the kernel's output, so nothing can absorb the correction.
+    i = ilang.i
+    mm_t = i("ik*jk~ijk|i:2,j:2|iji'j'k") >> i("+ijk~ij|i:2,j:2|iji'j'k0")
+    mm = i("ik*kj~ijk|i:2,k:2|ik0ji'k'") >> i("+ijk~ij|i:2,k:2|ikji'k'0")
+    exp = i("^ij~ij|i:2,j:2|iji'j'0")
+    row_sum = i("+ij~i|i:2,j:2|iji'j'0")
+    row_div = i("ij/i~ij|i:2,j:2|iji'j'1")
+    attention = mm_t >> exp >> (mm & row_sum) >> row_div
+    assert compile_error(attention) == (
+        'LowerError { message: "online reduction correction reached root without an accumulator" }')
+
+
+def test_softmax_alone_with_the_fused_loop_orders_is_refused(ilang):
+    # The README's fused orders applied to the softmax stages alone (no contraction in front, none
+    # behind): with the logits coming from a map rather than a graph input, the online row sum's
+    # correction has no `+` accumulator downstream.
+    i, I = ilang.i, ilang.I
+    logits = i("ij*ij~ij | i:16,j:16 | jii'j'")
+    shift = (I & i(">ij~i | i:16,j:16 | ji0i'j'")) >> i("ij-i~ij | i:16,j:16 | ji01i'j'")
+    exp = i("^ij~ij | i:16,j:16 | ji0i'j'")
+    norm = (I & i("+ij~i | i:16,j:16 | ji0i'j'")) >> i("ij/i~ij | i:16,j:16 | ji01i'j'")
+    assert "online reduction correction reached root without an accumulator" in compile_error(
+        logits >> shift >> exp >> norm)
+
+
+def test_staged_producer_must_be_split_like_its_consumer(ilang):
+    # compiler/src/lower/node_to_stage.rs:720-745 (case :1390-1421 for the extent kinds).
+    i = ilang.i
+    assert compile_error(i("+ij~i | i:4 | ii'j") >> i(">i~i | i:2 | ii'0")) == (
+        'LowerError { message: "producer extent kind Base([4]) does not match consumer extent kind Base([2])" }')
+    assert compile_error(i("+ij~i | i:4 | ii'j") >> i(">i~i || i0")) == (
+        'LowerError { message: "producer index 0 has 2 axes but consumer index 0 has 1 axes" }')
+    # Same splits: accepted.
+    (i("+ij~i | i:4 | ii'j") >> i(">i~i | i:4 | ii'0"))._compile()
+
+
+def test_online_reductions_other_than_sum_and_max_are_refused(ilang):
+    # compiler/src/lower/stage_to_kernel_program.rs:1127-1156: a row minimum consumed inside its
+    # own reduction loop.
+    i, I = ilang.i, ilang.I
+    logits = i("ij*ij~ij | i:16,j:16 | jii'j'")
+    c = logits >> (I & i("<ij~i | i:16,j:16 | ji0i'j'")) >> i("ij-i~ij | i:16,j:16 | ji01i'j'")
+    assert "requires online reduction lowering: fused reduction axis is consumed before completion" in compile_error(c)
+
+
+def test_online_max_needs_subtraction_then_exponentiation(ilang):
+    # compiler/src/lower/stage_to_kernel_program.rs:1594-1637.
+    i, I = ilang.i, ilang.I
+    logits = i("ij*ij~ij | i:16,j:16 | jii'j'")
+    online_max = I & i(">ij~i | i:16,j:16 | ji0i'j'")
+    assert "online max correction requires a subtraction use before exponentiation" in compile_error(
+        logits >> online_max >> i("ij*i~ij | i:16,j:16 | ji01i'j'"))
+    shifted = logits >> online_max >> i("ij-i~ij | i:16,j:16 | ji01i'j'")
+    assert "online max correction requires exponentiation before accumulation" in compile_error(
+        shifted >> i("-ij~ij | i:16,j:16 | ji0i'j'") >> i("+ij~i | i:16,j:16 | ji0i'j'"))
+
+
+def test_accepted_fused_schedules_still_compile(ilang):
+    # The README chain, its deferred-normalisation form and the naive five-kernel schedule.
+    assert steps_of(readme_attention(ilang)) == ["attention"]
+    assert steps_of(naive_attention(ilang)) == ["contract", "row_softmax", "contract"]
+    deferred_attention(ilang)._compile()
+
+
 def test_comparisons_and_logic_compile(ilang):
     # compiler/src/front/parser.rs:270-279, 374-413: every operator token in unary and binary form.
     for tok in (">>", ">=", "<<", "<=", "==", "!=", "&&", "||", "^^"):
@@ -267,8 +343,12 @@ def scaled_attention(ilang, kind="mul_right", batched=False):
     i, I = ilang.i, ilang.I
     b = "bh" if batched else ""
     mm_t = i(f"{b}ik*{b}jk~{b}ijk | i:16,j:16 | {b}jii'j'k") >> i(f"+{b}ijk~{b}ij | i:16,j:16 | {b}jii'j'k0")
-    scale = {"mul_left": f".*{b}ij~{b}ij", "mul_right": f"{b}ij*.~{b}ij", "div": f"{b}ij/.~{b}ij",
-             "rdiv": f"./{b}ij~{b}ij"}[kind]
+    # The scale is staged into the row maximum's loops, so it carries the same splits
+    # (node_to_stage.rs:720-745) and stages its own logits operand the same way.
+    scale = {"mul_left": f".*{b}ij~{b}ij | i:16,j:16 | {b}ji1i'j'",
+             "mul_right": f"{b}ij*.~{b}ij | i:16,j:16 | {b}ji0i'j'",
+             "div": f"{b}ij/.~{b}ij | i:16,j:16 | {b}ji0i'j'",
+             "rdiv": f"./{b}ij~{b}ij | i:16,j:16 | {b}ji1i'j'"}[kind]
     logits = ((I | mm_t) if kind in ("mul_left", "rdiv") else (mm_t | I)) >> i(scale)
     row_max_shift = (I & i(f">{b}ij~{b}i | i:16,j:16 | {b}ji0i'j'")) >> i(f"{b}ij-{b}i~{b}ij | i:16,j:16 | {b}ji01i'j'")
     exp = i(f"^{b}ij~{b}ij | i:16,j:16 | {b}ji0i'j'")
