@@ -17,6 +17,8 @@
 // back into the factor that takes S to the exponent.  With 16-bit P the softmax
 // warps pack two probabilities per tensor-memory column.
 //
+// Two kernels.  The arms with 32-bit operands (TF32, and TF32 x fp16) run the one described
+// here; the 16-bit arms run attention_pipelined_kernel further down, described there.
 // One CTA (384 threads) owns 128 query rows and walks the keys in tiles of 128:
 //   warp 0      TMA producer: K tiles ([128 keys][d]) and V^T tiles
 //               ([dv][128 keys]) as 128-byte-swizzled rows through a ring of
@@ -54,6 +56,7 @@
 // Roofline: tensor-bound, 4*Nq*Nk*d FLOP per head.
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -67,8 +70,10 @@ using namespace sm100;
 constexpr int kBQ = 128;           // query rows per CTA
 constexpr int kBKV = 128;          // keys per KV tile
 constexpr int kThreads = 384;
+constexpr int kThreadsPipelined = 768;    // roles, statistics, and sixteen softmax warps
 constexpr int kChunkBytes = 128 * 128;     // 128 rows of 128 bytes: 32 fp32 or 64 bf16 per row
-constexpr int kMaxRing = 3;
+constexpr int kMaxRing = 6;
+constexpr int kMaxDevices = 64;             // per-device bookkeeping (kernel attributes)
 
 // Arithmetic of the two contractions.  MIXED runs S = Q K^T on TF32 operands and O += P V on
 // fp16 ones: fp16 has TF32's 10-bit mantissa, P lies in [0, 1], and V is scaled per head by a
@@ -133,14 +138,18 @@ struct Shared {
   uint64_t kv_full[kMaxRing];
   uint64_t q_ready;
   uint64_t o_free;           // the epilogue of a piece has read O
-  uint64_t s_full[2];
+  uint64_t s_full[4];        // [tile & 1] in the first kernel, [tile & 3] in the pipelined one
   uint64_t p_full[2];
-  uint64_t pv_done[2];       // [KV tile parity]: see the note at its wait
+  uint64_t pv_done[4];       // likewise; see the note at its wait
+  uint64_t s_free[2];        // pipelined kernel: the softmax warps have read S[buf] into registers
   uint32_t tmem_slot;
   AbortState abort;
   int give_up;               // raised before a named barrier, read after it
+  float pub_m[4][kBQ];       // reference maximum per row for a tile, from the statistics warps
+  float row_mul[2][kBQ];     // [piece & 1]: log2(e) x the row's Q scale, for the statistics warps
   float half_max[2][2][kBQ]; // [iteration parity][warpgroup][row]
   float half_sum[2][kBQ];
+  float quarter_sum[4][kBQ]; // pipelined kernel: the four column quarters' shares of a row sum
 };
 
 // One contiguous run of key tiles of one row tile.
@@ -151,18 +160,26 @@ struct Piece {
   int ordinal;     // 0 = first tail piece of this CTA, 1 = a later one
 };
 
+// Walks this CTA's pieces.  The tail position is kept as (row tile, key tile) and advanced by
+// additions: the one division happens in pieces_begin, not per piece (every role of the CTA walks
+// the sequence, some of them twice to look one piece ahead).
 struct PieceCursor {
   int wave;
-  long long lo, cur, hi;
+  int tail_unit;     // row tile (within the tail) of the next piece
+  int kv_lo;         // its first key tile
+  int remaining;     // (row tile, key tile) pairs of the tail still to hand out
+  bool first;
 };
 
 __device__ __forceinline__ PieceCursor pieces_begin(const Params& p) {
   PieceCursor c;
   const int g = static_cast<int>(blockIdx.x);
   c.wave = 0;
-  c.lo = g * p.iters_base + min(g, p.iters_rem);
-  c.hi = c.lo + p.iters_base + (g < p.iters_rem ? 1 : 0);
-  c.cur = c.lo;
+  const long long lo = g * p.iters_base + min(g, p.iters_rem);
+  c.tail_unit = static_cast<int>(lo / p.kv_tiles);
+  c.kv_lo = static_cast<int>(lo - static_cast<long long>(c.tail_unit) * p.kv_tiles);
+  c.remaining = static_cast<int>(p.iters_base) + (g < p.iters_rem ? 1 : 0);
+  c.first = true;
   return c;
 }
 
@@ -177,16 +194,22 @@ __device__ __forceinline__ bool next_piece(const Params& p, PieceCursor& c, Piec
     ++c.wave;
     return true;
   }
-  if (c.cur >= c.hi) return false;
-  const int tail_unit = static_cast<int>(c.cur / p.kv_tiles);
-  out.unit = p.full_waves * p.ctas + tail_unit;
-  out.kv_lo = static_cast<int>(c.cur - static_cast<long long>(tail_unit) * p.kv_tiles);
-  out.n_kv = static_cast<int>(min(static_cast<long long>(p.kv_tiles - out.kv_lo), c.hi - c.cur));
+  if (c.remaining <= 0) return false;
+  out.unit = p.full_waves * p.ctas + c.tail_unit;
+  out.kv_lo = c.kv_lo;
+  out.n_kv = min(p.kv_tiles - c.kv_lo, c.remaining);
   out.whole = out.kv_lo == 0 && out.n_kv == p.kv_tiles;
-  out.ordinal = c.cur == c.lo ? 0 : 1;
-  c.cur += out.n_kv;
+  out.ordinal = c.first ? 0 : 1;
+  c.first = false;
+  c.remaining -= out.n_kv;
+  c.kv_lo += out.n_kv;
+  if (c.kv_lo == p.kv_tiles) {
+    c.kv_lo = 0;
+    ++c.tail_unit;
+  }
   return true;
 }
+
 
 // Two floats -> one 32-bit word of bf16 (round to nearest even), first value in the low half.
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -242,6 +265,13 @@ __device__ __forceinline__ float f16_hi(uint32_t pair) {
 #endif
 constexpr bool kHalfExp = IB_ATTN_HALF_EXP != 0;
 
+// Per-phase cycle counters (written to Params::prof) exist only in builds with
+// -DIB_ATTN_PROFILE=1; the shipped library compiles them out.
+#ifndef IB_ATTN_PROFILE
+#define IB_ATTN_PROFILE 0
+#endif
+constexpr bool kProf = IB_ATTN_PROFILE != 0;
+
 template <bool PROF>
 __device__ __forceinline__ long long tick() {
   return PROF ? clock64() : 0ll;
@@ -251,8 +281,255 @@ __device__ __forceinline__ void softmax_pair_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
-// PROF = true compiles in the cycle counters written to Params::prof.
-template <bool PROF, Arm ARM>
+
+// Q of one row tile: global -> operand type (nearest) -> tensor memory, this thread's 64
+// features [64h, 64h+64) of its row; then one arrival per warp on q_ready.
+// Returns the factor that takes this row's S to the exponent's units, K's tile scale aside:
+// log2(e), times the row's own power of two where Q is stored scaled.
+template <Arm ARM>
+__device__ __forceinline__ float stage_q_rows(const Params& p, Shared* sh, uint32_t tmem_q, int head,
+                                              int q_tile, int r, int h, int lane, int piece = -1) {
+  using G = Geometry<ARM>;
+  float row_mul = kLog2E32;
+  const long long row = static_cast<long long>(q_tile) * kBQ + r;
+  const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
+  const bool live = row < p.nq;
+  const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
+  // A scale on the logits is a scale on Q: (c q) . k = c (q . k).  Read here, once per row
+  // tile, rather than held in a register across the key loop.
+  float qs = 1.0f;
+  if (p.logit_scale) {
+    qs = __ldg(p.logit_scale);
+    if (p.logit_divide) qs = 1.0f / qs;
+  }
+  // This thread's 64 features [64h, 64h+64) of its row, rounded to the operand type.
+  auto load4 = [&](int col) {
+    float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (live && vec && col + 4 <= p.d) {
+      x = *reinterpret_cast<const float4*>(qrow + col);
+    } else if (live) {
+      if (col + 0 < p.d) x.x = qrow[col + 0];
+      if (col + 1 < p.d) x.y = qrow[col + 1];
+      if (col + 2 < p.d) x.z = qrow[col + 2];
+      if (col + 3 < p.d) x.w = qrow[col + 3];
+    }
+    x.x *= qs; x.y *= qs; x.z *= qs; x.w *= qs;
+    return x;
+  };
+  if (!G::kQkHalf) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int col0 = h * 64 + c * 32;
+      uint32_t v[32];
+#pragma unroll
+      for (int e = 0; e < 32; e += 4) {
+        const float4 x = load4(col0 + e);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
+      }
+      tmem_st_32x32(tmem_q + col0, v);
+    }
+  } else {
+    // 16-bit pairs, two features per column: features [64h, 64h+64) -> columns [32h, 32h+32).
+    // The whole row's largest magnitude decides the power of two that brings the row into
+    // [2^14, 2^15); the other half of the row is read for that alone (once per row tile,
+    // from L2, eight loads at a time), then this thread's own 64 features, all in flight
+    // together.
+    float m = 0.0f;
+    if (G::kScaledQk) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float4 other[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) other[e] = load4((h ^ 1) * 64 + half * 32 + 4 * e);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          m = fmaxf(m, fmaxf(fmaxf(fabsf(other[e].x), fabsf(other[e].y)),
+                             fmaxf(fabsf(other[e].z), fabsf(other[e].w))));
+      }
+    }
+    float4 own[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) own[e] = load4(h * 64 + 4 * e);
+    float inv = 1.0f;
+    if (G::kScaledQk) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e)
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(own[e].x), fabsf(own[e].y)),
+                           fmaxf(fabsf(own[e].z), fabsf(own[e].w))));
+      const float scale = f16_range_scale(m);
+      inv = 1.0f / scale;
+      row_mul = kLog2E32 * scale;
+    }
+    uint32_t v[32];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const float4 x = own[e];
+      if (G::kQkFmt == Fmt::F16) {
+        v[2 * e + 0] = pack_f16(x.x * inv, x.y * inv);
+        v[2 * e + 1] = pack_f16(x.z * inv, x.w * inv);
+      } else {
+        v[2 * e + 0] = pack_bf16(x.x, x.y);
+        v[2 * e + 1] = pack_bf16(x.z, x.w);
+      }
+    }
+    tmem_st_32x32(tmem_q + h * 32, v);
+  }
+  // Pipelined kernel: the statistics warps need the row's factor too (visible to them once
+  // q_ready has completed: the arrival below releases this store).
+  if (piece >= 0 && h == 0) sh->row_mul[piece & 1][r] = row_mul;
+  tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(&sh->q_ready);
+  return row_mul;
+}
+
+// End of a piece on the softmax warps: waits for the last P V, adds the two halves of the row
+// sum, normalises and stores this thread's columns [64h, 64h+64) of O (to the output, or to the
+// partial slot with its (m, l) when the piece covers only part of the keys).
+__device__ __forceinline__ void finish_piece(const Params& p, Shared* sh, uint32_t o_tmem, int h,
+                                             int r, long long row, int b, bool whole, int part_slot,
+                                             float l, float m_used, int dv_chunks,
+                                             uint64_t* last_pv_done, uint32_t last_parity,
+                                             bool& dead) {
+  if (!sh->give_up && !dead)
+    dead = !mbar_wait_warp(last_pv_done, last_parity, &sh->abort, p.status, 209);
+  sh->half_sum[h][r] = l;
+  if (dead) sh->give_up = 1;
+  softmax_pair_sync();
+  if (sh->give_up) return;
+  tc_fence_after_sync();
+  const float l_total = l + sh->half_sum[h ^ 1][r];
+  const float inv = (p.v_scale ? p.v_scale[b] : 1.0f) / l_total;
+  float* dst;
+  if (whole) {
+    dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
+  } else {
+    const size_t prow = static_cast<size_t>(part_slot) * kBQ + r;
+    dst = p.part_o + prow * p.dv;
+    if (h == 0) {
+      p.part_m[prow] = m_used;
+      p.part_l[prow] = l_total;
+    }
+  }
+  const bool vec_ok = (p.dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+  for (int c = h * 2; c < h * 2 + 2 && c < dv_chunks; ++c) {
+    uint32_t o[32];
+    tmem_ld_32x32(o_tmem + c * 32, o);
+    tmem_wait_ld();
+    if (row < p.nq || !whole) {
+      if (vec_ok && c * 32 + 32 <= p.dv) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          *reinterpret_cast<float4*>(dst + c * 32 + 4 * v) = make_float4(
+              __uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+              __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (c * 32 + e < p.dv) dst[c * 32 + e] = __uint_as_float(o[e]) * inv;
+      }
+    }
+  }
+}
+
+// TMA producer (one thread): streams the K and V^T tiles of this CTA's pieces through the
+// three-slot ring, in the order the MMA thread consumes them.
+template <Arm ARM>
+__device__ __forceinline__ void run_producer(const CUtensorMap* map_k, const CUtensorMap* map_vt,
+                                             const Params& p, Shared* sh, uint8_t* ring) {
+  using G = Geometry<ARM>;
+  constexpr int kRing = G::kRing;
+  constexpr int kSlotBytes = G::kSlotBytes;
+  constexpr int kBarMask = 1;
+  constexpr int kBarShift = 1;
+  AbortState* abort = &sh->abort;
+  const int d_chunks = (p.d + G::kQkChunkElems - 1) / G::kQkChunkElems;
+  tma_prefetch_descriptor(map_k);
+  tma_prefetch_descriptor(map_vt);
+  // K and V^T come from the preparation kernel before this one in the stream;
+  // this thread is the only one that reads them (Q, read by the softmax warps,
+  // is an input of the call and older than that kernel).
+  grid_dependency_wait();
+  int slot = 0;
+  bool ok = true;
+  long long waited = 0;
+  int b = 0;
+  // A ring slot is free again when the MMAs that read its tile have completed:
+  // Q K^T of tile t for a K tile (signalled on s_full[t & 1]), P V of tile t for
+  // a V tile (pv_done[t & 1]); t counts this CTA's key tiles.  The producer
+  // remembers who occupies each slot and waits for that event before reuse.  It
+  // meets every event once and in order.  A parity wait must never be two phases
+  // behind: with three slots and two barriers the next-but-one event on the same
+  // barrier needs a tile this producer has not loaded yet (K(t) and K(t + 2) are
+  // four loads apart).
+  uint64_t* occupant_bar[kRing] = {};
+  uint32_t occupant_parity[kRing] = {};
+  long long tile_k = 0, tile_v = 0;       // tile counters of the next K / V load
+  auto acquire = [&](int code) {
+    if (!occupant_bar[slot]) return;
+    const long long t0 = tick<kProf>();
+    ok = mbar_wait(occupant_bar[slot], occupant_parity[slot], abort, p.status, code);
+    waited += tick<kProf>() - t0;
+  };
+  auto load_k = [&](int j) {
+    acquire(201);
+    if (!ok) return;
+    uint8_t* dst = ring + slot * kSlotBytes;
+    mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
+    for (int c = 0; c < d_chunks; ++c)
+      tma_load_3d(dst + c * kChunkBytes, map_k, &sh->kv_full[slot], c * G::kQkChunkElems,
+                  j * kBKV, b);
+    occupant_bar[slot] = &sh->s_full[tile_k & kBarMask];
+    occupant_parity[slot] = static_cast<uint32_t>((tile_k >> kBarShift) & 1);
+    ++tile_k;
+    if (++slot == kRing) slot = 0;
+  };
+  auto load_v = [&](int j) {
+    acquire(202);
+    if (!ok) return;
+    uint8_t* dst = ring + slot * kSlotBytes;
+    mbar_arrive_expect_tx(&sh->kv_full[slot], G::kPvTileChunks * kChunkBytes);
+    for (int c = 0; c < G::kPvTileChunks; ++c)
+      tma_load_3d(dst + c * kChunkBytes, map_vt, &sh->kv_full[slot],
+                  j * kBKV + c * G::kPvChunkElems, 0, b);
+    occupant_bar[slot] = &sh->pv_done[tile_v & kBarMask];
+    occupant_parity[slot] = static_cast<uint32_t>((tile_v >> kBarShift) & 1);
+    ++tile_v;
+    if (++slot == kRing) slot = 0;
+  };
+  // Per piece, consumption order is K(0), then per tile K(j+1) before V(j).
+  PieceCursor cursor = pieces_begin(p);
+  Piece pc;
+  const bool q_prefetchable = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
+  while (ok && next_piece(p, cursor, pc)) {
+    b = pc.unit / p.q_tiles;
+    {
+      // Pull the Q rows of the piece after this one into L2 while this one runs.
+      PieceCursor ahead = cursor;
+      Piece nx;
+      if (q_prefetchable && next_piece(p, ahead, nx) && nx.unit != pc.unit) {
+        const int nb = nx.unit / p.q_tiles;
+        const long long row0 = static_cast<long long>(nx.unit - nb * p.q_tiles) * kBQ;
+        const long long rows = min(static_cast<long long>(kBQ), p.nq - row0);
+        prefetch_l2_bulk(p.q + (static_cast<size_t>(nb) * p.nq + row0) * p.d,
+                         static_cast<uint32_t>(rows * p.d * 4));
+      }
+    }
+    constexpr int kAhead = 1;
+    for (int jj = 0; ok && jj < kAhead && jj < pc.n_kv; ++jj) load_k(pc.kv_lo + jj);
+    for (int jj = 0; ok && jj < pc.n_kv; ++jj) {
+      if (jj + kAhead < pc.n_kv) load_k(pc.kv_lo + jj + kAhead);
+      if (ok) load_v(pc.kv_lo + jj);
+    }
+  }
+  if (kProf && p.prof) p.prof[blockIdx.x * 16 + 0] = waited;
+}
+
+template <Arm ARM>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_vt, const Params p) {
@@ -298,85 +575,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
   trigger_dependent_launch();
 
   if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_descriptor(&map_k);
-      tma_prefetch_descriptor(&map_vt);
-      // K and V^T come from the preparation kernel before this one in the stream;
-      // this thread is the only one that reads them (Q, read by the softmax warps,
-      // is an input of the call and older than that kernel).
-      grid_dependency_wait();
-      int slot = 0;
-      bool ok = true;
-      long long waited = 0;
-      int b = 0;
-      // A ring slot is free again when the MMAs that read its tile have completed:
-      // Q K^T of tile t for a K tile (signalled on s_full[t & 1]), P V of tile t for
-      // a V tile (pv_done[t & 1]); t counts this CTA's key tiles.  The producer
-      // remembers who occupies each slot and waits for that event before reuse.  It
-      // meets every event once and in order, and with three slots the next-but-one
-      // event on the same barrier needs a tile this producer has not loaded yet, so
-      // a parity wait is never two phases behind (a deeper ring would break that).
-      uint64_t* occupant_bar[kRing] = {};
-      uint32_t occupant_parity[kRing] = {};
-      long long tile_k = 0, tile_v = 0;       // tile counters of the next K / V load
-      auto acquire = [&](int code) {
-        if (!occupant_bar[slot]) return;
-        const long long t0 = tick<PROF>();
-        ok = mbar_wait(occupant_bar[slot], occupant_parity[slot], abort, p.status, code);
-        waited += tick<PROF>() - t0;
-      };
-      auto load_k = [&](int j) {
-        acquire(201);
-        if (!ok) return;
-        uint8_t* dst = ring + slot * kSlotBytes;
-        mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
-        for (int c = 0; c < d_chunks; ++c)
-          tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kQkChunkElems,
-                      j * kBKV, b);
-        occupant_bar[slot] = &sh->s_full[tile_k & 1];
-        occupant_parity[slot] = static_cast<uint32_t>((tile_k >> 1) & 1);
-        ++tile_k;
-        if (++slot == kRing) slot = 0;
-      };
-      auto load_v = [&](int j) {
-        acquire(202);
-        if (!ok) return;
-        uint8_t* dst = ring + slot * kSlotBytes;
-        mbar_arrive_expect_tx(&sh->kv_full[slot], G::kPvTileChunks * kChunkBytes);
-        for (int c = 0; c < G::kPvTileChunks; ++c)
-          tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[slot],
-                      j * kBKV + c * G::kPvChunkElems, 0, b);
-        occupant_bar[slot] = &sh->pv_done[tile_v & 1];
-        occupant_parity[slot] = static_cast<uint32_t>((tile_v >> 1) & 1);
-        ++tile_v;
-        if (++slot == kRing) slot = 0;
-      };
-      // Per piece, consumption order is K(0), then per tile K(j+1) before V(j).
-      PieceCursor cursor = pieces_begin(p);
-      Piece pc;
-      const bool q_prefetchable = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
-      while (ok && next_piece(p, cursor, pc)) {
-        b = pc.unit / p.q_tiles;
-        {
-          // Pull the Q rows of the piece after this one into L2 while this one runs.
-          PieceCursor ahead = cursor;
-          Piece nx;
-          if (q_prefetchable && next_piece(p, ahead, nx) && nx.unit != pc.unit) {
-            const int nb = nx.unit / p.q_tiles;
-            const long long row0 = static_cast<long long>(nx.unit - nb * p.q_tiles) * kBQ;
-            const long long rows = min(static_cast<long long>(kBQ), p.nq - row0);
-            prefetch_l2_bulk(p.q + (static_cast<size_t>(nb) * p.nq + row0) * p.d,
-                             static_cast<uint32_t>(rows * p.d * 4));
-          }
-        }
-        load_k(pc.kv_lo);
-        for (int jj = 0; ok && jj < pc.n_kv; ++jj) {
-          if (jj + 1 < pc.n_kv) load_k(pc.kv_lo + jj + 1);
-          if (ok) load_v(pc.kv_lo + jj);
-        }
-      }
-      if (PROF && p.prof) p.prof[blockIdx.x * 16 + 0] = waited;
-    }
+    if (lane == 0) run_producer<ARM>(&map_k, &map_vt, p, sh, ring);
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc_fmt(G::kQkFmt, kBQ, kBKV);
@@ -387,20 +586,20 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       uint32_t phase = 0;
       const uint32_t ring_addr = smem_u32(ring);
       long long wait_k = 0, wait_v = 0, wait_p = 0, wait_q = 0, issue_qk_cycles = 0, issue_pv_cycles = 0;
-      const long long t_start = tick<PROF>();
+      const long long t_start = tick<kProf>();
       bool ok = true;
       long long it = 0;                       // key tiles issued so far by this CTA
 
       // S[buf] = Q K^T from the K tile in the current slot (A = Q in tensor memory).
       auto issue_qk = [&](int buf) {
-        const long long t0 = tick<PROF>();
+        const long long t0 = tick<kProf>();
         if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 204))) return;
-        wait_k += tick<PROF>() - t0;
+        wait_k += tick<kProf>() - t0;
         tc_fence_after_sync();
         // One descriptor per slot; a K step moves it by a compile-time constant
         // (32 bytes inside the swizzled row, 16 KB to the next 32-feature chunk),
         // so the issuing thread spends one 64-bit add per MMA.
-        const long long ti = tick<PROF>();
+        const long long ti = tick<kProf>();
         const uint64_t k_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
         const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
         const uint32_t q_tmem = tmem_base + kTmemQ;
@@ -412,24 +611,24 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                          ks != 0 ? 1u : 0u);
         }
         mma_commit(&sh->s_full[buf]);          // S ready, and the K tile's slot is free
-        issue_qk_cycles += tick<PROF>() - ti;
+        issue_qk_cycles += tick<kProf>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
       // O += P[buf] V from the V^T tile in the current slot (A = P in tensor memory).
       auto issue_pv = [&](long long t, bool first_of_piece, int piece) {
         const int buf = static_cast<int>(t & 1);
-        long long t0 = tick<PROF>();
+        long long t0 = tick<kProf>();
         if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) return;
         // The first P V of a piece overwrites O: the piece before must have read it out.
         if (first_of_piece && piece > 0 &&
             !(ok = mbar_wait(&sh->o_free, static_cast<uint32_t>((piece - 1) & 1), abort, p.status, 210)))
           return;
-        wait_v += tick<PROF>() - t0;
-        t0 = tick<PROF>();
+        wait_v += tick<kProf>() - t0;
+        t0 = tick<kProf>();
         if (!(ok = mbar_wait(&sh->p_full[buf], (t >> 1) & 1, abort, p.status, 206))) return;
-        wait_p += tick<PROF>() - t0;
+        wait_p += tick<kProf>() - t0;
         tc_fence_after_sync();
-        const long long ti = tick<PROF>();
+        const long long ti = tick<kProf>();
         const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
         const uint32_t d_tmem = tmem_base + kTmemO;
         const uint32_t p_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
@@ -449,7 +648,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
           mma_ts_w<G::kPvHalf>(d_tmem, p_col(ks),
                        v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
         mma_commit(&sh->pv_done[buf]);         // O updated, and the V tile's slot is free
-        issue_pv_cycles += tick<PROF>() - ti;
+        issue_pv_cycles += tick<kProf>() - ti;
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       };
 
@@ -458,9 +657,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
         const int n_kv = pc.n_kv;
         // Q of this piece is in tensor memory.
-        const long long tq = tick<PROF>();
+        const long long tq = tick<kProf>();
         if (!(ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 203))) break;
-        wait_q += tick<PROF>() - tq;
+        wait_q += tick<kProf>() - tq;
         tc_fence_after_sync();
         issue_qk(static_cast<int>(it & 1));
         for (int jj = 0; ok && jj < n_kv; ++jj) {
@@ -469,13 +668,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         it += n_kv;
       }
-      if (PROF && p.prof) {
+      if (kProf && p.prof) {
         p.prof[blockIdx.x * 16 + 1] = wait_k;
         p.prof[blockIdx.x * 16 + 2] = wait_v;
         p.prof[blockIdx.x * 16 + 5] = issue_qk_cycles;
         p.prof[blockIdx.x * 16 + 6] = issue_pv_cycles;
         p.prof[blockIdx.x * 16 + 3] = wait_p;
-        p.prof[blockIdx.x * 16 + 4] = tick<PROF>() - t_start;
+        p.prof[blockIdx.x * 16 + 4] = tick<kProf>() - t_start;
         p.prof[blockIdx.x * 16 + 8] = wait_q;
       }
     }
@@ -489,107 +688,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     long long it = 0;                         // key tiles consumed so far by this CTA
     long long wait_s = 0;
     long long c_load = 0, c_max = 0, c_sync = 0, c_exp = 0, c_store = 0;   // PROF: cycles per phase
-    const long long t_start = tick<PROF>();
+    const long long t_start = tick<kProf>();
     bool dead = false;                        // a wait gave up; keep hitting the barriers only
     float row_mul = kLog2E32;                 // S of this thread's row -> exponent units (see stage_q)
 
-    // Q of one row tile: global -> operand type (nearest) -> tensor memory, this thread's 64
-    // features [64h, 64h+64) of its row; then one arrival per warp on q_ready.
-    // Returns the factor that takes this row's S to the exponent's units, K's tile scale aside:
-    // log2(e), times the row's own power of two where Q is stored scaled.
+    const uint32_t tmem_q = tmem_base + lane_bits + kTmemQ;   // this quadrant's rows of Q
     auto stage_q = [&](int head, int q_tile) -> float {
-      float row_mul = kLog2E32;
-      const long long row = static_cast<long long>(q_tile) * kBQ + r;
-      const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
-      const bool live = row < p.nq;
-      const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
-      // A scale on the logits is a scale on Q: (c q) . k = c (q . k).  Read here, once per row
-      // tile, rather than held in a register across the key loop.
-      float qs = 1.0f;
-      if (p.logit_scale) {
-        qs = __ldg(p.logit_scale);
-        if (p.logit_divide) qs = 1.0f / qs;
-      }
-      // This thread's 64 features [64h, 64h+64) of its row, rounded to the operand type.
-      auto load4 = [&](int col) {
-        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (live && vec && col + 4 <= p.d) {
-          x = *reinterpret_cast<const float4*>(qrow + col);
-        } else if (live) {
-          if (col + 0 < p.d) x.x = qrow[col + 0];
-          if (col + 1 < p.d) x.y = qrow[col + 1];
-          if (col + 2 < p.d) x.z = qrow[col + 2];
-          if (col + 3 < p.d) x.w = qrow[col + 3];
-        }
-        x.x *= qs; x.y *= qs; x.z *= qs; x.w *= qs;
-        return x;
-      };
-      if (!G::kQkHalf) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int col0 = h * 64 + c * 32;
-          uint32_t v[32];
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            const float4 x = load4(col0 + e);
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
-          }
-          tmem_st_32x32(tmem_base + lane_bits + kTmemQ + col0, v);
-        }
-      } else {
-        // 16-bit pairs, two features per column: features [64h, 64h+64) -> columns [32h, 32h+32).
-        // The whole row's largest magnitude decides the power of two that brings the row into
-        // [2^14, 2^15); the other half of the row is read for that alone (once per row tile,
-        // from L2, eight loads at a time), then this thread's own 64 features, all in flight
-        // together.
-        float m = 0.0f;
-        if (G::kScaledQk) {
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            float4 other[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) other[e] = load4((h ^ 1) * 64 + half * 32 + 4 * e);
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              m = fmaxf(m, fmaxf(fmaxf(fabsf(other[e].x), fabsf(other[e].y)),
-                                 fmaxf(fabsf(other[e].z), fabsf(other[e].w))));
-          }
-        }
-        float4 own[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) own[e] = load4(h * 64 + 4 * e);
-        float inv = 1.0f;
-        if (G::kScaledQk) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(own[e].x), fabsf(own[e].y)),
-                               fmaxf(fabsf(own[e].z), fabsf(own[e].w))));
-          const float scale = f16_range_scale(m);
-          inv = 1.0f / scale;
-          row_mul = kLog2E32 * scale;
-        }
-        uint32_t v[32];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float4 x = own[e];
-          if (G::kQkFmt == Fmt::F16) {
-            v[2 * e + 0] = pack_f16(x.x * inv, x.y * inv);
-            v[2 * e + 1] = pack_f16(x.z * inv, x.w * inv);
-          } else {
-            v[2 * e + 0] = pack_bf16(x.x, x.y);
-            v[2 * e + 1] = pack_bf16(x.z, x.w);
-          }
-        }
-        tmem_st_32x32(tmem_base + lane_bits + kTmemQ + h * 32, v);
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->q_ready);
-      return row_mul;
+      return stage_q_rows<ARM>(p, sh, tmem_q, head, q_tile, r, h, lane);
     };
 
     PieceCursor cursor = pieces_begin(p);
@@ -617,9 +722,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
                               static_cast<uint32_t>(h * 64);
       uint32_t s0[32], s1[32];
       if (!dead) {
-        const long long t0 = tick<PROF>();
+        const long long t0 = tick<kProf>();
         dead = !mbar_wait_warp(&sh->s_full[buf], (t >> 1) & 1, abort, p.status, 207);
-        wait_s += tick<PROF>() - t0;
+        wait_s += tick<kProf>() - t0;
       }
       // S -> exponent units: log2(e), times the scales Q's row and K's tile were stored over.
       // K's scales come from the preparation kernel; every read of them follows an S that was
@@ -632,14 +737,14 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         mul = row_mul * here;
       }
       float mx = -CUDART_INF_F;
-      long long tp = tick<PROF>();
+      long long tp = tick<kProf>();
       if (!dead) {
         tc_fence_after_sync();
         tmem_ld_32x32(s_tmem, s0);
         tmem_ld_32x32(s_tmem + 32, s1);
         tmem_wait_ld();
-        c_load += tick<PROF>() - tp;
-        tp = tick<PROF>();
+        c_load += tick<kProf>() - tp;
+        tp = tick<kProf>();
         const int col0 = (kv_lo + jj) * kBKV + h * 64;
         if (col0 + 64 > p.nk) {
 #pragma unroll
@@ -662,11 +767,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       } else {
         sh->give_up = 1;
       }
-      c_max += tick<PROF>() - tp;
-      tp = tick<PROF>();
+      c_max += tick<kProf>() - tp;
+      tp = tick<kProf>();
       softmax_pair_sync();
-      c_sync += tick<PROF>() - tp;
-      tp = tick<PROF>();
+      c_sync += tick<kProf>() - tp;
+      tp = tick<kProf>();
       if (sh->give_up) break;                 // uniform: every writer wrote before the barrier
       mx = fmaxf(mx, sh->half_max[buf][h ^ 1][r]);
 
@@ -727,8 +832,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
           sum1 += f16_hi(both);
         }
         l += sum0 + sum1;
-        c_exp += tick<PROF>() - tp;
-        tp = tick<PROF>();
+        c_exp += tick<kProf>() - tp;
+        tp = tick<kProf>();
         tmem_st_32x32(s_tmem, packed);
       } else {
       float sum0 = 0.0f, sum1 = 0.0f;
@@ -742,8 +847,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
         s1[c] = __float_as_uint(e1);
       }
       l += sum0 + sum1;
-      c_exp += tick<PROF>() - tp;
-      tp = tick<PROF>();
+      c_exp += tick<kProf>() - tp;
+      tp = tick<kProf>();
       if (!G::kPvHalf) {
         tmem_st_32x32(s_tmem, s0);
         tmem_st_32x32(s_tmem + 32, s1);
@@ -768,7 +873,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->p_full[buf]);
-      c_store += tick<PROF>() - tp;
+      c_store += tick<kProf>() - tp;
     }
 
     // ---- Q of the next piece, before this one's epilogue: every Q K^T of this piece has
@@ -785,47 +890,10 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     }
 
     // ---- epilogue: total row sum, normalise, store columns [64h, 64h+64) of O ----
-    if (!sh->give_up && !dead) {
+    {
       const long long last = it + n_kv - 1;
-      dead = !mbar_wait_warp(&sh->pv_done[last & 1], (last >> 1) & 1, abort, p.status, 209);
-    }
-    sh->half_sum[h][r] = l;
-    if (dead) sh->give_up = 1;
-    softmax_pair_sync();
-    if (!sh->give_up) {
-      tc_fence_after_sync();
-      const float l_total = l + sh->half_sum[h ^ 1][r];
-      const float inv = (p.v_scale ? p.v_scale[b] : 1.0f) / l_total;
-      float* dst;
-      if (whole) {
-        dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
-      } else {
-        const size_t prow = static_cast<size_t>(part_slot) * kBQ + r;
-        dst = p.part_o + prow * p.dv;
-        if (h == 0) {
-          p.part_m[prow] = m_used;
-          p.part_l[prow] = l_total;
-        }
-      }
-      const bool vec_ok = (p.dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
-      for (int c = h * 2; c < h * 2 + 2 && c < dv_chunks; ++c) {
-        uint32_t o[32];
-        tmem_ld_32x32(o_tmem + c * 32, o);
-        tmem_wait_ld();
-        if (row < p.nq || !whole) {
-          if (vec_ok && c * 32 + 32 <= p.dv) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              *reinterpret_cast<float4*>(dst + c * 32 + 4 * v) = make_float4(
-                  __uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-                  __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (c * 32 + e < p.dv) dst[c * 32 + e] = __uint_as_float(o[e]) * inv;
-          }
-        }
-      }
+      finish_piece(p, sh, o_tmem, h, r, row, b, whole, part_slot, l, m_used, dv_chunks,
+                   &sh->pv_done[last & 1], static_cast<uint32_t>((last >> 1) & 1), dead);
     }
     if (sh->give_up) break;
     // The epilogue's reads of O are complete (tcgen05.wait::ld above): the next piece's first
@@ -836,13 +904,732 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
     it += n_kv;
     row_mul = next_row_mul;
     }  // pieces
-    if (PROF && p.prof && quad == 0 && lane == 0 && h == 0) {
-      p.prof[blockIdx.x * 16 + 7] = tick<PROF>() - t_start - wait_s;
+    if (kProf && p.prof && quad == 0 && lane == 0 && h == 0) {
+      p.prof[blockIdx.x * 16 + 7] = tick<kProf>() - t_start - wait_s;
       p.prof[blockIdx.x * 16 + 9] = c_load;
       p.prof[blockIdx.x * 16 + 10] = c_max;
       p.prof[blockIdx.x * 16 + 11] = c_sync;
       p.prof[blockIdx.x * 16 + 12] = c_exp;
       p.prof[blockIdx.x * 16 + 13] = c_store;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- helpers of the pipelined kernel: a row is shared by four threads, one per quarter -------------
+
+// Q of one row tile for the pipelined kernel: this thread's 32 features [32 q4, 32 q4 + 32) of its
+// row as 16 packed 16-bit pairs into tensor-memory columns [16 q4, 16 q4 + 16), then one arrival
+// per warp on q_ready.  The fp16 arm stores the row over the power of two that brings its largest
+// magnitude into [2^14, 2^15) (every thread reads the whole row for that: 128 features, from L2).
+// Returns the factor that takes the row's S to exponent units, K's tile scale aside.
+template <Arm ARM>
+__device__ __forceinline__ float stage_q_quarter(const Params& p, Shared* sh, uint32_t tmem_q, int head,
+                                                 int q_tile, int r, int q4, int lane, int piece) {
+  using G = Geometry<ARM>;
+  float row_mul = kLog2E32;
+  const long long row = static_cast<long long>(q_tile) * kBQ + r;
+  const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
+  const bool live = row < p.nq;
+  const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
+  // A scale on the logits is a scale on Q: (c q) . k = c (q . k).
+  float qs = 1.0f;
+  if (p.logit_scale) {
+    qs = __ldg(p.logit_scale);
+    if (p.logit_divide) qs = 1.0f / qs;
+  }
+  auto load4 = [&](int col) {
+    float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (live && vec && col + 4 <= p.d) {
+      x = *reinterpret_cast<const float4*>(qrow + col);
+    } else if (live) {
+      if (col + 0 < p.d) x.x = qrow[col + 0];
+      if (col + 1 < p.d) x.y = qrow[col + 1];
+      if (col + 2 < p.d) x.z = qrow[col + 2];
+      if (col + 3 < p.d) x.w = qrow[col + 3];
+    }
+    x.x *= qs; x.y *= qs; x.z *= qs; x.w *= qs;
+    return x;
+  };
+  float inv = 1.0f;
+  if (G::kScaledQk) {
+    float m = 0.0f;
+#pragma unroll 1
+    for (int c = 0; c < 128; c += 16) {
+      float4 x[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = load4(c + 4 * e);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[e].x), fabsf(x[e].y)), fmaxf(fabsf(x[e].z), fabsf(x[e].w))));
+    }
+    const float scale = f16_range_scale(m);
+    inv = 1.0f / scale;
+    row_mul = kLog2E32 * scale;
+  }
+  uint32_t v[16];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float4 x = load4(q4 * 32 + 4 * e);
+    if (G::kQkFmt == Fmt::F16) {
+      v[2 * e + 0] = pack_f16(x.x * inv, x.y * inv);
+      v[2 * e + 1] = pack_f16(x.z * inv, x.w * inv);
+    } else {
+      v[2 * e + 0] = pack_bf16(x.x, x.y);
+      v[2 * e + 1] = pack_bf16(x.z, x.w);
+    }
+  }
+  tmem_st_32x16(tmem_q + q4 * 16, v);
+  // The statistics warps need the row's factor too (visible to them once q_ready has completed:
+  // the arrival below releases this store).
+  if (q4 == 0) sh->row_mul[piece & 1][r] = row_mul;
+  tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(&sh->q_ready);
+  return row_mul;
+}
+
+__device__ __forceinline__ void softmax_all_sync() {
+  asm volatile("bar.sync 1, 512;" ::: "memory");
+}
+// Named barriers with separate arriving and waiting sides (ids 2 .. 5 in the pipelined kernel).
+__device__ __forceinline__ void named_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// End of a piece for the pipelined kernel: waits for the last P V, adds the four quarters of the
+// row sum, normalises and stores this thread's 32 columns of O (to the output, or to the partial
+// slot with its (m, l) when the piece covers only part of the keys).
+__device__ __forceinline__ void finish_piece_quarter(const Params& p, Shared* sh, uint32_t o_tmem, int q4,
+                                                     int r, long long row, int b, bool whole,
+                                                     int part_slot, float l, float m_used,
+                                                     uint64_t* last_pv_done, uint32_t last_parity,
+                                                     bool& dead) {
+  if (!sh->give_up && !dead)
+    dead = !mbar_wait_warp(last_pv_done, last_parity, &sh->abort, p.status, 209);
+  sh->quarter_sum[q4][r] = l;
+  if (dead) sh->give_up = 1;
+  softmax_all_sync();
+  if (sh->give_up) return;
+  tc_fence_after_sync();
+  const float l_total = (sh->quarter_sum[0][r] + sh->quarter_sum[1][r]) + (sh->quarter_sum[2][r] + sh->quarter_sum[3][r]);
+  const float inv = (p.v_scale ? p.v_scale[b] : 1.0f) / l_total;
+  float* dst;
+  if (whole) {
+    dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
+  } else {
+    const size_t prow = static_cast<size_t>(part_slot) * kBQ + r;
+    dst = p.part_o + prow * p.dv;
+    if (q4 == 0) {
+      p.part_m[prow] = m_used;
+      p.part_l[prow] = l_total;
+    }
+  }
+  const int c = q4;
+  if (c * 32 < p.dv) {
+    const bool vec_ok = (p.dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+    uint32_t o[32];
+    tmem_ld_32x32(o_tmem + c * 32, o);
+    tmem_wait_ld();
+    if (row < p.nq || !whole) {
+      if (vec_ok && c * 32 + 32 <= p.dv) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          *reinterpret_cast<float4*>(dst + c * 32 + 4 * v) = make_float4(
+              __uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+              __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (c * 32 + e < p.dv) dst[c * 32 + e] = __uint_as_float(o[e]) * inv;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel of the 16-bit arms (fp16 over powers of two, and bf16).  Same tiles and work split
+// as above; 768 threads in five kinds of warps instead of three:
+//   warp 0        TMA producer (one thread): K(t) then V^T(t), each through a ring of three 32 KB
+//                 slots of its own
+//   warp 1        Q K^T issuer (one thread): S[t & 1] = Q K(t)^T, up to two tiles ahead of P V
+//   warp 3        P V issuer (one thread): O += P(t) V(t)
+//   warps 4-7     statistics: read S(t) first, keep every row's running maximum, rescale O when it
+//                 grows by more than 2^8 and publish the reference maximum of the tile
+//   warps 8-23    softmax: warp (q4, quad) turns columns 32 q4 .. 32 q4 + 31 of rows
+//                 32 quad .. 32 quad + 31 of S(t) into P(t) and keeps its quarter of the row sum
+// Tensor memory: Q 0..63 | P 64..127 | S0 128..255 | S1 256..383 | O 384..511.  Packed Q takes 64
+// columns, which leaves 64 for a buffer of P of its own: S[buf] is free again as soon as it has
+// been *read* (s_free[buf]), not once P V has consumed the P written over it.
+//
+// Why this shape.  Measured on B200 with microbenchmarks of the same instruction sequences:
+//   * the tensor pipe needs about 1140 - 1380 cycles per tile of 128 keys (16 MMAs of ~71 cycles
+//     with A in tensor memory) -- the bound to reach;
+//   * one pair of exponentials (two FFMA, cvt.rn.f16x2, ex2.approx.f16x2, HADD2) costs a scheduler
+//     9.4 cycles when two or more warps supply them from a loop resident in its instruction
+//     cache, i.e. ~600 cycles per tile: the special-function unit is not the bound;
+//   * the same sequence costs 2 - 4 times that when the scheduler's other warps issue other code
+//     in between (polling loops, a long unrolled body, several roles): what bounds the softmax side
+//     of this kernel is how fast instructions reach the warps.  The kernel with the exponentials
+//     removed runs at 1119 TFLOP/s on 8 heads of 16384 keys; with them 866 (fp16) / 1001 (bf16).
+// So: the four softmax warps of a scheduler run one short loop over the same tile; the row maxima,
+// which need all 128 columns of a row, moved out of that loop into the statistics warps, which
+// removes the exchange between column groups and the serial chain max -> exchange -> exp from it;
+// softmax warps wait for S(t) and its maximum on a named hardware barrier (bar.sync) rather than
+// by polling, so a waiting warp issues nothing (+5 to +8 %); Q K^T and P V are issued by two
+// threads so that neither stream waits behind the other's barrier in program order.
+// setmaxnreg moves registers from the role and statistics warps to the softmax warps.
+//
+constexpr uint32_t kTmemP = 64;            // pipelined kernel: packed P, beside packed Q (0..63)
+
+// Registers per thread after setmaxnreg.  setmaxnreg.inc blocks (without a limit) until the CTA's
+// pool holds the registers it asks for, and the pool is only what this CTA's own warps gave back:
+// the sum below must fit in what the CTA was launched with, kThreadsPipelined x the kernel's
+// register count.  The host checks that count before every first launch on a device.
+constexpr int kRegsRoles = 56, kRegsStats = 64, kRegsSoftmax = 88;
+constexpr int kRegsAtLaunch = 80;             // what ptxas reports for __launch_bounds__(768, 1)
+static_assert(128 * kRegsRoles + 128 * kRegsStats + 512 * kRegsSoftmax <= kThreadsPipelined * kRegsAtLaunch,
+              "the softmax warps would wait for registers nobody releases");
+
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+template <Arm ARM>
+__global__ void __launch_bounds__(kThreadsPipelined, 1)
+attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_vt, const Params p) {
+  using G = Geometry<ARM>;
+  static_assert(G::kQkHalf && G::kPvHalf, "the pipelined kernel is the one for 16-bit Q, K, P and V");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  constexpr int kRing = 6;                   // six 32 KB slots in the space of three 64 KB ones
+  constexpr int kSlotBytes = G::kSlotBytes;
+  static_assert(kRing * kSlotBytes <= kRingBytes, "ring does not fit");
+  uint8_t* ring = smem;
+  Shared* sh = reinterpret_cast<Shared*>(ring + kRingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRing; ++s) mbar_init(&sh->kv_full[s], 1);
+    mbar_init(&sh->q_ready, 16);           // one arrival per softmax warp
+    mbar_init(&sh->o_free, 16);
+    for (int u = 0; u < 4; ++u) {
+      mbar_init(&sh->s_full[u], 1);
+      mbar_init(&sh->pv_done[u], 1);
+    }
+    for (int u = 0; u < 2; ++u) {
+      mbar_init(&sh->p_full[u], 16);       // the sixteen softmax warps
+      mbar_init(&sh->s_free[u], 20);       // those sixteen and the four statistics warps have read S
+    }
+    sh->abort.flag = 0;
+    sh->give_up = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_slot, kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_slot;
+  AbortState* abort = &sh->abort;
+  trigger_dependent_launch();
+
+  if (warp < 4) {
+    setmaxnreg_dec<kRegsRoles>();
+    // Three single-thread roles, one per warp, each walking the same sequence of pieces and key
+    // tiles t = 0, 1, 2, ... of this CTA:
+    //   warp 0  producer: K tile t into slot t % 3 of the K ring once Q K^T of tile t - 3 is done,
+    //           then V^T tile t into slot t % 3 of the V ring once P V of tile t - 3 is
+    //   warp 1  Q K^T issuer: S[t & 1] = Q K(t)^T once the softmax warps have read S of tile t - 2
+    //   warp 3  P V issuer: O += P(t) V(t) once P(t) is in the P buffer
+    // Two issuing threads instead of one keep the two streams independent: with one thread issuing
+    // Q K^T(t + 2), P V(t), Q K^T(t + 3), ... in program order, a late P(t) (one warpgroup) held up
+    // the Q K^T the other warpgroup was about to need.  The tensor pipe runs the instructions of
+    // both threads in the order they reach it; every real dependence is a barrier wait.
+    constexpr int kRingK = 3;
+    const uint32_t ring_addr = smem_u32(ring);
+    if (warp == 0 && lane == 0) {
+      // One thread loads both operands, K(t) then V^T(t).  P V runs about two tiles behind Q K^T,
+      // so the V slot frees late and the K load behind it in program order waits with it (the
+      // Q K^T issuer then waits ~850 cycles a tile for K).  Both cures that were built cost more
+      // than that wait, because every warp of this kernel runs at the rate instructions reach it:
+      // a V producer of its own in warp 2 (one more instruction stream per SM: 880 -> 814 TFLOP/s
+      // on 8 heads of 16384), and one thread walking the sequence twice with V^T two tiles behind
+      // K (a longer loop for this thread, which then fell behind itself: 761).
+      tma_prefetch_descriptor(&map_k);
+      tma_prefetch_descriptor(&map_vt);
+      grid_dependency_wait();                 // K and V^T come from the preparation kernel before this one
+      const int d_chunks = (p.d + G::kQkChunkElems - 1) / G::kQkChunkElems;
+      const bool q_prefetchable = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
+      bool ok = true;
+      int t = 0, slot = 0;                    // tile counter of this CTA; its slot in either ring
+      long long waited = 0;
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      while (ok && next_piece(p, cursor, pc)) {
+        const int b = pc.unit / p.q_tiles;
+        {
+          // Pull the Q rows of the piece after this one into L2 while this one runs.
+          PieceCursor ahead = cursor;
+          Piece nx;
+          if (q_prefetchable && next_piece(p, ahead, nx) && nx.unit != pc.unit) {
+            const int nb = nx.unit / p.q_tiles;
+            const long long row0 = static_cast<long long>(nx.unit - nb * p.q_tiles) * kBQ;
+            const long long rows = min(static_cast<long long>(kBQ), p.nq - row0);
+            prefetch_l2_bulk(p.q + (static_cast<size_t>(nb) * p.nq + row0) * p.d,
+                             static_cast<uint32_t>(rows * p.d * 4));
+          }
+        }
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t, slot = slot + 1 == kRingK ? 0 : slot + 1) {
+          const int u = t - kRingK;
+          // K slot reuse: Q K^T of tile t - 3 has completed.  The next completion on that barrier
+          // is tile t + 1's, whose K this thread has not loaded yet, so the parity is unambiguous.
+          if (t >= kRingK) {
+            const long long t0 = tick<kProf>();
+            ok = mbar_wait(&sh->s_full[u & 3], static_cast<uint32_t>((u >> 2) & 1), abort, p.status, 201);
+            waited += tick<kProf>() - t0;
+            if (!ok) break;
+          }
+          uint8_t* dst = ring + slot * kSlotBytes;
+          mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
+          for (int c = 0; c < d_chunks; ++c)
+            tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kQkChunkElems,
+                        (pc.kv_lo + jj) * kBKV, b);
+          // V slot reuse: P V of tile t - 3 has completed (it needs nothing this thread has yet to load).
+          if (t >= kRingK) {
+            ok = mbar_wait(&sh->pv_done[u & 3], static_cast<uint32_t>((u >> 2) & 1), abort, p.status, 202);
+            if (!ok) break;
+          }
+          dst = ring + (kRingK + slot) * kSlotBytes;
+          mbar_arrive_expect_tx(&sh->kv_full[kRingK + slot], G::kPvTileChunks * kChunkBytes);
+          for (int c = 0; c < G::kPvTileChunks; ++c)
+            tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[kRingK + slot],
+                        (pc.kv_lo + jj) * kBKV + c * G::kPvChunkElems, 0, b);
+        }
+      }
+      if (kProf && p.prof) p.prof[blockIdx.x * 16 + 0] = waited;
+    } else if (warp == 1 && lane == 0) {
+      const uint32_t idesc_qk = make_idesc_fmt(G::kQkFmt, kBQ, kBKV);
+      const int k_steps = (p.d + G::kQkStepElems - 1) / G::kQkStepElems;
+      long long wait_k = 0, wait_q = 0, wait_f = 0, c_qk = 0;
+      const long long t_start = tick<kProf>();
+      bool ok = true;
+      int t = 0, slot = 0;
+      uint32_t phase = 0;                     // of the K ring's full barriers
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
+        // Q of this piece is in tensor memory.
+        long long t0 = tick<kProf>();
+        if (!(ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 203))) break;
+        wait_q += tick<kProf>() - t0;
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t) {
+          const int buf = t & 1;
+          t0 = tick<kProf>();
+          if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 204))) break;
+          wait_k += tick<kProf>() - t0;
+          t0 = tick<kProf>();
+          // S[buf] was last used by tile t - 2; the softmax warps have it in registers once
+          // s_free[buf] has completed for that tile.
+          if (t >= 2 && !(ok = mbar_wait(&sh->s_free[buf], static_cast<uint32_t>(((t >> 1) - 1) & 1),
+                                         abort, p.status, 211)))
+            break;
+          wait_f += tick<kProf>() - t0;
+          tc_fence_after_sync();
+          t0 = tick<kProf>();
+          const uint64_t k_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
+          const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
+          const uint32_t q_tmem = tmem_base + kTmemQ;
+#pragma unroll
+          for (int ks = 0; ks < G::kQkSteps; ++ks) {
+            if (ks < k_steps)
+              mma_ts<Kind::BF16>(d_tmem, q_tmem + ks * 8,
+                                 k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
+                                 ks != 0 ? 1u : 0u);
+          }
+          mma_commit(&sh->s_full[t & 3]);        // S ready, and the K tile's slot is free
+          c_qk += tick<kProf>() - t0;
+          if (++slot == kRingK) { slot = 0; phase ^= 1u; }
+        }
+      }
+      if (kProf && p.prof) {
+        p.prof[blockIdx.x * 16 + 1] = wait_k;
+        p.prof[blockIdx.x * 16 + 4] = tick<kProf>() - t_start;
+        p.prof[blockIdx.x * 16 + 5] = wait_f;
+        p.prof[blockIdx.x * 16 + 6] = c_qk;
+        p.prof[blockIdx.x * 16 + 8] = wait_q;
+      }
+    } else if (warp == 3 && lane == 0) {
+      const uint32_t n_pv = static_cast<uint32_t>((p.dv + 15) / 16 * 16);
+      const uint32_t idesc_pv = make_idesc_fmt(G::kPvFmt, kBQ, n_pv);
+      long long wait_v = 0, wait_p = 0, c_pv = 0;
+      bool ok = true;
+      int t = 0, slot = kRingK;
+      uint32_t phase = 0;                     // of the V ring's full barriers
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t) {
+          long long t0 = tick<kProf>();
+          if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) break;
+          // The first P V of a piece overwrites O: the piece before must have read it out.
+          if (jj == 0 && piece > 0 &&
+              !(ok = mbar_wait(&sh->o_free, static_cast<uint32_t>((piece - 1) & 1), abort, p.status, 210)))
+            break;
+          wait_v += tick<kProf>() - t0;
+          t0 = tick<kProf>();
+          if (!(ok = mbar_wait(&sh->p_full[t & 1], static_cast<uint32_t>((t >> 1) & 1), abort, p.status,
+                               206)))
+            break;
+          wait_p += tick<kProf>() - t0;
+          tc_fence_after_sync();
+          t0 = tick<kProf>();
+          const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
+          const uint32_t d_tmem = tmem_base + kTmemO;
+          const uint32_t p_tmem = tmem_base + kTmemP;
+          if (jj == 0) {
+            mma_ts<Kind::BF16>(d_tmem, p_tmem, v_desc, idesc_pv, 0u);
+          } else {
+            mma_ts<Kind::BF16>(d_tmem, p_tmem, v_desc, idesc_pv, 1u);
+          }
+#pragma unroll
+          for (int ks = 1; ks < G::kPvSteps; ++ks)
+            mma_ts<Kind::BF16>(d_tmem, p_tmem + ks * 8,
+                               v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
+          mma_commit(&sh->pv_done[t & 3]);       // O updated; the V tile's slot and the P buffer are free
+          c_pv += tick<kProf>() - t0;
+          if (++slot == 2 * kRingK) { slot = kRingK; phase ^= 1u; }
+        }
+      }
+      if (kProf && p.prof) {
+        p.prof[blockIdx.x * 16 + 2] = wait_v;
+        p.prof[blockIdx.x * 16 + 3] = wait_p;
+        p.prof[blockIdx.x * 16 + 14] = c_pv;
+      }
+    }
+  } else if (warp < 8) {
+    // ---- statistics warpgroup: the reference maximum of every row after every key tile --------
+    // Reads S(t) as soon as Q K^T has written it (16 columns at a time: this warpgroup gives its
+    // registers to the softmax warps), keeps the running maximum of its 128 rows over the piece,
+    // raises the reference when a tile exceeds it by more than 2^8, rescales O in that (rare) case,
+    // and publishes the reference for the softmax warpgroup that owns the tile.  Because one
+    // warpgroup sees every tile in order, the two softmax warpgroups need nothing from each other.
+    // (Every lane waits on the barriers here: the one-lane-polls form of the wait made the
+    // compiler ask for more than 96 registers in this branch, which the softmax warps need.)
+    setmaxnreg_dec<kRegsStats>();
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
+    const int dv16 = (p.dv + 15) / 16;
+    bool ok = true;
+    int t = 0;
+    PieceCursor cursor = pieces_begin(p);
+    Piece pc;
+    // On a failed wait this warp stops working but keeps arriving on the tiles' named barriers,
+    // so that the softmax warps, which block on them, always get through (they then see the
+    // abort flag and stop working too).
+    for (int piece = 0; next_piece(p, cursor, pc); ++piece) {
+      const int b = pc.unit / p.q_tiles;
+      // The rows' Q scales of this piece are in shared memory once Q has been staged.
+      if (ok) ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 215);
+      const float row_mul = G::kScaledQk && ok ? sh->row_mul[piece & 1][r] : kLog2E32;
+      float m_used = -CUDART_INF_F;
+#pragma unroll 1
+      for (int jj = 0; jj < pc.n_kv; ++jj, ++t) {
+        if (ok) ok = mbar_wait(&sh->s_full[t & 3], static_cast<uint32_t>((t >> 2) & 1), abort, p.status, 216);
+        if (ok) {
+          tc_fence_after_sync();
+          const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV);
+          const int col0 = (pc.kv_lo + jj) * kBKV;
+          float mx = -CUDART_INF_F;
+          float mul = row_mul;
+          if (G::kScaledQk) mul *= __ldg(p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + pc.kv_lo + jj);
+          // One block of 32 columns at a time (this warpgroup runs on 64 registers).
+#pragma unroll 1
+          for (int c = 0; c < kBKV; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(s_tmem + c, v);
+            tmem_wait_ld();
+            if (col0 + c + 32 > p.nk) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                if (col0 + c + e >= p.nk) v[e] = __float_as_uint(-CUDART_INF_F);
+            }
+            float m0 = mx, m1 = -CUDART_INF_F, m2 = m1, m3 = m1;
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+              m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+              m2 = max3(m2, __uint_as_float(v[e + 4]), __uint_as_float(v[e + 5]));
+              m3 = max3(m3, __uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
+            }
+            mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          }
+          // S[t & 1] has been read here; the softmax warps add their sixteen arrivals.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->s_free[t & 1]);
+          const float m_new = fmaxf(m_used, mx * mul);
+          const bool grow = m_new > m_used + kRescaleThreshold;
+          if (jj > 0 && __any_sync(0xffffffffu, grow)) {
+            // O holds the tiles up to t - 1 against the old reference once P V of tile t - 1 has
+            // completed; P(t) is computed against the new one only after the publication below.
+            ok = mbar_wait(&sh->pv_done[(t - 1) & 3], static_cast<uint32_t>(((t - 1) >> 2) & 1), abort,
+                           p.status, 208);
+            if (ok) {
+              tc_fence_after_sync();
+              const float factor = grow ? ex2_approx(m_used - m_new) : 1.0f;
+#pragma unroll 1
+              for (int c = 0; c < dv16; ++c) {
+                uint32_t o[16];
+                tmem_ld_32x16(o_tmem + c * 16, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                tmem_st_32x16(o_tmem + c * 16, o);
+              }
+              tmem_wait_st();
+              tc_fence_before_sync();
+            }
+          }
+          if (grow) m_used = m_new;
+          sh->pub_m[t & 3][r] = m_used;
+        }
+        // S(t) is ready and its reference maximum published: the softmax warps block on this
+        // named barrier (one of four, by tile) instead of polling, so that while they wait they
+        // issue nothing.
+        named_arrive(2 + (t & 3), 128 + 512);
+      }
+    }
+  } else {
+    // ---- softmax warps: sixteen, four per row quadrant; warp (q4, quad) holds key columns
+    // 32 q4 .. 32 q4 + 31 of rows 32 quad .. 32 quad + 31 of every tile, so that the four warps
+    // of a scheduler run the same short loop on the same tile at about the same time.
+    setmaxnreg_inc<kRegsSoftmax>();
+    const int q4 = (warp - 8) >> 2;           // column quarter of S, Q and O
+    const int quad = warp & 3;                // TMEM lane quadrant
+    const int r = quad * 32 + lane;           // row within the tile
+    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
+    const uint32_t p_tmem = tmem_base + lane_bits + kTmemP + static_cast<uint32_t>(q4 * 16);
+    const uint32_t tmem_q = tmem_base + lane_bits + kTmemQ;
+    int it = 0;                               // key tiles of the pieces before this one
+    long long wait_s = 0, c_a = 0, c_b = 0, c_exp = 0, c_tail = 0;   // kProf: cycles per phase
+    const long long t_start = tick<kProf>();
+    bool dead = false;                        // a wait gave up; keep hitting the barriers only
+    float row_mul = kLog2E32;
+
+    auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (dead) return;
+      dead = !mbar_wait_warp(bar, parity, abort, p.status, code);
+      if (!dead) tc_fence_after_sync();
+    };
+
+    PieceCursor cursor = pieces_begin(p);
+    Piece pc;
+    int piece = 0;
+    while (next_piece(p, cursor, pc)) {
+      const int kv_lo = pc.kv_lo, n_kv = pc.n_kv;
+      const int b = pc.unit / p.q_tiles;
+      const int qt = pc.unit - b * p.q_tiles;
+      const long long row = static_cast<long long>(qt) * kBQ + r;
+      const bool whole = pc.whole;
+      const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
+
+      if (piece == 0) row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, b, qt, r, q4, lane, 0);
+
+      float m_mine = -CUDART_INF_F;           // the reference maximum l is expressed against
+      float l = 0.0f;                         // this quarter's share of the row sum
+      float ks_ahead = 1.0f;                  // fp16 arm: K scale of the next tile
+      bool have_scale = false;
+
+#pragma unroll 1
+      for (int jj = 0; jj < n_kv; ++jj) {
+        const int t = it + jj;
+        uint32_t ra[32];
+        long long tp = tick<kProf>();
+        {
+          // S(t) has been written and read by the statistics warps, and its reference maximum is
+          // in shared memory: they arrive on this barrier after both.  A warp that has given up
+          // still comes here for every tile, so nobody is left blocked.
+          const long long t0 = tick<kProf>();
+          named_sync(2 + (t & 3), 128 + 512);
+          wait_s += tick<kProf>() - t0;
+        }
+        if (!dead && abort->flag) dead = true;
+        if (dead) continue;
+        tc_fence_after_sync();
+        const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV + q4 * 32);
+        tmem_ld_32x32(s_tmem, ra);
+        // S -> exponent units: log2(e), times the powers of two Q's row and K's tile were stored
+        // over.  K's scales come from the preparation kernel; every read of them follows an S that
+        // was computed from its K, so that kernel has completed.  The next tile's scale is fetched
+        // now, a tile ahead of its use.
+        float mul = kLog2E32;
+        if (G::kScaledQk) {
+          const float* ks = p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + kv_lo + jj;
+          const float here = have_scale ? ks_ahead : __ldg(ks);
+          have_scale = jj + 1 < n_kv;
+          if (have_scale) ks_ahead = __ldg(ks + 1);
+          mul = row_mul * here;
+        }
+        tmem_wait_ld();
+        // This quarter of S[t & 1] is in registers: with the other warps' arrivals, Q K^T of tile
+        // t + 2 may overwrite the buffer.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->s_free[t & 1]);
+        c_a += tick<kProf>() - tp;
+        tp = tick<kProf>();
+        // The reference maximum for this tile (the statistics warps have also rescaled O by now
+        // if it moved).
+        const float m_used = sh->pub_m[t & 3][r];
+        // The row sum moves to the new reference when that has changed (rarely after the first tiles).
+        if (m_mine != m_used) {
+          l = m_mine == -CUDART_INF_F ? 0.0f : l * ex2_approx(m_mine - m_used);
+          m_mine = m_used;
+        }
+        c_b += tick<kProf>() - tp;
+        tp = tick<kProf>();
+
+        // Keys past the end of the sequence (last tile only).
+        const int col0 = (kv_lo + jj) * kBKV + q4 * 32;
+        if (col0 + 32 > p.nk) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (col0 + c >= p.nk) ra[c] = __float_as_uint(-CUDART_INF_F);
+        }
+        // 16 pairs of exponentials; pair i leaves its packed result in ra[i], a register whose S
+        // value has been consumed by then.  Written as a software pipeline, each stage two or more
+        // pairs behind the one that feeds it: a warp issues in order, and an instruction whose
+        // operand comes from a special-function instruction issued just before it stalls the
+        // stream for that unit's latency.
+        float sum0 = 0.0f, sum1 = 0.0f;
+        if (G::kPvFmt == Fmt::F16 && kHalfExp) {
+          // x = S mul - m rounded to fp16, two exponentials per special-function instruction; the
+          // packed result is the P operand as it stands.  Row sums: eight pairs in fp16, then fp32.
+          float fa[4], fb[4];
+          uint32_t xp[4], ee[4];
+          uint32_t acc = 0u;
+#pragma unroll
+          for (int i = 0; i < 16 + 5; ++i) {
+            if (i < 16) {
+              fa[i & 3] = fmaf(__uint_as_float(ra[2 * i]), mul, -m_used);
+              fb[i & 3] = fmaf(__uint_as_float(ra[2 * i + 1]), mul, -m_used);
+            }
+            if (i >= 1 && i - 1 < 16) xp[(i - 1) & 3] = pack_f16(fa[(i - 1) & 3], fb[(i - 1) & 3]);
+            if (i >= 3 && i - 3 < 16) {
+              ee[(i - 3) & 3] = ex2_f16x2(xp[(i - 3) & 3]);
+              ra[i - 3] = ee[(i - 3) & 3];
+            }
+            if (i >= 5) {
+              acc = add_f16x2(acc, ee[(i - 5) & 3]);
+              if (((i - 5) & 7) == 7) {
+                sum0 += f16_lo(acc);
+                sum1 += f16_hi(acc);
+                acc = 0u;
+              }
+            }
+          }
+        } else {
+          float fa[4], fb[4], ea[4], eb[4];
+#pragma unroll
+          for (int i = 0; i < 16 + 4; ++i) {
+            if (i < 16) {
+              fa[i & 3] = fmaf(__uint_as_float(ra[2 * i]), mul, -m_used);
+              fb[i & 3] = fmaf(__uint_as_float(ra[2 * i + 1]), mul, -m_used);
+            }
+            if (i >= 1 && i - 1 < 16) {
+              ea[(i - 1) & 3] = ex2_approx(fa[(i - 1) & 3]);
+              eb[(i - 1) & 3] = ex2_approx(fb[(i - 1) & 3]);
+            }
+            if (i >= 4) {
+              const float y0 = ea[(i - 4) & 3], y1 = eb[(i - 4) & 3];
+              ra[i - 4] = G::kPvFmt == Fmt::BF16 ? pack_bf16(y0, y1) : pack_f16(y0, y1);
+              sum0 += y0;
+              sum1 += y1;
+            }
+          }
+        }
+        l += sum0 + sum1;
+        c_exp += tick<kProf>() - tp;
+        tp = tick<kProf>();
+        // There is one P buffer: it is free once P V of the tile before has completed, which it
+        // normally has by now (for the first tile of a piece the epilogue of the piece before has
+        // waited for it).
+        if (jj > 0) {
+          wait_bar(&sh->pv_done[(t - 1) & 3], static_cast<uint32_t>(((t - 1) >> 2) & 1), 212);
+          if (dead) continue;
+        }
+        {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) pk[c] = ra[c];
+          tmem_st_32x16(p_tmem, pk);          // keys 32 q4 .. 32 q4 + 31 of the tile
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->p_full[t & 1]);
+        c_tail += tick<kProf>() - tp;
+      }
+
+      // ---- end of the piece.  Every Q K^T of it has completed (its S was read above), so Q's
+      // columns may be restaged: Q of the next piece goes in before this one's epilogue, so that the
+      // Q K^T issuer can run the next piece's first tiles while O is being read out below.
+      const int last = it + n_kv - 1;
+      float next_row_mul = kLog2E32;
+      {
+        PieceCursor ahead = cursor;
+        Piece nx;
+        if (!dead && next_piece(p, ahead, nx)) {
+          const int nb = nx.unit / p.q_tiles;
+          next_row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, nb, nx.unit - nb * p.q_tiles, r, q4, lane, piece + 1);
+        }
+      }
+
+      finish_piece_quarter(p, sh, o_tmem, q4, r, row, b, whole, part_slot, l, m_mine,
+                           &sh->pv_done[last & 3], static_cast<uint32_t>((last >> 2) & 1), dead);
+      if (sh->give_up) break;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->o_free);
+      it += n_kv;
+      row_mul = next_row_mul;
+      ++piece;
+    }  // pieces
+    if (kProf && p.prof && quad == 0 && lane == 0 && q4 == 0) {
+      p.prof[blockIdx.x * 16 + 7] = tick<kProf>() - t_start - wait_s;
+      p.prof[blockIdx.x * 16 + 9] = c_a;
+      p.prof[blockIdx.x * 16 + 10] = c_b;
+      p.prof[blockIdx.x * 16 + 12] = c_exp;
+      p.prof[blockIdx.x * 16 + 13] = c_tail;
     }
   }
 
@@ -1030,24 +1817,36 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   if (d % 4 != 0 || d < 4 || d > 128 || dv < 1 || dv > 128)
     return fail("ib_attention: head dimensions outside the fused kernel's range");
   const int smem_bytes = 1024 + kRingBytes + static_cast<int>(sizeof(Shared)) + 64;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaSuccess;
-    const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::TF32>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::TF32>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::BF16>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::BF16>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::MIXED>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::MIXED>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<false, Arm::F16>),
-                              reinterpret_cast<const void*>(&attention_tf32_kernel<true, Arm::F16>)};
-    for (const void* fn : variants)
-      if (err == cudaSuccess)
-        err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (err != cudaSuccess)
-      return fail(std::string("ib_attention: cannot reserve shared memory: ") +
-                  cudaGetErrorString(err));
-    configured = true;
+  // The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of each kernel.
+  {
+    static std::mutex mutex;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+      return fail("ib_attention: cannot identify the current device");
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!configured[dev]) {
+      cudaError_t err = cudaSuccess;
+      const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::TF32>),
+                                reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::MIXED>),
+                                reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::BF16>),
+                                reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::F16>)};
+      for (const void* fn : variants)
+        if (err == cudaSuccess)
+          err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+      // The pipelined kernels redistribute registers between their warpgroups; see kRegsAtLaunch.
+      for (int v = 2; v < 4 && err == cudaSuccess; ++v) {
+        cudaFuncAttributes attr{};
+        err = cudaFuncGetAttributes(&attr, variants[v]);
+        if (err == cudaSuccess && attr.numRegs < kRegsAtLaunch)
+          return fail("ib_attention: the pipelined kernel was built with " + std::to_string(attr.numRegs) +
+                      " registers per thread, fewer than its register redistribution assumes");
+      }
+      if (err != cudaSuccess)
+        return fail(std::string("ib_attention: cannot reserve shared memory: ") +
+                    cudaGetErrorString(err));
+      configured[dev] = true;
+    }
   }
   Params p{};
   p.q = q;
@@ -1111,25 +1910,20 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   overlap.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(f16 || bf16 ? kThreadsPipelined : kThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = s;
   cfg.attrs = &overlap;
   cfg.numAttrs = g_dependent_launch && follows_prepare ? 1 : 0;
   cudaError_t launched;
-  const bool prof = p.prof != nullptr;
   if (f16)
-    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::F16>, map_k, map_vt, p)
-                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::F16>, map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_pipelined_kernel<Arm::F16>, map_k, map_vt, p);
   else if (bf16)
-    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::BF16>, map_k, map_vt, p)
-                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::BF16>, map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_pipelined_kernel<Arm::BF16>, map_k, map_vt, p);
   else if (mixed)
-    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::MIXED>, map_k, map_vt, p)
-                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::MIXED>, map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<Arm::MIXED>, map_k, map_vt, p);
   else
-    launched = prof ? cudaLaunchKernelEx(&cfg, attention_tf32_kernel<true, Arm::TF32>, map_k, map_vt, p)
-                    : cudaLaunchKernelEx(&cfg, attention_tf32_kernel<false, Arm::TF32>, map_k, map_vt, p);
+    launched = cudaLaunchKernelEx(&cfg, attention_tf32_kernel<Arm::TF32>, map_k, map_vt, p);
   if (launched != cudaSuccess)
     return fail(std::string("ib_attention (tcgen05): launch failed: ") + cudaGetErrorString(launched));
   count_launch();
@@ -1151,7 +1945,9 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
 
 }  // namespace ib
 
-// Undocumented hook for performance work: see g_attention_profile.
+#if IB_ATTN_PROFILE
+// Development builds only (-DIB_ATTN_PROFILE=1): device pointer to 16 counters per CTA.
 extern "C" void ib_debug_set_attention_profile(unsigned long long* device_counters) {
   ib::set_attention_profile(device_counters);
 }
+#endif

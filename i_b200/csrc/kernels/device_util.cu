@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "sm100.cuh"
 
 namespace ib {
 namespace {
@@ -103,14 +104,66 @@ int check_device_status(const char* what, cudaStream_t) {
 
 }  // namespace ib
 
-// Undocumented hook for kernel development: returns and clears the code a bounded
-// device-side wait left for the current device, 0 if none.
-extern "C" int ib_debug_take_device_status(void) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= ib::kMaxDevices) return 0;
-  std::lock_guard<std::mutex> lock(ib::g_status_mutex);
-  if (!ib::g_status_host[dev]) return 0;
-  const int code = *static_cast<volatile int*>(ib::g_status_host[dev]);
-  *static_cast<volatile int*>(ib::g_status_host[dev]) = 0;
-  return code;
+namespace ib {
+namespace {
+
+// mbar_wait with a limit in nanoseconds instead of a number of polls: for this self-test only.
+__device__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, sm100::AbortState* abort, int* status,
+                                int code, unsigned long long limit_ns) {
+  const unsigned long long start = sm100::global_timer_ns();
+  for (;;) {
+    if (sm100::mbar_try_wait(bar, parity)) return true;
+    if (abort->flag) return false;
+    if (sm100::global_timer_ns() - start > limit_ns) {
+      abort->flag = 1;
+      *reinterpret_cast<volatile int*>(status) = code;
+      __threadfence_system();
+      return false;
+    }
+  }
+}
+
+// One warp waits on a barrier that nothing ever arrives at, with the limit the caller gives.
+// The wait must give up: record its code in the status word, raise the abort flag and return
+// false, after which the kernel leaves through its ordinary exit.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ sm100::AbortState abort;
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(&bar, 1);
+    abort.flag = 0;
+    sm100::fence_barrier_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait_timed(&bar, 0, &abort, status, 250, limit_ns);
+  __syncthreads();
+  // Every thread sees the flag the waiter raised; a wait that came back "done" would be a bug.
+  if (threadIdx.x == 1 && ok && !abort.flag) *reinterpret_cast<volatile int*>(status) = 251;
+}
+
+}  // namespace
+}  // namespace ib
+
+// Failure detection, exercised without a fault: launches a kernel whose only wait can never be
+// satisfied and reports what the host sees afterwards.  The kernels of this library bound every
+// device-side wait (sm100.cuh: mbar_wait); a wait that runs out leaves a code in a host-mapped
+// status word and the call that synchronises next returns -1 with "a device-side wait timed
+// out".  This entry point makes that happen with a wait of `limit_ns` (a millisecond is plenty):
+// it returns -1 with that message when the timeout was detected and reported, which is the
+// expected outcome, and 0 if the wait did not time out (which would be a defect).  The context
+// stays usable; the next launch runs normally.
+extern "C" int ib_selftest_wait_timeout(unsigned long long limit_ns, void* stream) {
+  using namespace ib;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = device_status_word(s);
+  if (!status) return fail("ib_selftest_wait_timeout: cannot allocate the device status word");
+  if (limit_ns > 100000000ull) limit_ns = 100000000ull;    // at most 0.1 s
+  wait_timeout_selftest_kernel<<<1, 32, 0, s>>>(status, limit_ns);
+  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess)
+    return fail(std::string("ib_selftest_wait_timeout: ") + cudaGetErrorString(err));
+  count_launch();
+  return check_device_status("ib_selftest_wait_timeout", s);
 }

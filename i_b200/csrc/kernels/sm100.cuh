@@ -2,10 +2,10 @@
 // tensor copies, tensor memory (TMEM) management, tcgen05 MMA and the matrix /
 // instruction descriptors it takes.  Nothing here uses cluster multicast.
 //
-// Every wait is bounded: a wait that does not complete within kWaitLimitNs
-// records a code in a global status word, raises a CTA-wide abort flag and
-// returns false, so that a protocol bug surfaces as an error return instead of
-// a hung GPU.
+// Every wait is bounded: a wait that does not complete within kWaitSpinLimit
+// polls records a code in a global status word, raises a CTA-wide abort flag
+// and returns false, so that a protocol bug surfaces as an error return instead
+// of a hung GPU.
 #pragma once
 
 #include <cuda.h>
@@ -16,7 +16,6 @@
 namespace ib {
 namespace sm100 {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -74,23 +73,31 @@ struct AbortState {
 // Waits for the phase with the given parity.  Returns false (after recording
 // `code` in *status and raising the abort flag) when the limit is exceeded or
 // another role already aborted.
+//
+// The limit is a number of polls, not a time: mbarrier.try_wait suspends the
+// thread for a hardware-defined interval before it reports "not yet", so
+// kWaitSpinLimit polls last from some tens of milliseconds (no suspension at all)
+// to a few seconds, and the loop stays a handful of instructions.  That matters: the
+// attention kernels run several different instruction streams per SM
+// (producers, MMA issuers, statistics and softmax warps) and inline this wait
+// at some twenty places; with a clock-based limit (a %globaltimer read, 64-bit
+// compares) the waits alone added about 10 KB to what an SM executes per tile,
+// and the kernels became bound by instruction fetch.
+constexpr uint32_t kWaitSpinLimit = 1u << 22;
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, AbortState* abort,
                                           int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = global_timer_ns();
-  unsigned spins = 0;
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (abort->flag) return false;
-      if (global_timer_ns() - start > kWaitLimitNs) {
-        abort->flag = 1;
-        *reinterpret_cast<volatile int*>(status) = code;
-        __threadfence_system();
-        return false;
-      }
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (abort->flag) return false;
+    if (++spins > kWaitSpinLimit) {
+      abort->flag = 1;
+      *reinterpret_cast<volatile int*>(status) = code;
+      __threadfence_system();
+      return false;
     }
   }
+  return true;
 }
 
 // Whole-warp wait: lane 0 polls, the result is broadcast.  Keeps 31 of 32 lanes
@@ -202,6 +209,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
         "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
+      : "memory");
+}
+
+// The same for 16 columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
       : "memory");
 }
 
@@ -319,107 +348,6 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
                : "memory");
-}
-
-// ---- CTA pairs (cta_group::2) ----------------------------------------------
-// Two CTAs of a cluster drive one 256-row MMA: each holds its own 128 rows of A
-// and D (same tensor-memory columns in both) and half of the B rows in its own
-// shared memory at the same offset.  The even CTA of the pair issues the MMAs.
-
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// In a cluster, a shared::cta address carries the CTA's rank in bit 24; clearing
-// it names the same offset in the pair's even (leader) CTA.
-__device__ __forceinline__ uint32_t leader_cta_addr(uint32_t smem_addr) {
-  return smem_addr & 0xFEFFFFFFu;
-}
-
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                   smem_u32(smem_result)),
-               "r"(ncols)
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_relinquish_alloc_permit_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
-
-template <Kind KIND>
-__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  if (KIND == Kind::TF32) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-
-template <Kind KIND>
-__device__ __forceinline__ void mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  if (KIND == Kind::TF32) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-
-// One arrival on the barrier at this shared-memory offset in every CTA of
-// `cta_mask` once all MMAs issued so far by this thread have completed.
-__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-      "[%0], %1;" ::"r"(smem_u32(bar)),
-      "h"(cta_mask)
-      : "memory");
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {
