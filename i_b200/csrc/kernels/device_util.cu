@@ -167,3 +167,26 @@ extern "C" int ib_selftest_wait_timeout(unsigned long long limit_ns, void* strea
   count_launch();
   return check_device_status("ib_selftest_wait_timeout", s);
 }
+
+// Output assembly across GPUs of one node: queues, on `stream`, one device-to-device copy of
+// `bytes` from `src` to each of the `n_dsts` destinations, which are this process's mappings of
+// its peers' buffers.  The copies are DMA transfers over NVLink and take no SM from a kernel that
+// is running.  `after` (a cudaEvent_t, or null) is waited for first, `done` (a cudaEvent_t, or
+// null) is recorded behind the last copy, so a caller's whole publication step is this one call.
+// The reference has no counterpart (it runs on one thread of one process).
+extern "C" int ib_peer_publish(const void* src, void* const* dsts, int n_dsts, size_t bytes,
+                               void* after, void* done, void* stream) {
+  using namespace ib;
+  if (n_dsts < 0 || (n_dsts > 0 && !dsts)) return fail("ib_peer_publish: no destinations");
+  if (bytes > 0 && !src) return fail("ib_peer_publish: null source");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaSuccess;
+  if (after) err = cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(after), 0);
+  for (int i = 0; err == cudaSuccess && i < n_dsts; ++i) {
+    if (!dsts[i]) return fail("ib_peer_publish: null destination");
+    if (bytes > 0) err = cudaMemcpyAsync(dsts[i], src, bytes, cudaMemcpyDeviceToDevice, s);
+  }
+  if (err == cudaSuccess && done) err = cudaEventRecord(static_cast<cudaEvent_t>(done), s);
+  if (err != cudaSuccess) return fail(std::string("ib_peer_publish: ") + cudaGetErrorString(err));
+  return 0;
+}

@@ -100,16 +100,108 @@ def sharded_attention(attend, q, k, v, group=None, out=None):
     return out
 
 
+def chunk_bounds(n, chunks):
+    """Cuts n units into at most `chunks` contiguous, non-empty [lo, hi) blocks of near-equal size."""
+    chunks = max(1, min(chunks, n))
+    return [split_even(n, chunks, c) for c in range(chunks) if split_even(n, chunks, c)[1] >
+            split_even(n, chunks, c)[0]]
+
+
+def sharded_attention_chunked(attend_into, q, k, v, out, chunks=4, gather=None, slot=0, group=None,
+                              local_inputs=False):
+    """The head-sharded path with the assembly of the output overlapped with the computation.
+
+    This rank's heads are computed `chunks` blocks at a time; as soon as a block is done its rows
+    of the output travel to the other ranks while the next block is computed, so only the last
+    block's transfer is exposed.  `attend_into(o_part, q_part, k_part, v_part)` writes one block.
+
+      * with `gather` (a PeerGather whose shape is [heads per rank, rows, dv]): `out` is ignored,
+        the result is `gather.gathered(slot)` viewed as [heads, rows, dv]; copies run on copy
+        engines.  The caller ends a sequence of calls with `gather.finish()`.
+      * without: every block is all-gathered through torch.distributed (NCCL on GPUs, gloo on CPU)
+        into `out` ([heads, rows, dv], on every rank).
+
+    q, k, v hold the whole problem on every rank ([heads, ...]; only this rank's heads are read)
+    or, with `local_inputs`, just this rank's heads ([heads / world, ...]).  Heads must divide
+    evenly over the ranks (the uneven and the row-sharded cases go through sharded_attention).
+    Returns the assembled [heads, rows, dv] tensor.
+    """
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    heads = q.shape[0] * world if local_inputs else q.shape[0]
+    if heads % world:
+        raise ValueError("sharded_attention_chunked: %d heads do not divide over %d ranks" % (heads, world))
+    per = heads // world
+    lo = rank * per                  # this rank's first head in the assembled output
+    src = 0 if local_inputs else lo  # and in q, k, v
+    bounds = chunk_bounds(per, chunks)
+    if gather is not None:
+        import torch
+        mine = gather.local(slot)
+        main = torch.cuda.current_stream()
+        for a, b in bounds:
+            attend_into(mine[a:b], q[src + a:src + b], k[src + a:src + b], v[src + a:src + b])
+            done = gather.block_event(slot, a)
+            done.record(main)
+            gather.publish(slot, done, a, b)
+        return gather.gathered(slot).reshape((heads,) + tuple(mine.shape[1:]))
+    side = None
+    if world > 1 and out.is_cuda:
+        import torch
+        side = _side_stream(out.device)
+        main = torch.cuda.current_stream()
+    for a, b in bounds:
+        attend_into(out[lo + a:lo + b], q[src + a:src + b], k[src + a:src + b], v[src + a:src + b])
+        if world == 1:
+            continue
+        # Block [a, b) of every rank: gathered into a staging tensor [world, b - a, rows, dv], then
+        # placed (the blocks of one rank are not adjacent to the next rank's in `out`).  On GPUs the
+        # collective runs on a side stream, under the computation of the next block.
+        part = out[lo + a:lo + b]
+        if side is not None:
+            ready = torch.cuda.Event()
+            ready.record(main)
+            side.wait_event(ready)
+            torch.cuda.set_stream(side)
+        try:
+            staged = part.new_empty((world,) + tuple(part.shape))
+            dist.all_gather_into_tensor(staged.view(-1), part.reshape(-1), group=group)
+            for r in range(world):
+                if r != rank:
+                    out[r * per + a:r * per + b] = staged[r]
+        finally:
+            if side is not None:
+                torch.cuda.set_stream(main)
+    if side is not None:
+        main.wait_stream(side)
+    return out
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device):
+    import torch
+    key = (device.type, device.index)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 class PeerGather:
     """All-gather of per-rank output shards by copy engines over NVLink.
 
     Every rank owns a symmetric buffer `[slots][world][*shape]`; rank r computes
     into `local(slot)` (= its own row of its own buffer) and `publish(slot)`
-    queues one device-to-device copy per peer into row r of that peer's buffer.
-    The copies are DMA transfers: they use no SM, so they run entirely under the
-    next step's kernel, which a collective made of SM kernels cannot do while a
-    persistent kernel holds every SM.  `finish()` waits for this rank's copies
-    and then for everybody's (host barrier); after it every rank holds all rows.
+    queues one device-to-device copy per peer into row r of that peer's buffer
+    (one call into the library, ib_peer_publish: wait for the producer's event,
+    the copies, the completion event).  The copies are DMA transfers: they use no
+    SM, so they run entirely under the next kernel, which a collective made of SM
+    kernels cannot do while a persistent kernel holds every SM.  `finish()` waits
+    for this rank's copies and then for everybody's (host barrier); after it every
+    rank holds all rows.
 
     Needs torch symmetric memory (peer-mapped allocations); `available()` tells.
     """
@@ -123,9 +215,11 @@ class PeerGather:
             return False
 
     def __init__(self, shape, slots=2, group=None, device=None):
+        import ctypes
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
+        from . import ilang
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -137,6 +231,38 @@ class PeerGather:
                       self.handle.get_buffer(r, full, torch.float32) for r in range(self.world)]
         self.stream = torch.cuda.Stream(device=device)
         self._done = [None] * slots
+        # Byte geometry for the library call: one unit is one rank's row of one slot; a block of
+        # it is addressed by its offset along the unit's leading axis.
+        self._unit_bytes = 4
+        for n in shape:
+            self._unit_bytes *= n
+        self._lead = shape[0] if shape else 1
+        self._lead_bytes = self._unit_bytes // max(1, self._lead)
+        self._base = [t.data_ptr() for t in self.peers]
+        self._order = [(self.rank + step) % self.world for step in range(1, self.world)]
+        self._dsts = (ctypes.c_void_p * max(1, len(self._order)))()
+        self._lib = ilang.core()
+        self._lib.ib_peer_publish.restype = ctypes.c_int
+        self._lib.ib_peer_publish.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                              ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_void_p]
+        # Completion events, created up front (an event's handle exists once it has been recorded).
+        self._events = {}
+        self._block_events = {}
+
+    def _event(self, table, key, stream):
+        import torch
+        ev = table.get(key)
+        if ev is None:
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            table[key] = ev
+        return ev
+
+    def block_event(self, slot, block):
+        """A reusable event for the producer of block `block` of `slot` to record."""
+        import torch
+        return self._event(self._block_events, (slot, block), torch.cuda.current_stream())
 
     def local(self, slot):
         return self.buffer[slot, self.rank]
@@ -144,17 +270,21 @@ class PeerGather:
     def gathered(self, slot):
         return self.buffer[slot]
 
-    def publish(self, slot, after):
-        """Queue the copies of `local(slot)` to every peer once event `after` has fired."""
-        import torch
-        self.stream.wait_event(after)
-        with torch.cuda.stream(self.stream):
-            src = self.buffer[slot, self.rank]
-            for step in range(1, self.world):
-                peer = (self.rank + step) % self.world
-                self.peers[peer][slot, self.rank].copy_(src, non_blocking=True)
-            done = torch.cuda.Event()
-            done.record(self.stream)
+    def publish(self, slot, after, lo=None, hi=None):
+        """Queue the copies of `local(slot)` (entries [lo, hi) of its leading axis; all of it when
+        omitted) to every peer once event `after` has fired.  Returns the event recorded behind them."""
+        lo = 0 if lo is None else lo
+        hi = self._lead if hi is None else hi
+        offset = (slot * self.world + self.rank) * self._unit_bytes + lo * self._lead_bytes
+        for n, peer in enumerate(self._order):
+            self._dsts[n] = self._base[peer] + offset
+        done = self._event(self._events, (slot, lo), self.stream)
+        rc = self._lib.ib_peer_publish(self._base[self.rank] + offset, self._dsts, len(self._order),
+                                       (hi - lo) * self._lead_bytes, after.cuda_event, done.cuda_event,
+                                       self.stream.cuda_stream)
+        if rc != 0:
+            err = self._lib.i_error()
+            raise RuntimeError(err.decode() if err else "ib_peer_publish failed")
         self._done[slot] = done
         return done
 
