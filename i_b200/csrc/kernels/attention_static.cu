@@ -54,6 +54,8 @@ extern "C" int ib_attention_static(const float* q, const float* k, const float* 
                                    int v_kmajor, void* stream) {
   const size_t need =
       ib_attention_workspace_bytes(batch, nq, nk, d, dv, v_kmajor, IB_PRECISION_FP32);
+  if (need == SIZE_MAX)
+    return ib::fail("ib_attention_static: extents too large (an element count does not fit size_t)");
   if (need > kStaticScratchBytes)
     return ib::fail("ib_attention_static: batch*nq*nk = " + std::to_string(batch * nq * nk) +
                     " scores need " + std::to_string(need) + " bytes of scratch, the built-in " +

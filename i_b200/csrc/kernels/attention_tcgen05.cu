@@ -73,7 +73,6 @@ constexpr int kThreads = 384;
 constexpr int kThreadsPipelined = 768;    // roles, statistics, and sixteen softmax warps
 constexpr int kChunkBytes = 128 * 128;     // 128 rows of 128 bytes: 32 fp32 or 64 bf16 per row
 constexpr int kMaxRing = 6;
-constexpr int kMaxDevices = 64;             // per-device bookkeeping (kernel attributes)
 
 // Arithmetic of the two contractions.  MIXED runs S = Q K^T on TF32 operands and O += P V on
 // fp16 ones: fp16 has TF32's 10-bit mantissa, P lies in [0, 1], and V is scaled per head by a
@@ -1819,13 +1818,10 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   const int smem_bytes = 1024 + kRingBytes + static_cast<int>(sizeof(Shared)) + 64;
   // The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of each kernel.
   {
-    static std::mutex mutex;
-    static bool configured[kMaxDevices] = {};
+    static OncePerDevice configured;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
-      return fail("ib_attention: cannot identify the current device");
-    std::lock_guard<std::mutex> lock(mutex);
-    if (!configured[dev]) {
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail("ib_attention: cannot identify the current device");
+    const int rc = configured.run(dev, [smem_bytes] {
       cudaError_t err = cudaSuccess;
       const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::TF32>),
                                 reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::MIXED>),
@@ -1845,8 +1841,10 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
       if (err != cudaSuccess)
         return fail(std::string("ib_attention: cannot reserve shared memory: ") +
                     cudaGetErrorString(err));
-      configured[dev] = true;
-    }
+      return 0;
+    });
+    if (rc == -2) return fail("ib_attention: cannot identify the current device");
+    if (rc != 0) return rc;
   }
   Params p{};
   p.q = q;

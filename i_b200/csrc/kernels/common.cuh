@@ -6,6 +6,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <mutex>
 #include <string>
 
 #include "i_b200.h"
@@ -30,6 +31,30 @@ inline int check_launch(const char* what) {
 }
 
 constexpr int kNumSMs = 148;  // B200
+
+// Set-up that has to happen once per device and per kernel (function attributes such as the
+// opt-in to more than 48 KB of dynamic shared memory belong to the device's context, not to the
+// process): run(device, f) calls f the first time it sees `device` and remembers success.  A
+// failed f is tried again on the next call.  Safe to call from several threads.
+class OncePerDevice {
+ public:
+  static constexpr int kMaxDevices = 64;
+  // Returns f's result (0 = ok) on the first call for a device, 0 afterwards, -2 for a device
+  // number outside [0, kMaxDevices).
+  template <typename F>
+  int run(int device, F&& f) {
+    if (device < 0 || device >= kMaxDevices) return -2;
+    std::lock_guard<std::mutex> lock(mutex_);
+    if (done_[device]) return 0;
+    const int rc = f();
+    if (rc == 0) done_[device] = true;
+    return rc;
+  }
+
+ private:
+  std::mutex mutex_;
+  bool done_[kMaxDevices] = {};
+};
 
 // powf(2.71828175f, x), the reference C backend's exp
 // (compiler/src/backends/c/expr.rs:350-366 prints e as 2.71828175f).  x*log2(e32)

@@ -190,3 +190,23 @@ extern "C" int ib_peer_publish(const void* src, void* const* dsts, int n_dsts, s
   if (err != cudaSuccess) return fail(std::string("ib_peer_publish: ") + cudaGetErrorString(err));
   return 0;
 }
+
+// The per-device set-up bookkeeping (OncePerDevice), exercised without a GPU: pretends `devices`
+// devices each make `calls` calls, the first `failures` set-up attempts on every device failing.
+// Returns how many times the set-up function ran: devices * (min(failures, calls) + (calls >
+// failures ? 1 : 0)) when every device is set up exactly once after its failures.
+extern "C" int ib_selftest_once_per_device(int devices, int calls, int failures) {
+  ib::OncePerDevice once;
+  int ran = 0;
+  int attempts[ib::OncePerDevice::kMaxDevices] = {};
+  if (once.run(-1, [] { return 0; }) != -2 ||
+      once.run(ib::OncePerDevice::kMaxDevices, [] { return 0; }) != -2)
+    return -1;
+  for (int c = 0; c < calls; ++c)
+    for (int dev = 0; dev < devices && dev < ib::OncePerDevice::kMaxDevices; ++dev)
+      once.run(dev, [&] {
+        ++ran;
+        return attempts[dev]++ < failures ? -1 : 0;
+      });
+  return ran;
+}

@@ -1,5 +1,6 @@
 // ib_contract and ib_attention: precision choice, workspace carving and the
 // layout fix-ups that give the tensor-core kernels K-major operands.
+#include <initializer_list>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -11,20 +12,34 @@ constexpr double kTensorMinFlop = 268435456.0;  // 2^28: below this the fp32 arm
 size_t round_up(size_t x, size_t to) { return (x + to - 1) / to * to; }
 
 // Sub-allocator over the caller's workspace (256-byte granules).
+// Largest element count whose byte size, rounded up and summed a few times, stays inside size_t.
+constexpr size_t kMaxFloats = SIZE_MAX >> 6;
+
+// True when the product of the extents does not fit kMaxFloats (or overflows on the way).
+bool too_many_elements(std::initializer_list<size_t> extents) {
+  size_t product = 1;
+  for (size_t e : extents)
+    if (__builtin_mul_overflow(product, e, &product)) return true;
+  return product > kMaxFloats;
+}
+
 struct Carver {
   uint8_t* base;
   size_t size, used = 0;
   Carver(void* p, size_t n) : base(static_cast<uint8_t*>(p)), size(n) {}
   float* take(size_t floats) {
+    if (floats > kMaxFloats) return nullptr;
     size_t bytes = round_up(floats * sizeof(float), 256);
-    if (!base || used + bytes > size) return nullptr;
+    if (!base || bytes > size || used > size - bytes) return nullptr;
     float* out = reinterpret_cast<float*>(base + used);
     used += bytes;
     return out;
   }
 };
 
-size_t carve_bytes(size_t floats) { return round_up(floats * sizeof(float), 256); }
+size_t carve_bytes(size_t floats) {
+  return floats > kMaxFloats ? SIZE_MAX >> 4 : round_up(floats * sizeof(float), 256);
+}
 
 bool wants_tensor(int precision, double flop) {
   if (precision == IB_PRECISION_FP32) return false;
@@ -164,6 +179,11 @@ int prepared_kv(const float* k, const float* v, size_t batch, size_t nk, size_t 
 extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, size_t k,
                                               int a_kmajor, int b_kmajor, int precision) {
   using namespace ib;
+  // Extents whose element counts do not fit size_t: no workspace can serve them (ib_contract
+  // refuses the same extents).
+  if (too_many_elements({batch, m, k}) || too_many_elements({batch, n, k}) ||
+      too_many_elements({batch, m, n}))
+    return SIZE_MAX;
   if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
   const double flop = 2.0 * batch * m * n * k;
   if (!wants_tensor(precision, flop)) return 0;
@@ -198,6 +218,9 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
   using namespace ib;
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!a || !b || !c) return fail("ib_contract: null pointer");
+  if (too_many_elements({batch, m, k}) || too_many_elements({batch, n, k}) ||
+      too_many_elements({batch, m, n}))
+    return fail("ib_contract: extents too large (an element count does not fit size_t)");
   if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_F16)
     return fail("ib_contract: unknown precision");
   if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
@@ -294,6 +317,11 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
 extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t nk, size_t d,
                                                size_t dv, int v_kmajor, int precision) {
   using namespace ib;
+  // Extents whose element counts do not fit size_t: no workspace can serve them (ib_attention
+  // refuses the same extents).
+  if (too_many_elements({batch, nq, nk}) || too_many_elements({batch, nq, d > dv ? d : dv}) ||
+      too_many_elements({batch, nk, d > dv ? d : dv}))
+    return SIZE_MAX;
   const double flop = 4.0 * batch * nq * nk * d;
   if (wants_tensor(precision, flop) && attention_shape_ok(d, dv)) {
     // Rounded copy of K, V^T (rounded), and the KV-split partials; bf16 copies
@@ -320,6 +348,9 @@ extern "C" int ib_attention_scaled(const float* q, const float* k, const float* 
   if (nk == 0 || d == 0) return fail("ib_attention: empty key or feature axis");
   if (precision < IB_PRECISION_AUTO || precision > IB_PRECISION_F16)
     return fail("ib_attention: unknown precision");
+  if (too_many_elements({batch, nq, nk}) || too_many_elements({batch, nq, d > dv ? d : dv}) ||
+      too_many_elements({batch, nk, d > dv ? d : dv}))
+    return fail("ib_attention: extents too large (an element count does not fit size_t)");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (reinterpret_cast<uintptr_t>(workspace) & 255u)
     return fail("ib_attention: workspace must be 256-byte aligned");
@@ -367,6 +398,7 @@ extern "C" int ib_attention(const float* q, const float* k, const float* v, floa
 
 extern "C" size_t ib_attention_prepare_bytes(size_t batch, size_t nk, size_t d, size_t dv,
                                              int precision) {
+  if (ib::too_many_elements({batch, nk, 2 * (d > dv ? d : dv) + 16})) return SIZE_MAX;
   return ib::prepared_kv_bytes(batch, nk, d, dv, ib::attention_arm(precision));
 }
 
@@ -376,6 +408,8 @@ extern "C" int ib_attention_prepare(const float* k, const float* v, size_t batch
   using namespace ib;
   if (batch == 0) return 0;
   if (!k || !v) return fail("ib_attention_prepare: null pointer");
+  if (too_many_elements({batch, nk, 2 * (d > dv ? d : dv) + 16}))
+    return fail("ib_attention_prepare: extents too large (an element count does not fit size_t)");
   if (nk == 0 || !attention_shape_ok(d, dv))
     return fail("ib_attention_prepare: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
   if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO ||
@@ -390,6 +424,7 @@ extern "C" int ib_attention_prepare(const float* k, const float* v, size_t batch
 }
 
 extern "C" size_t ib_attention_run_workspace_bytes(size_t batch, size_t nq, size_t nk, size_t dv) {
+  if (ib::too_many_elements({batch, nq, nk})) return SIZE_MAX;
   return ib::carve_bytes(ib::attention_tcgen05_partial_floats(batch, nq, nk, dv, nullptr));
 }
 
@@ -399,6 +434,8 @@ extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, 
   using namespace ib;
   if (batch == 0 || nq == 0) return 0;
   if (!q || !prepared || !o) return fail("ib_attention_run: null pointer");
+  if (too_many_elements({batch, nq, nk}) || too_many_elements({batch, nk, 2 * (d > dv ? d : dv) + 16}))
+    return fail("ib_attention_run: extents too large (an element count does not fit size_t)");
   if (nk == 0 || !attention_shape_ok(d, dv))
     return fail("ib_attention_run: shape outside the fused kernel's range (d % 4 == 0, d and dv <= 128)");
   if (precision == IB_PRECISION_FP32 || precision < IB_PRECISION_AUTO ||

@@ -247,23 +247,26 @@ template <int BN, Kind KIND>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
            size_t n, size_t k, cudaStream_t s, const float* row_scale = nullptr,
            const float* col_scale = nullptr, bool f16_operands = false) {
-  static bool configured = false;
-  if (!configured) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail("ib_contract: cannot identify the current device");
+  // The opt-in to more than 48 KB of dynamic shared memory is per device (and per instantiation).
+  static OncePerDevice configured;
+  const int rc = configured.run(dev, [] {
     cudaError_t err = cudaFuncSetAttribute(gemm_tf32_kernel<BN, KIND>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Smem<BN>::kTotal);
     if (err != cudaSuccess)
       return fail(std::string("ib_contract: cannot reserve shared memory: ") +
                   cudaGetErrorString(err));
-    configured = true;
-  }
+    return 0;
+  });
+  if (rc == -2) return fail("ib_contract: cannot identify the current device");
+  if (rc != 0) return rc;
   int* status = device_status_word(s);
   if (!status) return fail("ib_contract: cannot allocate the device status word");
   const size_t tiles = ((m + kBM - 1) / kBM) * ((n + BN - 1) / BN) * batch;
   int sms = kNumSMs;
-  int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess)
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = static_cast<int>(tiles < static_cast<size_t>(sms) ? tiles : sms);
   gemm_tf32_kernel<BN, KIND><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
       map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),

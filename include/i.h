@@ -16,6 +16,11 @@
  *  - tensors are dense row-major float32; `data` may be a host pointer (copied
  *    to the GPU and back inside the call) or a CUDA device pointer (used in
  *    place).  Inputs and outputs are borrowed for the duration of the call.
+ *    i_exec_into runs on a stream of the library's own, which is ordered behind
+ *    no stream of the caller: device operands must be complete when the call is
+ *    made (synchronise the stream that produced them first); the call returns
+ *    when the outputs are complete.  i_b200_exec_into (i_b200.h) takes the
+ *    caller's stream instead and needs no such synchronisation.
  *  - i_exec_into and i_exec run on the GPU and fail with an i_error() message
  *    when no CUDA device is usable; there is no CPU fallback.
  */

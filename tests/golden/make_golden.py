@@ -34,7 +34,7 @@ def attention_case(name, seed, nq, nk, d, dv, scale=True):
 def main():
     if not oracle.have_reference():
         raise SystemExit("oracle/_ref is not built; run `make -C oracle` with the reference present")
-    # BASELINE config 1: README attention, 128x64, seed 0, Q pre-scaled by 1/sqrt(64).
+    # The reference README attention, 128x64, seed 0, Q pre-scaled by 1/sqrt(64).
     attention_case("attention_cfg1_128x64_seed0", 0, 128, 128, 64, 64)
     # Ragged in every extent (tail guards of the 16-wide tiles).
     attention_case("attention_ragged_100x40_seed5", 5, 100, 77, 40, 24)

@@ -13,7 +13,8 @@ import numpy as np
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE_PY = "/root/reference/ilang-python"
+# The reference's own front-end scripts, put there unmodified by `make -C oracle frontend`.
+REFERENCE_PY = os.path.join(ROOT, "baseline", "_ref", "ilang-python")
 
 
 def graph_of(component):
@@ -527,7 +528,8 @@ def test_precision_switch(ilang):
         c.set_precision("fp64")
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_PY), reason="reference checkout absent")
+@pytest.mark.skipif(not os.path.isfile(os.path.join(REFERENCE_PY, "ilang.py")),
+                    reason="the reference's front-end has not been fetched (make -C oracle frontend)")
 def test_unmodified_reference_frontend_binds_this_library(ilang):
     """The reference's own ilang.py, selected by ILANG_CORE_LIB, builds and
     compiles the README attention against this library (no exec without a GPU)."""

@@ -412,7 +412,7 @@ def test_reduce_rejects_non_reducible(lib, oracle, torch):
                                    (8, 8192), (3, 16384), (2, 20001), (1, 1), (5, 12000), (3, 20000),
                                    (2, 32768), (2, 40000)])
 def test_row_softmax(lib, oracle, torch, shape):
-    x = 2.0 * rand(shape, 10)                        # N(0, 4) like BASELINE config 2
+    x = 2.0 * rand(shape, 10)                        # N(0, 4), the published row-softmax case
     d = dev(torch, x)
     y = torch.empty_like(d)
     ok(lib, lib.ib_row_softmax(d.data_ptr(), y.data_ptr(), shape[0], shape[1], None))
@@ -562,7 +562,7 @@ def test_contract_tf32_batched(lib, oracle, torch):
 
 
 def test_contract_config3_sample_and_checksum(lib, oracle, torch):
-    # BASELINE config 3: A, B 8192x4096 U(-1,1) seed 2 -> C 8192x8192 on the TF32 arm.
+    # The published mm_t case: A, B 8192x4096 U(-1,1) seed 2 -> C 8192x8192 on the TF32 arm.
     rng = np.random.default_rng(2)
     a = 2 * rng.random((8192, 4096), dtype=np.float32) - 1
     b = 2 * rng.random((8192, 4096), dtype=np.float32) - 1
@@ -845,7 +845,7 @@ def test_attention_large_scores_stay_finite(lib, oracle, torch):
 
 
 def test_attention_config4_sample_and_checksum(lib, oracle, torch):
-    # BASELINE config 4: seq 16384, d 128, N(0,1) seed 3, Q scaled by 1/sqrt(128).
+    # The headline attention case: seq 16384, d 128, N(0,1) seed 3, Q scaled by 1/sqrt(128).
     rng = np.random.default_rng(3)
     q = rng.standard_normal((16384, 128), dtype=np.float32)
     k = rng.standard_normal((16384, 128), dtype=np.float32)

@@ -1,0 +1,60 @@
+"""Host-side checks of the kernel library that need no GPU: extents whose element counts do not
+fit size_t are refused before anything is launched, and kernel attributes are set once per device."""
+import ctypes
+
+import pytest
+
+from conftest import last_error
+
+SIZE_MAX = ctypes.c_size_t(-1).value
+FP32, AUTO, TF32 = 1, 0, 2
+
+
+def declare(lib):
+    sz, ci, vp = ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p
+    lib.ib_attention_workspace_bytes.restype = sz
+    lib.ib_attention_workspace_bytes.argtypes = [sz, sz, sz, sz, sz, ci, ci]
+    lib.ib_contract_workspace_bytes.restype = sz
+    lib.ib_contract_workspace_bytes.argtypes = [sz] * 4 + [ci] * 3
+    lib.ib_attention.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, ci, ci, sz, vp, sz, vp]
+    lib.ib_attention_static.argtypes = [vp, vp, vp, vp, sz, sz, sz, sz, sz, ci, vp]
+    lib.ib_contract.argtypes = [vp, vp, vp, sz, sz, sz, sz, ci, ci, ci, vp, sz, vp]
+    lib.ib_attention_run_workspace_bytes.restype = sz
+    lib.ib_attention_run_workspace_bytes.argtypes = [sz] * 4
+    lib.ib_selftest_once_per_device.restype = ci
+    lib.ib_selftest_once_per_device.argtypes = [ci, ci, ci]
+
+
+# batch * nq * nk = 2^62 floats: times four bytes that wraps to zero.
+WRAPPING = (2048, 1 << 21, 1 << 30, 1, 1)
+
+
+@pytest.mark.parametrize("precision", [FP32, AUTO, TF32])
+def test_workspace_size_of_wrapping_extents_is_unsatisfiable(lib, precision):
+    declare(lib)
+    batch, nq, nk, d, dv = WRAPPING
+    assert lib.ib_attention_workspace_bytes(batch, nq, nk, d, dv, 0, precision) == SIZE_MAX
+    assert lib.ib_attention_run_workspace_bytes(batch, nq, nk, dv) == SIZE_MAX
+    assert lib.ib_contract_workspace_bytes(1 << 22, 1 << 21, 1 << 21, 4, 0, 0, precision) == SIZE_MAX
+    # Ordinary extents are unaffected.
+    assert 0 < lib.ib_attention_workspace_bytes(1, 16384, 16384, 128, 128, 0, AUTO) < 1 << 30
+
+
+def test_entry_points_refuse_wrapping_extents_before_touching_the_gpu(lib):
+    declare(lib)
+    batch, nq, nk, d, dv = WRAPPING
+    fake = ctypes.c_void_p(256)            # never dereferenced: the refusal comes first
+    rc = lib.ib_attention(fake, fake, fake, fake, batch, nq, nk, d, dv, 0, FP32, 0, fake, 1 << 25, None)
+    assert rc == -1 and "extents too large" in last_error(lib)
+    rc = lib.ib_attention_static(fake, fake, fake, fake, batch, nq, nk, d, dv, 0, None)
+    assert rc == -1 and "extents too large" in last_error(lib)
+    rc = lib.ib_contract(fake, fake, fake, 1 << 22, 1 << 21, 1 << 21, 4, 1, 1, FP32, None, 0, None)
+    assert rc == -1 and "extents too large" in last_error(lib)
+
+
+def test_kernel_attributes_are_set_once_per_device(lib):
+    declare(lib)
+    assert lib.ib_selftest_once_per_device(4, 5, 0) == 4          # once each, however many calls
+    assert lib.ib_selftest_once_per_device(8, 3, 0) == 8
+    assert lib.ib_selftest_once_per_device(4, 5, 2) == 12         # two failures are retried, then once
+    assert lib.ib_selftest_once_per_device(3, 1, 2) == 3          # a failure is not remembered as done

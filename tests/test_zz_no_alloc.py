@@ -79,3 +79,28 @@ def test_static_scratch_attention_refuses_oversize(lib):
     assert rc == -1
     msg = last_error(lib)
     assert "built-in array holds 33554432" in msg and "use ib_attention" in msg
+
+
+def test_static_scratch_attention_allocates_nothing_once_set_up(lib):
+    """After the first call on a device (which loads the module that holds the array and may
+    reserve it then), a call leaves the device's free memory exactly where it was."""
+    import torch
+    declare(lib)
+    q = torch.randn(1, 256, 64, device="cuda")
+    k = torch.randn(1, 512, 64, device="cuda")
+    v = torch.randn(1, 512, 32, device="cuda")
+    o = torch.empty(1, 256, 32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = lib.ib_attention_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, 256, 512,
+                                     64, 32, 0, stream)
+        assert rc == 0, last_error(lib)
+        torch.cuda.synchronize()
+
+    call()                                   # set-up call
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
