@@ -662,19 +662,29 @@ std::string Plan::describe() const {
       }
     }
     if (s.kind == StepKind::Attention || s.kind == StepKind::Contract) {
-      const size_t row_tile = 128, col_tile = s.kind == StepKind::Attention ? 128 : 256;
-      os << "    tiles: " << row_tile << " rows x " << col_tile
-         << (s.kind == StepKind::Attention ? " keys per step, K/V ring of 3 x 64 KB"
-                                            : " columns x 32 deep, 4-stage TMA ring");
-      auto fits = [](size_t tile, size_t granule) { return granule == 0 || tile % granule == 0; };
-      if (fits(row_tile, s.hint.row_split) && fits(col_tile, s.hint.col_split))
-        os << "; whole multiples of the schedule's granules\n";
-      else
-        os << "; the schedule's granules do not divide them, results are unaffected\n";
+      const Geometry g = choose_geometry(s.kind, s.hint);
+      os << "    geometry: 128 rows x ";
+      if (s.kind == StepKind::Attention) {
+        os << "128 keys per step; a row block's key range ";
+        if (g.kv_granule == Geometry::kNever)
+          os << "stays on one SM (row axis outermost in the schedule), no merge kernel\n";
+        else
+          os << "may be divided between SMs at multiples of "
+             << (g.kv_granule ? (g.kv_granule + 127) / 128 * 128 : size_t(128)) << " keys"
+             << (g.kv_granule ? " (the schedule's key split)\n" : "\n");
+      } else {
+        if (g.col_tile) os << g.col_tile << " columns (the schedule's column split)";
+        else os << "128 or 256 columns by the output's width";
+        os << " x 32 deep, 4-stage TMA ring; tiles walked ";
+        if (g.col_group == Geometry::kNever) os << "row by row (row axis outermost in the schedule)\n";
+        else os << "in groups of 12 column tiles\n";
+      }
     }
     if (s.hint.row_split || s.hint.col_split || s.hint.staged)
       os << "    schedule: row granule " << s.hint.row_split << ", column granule "
-         << s.hint.col_split << ", " << (s.hint.reduce_outer ? "reduced-axis tiles outermost" : "row tiles outermost")
+         << s.hint.col_split << ", "
+         << (s.hint.reduce_outer ? (s.kind == StepKind::Contract ? "column tiles outermost" : "reduced-axis tiles outermost")
+                                 : "row tiles outermost")
          << ", " << (s.hint.staged ? "producers staged (fused)" : "producers materialised") << "\n";
     os << "    nodes:";
     for (size_t n : s.nodes) os << " n" << n;
@@ -684,6 +694,20 @@ std::string Plan::describe() const {
   for (const auto& o : outputs) os << " " << buffer_name(o);
   os << "\n";
   return os.str();
+}
+
+Geometry choose_geometry(StepKind kind, const ScheduleHint& hint) {
+  Geometry g;
+  const bool scheduled = hint.row_split != 0 || hint.col_split != 0;
+  if (!scheduled) return g;
+  if (kind == StepKind::Contract) {
+    if (hint.col_split >= 256) g.col_tile = 256;
+    else if (hint.col_split >= 128) g.col_tile = 128;
+    if (!hint.reduce_outer) g.col_group = Geometry::kNever;   // row axis outermost: row by row
+  } else if (kind == StepKind::Attention) {
+    g.kv_granule = hint.reduce_outer ? hint.col_split : Geometry::kNever;
+  }
+  return g;
 }
 
 std::string describe_graph(const Graph& g) {

@@ -50,6 +50,26 @@ struct ScheduleHint {
   bool staged = false;         // producers are staged into the consumer's loops
 };
 
+// What the schedule segment decides about a tensor-core kernel's geometry (zeros: the kernel's
+// own choice, which is what a component without a schedule gets).  The reference turns splits and
+// loop order into its loop nest (compiler/src/lower/node_to_stage.rs:593-692); here they select
+// among the geometries the kernels have:
+//   Contract   col_tile   output columns per tile: a column split of 256 or more asks for 256,
+//                         one in [128, 256) for 128; finer splits than any MMA tile leave it open
+//              col_group  column tiles per raster group: with the row axis outermost in the loop
+//                         order the tiles are walked row by row (every column tile in one group),
+//                         with the column axis outermost in column groups of 12
+//   Attention  kv_granule keys: with the key axis outermost, the key range of a block of query
+//                         rows may be divided between SMs at multiples of the key split (rounded
+//                         up to 128-key tiles); with the row axis outermost a row block's keys
+//                         stay on one SM (kNever) and no merge kernel runs
+struct Geometry {
+  static constexpr size_t kNever = static_cast<size_t>(-1);
+  size_t col_tile = 0, col_group = 0, kv_granule = 0;
+};
+Geometry choose_geometry(StepKind kind, const ScheduleHint& hint);
+
+
 // One operator of a MapChain.  Operand codes: kChainNone (unary form), kChainPrev (the result of
 // the operator before it), or an index into Step::in.
 constexpr int kChainNone = -1;

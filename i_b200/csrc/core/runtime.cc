@@ -452,8 +452,11 @@ int run_contract(const Step& step, const std::vector<size_t>& extent, DeviceBuff
     set_error(*err);
     return -1;
   }
-  return ib_contract(a, b, out, batch, m, n, k, a_kmajor, b_kmajor, precision, ws, ws_bytes,
-                     dev.stream);
+  // A result stored [n][m] swaps the roles of the two output axes, and with them what the
+  // schedule said about rows and columns; the geometry is then left to the kernel.
+  const Geometry g = f.swap_out ? Geometry{} : choose_geometry(StepKind::Contract, step.hint);
+  return ib_contract_tiled(a, b, out, batch, m, n, k, a_kmajor, b_kmajor, precision, g.col_tile,
+                           g.col_group, ws, ws_bytes, dev.stream);
 }
 
 int run_attention(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev, float* out,
@@ -474,7 +477,8 @@ int run_attention(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev
   const float* scale = step.in.size() == 4 ? dev.get(step.in[3].buffer) : nullptr;
   return ib_attention_scaled(dev.get(step.in[0].buffer), dev.get(step.in[1].buffer),
                              dev.get(step.in[2].buffer), out, dims.batch, dims.nq, dims.nk, dims.d,
-                             dims.dv, dims.v_kmajor, precision, step.hint.col_split, scale,
+                             dims.dv, dims.v_kmajor, precision,
+                             choose_geometry(StepKind::Attention, step.hint).kv_granule, scale,
                              step.op == Op::Div, ws, ws_bytes, dev.stream);
 }
 
@@ -761,7 +765,9 @@ int pipelined_host_attention(const i_program* program, const ShapeTable& shapes,
         if (rc == 0)
           rc = ib_attention(dq + h0 * q_floats, dk + h0 * k_floats, dv + h0 * v_floats,
                             dout + h0 * o_floats, heads, dims.nq, dims.nk, dims.d, dims.dv,
-                            dims.v_kmajor, precision, step.hint.col_split, ws, ws_bytes, stream);
+                            dims.v_kmajor, precision,
+                            choose_geometry(StepKind::Attention, step.hint).kv_granule, ws, ws_bytes,
+                            stream);
         signal(stream, side->out, "ordering a download");
         ok(cudaMemcpyAsync(ho + h0 * o_floats, dout + h0 * o_floats, heads * o_floats * f,
                            cudaMemcpyDeviceToHost, side->out), "downloading O");

@@ -119,7 +119,9 @@ struct Params {
   int kv_tiles;        // 128-key tiles per head
   int ctas;               // G
   int full_waves;         // whole row tiles every CTA takes before the tail
-  long long iters_base;   // tail (row tile, key tile) pairs per CTA: CTA g takes iters_base, plus
+  int coarse;          // key tiles per granule: a row tile's keys are divided among CTAs only at
+  int kv_coarse;       // multiples of it; kv_coarse = granules per row tile (the last may be short)
+  long long iters_base;   // tail (row tile, granule) pairs per CTA: CTA g takes iters_base, plus
   int iters_rem;          // one more when g < iters_rem
   const float* v_scale;   // mixed arm: V^T holds V / v_scale[head] (a power of two); else null
   const float* k_tile_scale;  // fp16 arm: K holds K / k_tile_scale[head][key tile] (powers of two)
@@ -165,8 +167,8 @@ struct Piece {
 struct PieceCursor {
   int wave;
   int tail_unit;     // row tile (within the tail) of the next piece
-  int kv_lo;         // its first key tile
-  int remaining;     // (row tile, key tile) pairs of the tail still to hand out
+  int kv_lo;         // its first granule of key tiles
+  int remaining;     // (row tile, granule) pairs of the tail still to hand out
   bool first;
 };
 
@@ -175,8 +177,8 @@ __device__ __forceinline__ PieceCursor pieces_begin(const Params& p) {
   const int g = static_cast<int>(blockIdx.x);
   c.wave = 0;
   const long long lo = g * p.iters_base + min(g, p.iters_rem);
-  c.tail_unit = static_cast<int>(lo / p.kv_tiles);
-  c.kv_lo = static_cast<int>(lo - static_cast<long long>(c.tail_unit) * p.kv_tiles);
+  c.tail_unit = static_cast<int>(lo / p.kv_coarse);
+  c.kv_lo = static_cast<int>(lo - static_cast<long long>(c.tail_unit) * p.kv_coarse);
   c.remaining = static_cast<int>(p.iters_base) + (g < p.iters_rem ? 1 : 0);
   c.first = true;
   return c;
@@ -195,14 +197,15 @@ __device__ __forceinline__ bool next_piece(const Params& p, PieceCursor& c, Piec
   }
   if (c.remaining <= 0) return false;
   out.unit = p.full_waves * p.ctas + c.tail_unit;
-  out.kv_lo = c.kv_lo;
-  out.n_kv = min(p.kv_tiles - c.kv_lo, c.remaining);
-  out.whole = out.kv_lo == 0 && out.n_kv == p.kv_tiles;
+  const int granules = min(p.kv_coarse - c.kv_lo, c.remaining);
+  out.kv_lo = c.kv_lo * p.coarse;
+  out.n_kv = min(p.kv_tiles - out.kv_lo, granules * p.coarse);
+  out.whole = c.kv_lo == 0 && granules == p.kv_coarse;
   out.ordinal = c.first ? 0 : 1;
   c.first = false;
-  c.remaining -= out.n_kv;
-  c.kv_lo += out.n_kv;
-  if (c.kv_lo == p.kv_tiles) {
+  c.remaining -= granules;
+  c.kv_lo += granules;
+  if (c.kv_lo == p.kv_coarse) {
     c.kv_lo = 0;
     ++c.tail_unit;
   }
@@ -1650,9 +1653,9 @@ struct CombineArgs {
   const float* part_m;
   const float* part_l;
   float* o;
-  int nq, dv, q_tiles, kv_tiles, ctas;
+  int nq, dv, q_tiles, kv_tiles, ctas;   // kv_tiles: granules per row tile (Params::kv_coarse)
   int first_tail_unit;     // row tiles before it were taken whole
-  long long iters_base;    // the tail's flat (row tile, key tile) sequence, cut as in the main kernel
+  long long iters_base;    // the tail's flat (row tile, granule) sequence, cut as in the main kernel
   int iters_rem;
 };
 
@@ -1758,13 +1761,21 @@ attention_combine_kernel(const CombineArgs a) {
 unsigned long long* g_attention_profile = nullptr;
 
 // Number of CTAs for a call: one per SM, fewer when there is too little work to
-// give each at least two key tiles.
-int choose_ctas(long long units, long long kv_tiles, int sms) {
+// give each at least two key tiles, or one granule at which a row tile's keys may be divided.
+int choose_ctas(long long units, long long kv_tiles, long long kv_coarse, int sms) {
   if (units >= sms) return sms;
   long long g = units * kv_tiles / 2;
+  if (g > units * kv_coarse) g = units * kv_coarse;
   if (g < 1) g = 1;
   if (g > sms) g = sms;
   return static_cast<int>(g);
+}
+
+// Key tiles per granule for a caller's granule in keys (0 = one tile; never more than a row's).
+long long granule_tiles(size_t kv_granule, long long kv_tiles) {
+  long long t = kv_granule == 0 ? 1 : static_cast<long long>((kv_granule - 1) / kBKV + 1);
+  if (kv_granule > static_cast<size_t>(kv_tiles) * kBKV) t = kv_tiles;
+  return t < 1 ? 1 : (t > kv_tiles ? kv_tiles : t);
 }
 
 // SMs the persistent kernel leaves free (for a communication kernel running next to it).
@@ -1794,7 +1805,8 @@ int reserved_sms() { return g_reserved_sms.load(); }
 size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size_t dv, int* ctas_out) {
   const long long units = static_cast<long long>((nq + kBQ - 1) / kBQ) * static_cast<long long>(batch);
   const long long kv_tiles = static_cast<long long>((nk + kBKV - 1) / kBKV);
-  const int ctas = choose_ctas(units, kv_tiles, device_sms());
+  // The finest division (one key tile) gives the most CTAs: the size below serves every granule.
+  const int ctas = choose_ctas(units, kv_tiles, kv_tiles, device_sms());
   if (ctas_out) *ctas_out = ctas;
   // Two pieces per CTA (the ends of its range), 128 rows each, O plus (m, l).
   return static_cast<size_t>(2) * ctas * kBQ * (dv + 2);
@@ -1804,7 +1816,7 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
                       AttentionArm arm, const float* v_scale, const float* k_tile_scale,
                       const float* logit_scale, bool logit_divide, bool follows_prepare,
-                      float* partials, cudaStream_t s) {
+                      float* partials, size_t kv_granule, cudaStream_t s) {
   const bool f16 = arm == AttentionArm::F16;
   const bool bf16 = arm == AttentionArm::BF16 || f16;      // K is 16-bit
   const bool mixed = arm == AttentionArm::MIXED || f16;    // V^T is fp16 over per-head scales
@@ -1855,14 +1867,17 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   p.batch = static_cast<int>(batch);
   p.q_tiles = static_cast<int>((nq + kBQ - 1) / kBQ);
   p.kv_tiles = static_cast<int>((nk + kBKV - 1) / kBKV);
-  int ctas = 1;
-  attention_tcgen05_partial_floats(batch, nq, nk, dv, &ctas);
   if (!partials) return fail("ib_attention: workspace for partial results is missing");
   const long long units = static_cast<long long>(p.q_tiles) * p.batch;
+  // Where a row tile's key range may be cut between CTAs: at multiples of the caller's granule
+  // (whole 128-key tiles); a granule of the whole range or more means never.
+  p.coarse = static_cast<int>(granule_tiles(kv_granule, p.kv_tiles));
+  p.kv_coarse = (p.kv_tiles + p.coarse - 1) / p.coarse;
+  const int ctas = choose_ctas(units, p.kv_tiles, p.kv_coarse, device_sms());
   p.ctas = ctas;
   p.full_waves = static_cast<int>(units / ctas);
   const long long tail_units = units - static_cast<long long>(p.full_waves) * ctas;
-  const long long tail_iters = tail_units * p.kv_tiles;
+  const long long tail_iters = tail_units * p.kv_coarse;
   p.iters_base = tail_iters / ctas;
   p.iters_rem = static_cast<int>(tail_iters % ctas);
   p.o = o;
@@ -1926,8 +1941,8 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
     return fail(std::string("ib_attention (tcgen05): launch failed: ") + cudaGetErrorString(launched));
   count_launch();
   // Tail row tiles shared by several CTA ranges exist unless the ranges fall on tile boundaries.
-  if (tail_units > 0 && !(p.iters_rem == 0 && p.iters_base % p.kv_tiles == 0)) {
-    CombineArgs a{p.part_o, p.part_m, p.part_l, o, p.nq, p.dv, p.q_tiles, p.kv_tiles, ctas,
+  if (tail_units > 0 && !(p.iters_rem == 0 && p.iters_base % p.kv_coarse == 0)) {
+    CombineArgs a{p.part_o, p.part_m, p.part_l, o, p.nq, p.dv, p.q_tiles, p.kv_coarse, ctas,
                   p.full_waves * ctas, p.iters_base, p.iters_rem};
     cfg.numAttrs = g_dependent_launch ? 1 : 0;
     cfg.gridDim = dim3(static_cast<unsigned>(tail_units * 8));

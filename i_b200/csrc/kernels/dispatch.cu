@@ -215,7 +215,20 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
 extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batch, size_t m,
                            size_t n, size_t k, int a_kmajor, int b_kmajor, int precision,
                            void* workspace, size_t workspace_bytes, void* stream) {
+  return ib_contract_tiled(a, b, c, batch, m, n, k, a_kmajor, b_kmajor, precision, 0, 0, workspace,
+                           workspace_bytes, stream);
+}
+
+extern "C" int ib_contract_tiled(const float* a, const float* b, float* c, size_t batch, size_t m,
+                                 size_t n, size_t k, int a_kmajor, int b_kmajor, int precision,
+                                 size_t col_tile, size_t col_group, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
   using namespace ib;
+  if (col_tile != 0 && col_tile != 128 && col_tile != 256)
+    return fail("ib_contract: col_tile must be 0, 128 or 256");
+  GemmGeometry geometry;
+  geometry.col_tile = static_cast<int>(col_tile);
+  geometry.group_n = static_cast<int>(col_group > (1u << 20) ? (1u << 20) : col_group);
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!a || !b || !c) return fail("ib_contract: null pointer");
   if (too_many_elements({batch, m, k}) || too_many_elements({batch, n, k}) ||
@@ -262,7 +275,7 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
     }
     if (int rc = convert_f16_rows_scaled(ak, a16, a_scale, batch * m, k, kp, s)) return rc;
     if (int rc = convert_f16_rows_scaled(bk, b16, b_scale, batch * n, k, kp, s)) return rc;
-    return gemm_tcgen05_f16(a16, b16, a_scale, b_scale, c, batch, m, n, k, kp, s);
+    return gemm_tcgen05_f16(a16, b16, a_scale, b_scale, c, batch, m, n, k, kp, s, geometry);
   }
   if (precision == IB_PRECISION_BF16) {
     if (reinterpret_cast<uintptr_t>(workspace) & 255u)
@@ -289,7 +302,7 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
     }
     if (int rc = convert_bf16_rows(ak, a16, batch * m, k, kp, s)) return rc;
     if (int rc = convert_bf16_rows(bk, b16, batch * n, k, kp, s)) return rc;
-    return gemm_tcgen05_bf16(a16, b16, c, batch, m, n, k, kp, s);
+    return gemm_tcgen05_bf16(a16, b16, c, batch, m, n, k, kp, s, geometry);
   }
   if (wants_tensor(precision, flop) && contract_shape_ok(k)) {
     Carver ws(workspace, workspace_bytes);
@@ -307,7 +320,8 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
       if (int rc = transpose_batched(b, t, batch, k, n, k, false, s)) return rc;   // [k][n] -> [n][k]
       bk = t;
     }
-    if (gemm_tcgen05_supported(ak, bk, c, m, n, k)) return gemm_tcgen05(ak, bk, c, batch, m, n, k, s);
+    if (gemm_tcgen05_supported(ak, bk, c, m, n, k))
+      return gemm_tcgen05(ak, bk, c, batch, m, n, k, s, geometry);
     // Misaligned base pointers: the fp32 arm takes any layout.
     return contract_simt(ak, bk, c, batch, m, n, k, true, true, s);
   }
@@ -342,7 +356,6 @@ extern "C" int ib_attention_scaled(const float* q, const float* k, const float* 
                                    const float* logit_scale, int logit_divide, void* workspace,
                                    size_t workspace_bytes, void* stream) {
   using namespace ib;
-  (void)kv_tile;
   if (batch == 0 || nq == 0 || dv == 0) return 0;
   if (!q || !k || !v || !o) return fail("ib_attention: null pointer");
   if (nk == 0 || d == 0) return fail("ib_attention: empty key or feature axis");
@@ -368,7 +381,7 @@ extern "C" int ib_attention_scaled(const float* q, const float* k, const float* 
       return fail("ib_attention: workspace too small (see ib_attention_workspace_bytes)");
     return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch,
                              kv.arm, kv.v_scale, kv.k_tile_scale, logit_scale, logit_divide != 0, true,
-                             partials, s);
+                             partials, kv_tile, s);
   }
 
   float* scores = ws.take(batch * nq * nk);
@@ -454,7 +467,7 @@ extern "C" int ib_attention_run(const float* q, const void* prepared, float* o, 
   if (!partials)
     return fail("ib_attention_run: workspace too small (see ib_attention_run_workspace_bytes)");
   return attention_tcgen05(q, kv.k, kv.vt, o, batch, nq, nk, d, dv, kv.d_pitch, kv.nk_pitch, kv.arm,
-                           kv.v_scale, kv.k_tile_scale, nullptr, false, false, partials,
+                           kv.v_scale, kv.k_tile_scale, nullptr, false, false, partials, 0,
                            static_cast<cudaStream_t>(stream));
 }
 

@@ -27,7 +27,7 @@ using namespace sm100;
 constexpr int kBM = 128;
 constexpr int kBK = 32;            // fp32 per 128-byte swizzled row
 constexpr int kStages = 4;
-constexpr int kGroupN = 12;        // n-tiles per raster group
+constexpr int kGroupN = 12;        // n-tiles per raster group unless the caller's geometry says otherwise
 constexpr int kThreads = 192;
 
 template <int BN>
@@ -43,18 +43,21 @@ struct TileCoord {
   int batch, m_tile, n_tile;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(long long id, int tiles_m, int tiles_n) {
+// Tiles are walked in groups of `group_n` column tiles: all row tiles of a group (row tile
+// outer, the group's column tiles inner) before the next group.  group_n = 1 walks column by
+// column, group_n >= tiles_n row by row.
+__device__ __forceinline__ TileCoord tile_coord(long long id, int tiles_m, int tiles_n, int group_n) {
   const long long per_batch = static_cast<long long>(tiles_m) * tiles_n;
   TileCoord t;
   t.batch = static_cast<int>(id / per_batch);
   long long within = id - t.batch * per_batch;
-  const long long group_span = static_cast<long long>(tiles_m) * kGroupN;
+  const long long group_span = static_cast<long long>(tiles_m) * group_n;
   int group = static_cast<int>(within / group_span);
   long long in_group = within - group * group_span;
-  int width = tiles_n - group * kGroupN;
-  if (width > kGroupN) width = kGroupN;
+  int width = tiles_n - group * group_n;
+  if (width > group_n) width = group_n;
   t.m_tile = static_cast<int>(in_group / width);
-  t.n_tile = group * kGroupN + static_cast<int>(in_group % width);
+  t.n_tile = group * group_n + static_cast<int>(in_group % width);
   return t;
 }
 
@@ -66,7 +69,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  float* __restrict__ c, int m, int n, int k, int batch, int* status,
                  const float* __restrict__ row_scale, const float* __restrict__ col_scale,
-                 int f16_operands) {
+                 int f16_operands, int group_n) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -116,7 +119,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (long long id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
-        const TileCoord t = tile_coord(id, tiles_m, tiles_n);
+        const TileCoord t = tile_coord(id, tiles_m, tiles_n, group_n);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort, status, 101))) break;
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -178,7 +181,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     const bool vec_ok = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
     for (long long id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
-      const TileCoord t = tile_coord(id, tiles_m, tiles_n);
+      const TileCoord t = tile_coord(id, tiles_m, tiles_n, group_n);
       ok = mbar_wait(&acc_full[acc], acc_phase, abort, status, 104);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -245,7 +248,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 template <int BN, Kind KIND>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
-           size_t n, size_t k, cudaStream_t s, const float* row_scale = nullptr,
+           size_t n, size_t k, cudaStream_t s, int group_n, const float* row_scale = nullptr,
            const float* col_scale = nullptr, bool f16_operands = false) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail("ib_contract: cannot identify the current device");
@@ -270,7 +273,8 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t 
   const int grid = static_cast<int>(tiles < static_cast<size_t>(sms) ? tiles : sms);
   gemm_tf32_kernel<BN, KIND><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
       map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-      static_cast<int>(batch), status, row_scale, col_scale, f16_operands ? 1 : 0);
+      static_cast<int>(batch), status, row_scale, col_scale, f16_operands ? 1 : 0,
+      group_n > 0 ? group_n : kGroupN);
   return check_launch("ib_contract (tcgen05 tf32)");
 }
 
@@ -283,49 +287,54 @@ bool gemm_tcgen05_supported(const float* a, const float* b, const float* c, size
          m < (1u << 30) && n < (1u << 30) && k < (1u << 30);
 }
 
+// Column tile: the caller's choice (128 or 256) when it gives one, else by the output's width.
+static bool wide_tile(const GemmGeometry& g, size_t n) {
+  return g.col_tile ? g.col_tile > 128 : n > 128;
+}
+
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                 size_t k, cudaStream_t s) {
+                 size_t k, cudaStream_t s, GemmGeometry g) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!gemm_tcgen05_supported(a, b, c, m, n, k))
     return fail("ib_contract: shape or alignment not supported by the tensor-core arm");
   if (batch >= (1u << 30)) return fail("ib_contract: too many batch entries");
-  const bool wide = n > 128;
+  const bool wide = wide_tile(g, n);
   CUtensorMap map_a, map_b;
   if (int rc = make_tensor_map_f32(&map_a, a, batch, m, k, k, m * k, kBM)) return rc;
   if (int rc = make_tensor_map_f32(&map_b, b, batch, n, k, k, n * k, wide ? 256 : 128)) return rc;
-  return wide ? launch<256, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s)
-              : launch<128, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s);
+  return wide ? launch<256, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n)
+              : launch<128, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n);
 }
 
 int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
-                      size_t k, size_t k_pitch, cudaStream_t s) {
+                      size_t k, size_t k_pitch, cudaStream_t s, GemmGeometry g) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (k_pitch % 8 != 0 || k_pitch < k || !c || m >= (1u << 30) || n >= (1u << 30) ||
       k >= (1u << 30) || batch >= (1u << 30))
     return fail("ib_contract: shape not supported by the bf16 tensor-core arm");
-  const bool wide = n > 128;
+  const bool wide = wide_tile(g, n);
   CUtensorMap map_a, map_b;
   if (int rc = make_tensor_map_bf16(&map_a, a16, batch, m, k, k_pitch, m * k_pitch, kBM)) return rc;
   if (int rc = make_tensor_map_bf16(&map_b, b16, batch, n, k, k_pitch, n * k_pitch, wide ? 256 : 128))
     return rc;
-  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s)
-              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s);
+  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n)
+              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n);
 }
 
 int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, const float* b_scale,
                      float* c, size_t batch, size_t m, size_t n, size_t k, size_t k_pitch,
-                     cudaStream_t s) {
+                     cudaStream_t s, GemmGeometry g) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (k_pitch % 8 != 0 || k_pitch < k || !c || !a_scale || !b_scale || m >= (1u << 30) ||
       n >= (1u << 30) || k >= (1u << 30) || batch >= (1u << 30))
     return fail("ib_contract: shape not supported by the fp16 tensor-core arm");
-  const bool wide = n > 128;
+  const bool wide = wide_tile(g, n);
   CUtensorMap map_a, map_b;
   if (int rc = make_tensor_map_bf16(&map_a, a16, batch, m, k, k_pitch, m * k_pitch, kBM)) return rc;
   if (int rc = make_tensor_map_bf16(&map_b, b16, batch, n, k, k_pitch, n * k_pitch, wide ? 256 : 128))
     return rc;
-  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, a_scale, b_scale, true)
-              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, a_scale, b_scale, true);
+  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, a_scale, b_scale, true)
+              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, a_scale, b_scale, true);
 }
 
 }  // namespace ib

@@ -48,8 +48,15 @@ int check_device_status(const char* what, cudaStream_t s);
 // K-major fp32 fed to tcgen05 kind::tf32.
 bool gemm_tcgen05_supported(const float* a, const float* b, const float* c, size_t m, size_t n,
                             size_t k);
+// Tile geometry a caller may fix (zeros = the kernel's own choice): output columns per tile (128 or
+// 256), and how many column tiles form a group that is walked over all row tiles before the next
+// group (1 = column by column, at least the number of column tiles = row by row; default 12).
+struct GemmGeometry {
+  int col_tile = 0;
+  int group_n = 0;
+};
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                 size_t k, cudaStream_t s);
+                 size_t k, cudaStream_t s, GemmGeometry g = {});
 // Same contraction with bf16 operands a16 / b16 ([b][rows][k_pitch] bf16, k_pitch a multiple of 8)
 // fed to tcgen05 kind::f16, fp32 accumulation.
 // The same on fp16 operands stored over one power of two per row (a16[b][i][:] = A / a_scale[b][i],
@@ -57,9 +64,9 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
 // at the 16-bit issue rate.
 int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, const float* b_scale,
                      float* c, size_t batch, size_t m, size_t n, size_t k, size_t k_pitch,
-                     cudaStream_t s);
+                     cudaStream_t s, GemmGeometry g = {});
 int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
-                      size_t k, size_t k_pitch, cudaStream_t s);
+                      size_t k, size_t k_pitch, cudaStream_t s, GemmGeometry g = {});
 // out[r][c] = bf16(in[r][c]) (round to nearest even) for a [rows][cols] fp32 array; `out_pitch` in
 // elements, columns cols..out_pitch-1 are zeroed.
 // fp16 rows over one power of two each: out[r][c] = fp16(in[r][c] / scale[r]), scale[r] bringing the
@@ -80,13 +87,15 @@ size_t attention_tcgen05_partial_floats(size_t batch, size_t nq, size_t nk, size
 // O += P V in fp16 (same 10-bit mantissa); F16 — k fp16 holding K / k_tile_scale[head][key / 128]
 // ([b][nk][d_pitch], d_pitch % 8 == 0), vt as in MIXED: both contractions in fp16.  follows_prepare: the kernel before this call in the
 // stream is the one that wrote k and vt (the launch may then overlap its tail).  logit_scale: one
-// float on the device, or null; the logits are S * it, or S / it with logit_divide.
+// float on the device, or null; the logits are S * it, or S / it with logit_divide.  kv_granule:
+// a row tile's key range is divided between CTAs only at multiples of this many keys (rounded up
+// to whole 128-key tiles; 0 = one tile); nk or more = never divided, and no merge kernel runs.
 enum class AttentionArm { TF32, BF16, MIXED, F16 };
 int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, size_t batch,
                       size_t nq, size_t nk, size_t d, size_t dv, size_t d_pitch, size_t nk_pitch,
                       AttentionArm arm, const float* v_scale, const float* k_tile_scale,
                       const float* logit_scale, bool logit_divide, bool follows_prepare,
-                      float* partials, cudaStream_t s);
+                      float* partials, size_t kv_granule, cudaStream_t s);
 // Mixed-arm operand preparation: kr = K rounded to TF32; vt16[b][c][nk_pitch] = fp16(V^T / scale[b])
 // with scale[b] the power of two that brings the head's largest |V| into [2^14, 2^15); block_max
 // is scratch of batch * kAbsmaxBlocks floats.

@@ -550,3 +550,23 @@ def test_unmodified_reference_frontend_binds_this_library(ilang):
     env = dict(os.environ, ILANG_CORE_LIB=ilang.DEFAULT_LIB, PYTHONPATH=REFERENCE_PY)
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
     assert out.returncode == 0 and "bound" in out.stdout, out.stderr
+
+
+def test_schedule_segment_chooses_the_kernel_geometry(ilang):
+    """Splits and loop order reach the plan: i_code names the geometry each step will run with."""
+    i = ilang.i
+
+    def mm_t(split, order):
+        return i("ik*jk~ijk | %s | %s" % (split, order)) >> i("+ijk~ij | %s | %s0" % (split, order))
+
+    def geometry(component):
+        return re.search(r"^\s*geometry: (.*)$", component._code(), re.M).group(1)
+
+    plain = geometry(i("ik*jk~ijk") >> i("+ijk~ij"))
+    readme = geometry(mm_t("i:16,j:16", "jii'j'k"))
+    narrow = geometry(mm_t("i:128,j:128", "ijj'i'k"))
+    wide = geometry(mm_t("i:128,j:256", "jii'j'k"))
+    assert plain == readme                     # splits finer than any MMA tile leave the choice open
+    assert "128 columns (the schedule's column split)" in narrow and "row by row" in narrow
+    assert "256 columns (the schedule's column split)" in wide and "groups of 12" in wide
+    assert len({readme, narrow, wide}) == 3
