@@ -151,6 +151,7 @@ struct Shared {
   float half_max[2][2][kBQ]; // [iteration parity][warpgroup][row]
   float half_sum[2][kBQ];
   float quarter_sum[4][kBQ]; // pipelined kernel: the four column quarters' shares of a row sum
+  float q_absmax[4][kBQ];    // pipelined kernel: their shares of a Q row's largest magnitude
 };
 
 // One contiguous run of key tiles of one row tile.
@@ -932,14 +933,25 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
 // per warp on q_ready.  The fp16 arm stores the row over the power of two that brings its largest
 // magnitude into [2^14, 2^15) (every thread reads the whole row for that: 128 features, from L2).
 // Returns the factor that takes the row's S to exponent units, K's tile scale aside.
+__device__ __forceinline__ void softmax_all_sync() {
+  asm volatile("bar.sync 1, 512;" ::: "memory");
+}
+
+// Q of one piece into tensor memory, by the sixteen softmax warps of the pipelined kernel: thread
+// (q4, r) loads columns 32 q4 .. 32 q4 + 31 of row r (eight 16-byte loads, all in flight at once;
+// the producer has prefetched the rows into L2), and stores them packed to 16 bits.  On the fp16
+// arm the row's largest magnitude decides the power of two it is stored over; the four quarters
+// of a row meet through shared memory and the 512-thread barrier, which every softmax warp must
+// therefore reach: a warp that has given up (`idle`) comes here too and only skips the work.
 template <Arm ARM>
 __device__ __forceinline__ float stage_q_quarter(const Params& p, Shared* sh, uint32_t tmem_q, int head,
-                                                 int q_tile, int r, int q4, int lane, int piece) {
+                                                 int q_tile, int r, int q4, int lane, int piece,
+                                                 bool idle) {
   using G = Geometry<ARM>;
   float row_mul = kLog2E32;
   const long long row = static_cast<long long>(q_tile) * kBQ + r;
   const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
-  const bool live = row < p.nq;
+  const bool live = row < p.nq && !idle;
   const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
   // A scale on the logits is a scale on Q: (c q) . k = c (q . k).
   float qs = 1.0f;
@@ -947,45 +959,45 @@ __device__ __forceinline__ float stage_q_quarter(const Params& p, Shared* sh, ui
     qs = __ldg(p.logit_scale);
     if (p.logit_divide) qs = 1.0f / qs;
   }
-  auto load4 = [&](int col) {
-    float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float4 x[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int col = q4 * 32 + 4 * e;
+    x[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (live && vec && col + 4 <= p.d) {
-      x = *reinterpret_cast<const float4*>(qrow + col);
+      x[e] = *reinterpret_cast<const float4*>(qrow + col);
     } else if (live) {
-      if (col + 0 < p.d) x.x = qrow[col + 0];
-      if (col + 1 < p.d) x.y = qrow[col + 1];
-      if (col + 2 < p.d) x.z = qrow[col + 2];
-      if (col + 3 < p.d) x.w = qrow[col + 3];
+      if (col + 0 < p.d) x[e].x = qrow[col + 0];
+      if (col + 1 < p.d) x[e].y = qrow[col + 1];
+      if (col + 2 < p.d) x[e].z = qrow[col + 2];
+      if (col + 3 < p.d) x[e].w = qrow[col + 3];
     }
-    x.x *= qs; x.y *= qs; x.z *= qs; x.w *= qs;
-    return x;
-  };
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { x[e].x *= qs; x[e].y *= qs; x[e].z *= qs; x[e].w *= qs; }
   float inv = 1.0f;
   if (G::kScaledQk) {
     float m = 0.0f;
-#pragma unroll 1
-    for (int c = 0; c < 128; c += 16) {
-      float4 x[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) x[e] = load4(c + 4 * e);
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[e].x), fabsf(x[e].y)), fmaxf(fabsf(x[e].z), fabsf(x[e].w))));
-    }
+    for (int e = 0; e < 8; ++e)
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(x[e].x), fabsf(x[e].y)), fmaxf(fabsf(x[e].z), fabsf(x[e].w))));
+    sh->q_absmax[q4][r] = m;
+    softmax_all_sync();
+    m = fmaxf(fmaxf(sh->q_absmax[0][r], sh->q_absmax[1][r]), fmaxf(sh->q_absmax[2][r], sh->q_absmax[3][r]));
     const float scale = f16_range_scale(m);
     inv = 1.0f / scale;
     row_mul = kLog2E32 * scale;
   }
+  if (idle) return row_mul;
   uint32_t v[16];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    const float4 x = load4(q4 * 32 + 4 * e);
     if (G::kQkFmt == Fmt::F16) {
-      v[2 * e + 0] = pack_f16(x.x * inv, x.y * inv);
-      v[2 * e + 1] = pack_f16(x.z * inv, x.w * inv);
+      v[2 * e + 0] = pack_f16(x[e].x * inv, x[e].y * inv);
+      v[2 * e + 1] = pack_f16(x[e].z * inv, x[e].w * inv);
     } else {
-      v[2 * e + 0] = pack_bf16(x.x, x.y);
-      v[2 * e + 1] = pack_bf16(x.z, x.w);
+      v[2 * e + 0] = pack_bf16(x[e].x, x[e].y);
+      v[2 * e + 1] = pack_bf16(x[e].z, x[e].w);
     }
   }
   tmem_st_32x16(tmem_q + q4 * 16, v);
@@ -999,9 +1011,6 @@ __device__ __forceinline__ float stage_q_quarter(const Params& p, Shared* sh, ui
   return row_mul;
 }
 
-__device__ __forceinline__ void softmax_all_sync() {
-  asm volatile("bar.sync 1, 512;" ::: "memory");
-}
 // Named barriers with separate arriving and waiting sides (ids 2 .. 5 in the pipelined kernel).
 __device__ __forceinline__ void named_arrive(int id, int threads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -1464,7 +1473,22 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
       const bool whole = pc.whole;
       const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
 
-      if (piece == 0) row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, b, qt, r, q4, lane, 0);
+      if (piece == 0) row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, b, qt, r, q4, lane, 0, false);
+
+      // The piece after this one, whose Q is staged from inside the tile loop.
+      float next_row_mul = kLog2E32;
+      bool has_next = false;
+      int next_b = 0, next_qt = 0;
+      {
+        PieceCursor ahead = cursor;
+        Piece nx;
+        if (next_piece(p, ahead, nx)) {
+          has_next = true;
+          next_b = nx.unit / p.q_tiles;
+          next_qt = nx.unit - next_b * p.q_tiles;
+        }
+      }
+      const int stage_at = n_kv >= 2 ? n_kv - 2 : 0;
 
       float m_mine = -CUDART_INF_F;           // the reference maximum l is expressed against
       float l = 0.0f;                         // this quarter's share of the row sum
@@ -1485,6 +1509,16 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
           wait_s += tick<kProf>() - t0;
         }
         if (!dead && abort->flag) dead = true;
+        // Q of the next piece goes into tensor memory as soon as the last Q K^T of this one has
+        // completed, which is about two tiles before the softmax warps are done with the piece:
+        // the issuer then has the next piece's first tiles computed by the time they get there.
+        // Here, two tiles from the end, Q K^T of the last tile was issued when S of the tile
+        // before this one was read; the wait below is normally over before it starts.
+        if (jj == stage_at && has_next) {
+          const int last_t = it + n_kv - 1;
+          if (jj < n_kv - 1) wait_bar(&sh->s_full[last_t & 3], static_cast<uint32_t>((last_t >> 2) & 1), 217);
+          next_row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, next_b, next_qt, r, q4, lane, piece + 1, dead);
+        }
         if (dead) continue;
         tc_fence_after_sync();
         const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV + q4 * 32);
@@ -1602,20 +1636,7 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
         c_tail += tick<kProf>() - tp;
       }
 
-      // ---- end of the piece.  Every Q K^T of it has completed (its S was read above), so Q's
-      // columns may be restaged: Q of the next piece goes in before this one's epilogue, so that the
-      // Q K^T issuer can run the next piece's first tiles while O is being read out below.
       const int last = it + n_kv - 1;
-      float next_row_mul = kLog2E32;
-      {
-        PieceCursor ahead = cursor;
-        Piece nx;
-        if (!dead && next_piece(p, ahead, nx)) {
-          const int nb = nx.unit / p.q_tiles;
-          next_row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, nb, nx.unit - nb * p.q_tiles, r, q4, lane, piece + 1);
-        }
-      }
-
       finish_piece_quarter(p, sh, o_tmem, q4, r, row, b, whole, part_slot, l, m_mine,
                            &sh->pv_done[last & 3], static_cast<uint32_t>((last >> 2) & 1), dead);
       if (sh->give_up) break;
