@@ -836,12 +836,31 @@ def test_attention_two_phase_rejects_fp32_arm(lib, torch):
     assert lib.ib_attention_uses_tensor_arm(1, 16384, 16384, 130, 128, TF32) == 0
 
 
-def test_attention_large_scores_stay_finite(lib, oracle, torch):
-    # Unscaled Q: scores of magnitude ~ sqrt(d) * 4, the running maximum moves a lot.
+def round_to_tf32(x):
+    """fp32 -> nearest value with a 10-bit mantissa (ties to even), as the tensor arms store Q and K."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0xFFF + ((bits >> 13) & 1)) & ~np.uint64(0x1FFF)
+    return bits.astype(np.uint32).view(np.float32).reshape(np.shape(x))
+
+
+@pytest.mark.parametrize("precision", [TF32, TF32_F16, F16])
+def test_attention_large_scores_stay_finite(lib, oracle, torch, precision):
+    # Unscaled Q: logits up to ~ +-130, a peaky softmax whose running maximum moves a lot.  Two
+    # comparisons.  Against the reference arithmetic on the operands the tensor cores see (Q and K
+    # rounded to a 10-bit mantissa) the kernel has to meet the ordinary bound: what is left is its
+    # own work (fp32 accumulation order, P and V rounding, the exponential).  Against the reference
+    # on the unrounded operands the distance is dominated by the rounding of Q and K itself: a logit
+    # of magnitude 100 moves by up to 100 * 2^-11 = 0.05, i.e. its probability by 5 %, whatever the
+    # kernel does afterwards; that comparison only has to stay within 2e-2 of the output's peak.
     q, k, v = rand((256, 128), 21) * 3, rand((1024, 128), 22), rand((1024, 128), 23)
-    got = run_attention(lib, torch, q, k, v, TF32)
+    got = run_attention(lib, torch, q, k, v, precision)
     assert np.isfinite(got).all()
-    assert max_rel_to_peak(got, oracle.attention_fused(q, k, v)) <= 2e-2   # peaky softmax, TF32 scores
+    same_operands = max_rel_to_peak(got, oracle.attention_fused(round_to_tf32(q), round_to_tf32(k), v))
+    unrounded = max_rel_to_peak(got, oracle.attention_fused(q, k, v))
+    print("large scores, precision %d: %.2e against rounded operands, %.2e against unrounded"
+          % (precision, same_operands, unrounded))
+    assert same_operands <= TOL_TF32
+    assert unrounded <= 2e-2
 
 
 def test_attention_config4_sample_and_checksum(lib, oracle, torch):
