@@ -404,9 +404,9 @@ struct PrepareMixedArgs {
   __half* k16; float* k_tile_scale; size_t d, d_pitch, kv_tiles;
 };
 
-// fp16(V^T / scale[head]) — through 64x64 shared-memory tiles when V is [keys][dv], as plain rows
-// when it is already [dv][keys].  The per-head maxima come from the kernel before this one.
-__device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (*tile)[129],
+// fp16(V^T / scale[head]) — through shared memory in steps of 64 keys when V is [keys][dv], as plain
+// rows when it is already [dv][keys].  The per-head maxima come from the kernel before this one.
+__device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, uint32_t (*words)[32],
                                               float* scratch) {
   sm100::grid_dependency_wait();
   if (a.v_kmajor) {
@@ -440,8 +440,13 @@ __device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (
     }
     return;
   }
-  // 64 keys x all dv features per step: eight 16-byte loads in flight per thread, one barrier pair
-  // per 32 KB instead of per 16 KB.
+  // 64 keys x all dv features per step.  Warp w takes key pairs 4w .. 4w + 3 of the step; lane l
+  // loads features 4l .. 4l + 3 of both keys of a pair (two coalesced 512-byte rows), so eight
+  // 16-byte loads are in flight per thread.  A pair of keys of one feature is one fp16x2 word of
+  // V^T; it goes through shared memory as word [feature][pair ^ (feature / 4)]: the 32 lanes of a
+  // store (32 feature groups, one pair) and the 32 lanes of a read (one feature, 32 pairs) each
+  // hit 32 different banks.  A warp then writes a feature's 64 keys as one 128-byte line.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t tiles_k = (a.nk_pitch + 63) / 64;
   const size_t total = a.batch * tiles_k;
   const bool vec_in = a.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
@@ -457,14 +462,14 @@ __device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (
     if (k0 == 0 && threadIdx.x == 0) a.scale[b] = 1.0f / inv;   // the block with the head's first tile
     const float* src = a.v + b * a.nk * a.dv;
     __half* dst = a.vt16 + b * a.dv * a.nk_pitch;
+    const int c = lane * 4;                               // first feature of this lane's group
     float4 x[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      const int e = threadIdx.x + u * 256;
-      const int r = e >> 5, c = (e & 31) * 4;           // r: key, c: feature (contiguous in V)
+      const size_t key = k0 + static_cast<size_t>(2 * (warp * 4 + (u >> 1)) + (u & 1));
       x[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      if (k0 + r < a.nk && static_cast<size_t>(c) < a.dv) {
-        const float* row = src + (k0 + r) * a.dv + c;
+      if (key < a.nk && static_cast<size_t>(c) < a.dv) {
+        const float* row = src + key * a.dv + c;
         if (vec_in && static_cast<size_t>(c) + 4 <= a.dv) {
           x[u] = __ldcs(reinterpret_cast<const float4*>(row));
         } else {
@@ -476,22 +481,26 @@ __device__ __forceinline__ void prepare_v_f16(const PrepareMixedArgs& a, float (
       }
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int e = threadIdx.x + u * 256;
-      const int r = e >> 5, c = (e & 31) * 4;
-      tile[r][c + 0] = x[u].x * inv; tile[r][c + 1] = x[u].y * inv;
-      tile[r][c + 2] = x[u].z * inv; tile[r][c + 3] = x[u].w * inv;
+    for (int u = 0; u < 8; u += 2) {
+      const int pair = warp * 4 + (u >> 1);
+      const int col = pair ^ lane;                        // (feature / 4) & 31 == lane for all four
+      const __half2 w0 = __floats2half2_rn(x[u].x * inv, x[u + 1].x * inv);
+      const __half2 w1 = __floats2half2_rn(x[u].y * inv, x[u + 1].y * inv);
+      const __half2 w2 = __floats2half2_rn(x[u].z * inv, x[u + 1].z * inv);
+      const __half2 w3 = __floats2half2_rn(x[u].w * inv, x[u + 1].w * inv);
+      words[c + 0][col] = *reinterpret_cast<const uint32_t*>(&w0);
+      words[c + 1][col] = *reinterpret_cast<const uint32_t*>(&w1);
+      words[c + 2][col] = *reinterpret_cast<const uint32_t*>(&w2);
+      words[c + 3][col] = *reinterpret_cast<const uint32_t*>(&w3);
     }
     __syncthreads();
-    // dv features x 64 keys out: 16 groups of 4 keys (8 bytes) per feature row; keys past nk (up
-    // to the pitch) are written as the zeros the load left in the tile.
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int e = threadIdx.x + u * 256;
-      const int c = e >> 4, r = (e & 15) * 4;           // c: feature, r: first key of the group
-      if (static_cast<size_t>(c) < a.dv && k0 + r < a.nk_pitch)
-        *reinterpret_cast<uint2*>(dst + c * a.nk_pitch + k0 + r) =
-            pack4_f16(tile[r][c], tile[r + 1][c], tile[r + 2][c], tile[r + 3][c]);
+    // Feature rows warp, warp + 8, ...: lane = key pair.  Keys past nk (up to the pitch, which is
+    // even) are written as the zeros the loads left.
+#pragma unroll 4
+    for (int f = warp; f < 128; f += 8) {
+      if (static_cast<size_t>(f) < a.dv && k0 + 2 * lane < a.nk_pitch)
+        *reinterpret_cast<uint32_t*>(dst + static_cast<size_t>(f) * a.nk_pitch + k0 + 2 * lane) =
+            words[f][lane ^ ((f >> 2) & 31)];
     }
     __syncthreads();
   }
@@ -611,12 +620,12 @@ prepare_attention_mixed_kernel(PrepareMixedArgs a) {
 template <bool FEW_TILES>
 __global__ void __launch_bounds__(256)
 prepare_attention_f16_kernel(PrepareMixedArgs a, int halves) {
-  __shared__ float tile[64][129];
+  __shared__ uint32_t words[128][32];      // a step of V^T: 128 features x 32 key pairs (fp16x2)
   __shared__ float scratch[8];
   sm100::trigger_dependent_launch();       // see prepare_attention_kernel
   // halves: 3 = this grid does both (blockIdx.y picks), 1 = K only, 2 = V only.
   if ((halves == 3 ? blockIdx.y : halves - 1) == 1) {
-    prepare_v_f16(a, tile, scratch);
+    prepare_v_f16(a, words, scratch);
     return;
   }
   const size_t quads = a.d_pitch / 4;       // 4-column groups per (padded) key row, at most 32
