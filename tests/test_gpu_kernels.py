@@ -851,7 +851,7 @@ def test_attention_large_scores_stay_finite(lib, oracle, torch, precision):
     # own work (fp32 accumulation order, P and V rounding, the exponential).  Against the reference
     # on the unrounded operands the distance is dominated by the rounding of Q and K itself: a logit
     # of magnitude 100 moves by up to 100 * 2^-11 = 0.05, i.e. its probability by 5 %, whatever the
-    # kernel does afterwards; that comparison only has to stay within 2e-2 of the output's peak.
+    # kernel does afterwards; measured 5.5e-3 of the output's peak on every arm, bound 1e-2.
     q, k, v = rand((256, 128), 21) * 3, rand((1024, 128), 22), rand((1024, 128), 23)
     got = run_attention(lib, torch, q, k, v, precision)
     assert np.isfinite(got).all()
@@ -860,7 +860,7 @@ def test_attention_large_scores_stay_finite(lib, oracle, torch, precision):
     print("large scores, precision %d: %.2e against rounded operands, %.2e against unrounded"
           % (precision, same_operands, unrounded))
     assert same_operands <= TOL_TF32
-    assert unrounded <= 2e-2
+    assert unrounded <= 1e-2
 
 
 def test_attention_config4_sample_and_checksum(lib, oracle, torch):
