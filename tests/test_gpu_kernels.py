@@ -879,3 +879,30 @@ def test_attention_config4_sample_and_checksum(lib, oracle, torch):
     ones = np.ones_like(v)
     got1 = run_attention(lib, torch, q, k, ones, TF32)
     assert np.abs(got1 - 1.0).max() < 2e-3
+
+
+@pytest.mark.parametrize("batch,nq,nk", [(40, 640, 100), (40, 640, 256), (37, 700, 300), (3, 8192, 130),
+                                         (150, 128, 128), (300, 100, 1), (2, 19000, 384)])
+@pytest.mark.parametrize("precision,tol", [(F16, TOL_TF32), (BF16, TOL_BF16)])
+def test_attention_many_row_blocks_of_few_key_tiles(lib, torch, batch, nq, nk, precision, tol):
+    # More row blocks than SMs and one to three key tiles each: every CTA walks several pieces, and
+    # the next block's Q is staged from inside the first (or only) tile of the current one.
+    d, dv = 64, 48
+    g = torch.Generator(device="cuda")
+    g.manual_seed(batch * 7 + nk)
+    q = torch.randn(batch, nq, d, device="cuda", generator=g) * d ** -0.5
+    k = torch.randn(batch, nk, d, device="cuda", generator=g)
+    v = torch.randn(batch, nk, dv, device="cuda", generator=g)
+    o = torch.full((batch, nq, dv), float("nan"), device="cuda")
+    ws_bytes = lib.ib_attention_workspace_bytes(batch, nq, nk, d, dv, 0, precision)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    ok(lib, lib.ib_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), batch, nq, nk, d, dv,
+                             0, precision, 0, ws.data_ptr(), ws_bytes, None))
+    torch.cuda.synchronize()
+    assert lib.ib_attention_uses_tensor_arm(batch, nq, nk, d, dv, precision) == 1
+    # Same operator in plain fp32 PyTorch (the CPU oracle would take minutes at these sizes; it
+    # pins the kernels on the other attention tests).
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = torch.softmax(q @ k.transpose(1, 2), dim=-1) @ v
+    assert torch.isfinite(o).all()
+    assert ((o - ref).abs().max() / ref.abs().max()).item() <= tol
