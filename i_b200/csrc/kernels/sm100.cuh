@@ -350,6 +350,159 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) ----------------------------------------------
+// Two CTAs of a cluster drive one 256-row MMA: each holds its own 128 rows of A
+// and D (same tensor-memory columns in both) and half of the B rows in its own
+// shared memory at the same offset.  The even CTA of the pair issues the MMAs.
+// Used by the pair GEMM kernel.  Operand loads are plain per-CTA TMA loads (no
+// cluster multicast, no cta_group qualifier on a load); only barrier arrivals
+// cross between the two CTAs.
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The shared::cluster address of the same shared-memory offset in the cluster's CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_addr_of(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+
+// The same without a release fence: for a thread that only forwards a signal and has written
+// nothing itself (the fence of the releasing form costs such a thread about a thousand cycles per
+// arrival, measured).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_alloc_permit_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+
+template <Kind KIND>
+__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  if (KIND == Kind::TF32) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+// One arrival on the barrier at this shared-memory offset in every CTA of
+// `cta_mask` once all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
+
+// mbarrier test whose acquire covers the cluster: for a barrier a peer CTA arrives on.  test_wait
+// returns at once (try_wait may suspend the thread for a while first).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Both barriers of a stage in one go (a local one and one a peer arrives on): the two tests are
+// issued back to back, so the caller pays one shared-memory round trip, not two.
+__device__ __forceinline__ bool mbar_test_both_cluster(uint64_t* a, uint64_t* b, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %3;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 q, [%2], %3;\n\t"
+      "and.pred p, p, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_u32(a)), "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_both_cluster(uint64_t* a, uint64_t* b, uint32_t parity,
+                                                       AbortState* abort, int* status, int code) {
+  uint32_t spins = 0;
+  while (!mbar_test_both_cluster(a, b, parity)) {
+    if (abort->flag) return false;
+    if (++spins > 64u * kWaitSpinLimit) {
+      abort->flag = 1;
+      *reinterpret_cast<volatile int*>(status) = code;
+      __threadfence_system();
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, AbortState* abort,
+                                                  int* status, int code) {
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (abort->flag) return false;
+    if (++spins > 64u * kWaitSpinLimit) {        // plain polls: a few tens of cycles each
+      abort->flag = 1;
+      *reinterpret_cast<volatile int*>(status) = code;
+      __threadfence_system();
+      return false;
+    }
+  }
+  return true;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
