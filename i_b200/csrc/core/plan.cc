@@ -674,7 +674,7 @@ std::string Plan::describe() const {
              << (g.kv_granule ? " (the schedule's key split)\n" : "\n");
       } else {
         if (g.col_tile) os << g.col_tile << " columns (the schedule's column split)";
-        else os << "128 or 256 columns by the output's width";
+        else os << "128 or 256 columns by the output's width (256 rows x 256 columns per CTA pair when it has them)";
         os << " x 32 deep, 4-stage TMA ring; tiles walked ";
         if (g.col_group == Geometry::kNever) os << "row by row (row axis outermost in the schedule)\n";
         else os << "in groups of 12 column tiles\n";

@@ -55,7 +55,9 @@ struct ScheduleHint {
 // loop order into its loop nest (compiler/src/lower/node_to_stage.rs:593-692); here they select
 // among the geometries the kernels have:
 //   Contract   col_tile   output columns per tile: a column split of 256 or more asks for 256,
-//                         one in [128, 256) for 128; finer splits than any MMA tile leave it open
+//                         one in [128, 256) for 128 (both on the single-CTA kernel); finer splits
+//                         than any MMA tile leave it open (CTA pairs on 256 x 256 tiles when the
+//                         output has them)
 //              col_group  column tiles per raster group: with the row axis outermost in the loop
 //                         order the tiles are walked row by row (every column tile in one group),
 //                         with the column axis outermost in column groups of 12
