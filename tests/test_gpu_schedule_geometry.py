@@ -103,3 +103,39 @@ def test_contraction_column_split_and_loop_order_select_the_tiles(ilang, oracle)
     # The tile shape and the walk change which SM computes what, not the arithmetic of an element.
     assert np.array_equal(outs["readme"], outs["128 columns, row by row"])
     assert np.array_equal(outs["readme"], outs["256 columns"])
+
+
+@pytest.mark.parametrize("batch,m,n,k", [(1, 256, 256, 32), (1, 257, 259, 36), (1, 300, 700, 100),
+                                         (3, 384, 512, 128), (2, 1000, 1300, 260), (1, 4096, 256, 64),
+                                         (1, 256, 4096, 4), (5, 511, 513, 68)])
+@pytest.mark.parametrize("precision", [2, 3, 5])          # TF32, BF16, scaled fp16
+def test_pair_kernel_matches_the_single_cta_kernel_bit_for_bit(lib, batch, m, n, k, precision):
+    """Outputs of at least 256 x 256 run on CTA pairs (M = 256 MMAs over 256 x 256 tiles) unless the
+    caller fixes the column tile; a fixed tile of 256 runs the single-CTA kernel.  Same products,
+    same order of accumulation over K: the results have to be identical, ragged edges included."""
+    import ctypes
+    import torch
+    vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    lib.ib_contract_tiled.argtypes = [vp, vp, vp, sz, sz, sz, sz, ci, ci, ci, sz, sz, vp, sz, vp]
+    lib.ib_contract_tiled.restype = ci
+    lib.ib_contract_workspace_bytes.restype = sz
+    lib.ib_contract_workspace_bytes.argtypes = [sz] * 4 + [ci] * 3
+    g = torch.Generator(device="cuda")
+    g.manual_seed(m * 3 + n * 5 + k)
+    a = 2 * torch.rand(batch, m, k, device="cuda", generator=g) - 1
+    b = 2 * torch.rand(batch, n, k, device="cuda", generator=g) - 1
+    wb = lib.ib_contract_workspace_bytes(batch, m, n, k, 1, 1, precision)
+    ws = torch.empty(max(wb, 256), dtype=torch.uint8, device="cuda")
+    outs = []
+    for tile in (0, 256):
+        c = torch.full((batch, m, n), float("nan"), device="cuda")
+        rc = lib.ib_contract_tiled(a.data_ptr(), b.data_ptr(), c.data_ptr(), batch, m, n, k, 1, 1, precision,
+                                   tile, 0, ws.data_ptr(), wb, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        outs.append(c)
+    assert torch.isfinite(outs[0]).all()
+    assert torch.equal(outs[0], outs[1])
+    ref = (a.double() @ b.double().transpose(1, 2)).float()
+    tol = 2e-2 if precision == 3 else 5e-3
+    assert ((outs[0] - ref).abs().max() / ref.abs().max()).item() <= tol
