@@ -1567,33 +1567,11 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
         // operand comes from a special-function instruction issued just before it stalls the
         // stream for that unit's latency.
         float sum0 = 0.0f, sum1 = 0.0f;
-        if (G::kPvFmt == Fmt::F16 && kHalfExp) {
-          // x = S mul - m rounded to fp16, two exponentials per special-function instruction; the
-          // packed result is the P operand as it stands.  Row sums: eight pairs in fp16, then fp32.
-          float fa[4], fb[4];
-          uint32_t xp[4], ee[4];
-          uint32_t acc = 0u;
-#pragma unroll
-          for (int i = 0; i < 16 + 5; ++i) {
-            if (i < 16) {
-              fa[i & 3] = fmaf(__uint_as_float(ra[2 * i]), mul, -m_used);
-              fb[i & 3] = fmaf(__uint_as_float(ra[2 * i + 1]), mul, -m_used);
-            }
-            if (i >= 1 && i - 1 < 16) xp[(i - 1) & 3] = pack_f16(fa[(i - 1) & 3], fb[(i - 1) & 3]);
-            if (i >= 3 && i - 3 < 16) {
-              ee[(i - 3) & 3] = ex2_f16x2(xp[(i - 3) & 3]);
-              ra[i - 3] = ee[(i - 3) & 3];
-            }
-            if (i >= 5) {
-              acc = add_f16x2(acc, ee[(i - 5) & 3]);
-              if (((i - 5) & 7) == 7) {
-                sum0 += f16_lo(acc);
-                sum1 += f16_hi(acc);
-                acc = 0u;
-              }
-            }
-          }
-        } else {
+        {
+          // Two fp32 exponentials per pair, then one conversion of the pair to the operand type.
+          // (Exponentials taken two at a time on fp16 arguments, ex2.approx.f16x2, whose packed
+          // result would be the P operand as it stands, measured slower in this kernel: 871
+          // against 917 TFLOP/s on 8 heads of 16384.)
           float fa[4], fb[4], ea[4], eb[4];
 #pragma unroll
           for (int i = 0; i < 16 + 4; ++i) {
