@@ -152,6 +152,7 @@ struct Shared {
   float half_sum[2][kBQ];
   float quarter_sum[4][kBQ]; // pipelined kernel: the four column quarters' shares of a row sum
   float q_absmax[4][kBQ];    // pipelined kernel: their shares of a Q row's largest magnitude
+  uint64_t m_ready[4];       // alternating kernel: [tile & 3], the tile's reference maximum is published
 };
 
 // One contiguous run of key tiles of one row tile.
@@ -1643,6 +1644,628 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
   }
 }
 
+// Q of one piece into tensor memory, by the eight softmax warps of the alternating kernel: thread
+// (h, r) loads columns 64 h .. 64 h + 63 of row r (sixteen 16-byte loads, all in flight at once;
+// the producer has prefetched the rows into L2) and stores them packed to 16 bits.  On the fp16
+// arm the two halves of a row's largest magnitude meet through shared memory and the 256-thread
+// barrier, which every softmax warp must therefore reach: a warp that has given up (`idle`) comes
+// here too and only skips the work.
+template <Arm ARM>
+__device__ __forceinline__ float stage_q_half(const Params& p, Shared* sh, uint32_t tmem_q, int head,
+                                              int q_tile, int r, int h, int lane, int piece, bool idle) {
+  using G = Geometry<ARM>;
+  float row_mul = kLog2E32;
+  const long long row = static_cast<long long>(q_tile) * kBQ + r;
+  const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
+  const bool live = row < p.nq && !idle;
+  const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
+  float qs = 1.0f;                             // a scale on the logits is a scale on Q
+  if (p.logit_scale) {
+    qs = __ldg(p.logit_scale);
+    if (p.logit_divide) qs = 1.0f / qs;
+  }
+  float4 x[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const int col = h * 64 + 4 * e;
+    x[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (live && vec && col + 4 <= p.d) {
+      x[e] = *reinterpret_cast<const float4*>(qrow + col);
+    } else if (live) {
+      if (col + 0 < p.d) x[e].x = qrow[col + 0];
+      if (col + 1 < p.d) x[e].y = qrow[col + 1];
+      if (col + 2 < p.d) x[e].z = qrow[col + 2];
+      if (col + 3 < p.d) x[e].w = qrow[col + 3];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 16; ++e) { x[e].x *= qs; x[e].y *= qs; x[e].z *= qs; x[e].w *= qs; }
+  float inv = 1.0f;
+  if (G::kScaledQk) {
+    float m = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e)
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(x[e].x), fabsf(x[e].y)), fmaxf(fabsf(x[e].z), fabsf(x[e].w))));
+    sh->q_absmax[h][r] = m;
+    softmax_pair_sync();
+    m = fmaxf(sh->q_absmax[0][r], sh->q_absmax[1][r]);
+    const float scale = f16_range_scale(m);
+    inv = 1.0f / scale;
+    row_mul = kLog2E32 * scale;
+  }
+  if (idle) return row_mul;
+  uint32_t v[32];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    if (G::kQkFmt == Fmt::F16) {
+      v[2 * e + 0] = pack_f16(x[e].x * inv, x[e].y * inv);
+      v[2 * e + 1] = pack_f16(x[e].z * inv, x[e].w * inv);
+    } else {
+      v[2 * e + 0] = pack_bf16(x[e].x, x[e].y);
+      v[2 * e + 1] = pack_bf16(x[e].z, x[e].w);
+    }
+  }
+  tmem_st_32x32(tmem_q + h * 32, v);
+  // The statistics warps need the row's factor too (visible to them once q_ready has completed).
+  if (h == 0) sh->row_mul[piece & 1][r] = row_mul;
+  tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(&sh->q_ready);
+  return row_mul;
+}
+
+// The same kernel with eight softmax warps in two warpgroups that take alternate key tiles.
+constexpr int kThreadsAlternating = 512;
+constexpr int kAltRegsRoles = 56, kAltRegsStats = 64, kAltRegsSoftmax = 192;
+constexpr int kAltRegsAtLaunch = 128;
+static_assert(128 * kAltRegsRoles + 128 * kAltRegsStats + 256 * kAltRegsSoftmax <=
+                  kThreadsAlternating * kAltRegsAtLaunch,
+              "the softmax warps would wait for registers nobody releases");
+
+template <Arm ARM>
+__global__ void __launch_bounds__(kThreadsAlternating, 1)
+attention_alternating_kernel(const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_vt, const Params p) {
+  using G = Geometry<ARM>;
+  static_assert(G::kQkHalf && G::kPvHalf, "the pipelined kernel is the one for 16-bit Q, K, P and V");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  constexpr int kRing = 6;                   // six 32 KB slots in the space of three 64 KB ones
+  constexpr int kSlotBytes = G::kSlotBytes;
+  static_assert(kRing * kSlotBytes <= kRingBytes, "ring does not fit");
+  uint8_t* ring = smem;
+  Shared* sh = reinterpret_cast<Shared*>(ring + kRingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRing; ++s) mbar_init(&sh->kv_full[s], 1);
+    mbar_init(&sh->q_ready, 8);            // one arrival per softmax warp
+    mbar_init(&sh->o_free, 8);
+    for (int u = 0; u < 4; ++u) {
+      mbar_init(&sh->s_full[u], 1);
+      mbar_init(&sh->pv_done[u], 1);
+    }
+    for (int u = 0; u < 2; ++u) {
+      mbar_init(&sh->p_full[u], 4);        // the four warps of the softmax warpgroup that owns the tile
+      mbar_init(&sh->s_free[u], 8);        // those four and the four statistics warps have read S
+    }
+    for (int u = 0; u < 4; ++u) {
+      mbar_init(&sh->m_ready[u], 4);       // the four statistics warps (read at the end of a piece)
+    }
+    sh->abort.flag = 0;
+    sh->give_up = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_slot, kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_slot;
+  AbortState* abort = &sh->abort;
+  trigger_dependent_launch();
+
+  if (warp < 4) {
+    setmaxnreg_dec<kAltRegsRoles>();
+    // Three single-thread roles, one per warp, each walking the same sequence of pieces and key
+    // tiles t = 0, 1, 2, ... of this CTA:
+    //   warp 0  producer: K tile t into slot t % 3 of the K ring once Q K^T of tile t - 3 is done,
+    //           then V^T tile t into slot t % 3 of the V ring once P V of tile t - 3 is
+    //   warp 1  Q K^T issuer: S[t & 1] = Q K(t)^T once the softmax warps have read S of tile t - 2
+    //   warp 3  P V issuer: O += P(t) V(t) once P(t) is in the P buffer
+    // Two issuing threads instead of one keep the two streams independent: with one thread issuing
+    // Q K^T(t + 2), P V(t), Q K^T(t + 3), ... in program order, a late P(t) (one warpgroup) held up
+    // the Q K^T the other warpgroup was about to need.  The tensor pipe runs the instructions of
+    // both threads in the order they reach it; every real dependence is a barrier wait.
+    constexpr int kRingK = 3;
+    const uint32_t ring_addr = smem_u32(ring);
+    if (warp == 0 && lane == 0) {
+      // K producer: K(t) into slot t % 3 of the K ring once Q K^T of tile t - 3 has completed.
+      tma_prefetch_descriptor(&map_k);
+      grid_dependency_wait();                 // K comes from the preparation kernel before this one
+      const int d_chunks = (p.d + G::kQkChunkElems - 1) / G::kQkChunkElems;
+      const bool q_prefetchable = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
+      bool ok = true;
+      int t = 0, slot = 0;                    // tile counter of this CTA; its slot in the ring
+      long long waited = 0;
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      while (ok && next_piece(p, cursor, pc)) {
+        const int b = pc.unit / p.q_tiles;
+        {
+          // Pull the Q rows of the piece after this one into L2 while this one runs.
+          PieceCursor ahead = cursor;
+          Piece nx;
+          if (q_prefetchable && next_piece(p, ahead, nx) && nx.unit != pc.unit) {
+            const int nb = nx.unit / p.q_tiles;
+            const long long row0 = static_cast<long long>(nx.unit - nb * p.q_tiles) * kBQ;
+            const long long rows = min(static_cast<long long>(kBQ), p.nq - row0);
+            prefetch_l2_bulk(p.q + (static_cast<size_t>(nb) * p.nq + row0) * p.d,
+                             static_cast<uint32_t>(rows * p.d * 4));
+          }
+        }
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t, slot = slot + 1 == kRingK ? 0 : slot + 1) {
+          const int u = t - kRingK;
+          // Slot reuse: Q K^T of tile t - 3 has completed.  The next completion on that barrier
+          // is tile t + 1's, whose K this thread has not loaded yet, so the parity is unambiguous.
+          if (t >= kRingK) {
+            const long long t0 = tick<kProf>();
+            ok = mbar_wait(&sh->s_full[u & 3], static_cast<uint32_t>((u >> 2) & 1), abort, p.status, 201);
+            waited += tick<kProf>() - t0;
+            if (!ok) break;
+          }
+          uint8_t* dst = ring + slot * kSlotBytes;
+          mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
+          for (int c = 0; c < d_chunks; ++c)
+            tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kQkChunkElems,
+                        (pc.kv_lo + jj) * kBKV, b);
+        }
+      }
+      if (kProf && p.prof) p.prof[blockIdx.x * 16 + 0] = waited;
+    } else if (warp == 2 && lane == 0) {
+      // V producer: V^T(t) into slot t % 3 of the V ring once P V of tile t - 3 has completed.  A
+      // thread of its own: P V runs about two tiles behind Q K^T, and behind one thread that
+      // loads K(t) then V^T(t) the K loads waited with the V slots, and the Q K^T issuer for K.
+      tma_prefetch_descriptor(&map_vt);
+      grid_dependency_wait();                 // V^T comes from the preparation kernel before this one
+      bool ok = true;
+      int t = 0, slot = 0;
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      while (ok && next_piece(p, cursor, pc)) {
+        const int b = pc.unit / p.q_tiles;
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t, slot = slot + 1 == kRingK ? 0 : slot + 1) {
+          const int u = t - kRingK;
+          if (t >= kRingK) {
+            ok = mbar_wait(&sh->pv_done[u & 3], static_cast<uint32_t>((u >> 2) & 1), abort, p.status, 202);
+            if (!ok) break;
+          }
+          uint8_t* dst = ring + (kRingK + slot) * kSlotBytes;
+          mbar_arrive_expect_tx(&sh->kv_full[kRingK + slot], G::kPvTileChunks * kChunkBytes);
+          for (int c = 0; c < G::kPvTileChunks; ++c)
+            tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[kRingK + slot],
+                        (pc.kv_lo + jj) * kBKV + c * G::kPvChunkElems, 0, b);
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      const uint32_t idesc_qk = make_idesc_fmt(G::kQkFmt, kBQ, kBKV);
+      const int k_steps = (p.d + G::kQkStepElems - 1) / G::kQkStepElems;
+      long long wait_k = 0, wait_q = 0, wait_f = 0, c_qk = 0;
+      const long long t_start = tick<kProf>();
+      bool ok = true;
+      int t = 0, slot = 0;
+      uint32_t phase = 0;                     // of the K ring's full barriers
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
+        // Q of this piece is in tensor memory.
+        long long t0 = tick<kProf>();
+        if (!(ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 203))) break;
+        wait_q += tick<kProf>() - t0;
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t) {
+          const int buf = t & 1;
+          t0 = tick<kProf>();
+          if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 204))) break;
+          wait_k += tick<kProf>() - t0;
+          t0 = tick<kProf>();
+          // S[buf] was last used by tile t - 2; the softmax warps have it in registers once
+          // s_free[buf] has completed for that tile.
+          if (t >= 2 && !(ok = mbar_wait(&sh->s_free[buf], static_cast<uint32_t>(((t >> 1) - 1) & 1),
+                                         abort, p.status, 211)))
+            break;
+          wait_f += tick<kProf>() - t0;
+          tc_fence_after_sync();
+          t0 = tick<kProf>();
+          const uint64_t k_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
+          const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
+          const uint32_t q_tmem = tmem_base + kTmemQ;
+#pragma unroll
+          for (int ks = 0; ks < G::kQkSteps; ++ks) {
+            if (ks < k_steps)
+              mma_ts<Kind::BF16>(d_tmem, q_tmem + ks * 8,
+                                 k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
+                                 ks != 0 ? 1u : 0u);
+          }
+          mma_commit(&sh->s_full[t & 3]);        // S ready, and the K tile's slot is free
+          c_qk += tick<kProf>() - t0;
+          if (++slot == kRingK) { slot = 0; phase ^= 1u; }
+        }
+      }
+      if (kProf && p.prof) {
+        p.prof[blockIdx.x * 16 + 1] = wait_k;
+        p.prof[blockIdx.x * 16 + 4] = tick<kProf>() - t_start;
+        p.prof[blockIdx.x * 16 + 5] = wait_f;
+        p.prof[blockIdx.x * 16 + 6] = c_qk;
+        p.prof[blockIdx.x * 16 + 8] = wait_q;
+      }
+    } else if (warp == 3 && lane == 0) {
+      const uint32_t n_pv = static_cast<uint32_t>((p.dv + 15) / 16 * 16);
+      const uint32_t idesc_pv = make_idesc_fmt(G::kPvFmt, kBQ, n_pv);
+      long long wait_v = 0, wait_p = 0, c_pv = 0;
+      bool ok = true;
+      int t = 0, slot = kRingK;
+      uint32_t phase = 0;                     // of the V ring's full barriers
+      PieceCursor cursor = pieces_begin(p);
+      Piece pc;
+      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
+#pragma unroll 1
+        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t) {
+          long long t0 = tick<kProf>();
+          if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) break;
+          // The first P V of a piece overwrites O: the piece before must have read it out.
+          if (jj == 0 && piece > 0 &&
+              !(ok = mbar_wait(&sh->o_free, static_cast<uint32_t>((piece - 1) & 1), abort, p.status, 210)))
+            break;
+          wait_v += tick<kProf>() - t0;
+          t0 = tick<kProf>();
+          if (!(ok = mbar_wait(&sh->p_full[t & 1], static_cast<uint32_t>((t >> 1) & 1), abort, p.status,
+                               206)))
+            break;
+          wait_p += tick<kProf>() - t0;
+          tc_fence_after_sync();
+          t0 = tick<kProf>();
+          const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
+          const uint32_t d_tmem = tmem_base + kTmemO;
+          const uint32_t p_tmem = tmem_base + kTmemP;
+          if (jj == 0) {
+            mma_ts<Kind::BF16>(d_tmem, p_tmem, v_desc, idesc_pv, 0u);
+          } else {
+            mma_ts<Kind::BF16>(d_tmem, p_tmem, v_desc, idesc_pv, 1u);
+          }
+#pragma unroll
+          for (int ks = 1; ks < G::kPvSteps; ++ks)
+            mma_ts<Kind::BF16>(d_tmem, p_tmem + ks * 8,
+                               v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
+          mma_commit(&sh->pv_done[t & 3]);       // O updated; the V tile's slot and the P buffer are free
+          c_pv += tick<kProf>() - t0;
+          if (++slot == 2 * kRingK) { slot = kRingK; phase ^= 1u; }
+        }
+      }
+      if (kProf && p.prof) {
+        p.prof[blockIdx.x * 16 + 2] = wait_v;
+        p.prof[blockIdx.x * 16 + 3] = wait_p;
+        p.prof[blockIdx.x * 16 + 14] = c_pv;
+      }
+    }
+  } else if (warp < 8) {
+    // ---- statistics warpgroup: the reference maximum of every row after every key tile --------
+    // Reads S(t) as soon as Q K^T has written it (16 columns at a time: this warpgroup gives its
+    // registers to the softmax warps), keeps the running maximum of its 128 rows over the piece,
+    // raises the reference when a tile exceeds it by more than 2^8, rescales O in that (rare) case,
+    // and publishes the reference for the softmax warpgroup that owns the tile.  Because one
+    // warpgroup sees every tile in order, the two softmax warpgroups need nothing from each other.
+    // (Every lane waits on the barriers here: the one-lane-polls form of the wait made the
+    // compiler ask for more than 96 registers in this branch, which the softmax warps need.)
+    setmaxnreg_dec<kAltRegsStats>();
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
+    const int dv16 = (p.dv + 15) / 16;
+    bool ok = true;
+    int t = 0;
+    PieceCursor cursor = pieces_begin(p);
+    Piece pc;
+    // On a failed wait this warp stops working but keeps arriving on the tiles' named barriers,
+    // so that the softmax warps, which block on them, always get through (they then see the
+    // abort flag and stop working too).
+    for (int piece = 0; next_piece(p, cursor, pc); ++piece) {
+      const int b = pc.unit / p.q_tiles;
+      // The rows' Q scales of this piece are in shared memory once Q has been staged.
+      if (ok) ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 215);
+      const float row_mul = G::kScaledQk && ok ? sh->row_mul[piece & 1][r] : kLog2E32;
+      float m_used = -CUDART_INF_F;
+#pragma unroll 1
+      for (int jj = 0; jj < pc.n_kv; ++jj, ++t) {
+        if (ok) ok = mbar_wait(&sh->s_full[t & 3], static_cast<uint32_t>((t >> 2) & 1), abort, p.status, 216);
+        if (ok) {
+          tc_fence_after_sync();
+          const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV);
+          const int col0 = (pc.kv_lo + jj) * kBKV;
+          float mx = -CUDART_INF_F;
+          float mul = row_mul;
+          if (G::kScaledQk) mul *= __ldg(p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + pc.kv_lo + jj);
+          // One block of 32 columns at a time (this warpgroup runs on 64 registers).
+#pragma unroll 1
+          for (int c = 0; c < kBKV; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(s_tmem + c, v);
+            tmem_wait_ld();
+            if (col0 + c + 32 > p.nk) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                if (col0 + c + e >= p.nk) v[e] = __float_as_uint(-CUDART_INF_F);
+            }
+            float m0 = mx, m1 = -CUDART_INF_F, m2 = m1, m3 = m1;
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+              m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+              m2 = max3(m2, __uint_as_float(v[e + 4]), __uint_as_float(v[e + 5]));
+              m3 = max3(m3, __uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
+            }
+            mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          }
+          // S[t & 1] has been read here; the softmax warpgroup that owns the tile adds four arrivals.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->s_free[t & 1]);
+          const float m_new = fmaxf(m_used, mx * mul);
+          const bool grow = m_new > m_used + kRescaleThreshold;
+          if (jj > 0 && __any_sync(0xffffffffu, grow)) {
+            // O holds the tiles up to t - 1 against the old reference once P V of tile t - 1 has
+            // completed; P(t) is computed against the new one only after the publication below.
+            ok = mbar_wait(&sh->pv_done[(t - 1) & 3], static_cast<uint32_t>(((t - 1) >> 2) & 1), abort,
+                           p.status, 208);
+            if (ok) {
+              tc_fence_after_sync();
+              const float factor = grow ? ex2_approx(m_used - m_new) : 1.0f;
+#pragma unroll 1
+              for (int c = 0; c < dv16; ++c) {
+                uint32_t o[16];
+                tmem_ld_32x16(o_tmem + c * 16, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                tmem_st_32x16(o_tmem + c * 16, o);
+              }
+              tmem_wait_st();
+              tc_fence_before_sync();
+            }
+          }
+          if (grow) m_used = m_new;
+          sh->pub_m[t & 3][r] = m_used;
+        }
+        // S(t) is ready and its reference maximum published: the softmax warps block on this
+        // named barrier (one of four, by tile) instead of polling, so that while they wait they
+        // issue nothing.
+        named_arrive(2 + (t & 3), 128 + 128);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->m_ready[t & 3]);
+      }
+    }
+  } else {
+    // ---- softmax warpgroups: h = 0 takes the key tiles at even positions of this CTA's sequence,
+    // h = 1 the odd ones; a warp holds all 128 columns of its 32 rows of a tile.  Per tile a warp
+    // then makes two round trips to tensor memory (S in, P out) for twice the arithmetic of a
+    // warp that shares every tile with three others.
+    setmaxnreg_inc<kAltRegsSoftmax>();
+    const int h = (warp - 8) >> 2;            // warpgroup: tiles of parity h; column half h of Q and O
+    const int quad = warp & 3;                // TMEM lane quadrant
+    const int r = quad * 32 + lane;           // row within the tile
+    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
+    const uint32_t p_tmem = tmem_base + lane_bits + kTmemP;
+    const uint32_t tmem_q = tmem_base + lane_bits + kTmemQ;
+    const int dv_chunks = (p.dv + 31) / 32;
+    int it = 0;                               // key tiles of the pieces before this one
+    long long wait_s = 0, c_a = 0, c_b = 0, c_exp = 0, c_tail = 0;   // kProf: cycles per phase
+    const long long t_start = tick<kProf>();
+    bool dead = false;                        // a wait gave up; keep hitting the barriers only
+    float row_mul = kLog2E32;
+
+    auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (dead) return;
+      dead = !mbar_wait_warp(bar, parity, abort, p.status, code);
+      if (!dead) tc_fence_after_sync();
+    };
+
+    PieceCursor cursor = pieces_begin(p);
+    Piece pc;
+    int piece = 0;
+    while (next_piece(p, cursor, pc)) {
+      const int kv_lo = pc.kv_lo, n_kv = pc.n_kv;
+      const int b = pc.unit / p.q_tiles;
+      const int qt = pc.unit - b * p.q_tiles;
+      const long long row = static_cast<long long>(qt) * kBQ + r;
+      const bool whole = pc.whole;
+      const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
+
+      if (piece == 0) row_mul = stage_q_half<ARM>(p, sh, tmem_q, b, qt, r, h, lane, 0, false);
+
+      // The piece after this one, whose Q is staged at the end of this one.
+      float next_row_mul = kLog2E32;
+      bool has_next = false;
+      int next_b = 0, next_qt = 0;
+      {
+        PieceCursor ahead = cursor;
+        Piece nx;
+        if (next_piece(p, ahead, nx)) {
+          has_next = true;
+          next_b = nx.unit / p.q_tiles;
+          next_qt = nx.unit - next_b * p.q_tiles;
+        }
+      }
+      const int last = it + n_kv - 1;
+
+      float m_mine = -CUDART_INF_F;           // the reference maximum l is expressed against
+      float l = 0.0f;                         // row sum over this warpgroup's tiles
+      float ks_ahead = 1.0f;                  // fp16 arm: K scale of this warpgroup's next tile
+      bool have_scale = false;
+
+#pragma unroll 1
+      for (int jj = (it ^ h) & 1; jj < n_kv; jj += 2) {
+        const int t = it + jj;
+        uint32_t ra[32], rb[32], rc[32], rd[32];
+        long long tp = tick<kProf>();
+        {
+          // S(t) has been written and read by the statistics warps, and its reference maximum is
+          // in shared memory: they arrive on this barrier after both.  A warp that has given up
+          // still comes here for every tile of its warpgroup, so nobody is left blocked.
+          const long long t0 = tick<kProf>();
+          named_sync(2 + (t & 3), 128 + 128);
+          wait_s += tick<kProf>() - t0;
+        }
+        if (!dead && abort->flag) dead = true;
+        if (dead) continue;
+        tc_fence_after_sync();
+        const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV);
+        tmem_ld_32x32(s_tmem, ra);
+        tmem_ld_32x32(s_tmem + 32, rb);
+        tmem_ld_32x32(s_tmem + 64, rc);
+        tmem_ld_32x32(s_tmem + 96, rd);
+        float mul = kLog2E32;
+        if (G::kScaledQk) {
+          const float* ks = p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + kv_lo + jj;
+          const float here = have_scale ? ks_ahead : __ldg(ks);
+          have_scale = jj + 2 < n_kv;
+          if (have_scale) ks_ahead = __ldg(ks + 2);
+          mul = row_mul * here;
+        }
+        const float m_used = sh->pub_m[t & 3][r];
+        if (m_mine != m_used) {
+          l = m_mine == -CUDART_INF_F ? 0.0f : l * ex2_approx(m_mine - m_used);
+          m_mine = m_used;
+        }
+        tmem_wait_ld();
+        // S[t & 1] is in registers: with the statistics warps' arrivals, Q K^T of tile t + 2 may
+        // overwrite it.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->s_free[t & 1]);
+        c_a += tick<kProf>() - tp;
+        tp = tick<kProf>();
+
+        // Keys past the end of the sequence (last tile only).
+        const int col0 = (kv_lo + jj) * kBKV;
+        if (col0 + kBKV > p.nk) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (col0 + c >= p.nk) ra[c] = __float_as_uint(-CUDART_INF_F);
+            if (col0 + 32 + c >= p.nk) rb[c] = __float_as_uint(-CUDART_INF_F);
+            if (col0 + 64 + c >= p.nk) rc[c] = __float_as_uint(-CUDART_INF_F);
+            if (col0 + 96 + c >= p.nk) rd[c] = __float_as_uint(-CUDART_INF_F);
+          }
+        }
+        float sum0 = 0.0f, sum1 = 0.0f;
+        // 16 pairs of exponentials from `src` into dst[off .. off + 15], as a software pipeline.
+        auto exp_block = [&](const uint32_t (&src)[32], uint32_t (&dst)[32], int off) {
+          float fa[4], fb[4], ea[4], eb[4];
+#pragma unroll
+          for (int i = 0; i < 16 + 4; ++i) {
+            if (i < 16) {
+              fa[i & 3] = fmaf(__uint_as_float(src[2 * i]), mul, -m_used);
+              fb[i & 3] = fmaf(__uint_as_float(src[2 * i + 1]), mul, -m_used);
+            }
+            if (i >= 1 && i - 1 < 16) {
+              ea[(i - 1) & 3] = ex2_approx(fa[(i - 1) & 3]);
+              eb[(i - 1) & 3] = ex2_approx(fb[(i - 1) & 3]);
+            }
+            if (i >= 4) {
+              const float y0 = ea[(i - 4) & 3], y1 = eb[(i - 4) & 3];
+              dst[off + i - 4] = G::kPvFmt == Fmt::BF16 ? pack_bf16(y0, y1) : pack_f16(y0, y1);
+              sum0 += y0;
+              sum1 += y1;
+            }
+          }
+        };
+        // The two halves of the tile run through the same 32 pairs of code in a loop that is not
+        // unrolled (the second half's values are moved into the first half's registers), so that
+        // what a softmax warp executes per tile stays short.
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          exp_block(ra, ra, 0);               // pair i lands in a register already consumed
+          exp_block(rb, ra, 16);
+          if (half == 0) {
+            // P of keys 0 .. 63 moves to rd, the second half of S into ra and rb.
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              rb[c] = rd[c];
+              rd[c] = ra[c];
+              ra[c] = rc[c];
+            }
+          }
+        }
+        l += sum0 + sum1;
+        c_exp += tick<kProf>() - tp;
+        tp = tick<kProf>();
+        // There is one P buffer for both warpgroups: it is free once P V of the tile before (the
+        // other warpgroup's) has completed.
+        if (jj > 0) {
+          wait_bar(&sh->pv_done[(t - 1) & 3], static_cast<uint32_t>(((t - 1) >> 2) & 1), 212);
+          if (dead) continue;
+        }
+        tmem_st_32x32(p_tmem, rd);            // keys 0 .. 63 of the tile
+        tmem_st_32x32(p_tmem + 32, ra);       // keys 64 .. 127
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->p_full[t & 1]);
+        c_tail += tick<kProf>() - tp;
+      }
+
+      // ---- end of the piece.  Both warpgroups need the final reference maximum, and Q's columns
+      // may only be restaged once the last Q K^T has completed, which the warpgroup that did not
+      // read that S has to wait for.
+      float m_final = m_mine;
+      if ((last & 1) != h) {
+        wait_bar(&sh->s_full[last & 3], static_cast<uint32_t>((last >> 2) & 1), 214);
+        wait_bar(&sh->m_ready[last & 3], static_cast<uint32_t>((last >> 2) & 1), 218);
+        if (!dead) m_final = sh->pub_m[last & 3][r];
+      }
+      if (!dead && m_mine != m_final) l = m_mine == -CUDART_INF_F ? 0.0f : l * ex2_approx(m_mine - m_final);
+      // Q of the next piece, before this one's epilogue, so that the Q K^T issuer can run the next
+      // piece's first tiles while O is being read out below.  (The warpgroup that owns the last
+      // tile has seen its S; the other one waited for it above.)
+      if (has_next) next_row_mul = stage_q_half<ARM>(p, sh, tmem_q, next_b, next_qt, r, h, lane, piece + 1, dead);
+
+      finish_piece(p, sh, o_tmem, h, r, row, b, whole, part_slot, l, m_final, dv_chunks,
+                   &sh->pv_done[last & 3], static_cast<uint32_t>((last >> 2) & 1), dead);
+      if (sh->give_up) break;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->o_free);
+      it += n_kv;
+      row_mul = next_row_mul;
+      ++piece;
+    }  // pieces
+    if (kProf && p.prof && quad == 0 && lane == 0 && h == 0) {
+      p.prof[blockIdx.x * 16 + 7] = tick<kProf>() - t_start - wait_s;
+      p.prof[blockIdx.x * 16 + 9] = c_a;
+      p.prof[blockIdx.x * 16 + 10] = c_b;
+      p.prof[blockIdx.x * 16 + 12] = c_exp;
+      p.prof[blockIdx.x * 16 + 13] = c_tail;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // Merges the pieces of every row tile that more than one CTA range touched:
 // O = sum_s w_s O_s / sum_s w_s with w_s = l_s 2^(m_s - max m).  One CTA per row
 // tile; which pieces exist follows from the same range arithmetic the main
@@ -1837,15 +2460,17 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
       const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::TF32>),
                                 reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::MIXED>),
                                 reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::BF16>),
-                                reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::F16>)};
+                                reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::F16>),
+                                reinterpret_cast<const void*>(&attention_alternating_kernel<Arm::BF16>),
+                                reinterpret_cast<const void*>(&attention_alternating_kernel<Arm::F16>)};
       for (const void* fn : variants)
         if (err == cudaSuccess)
           err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
       // The pipelined kernels redistribute registers between their warpgroups; see kRegsAtLaunch.
-      for (int v = 2; v < 4 && err == cudaSuccess; ++v) {
+      for (int v = 2; v < 6 && err == cudaSuccess; ++v) {
         cudaFuncAttributes attr{};
         err = cudaFuncGetAttributes(&attr, variants[v]);
-        if (err == cudaSuccess && attr.numRegs < kRegsAtLaunch)
+        if (err == cudaSuccess && attr.numRegs < (v < 4 ? kRegsAtLaunch : kAltRegsAtLaunch))
           return fail("ib_attention: the pipelined kernel was built with " + std::to_string(attr.numRegs) +
                       " registers per thread, fewer than its register redistribution assumes");
       }
@@ -1922,13 +2547,21 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   overlap.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
-  cfg.blockDim = dim3(f16 || bf16 ? kThreadsPipelined : kThreads);
+  static const bool alternating = [] {
+    const char* v = std::getenv("I_B200_ATTN_ALTERNATING");
+    return v && v[0] == '1';
+  }();
+  cfg.blockDim = dim3(f16 || bf16 ? (alternating ? kThreadsAlternating : kThreadsPipelined) : kThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = s;
   cfg.attrs = &overlap;
   cfg.numAttrs = g_dependent_launch && follows_prepare ? 1 : 0;
   cudaError_t launched;
-  if (f16)
+  if (f16 && alternating)
+    launched = cudaLaunchKernelEx(&cfg, attention_alternating_kernel<Arm::F16>, map_k, map_vt, p);
+  else if (bf16 && alternating)
+    launched = cudaLaunchKernelEx(&cfg, attention_alternating_kernel<Arm::BF16>, map_k, map_vt, p);
+  else if (f16)
     launched = cudaLaunchKernelEx(&cfg, attention_pipelined_kernel<Arm::F16>, map_k, map_vt, p);
   else if (bf16)
     launched = cudaLaunchKernelEx(&cfg, attention_pipelined_kernel<Arm::BF16>, map_k, map_vt, p);
