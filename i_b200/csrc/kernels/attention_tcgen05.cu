@@ -70,7 +70,7 @@ using namespace sm100;
 constexpr int kBQ = 128;           // query rows per CTA
 constexpr int kBKV = 128;          // keys per KV tile
 constexpr int kThreads = 384;
-constexpr int kThreadsPipelined = 768;    // roles, statistics, and sixteen softmax warps
+constexpr int kThreadsPipelined = 512;    // roles, statistics, and two softmax warpgroups
 constexpr int kChunkBytes = 128 * 128;     // 128 rows of 128 bytes: 32 fp32 or 64 bf16 per row
 constexpr int kMaxRing = 6;
 
@@ -150,9 +150,8 @@ struct Shared {
   float row_mul[2][kBQ];     // [piece & 1]: log2(e) x the row's Q scale, for the statistics warps
   float half_max[2][2][kBQ]; // [iteration parity][warpgroup][row]
   float half_sum[2][kBQ];
-  float quarter_sum[4][kBQ]; // pipelined kernel: the four column quarters' shares of a row sum
-  float q_absmax[4][kBQ];    // pipelined kernel: their shares of a Q row's largest magnitude
-  uint64_t m_ready[4];       // alternating kernel: [tile & 3], the tile's reference maximum is published
+  float q_absmax[2][kBQ];    // pipelined kernel: the two column halves' shares of a Q row's largest magnitude
+  uint64_t m_ready[4];       // pipelined kernel: [tile & 3], the tile's reference maximum is published
 };
 
 // One contiguous run of key tiles of one row tile.
@@ -934,83 +933,6 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap map_k,
 // per warp on q_ready.  The fp16 arm stores the row over the power of two that brings its largest
 // magnitude into [2^14, 2^15) (every thread reads the whole row for that: 128 features, from L2).
 // Returns the factor that takes the row's S to exponent units, K's tile scale aside.
-__device__ __forceinline__ void softmax_all_sync() {
-  asm volatile("bar.sync 1, 512;" ::: "memory");
-}
-
-// Q of one piece into tensor memory, by the sixteen softmax warps of the pipelined kernel: thread
-// (q4, r) loads columns 32 q4 .. 32 q4 + 31 of row r (eight 16-byte loads, all in flight at once;
-// the producer has prefetched the rows into L2), and stores them packed to 16 bits.  On the fp16
-// arm the row's largest magnitude decides the power of two it is stored over; the four quarters
-// of a row meet through shared memory and the 512-thread barrier, which every softmax warp must
-// therefore reach: a warp that has given up (`idle`) comes here too and only skips the work.
-template <Arm ARM>
-__device__ __forceinline__ float stage_q_quarter(const Params& p, Shared* sh, uint32_t tmem_q, int head,
-                                                 int q_tile, int r, int q4, int lane, int piece,
-                                                 bool idle) {
-  using G = Geometry<ARM>;
-  float row_mul = kLog2E32;
-  const long long row = static_cast<long long>(q_tile) * kBQ + r;
-  const float* qrow = p.q + (static_cast<size_t>(head) * p.nq + row) * p.d;
-  const bool live = row < p.nq && !idle;
-  const bool vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0 && p.d % 4 == 0;
-  // A scale on the logits is a scale on Q: (c q) . k = c (q . k).
-  float qs = 1.0f;
-  if (p.logit_scale) {
-    qs = __ldg(p.logit_scale);
-    if (p.logit_divide) qs = 1.0f / qs;
-  }
-  float4 x[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const int col = q4 * 32 + 4 * e;
-    x[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (live && vec && col + 4 <= p.d) {
-      x[e] = *reinterpret_cast<const float4*>(qrow + col);
-    } else if (live) {
-      if (col + 0 < p.d) x[e].x = qrow[col + 0];
-      if (col + 1 < p.d) x[e].y = qrow[col + 1];
-      if (col + 2 < p.d) x[e].z = qrow[col + 2];
-      if (col + 3 < p.d) x[e].w = qrow[col + 3];
-    }
-  }
-#pragma unroll
-  for (int e = 0; e < 8; ++e) { x[e].x *= qs; x[e].y *= qs; x[e].z *= qs; x[e].w *= qs; }
-  float inv = 1.0f;
-  if (G::kScaledQk) {
-    float m = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e)
-      m = fmaxf(m, fmaxf(fmaxf(fabsf(x[e].x), fabsf(x[e].y)), fmaxf(fabsf(x[e].z), fabsf(x[e].w))));
-    sh->q_absmax[q4][r] = m;
-    softmax_all_sync();
-    m = fmaxf(fmaxf(sh->q_absmax[0][r], sh->q_absmax[1][r]), fmaxf(sh->q_absmax[2][r], sh->q_absmax[3][r]));
-    const float scale = f16_range_scale(m);
-    inv = 1.0f / scale;
-    row_mul = kLog2E32 * scale;
-  }
-  if (idle) return row_mul;
-  uint32_t v[16];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    if (G::kQkFmt == Fmt::F16) {
-      v[2 * e + 0] = pack_f16(x[e].x * inv, x[e].y * inv);
-      v[2 * e + 1] = pack_f16(x[e].z * inv, x[e].w * inv);
-    } else {
-      v[2 * e + 0] = pack_bf16(x[e].x, x[e].y);
-      v[2 * e + 1] = pack_bf16(x[e].z, x[e].w);
-    }
-  }
-  tmem_st_32x16(tmem_q + q4 * 16, v);
-  // The statistics warps need the row's factor too (visible to them once q_ready has completed:
-  // the arrival below releases this store).
-  if (q4 == 0) sh->row_mul[piece & 1][r] = row_mul;
-  tmem_wait_st();
-  tc_fence_before_sync();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(&sh->q_ready);
-  return row_mul;
-}
 
 // Named barriers with separate arriving and waiting sides (ids 2 .. 5 in the pipelined kernel).
 __device__ __forceinline__ void named_arrive(int id, int threads) {
@@ -1020,87 +942,47 @@ __device__ __forceinline__ void named_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// End of a piece for the pipelined kernel: waits for the last P V, adds the four quarters of the
-// row sum, normalises and stores this thread's 32 columns of O (to the output, or to the partial
-// slot with its (m, l) when the piece covers only part of the keys).
-__device__ __forceinline__ void finish_piece_quarter(const Params& p, Shared* sh, uint32_t o_tmem, int q4,
-                                                     int r, long long row, int b, bool whole,
-                                                     int part_slot, float l, float m_used,
-                                                     uint64_t* last_pv_done, uint32_t last_parity,
-                                                     bool& dead) {
-  if (!sh->give_up && !dead)
-    dead = !mbar_wait_warp(last_pv_done, last_parity, &sh->abort, p.status, 209);
-  sh->quarter_sum[q4][r] = l;
-  if (dead) sh->give_up = 1;
-  softmax_all_sync();
-  if (sh->give_up) return;
-  tc_fence_after_sync();
-  const float l_total = (sh->quarter_sum[0][r] + sh->quarter_sum[1][r]) + (sh->quarter_sum[2][r] + sh->quarter_sum[3][r]);
-  const float inv = (p.v_scale ? p.v_scale[b] : 1.0f) / l_total;
-  float* dst;
-  if (whole) {
-    dst = p.o + (static_cast<size_t>(b) * p.nq + row) * p.dv;
-  } else {
-    const size_t prow = static_cast<size_t>(part_slot) * kBQ + r;
-    dst = p.part_o + prow * p.dv;
-    if (q4 == 0) {
-      p.part_m[prow] = m_used;
-      p.part_l[prow] = l_total;
-    }
-  }
-  const int c = q4;
-  if (c * 32 < p.dv) {
-    const bool vec_ok = (p.dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
-    uint32_t o[32];
-    tmem_ld_32x32(o_tmem + c * 32, o);
-    tmem_wait_ld();
-    if (row < p.nq || !whole) {
-      if (vec_ok && c * 32 + 32 <= p.dv) {
-#pragma unroll
-        for (int v = 0; v < 8; ++v)
-          *reinterpret_cast<float4*>(dst + c * 32 + 4 * v) = make_float4(
-              __uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-              __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e)
-          if (c * 32 + e < p.dv) dst[c * 32 + e] = __uint_as_float(o[e]) * inv;
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------------------------
 // The kernel of the 16-bit arms (fp16 over powers of two, and bf16).  Same tiles and work split
-// as above; 768 threads in five kinds of warps instead of three:
-//   warp 0        TMA producer (one thread): K(t) then V^T(t), each through a ring of three 32 KB
-//                 slots of its own
+// as above; 512 threads in six kinds of warps instead of three:
+//   warp 0        K producer (one thread): K(t) through a ring of three 32 KB slots
 //   warp 1        Q K^T issuer (one thread): S[t & 1] = Q K(t)^T, up to two tiles ahead of P V
+//   warp 2        V producer (one thread): V^T(t) through a ring of three 32 KB slots of its own
 //   warp 3        P V issuer (one thread): O += P(t) V(t)
 //   warps 4-7     statistics: read S(t) first, keep every row's running maximum, rescale O when it
 //                 grows by more than 2^8 and publish the reference maximum of the tile
-//   warps 8-23    softmax: warp (q4, quad) turns columns 32 q4 .. 32 q4 + 31 of rows
-//                 32 quad .. 32 quad + 31 of S(t) into P(t) and keeps its quarter of the row sum
+//   warps 8-15    softmax: two warpgroups; warpgroup h takes the tiles at positions of parity h in
+//                 this CTA's sequence, a warp all 128 columns of its 32 rows of such a tile
 // Tensor memory: Q 0..63 | P 64..127 | S0 128..255 | S1 256..383 | O 384..511.  Packed Q takes 64
 // columns, which leaves 64 for a buffer of P of its own: S[buf] is free again as soon as it has
 // been *read* (s_free[buf]), not once P V has consumed the P written over it.
 //
-// Why this shape.  Measured on B200 with microbenchmarks of the same instruction sequences:
+// Why this shape.  Measured on B200, with microbenchmarks and with builds of the kernel that leave
+// parts out:
 //   * the tensor pipe needs about 1140 - 1380 cycles per tile of 128 keys (16 MMAs of ~71 cycles
-//     with A in tensor memory) -- the bound to reach;
-//   * one pair of exponentials (two FFMA, cvt.rn.f16x2, ex2.approx.f16x2, HADD2) costs a scheduler
-//     9.4 cycles when two or more warps supply them from a loop resident in its instruction
-//     cache, i.e. ~600 cycles per tile: the special-function unit is not the bound;
-//   * the same sequence costs 2 - 4 times that when the scheduler's other warps issue other code
-//     in between (polling loops, a long unrolled body, several roles): what bounds the softmax side
-//     of this kernel is how fast instructions reach the warps.  The kernel with the exponentials
-//     removed runs at 1119 TFLOP/s on 8 heads of 16384 keys; with them 866 (fp16) / 1001 (bf16).
-// So: the four softmax warps of a scheduler run one short loop over the same tile; the row maxima,
-// which need all 128 columns of a row, moved out of that loop into the statistics warps, which
-// removes the exchange between column groups and the serial chain max -> exchange -> exp from it;
-// softmax warps wait for S(t) and its maximum on a named hardware barrier (bar.sync) rather than
-// by polling, so a waiting warp issues nothing (+5 to +8 %); Q K^T and P V are issued by two
-// threads so that neither stream waits behind the other's barrier in program order.
+//     with A in tensor memory) -- the bound to reach; with the exponentials compiled out the
+//     kernel runs at 1119 TFLOP/s on 8 heads of 16384 keys;
+//   * a round trip of a warp to tensor memory (tcgen05.ld or st plus its wait) takes 400 - 700
+//     cycles in the running kernel, and tcgen05.wait::ld waits for every load in flight, so loads
+//     cannot be pipelined against arithmetic inside a warp.  A softmax warp that shares every tile
+//     with three others (sixteen warps of 32 columns: the form this kernel had before) pays two
+//     round trips per tile for a quarter of a row; a warp that takes whole rows of every other
+//     tile pays them for four times the arithmetic, and the other warpgroup's exponentials run
+//     meanwhile: 918 -> 972 TFLOP/s on 8 heads;
+//   * the row maxima need all 128 columns of a row and sit in front of the exponentials; in the
+//     statistics warps they are off the softmax warps' path, and because those warps see every
+//     tile in order the two softmax warpgroups need nothing from each other;
+//   * softmax warps wait for S(t) and its maximum on a named hardware barrier (bar.sync) rather
+//     than by polling an mbarrier, so a waiting warp issues nothing (+5 to +8 %);
+//   * Q K^T and P V are issued by two threads, K and V^T loaded by two, so that no stream waits
+//     behind another's barrier in program order (one producer thread for both operands left the
+//     Q K^T issuer waiting ~850 cycles a tile for K);
+//   * two fp32 exponentials and one conversion of the pair beat ex2.approx.f16x2 on a converted
+//     pair here (866 -> 918 in the sixteen-warp form), although the packed form was the faster
+//     one in the 384-thread kernel above;
+//   * Q of the next row block staged with one round of loads (each thread its own 64 columns, the
+//     two halves of a row's largest magnitude meeting through shared memory) instead of nine
+//     dependent rounds: 754 -> 829 TFLOP/s on one head of 16384, 972 -> 1015 on eight.
 // setmaxnreg moves registers from the role and statistics warps to the softmax warps.
 //
 constexpr uint32_t kTmemP = 64;            // pipelined kernel: packed P, beside packed Q (0..63)
@@ -1109,9 +991,9 @@ constexpr uint32_t kTmemP = 64;            // pipelined kernel: packed P, beside
 // pool holds the registers it asks for, and the pool is only what this CTA's own warps gave back:
 // the sum below must fit in what the CTA was launched with, kThreadsPipelined x the kernel's
 // register count.  The host checks that count before every first launch on a device.
-constexpr int kRegsRoles = 56, kRegsStats = 64, kRegsSoftmax = 88;
-constexpr int kRegsAtLaunch = 80;             // what ptxas reports for __launch_bounds__(768, 1)
-static_assert(128 * kRegsRoles + 128 * kRegsStats + 512 * kRegsSoftmax <= kThreadsPipelined * kRegsAtLaunch,
+constexpr int kRegsRoles = 56, kRegsStats = 64, kRegsSoftmax = 192;
+constexpr int kRegsAtLaunch = 128;            // what ptxas reports for __launch_bounds__(512, 1)
+static_assert(128 * kRegsRoles + 128 * kRegsStats + 256 * kRegsSoftmax <= kThreadsPipelined * kRegsAtLaunch,
               "the softmax warps would wait for registers nobody releases");
 
 template <int N>
@@ -1123,528 +1005,7 @@ __device__ __forceinline__ void setmaxnreg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-template <Arm ARM>
-__global__ void __launch_bounds__(kThreadsPipelined, 1)
-attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
-                           const __grid_constant__ CUtensorMap map_vt, const Params p) {
-  using G = Geometry<ARM>;
-  static_assert(G::kQkHalf && G::kPvHalf, "the pipelined kernel is the one for 16-bit Q, K, P and V");
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  constexpr int kRing = 6;                   // six 32 KB slots in the space of three 64 KB ones
-  constexpr int kSlotBytes = G::kSlotBytes;
-  static_assert(kRing * kSlotBytes <= kRingBytes, "ring does not fit");
-  uint8_t* ring = smem;
-  Shared* sh = reinterpret_cast<Shared*>(ring + kRingBytes);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kRing; ++s) mbar_init(&sh->kv_full[s], 1);
-    mbar_init(&sh->q_ready, 16);           // one arrival per softmax warp
-    mbar_init(&sh->o_free, 16);
-    for (int u = 0; u < 4; ++u) {
-      mbar_init(&sh->s_full[u], 1);
-      mbar_init(&sh->pv_done[u], 1);
-    }
-    for (int u = 0; u < 2; ++u) {
-      mbar_init(&sh->p_full[u], 16);       // the sixteen softmax warps
-      mbar_init(&sh->s_free[u], 20);       // those sixteen and the four statistics warps have read S
-    }
-    sh->abort.flag = 0;
-    sh->give_up = 0;
-    fence_barrier_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(&sh->tmem_slot, kTmemCols);
-    tmem_relinquish_alloc_permit();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = sh->tmem_slot;
-  AbortState* abort = &sh->abort;
-  trigger_dependent_launch();
-
-  if (warp < 4) {
-    setmaxnreg_dec<kRegsRoles>();
-    // Three single-thread roles, one per warp, each walking the same sequence of pieces and key
-    // tiles t = 0, 1, 2, ... of this CTA:
-    //   warp 0  producer: K tile t into slot t % 3 of the K ring once Q K^T of tile t - 3 is done,
-    //           then V^T tile t into slot t % 3 of the V ring once P V of tile t - 3 is
-    //   warp 1  Q K^T issuer: S[t & 1] = Q K(t)^T once the softmax warps have read S of tile t - 2
-    //   warp 3  P V issuer: O += P(t) V(t) once P(t) is in the P buffer
-    // Two issuing threads instead of one keep the two streams independent: with one thread issuing
-    // Q K^T(t + 2), P V(t), Q K^T(t + 3), ... in program order, a late P(t) (one warpgroup) held up
-    // the Q K^T the other warpgroup was about to need.  The tensor pipe runs the instructions of
-    // both threads in the order they reach it; every real dependence is a barrier wait.
-    constexpr int kRingK = 3;
-    const uint32_t ring_addr = smem_u32(ring);
-    if (warp == 0 && lane == 0) {
-      // One thread loads both operands, K(t) then V^T(t).  P V runs about two tiles behind Q K^T,
-      // so the V slot frees late and the K load behind it in program order waits with it (the
-      // Q K^T issuer then waits ~850 cycles a tile for K).  Both cures that were built cost more
-      // than that wait, because every warp of this kernel runs at the rate instructions reach it:
-      // a V producer of its own in warp 2 (one more instruction stream per SM: 880 -> 814 TFLOP/s
-      // on 8 heads of 16384), and one thread walking the sequence twice with V^T two tiles behind
-      // K (a longer loop for this thread, which then fell behind itself: 761).
-      tma_prefetch_descriptor(&map_k);
-      tma_prefetch_descriptor(&map_vt);
-      grid_dependency_wait();                 // K and V^T come from the preparation kernel before this one
-      const int d_chunks = (p.d + G::kQkChunkElems - 1) / G::kQkChunkElems;
-      const bool q_prefetchable = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
-      bool ok = true;
-      int t = 0, slot = 0;                    // tile counter of this CTA; its slot in either ring
-      long long waited = 0;
-      PieceCursor cursor = pieces_begin(p);
-      Piece pc;
-      while (ok && next_piece(p, cursor, pc)) {
-        const int b = pc.unit / p.q_tiles;
-        {
-          // Pull the Q rows of the piece after this one into L2 while this one runs.
-          PieceCursor ahead = cursor;
-          Piece nx;
-          if (q_prefetchable && next_piece(p, ahead, nx) && nx.unit != pc.unit) {
-            const int nb = nx.unit / p.q_tiles;
-            const long long row0 = static_cast<long long>(nx.unit - nb * p.q_tiles) * kBQ;
-            const long long rows = min(static_cast<long long>(kBQ), p.nq - row0);
-            prefetch_l2_bulk(p.q + (static_cast<size_t>(nb) * p.nq + row0) * p.d,
-                             static_cast<uint32_t>(rows * p.d * 4));
-          }
-        }
-#pragma unroll 1
-        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t, slot = slot + 1 == kRingK ? 0 : slot + 1) {
-          const int u = t - kRingK;
-          // K slot reuse: Q K^T of tile t - 3 has completed.  The next completion on that barrier
-          // is tile t + 1's, whose K this thread has not loaded yet, so the parity is unambiguous.
-          if (t >= kRingK) {
-            const long long t0 = tick<kProf>();
-            ok = mbar_wait(&sh->s_full[u & 3], static_cast<uint32_t>((u >> 2) & 1), abort, p.status, 201);
-            waited += tick<kProf>() - t0;
-            if (!ok) break;
-          }
-          uint8_t* dst = ring + slot * kSlotBytes;
-          mbar_arrive_expect_tx(&sh->kv_full[slot], d_chunks * kChunkBytes);
-          for (int c = 0; c < d_chunks; ++c)
-            tma_load_3d(dst + c * kChunkBytes, &map_k, &sh->kv_full[slot], c * G::kQkChunkElems,
-                        (pc.kv_lo + jj) * kBKV, b);
-          // V slot reuse: P V of tile t - 3 has completed (it needs nothing this thread has yet to load).
-          if (t >= kRingK) {
-            ok = mbar_wait(&sh->pv_done[u & 3], static_cast<uint32_t>((u >> 2) & 1), abort, p.status, 202);
-            if (!ok) break;
-          }
-          dst = ring + (kRingK + slot) * kSlotBytes;
-          mbar_arrive_expect_tx(&sh->kv_full[kRingK + slot], G::kPvTileChunks * kChunkBytes);
-          for (int c = 0; c < G::kPvTileChunks; ++c)
-            tma_load_3d(dst + c * kChunkBytes, &map_vt, &sh->kv_full[kRingK + slot],
-                        (pc.kv_lo + jj) * kBKV + c * G::kPvChunkElems, 0, b);
-        }
-      }
-      if (kProf && p.prof) p.prof[blockIdx.x * 16 + 0] = waited;
-    } else if (warp == 1 && lane == 0) {
-      const uint32_t idesc_qk = make_idesc_fmt(G::kQkFmt, kBQ, kBKV);
-      const int k_steps = (p.d + G::kQkStepElems - 1) / G::kQkStepElems;
-      long long wait_k = 0, wait_q = 0, wait_f = 0, c_qk = 0;
-      const long long t_start = tick<kProf>();
-      bool ok = true;
-      int t = 0, slot = 0;
-      uint32_t phase = 0;                     // of the K ring's full barriers
-      PieceCursor cursor = pieces_begin(p);
-      Piece pc;
-      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
-        // Q of this piece is in tensor memory.
-        long long t0 = tick<kProf>();
-        if (!(ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 203))) break;
-        wait_q += tick<kProf>() - t0;
-#pragma unroll 1
-        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t) {
-          const int buf = t & 1;
-          t0 = tick<kProf>();
-          if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 204))) break;
-          wait_k += tick<kProf>() - t0;
-          t0 = tick<kProf>();
-          // S[buf] was last used by tile t - 2; the softmax warps have it in registers once
-          // s_free[buf] has completed for that tile.
-          if (t >= 2 && !(ok = mbar_wait(&sh->s_free[buf], static_cast<uint32_t>(((t >> 1) - 1) & 1),
-                                         abort, p.status, 211)))
-            break;
-          wait_f += tick<kProf>() - t0;
-          tc_fence_after_sync();
-          t0 = tick<kProf>();
-          const uint64_t k_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
-          const uint32_t d_tmem = tmem_base + kTmemS + static_cast<uint32_t>(buf * kBKV);
-          const uint32_t q_tmem = tmem_base + kTmemQ;
-#pragma unroll
-          for (int ks = 0; ks < G::kQkSteps; ++ks) {
-            if (ks < k_steps)
-              mma_ts<Kind::BF16>(d_tmem, q_tmem + ks * 8,
-                                 k_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_qk,
-                                 ks != 0 ? 1u : 0u);
-          }
-          mma_commit(&sh->s_full[t & 3]);        // S ready, and the K tile's slot is free
-          c_qk += tick<kProf>() - t0;
-          if (++slot == kRingK) { slot = 0; phase ^= 1u; }
-        }
-      }
-      if (kProf && p.prof) {
-        p.prof[blockIdx.x * 16 + 1] = wait_k;
-        p.prof[blockIdx.x * 16 + 4] = tick<kProf>() - t_start;
-        p.prof[blockIdx.x * 16 + 5] = wait_f;
-        p.prof[blockIdx.x * 16 + 6] = c_qk;
-        p.prof[blockIdx.x * 16 + 8] = wait_q;
-      }
-    } else if (warp == 3 && lane == 0) {
-      const uint32_t n_pv = static_cast<uint32_t>((p.dv + 15) / 16 * 16);
-      const uint32_t idesc_pv = make_idesc_fmt(G::kPvFmt, kBQ, n_pv);
-      long long wait_v = 0, wait_p = 0, c_pv = 0;
-      bool ok = true;
-      int t = 0, slot = kRingK;
-      uint32_t phase = 0;                     // of the V ring's full barriers
-      PieceCursor cursor = pieces_begin(p);
-      Piece pc;
-      for (int piece = 0; ok && next_piece(p, cursor, pc); ++piece) {
-#pragma unroll 1
-        for (int jj = 0; ok && jj < pc.n_kv; ++jj, ++t) {
-          long long t0 = tick<kProf>();
-          if (!(ok = mbar_wait(&sh->kv_full[slot], phase, abort, p.status, 205))) break;
-          // The first P V of a piece overwrites O: the piece before must have read it out.
-          if (jj == 0 && piece > 0 &&
-              !(ok = mbar_wait(&sh->o_free, static_cast<uint32_t>((piece - 1) & 1), abort, p.status, 210)))
-            break;
-          wait_v += tick<kProf>() - t0;
-          t0 = tick<kProf>();
-          if (!(ok = mbar_wait(&sh->p_full[t & 1], static_cast<uint32_t>((t >> 1) & 1), abort, p.status,
-                               206)))
-            break;
-          wait_p += tick<kProf>() - t0;
-          tc_fence_after_sync();
-          t0 = tick<kProf>();
-          const uint64_t v_desc = make_smem_desc_sw128(ring_addr + slot * kSlotBytes);
-          const uint32_t d_tmem = tmem_base + kTmemO;
-          const uint32_t p_tmem = tmem_base + kTmemP;
-          if (jj == 0) {
-            mma_ts<Kind::BF16>(d_tmem, p_tmem, v_desc, idesc_pv, 0u);
-          } else {
-            mma_ts<Kind::BF16>(d_tmem, p_tmem, v_desc, idesc_pv, 1u);
-          }
-#pragma unroll
-          for (int ks = 1; ks < G::kPvSteps; ++ks)
-            mma_ts<Kind::BF16>(d_tmem, p_tmem + ks * 8,
-                               v_desc + (((ks >> 2) * kChunkBytes + (ks & 3) * 32) >> 4), idesc_pv, 1u);
-          mma_commit(&sh->pv_done[t & 3]);       // O updated; the V tile's slot and the P buffer are free
-          c_pv += tick<kProf>() - t0;
-          if (++slot == 2 * kRingK) { slot = kRingK; phase ^= 1u; }
-        }
-      }
-      if (kProf && p.prof) {
-        p.prof[blockIdx.x * 16 + 2] = wait_v;
-        p.prof[blockIdx.x * 16 + 3] = wait_p;
-        p.prof[blockIdx.x * 16 + 14] = c_pv;
-      }
-    }
-  } else if (warp < 8) {
-    // ---- statistics warpgroup: the reference maximum of every row after every key tile --------
-    // Reads S(t) as soon as Q K^T has written it (16 columns at a time: this warpgroup gives its
-    // registers to the softmax warps), keeps the running maximum of its 128 rows over the piece,
-    // raises the reference when a tile exceeds it by more than 2^8, rescales O in that (rare) case,
-    // and publishes the reference for the softmax warpgroup that owns the tile.  Because one
-    // warpgroup sees every tile in order, the two softmax warpgroups need nothing from each other.
-    // (Every lane waits on the barriers here: the one-lane-polls form of the wait made the
-    // compiler ask for more than 96 registers in this branch, which the softmax warps need.)
-    setmaxnreg_dec<kRegsStats>();
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
-    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
-    const int dv16 = (p.dv + 15) / 16;
-    bool ok = true;
-    int t = 0;
-    PieceCursor cursor = pieces_begin(p);
-    Piece pc;
-    // On a failed wait this warp stops working but keeps arriving on the tiles' named barriers,
-    // so that the softmax warps, which block on them, always get through (they then see the
-    // abort flag and stop working too).
-    for (int piece = 0; next_piece(p, cursor, pc); ++piece) {
-      const int b = pc.unit / p.q_tiles;
-      // The rows' Q scales of this piece are in shared memory once Q has been staged.
-      if (ok) ok = mbar_wait(&sh->q_ready, piece & 1, abort, p.status, 215);
-      const float row_mul = G::kScaledQk && ok ? sh->row_mul[piece & 1][r] : kLog2E32;
-      float m_used = -CUDART_INF_F;
-#pragma unroll 1
-      for (int jj = 0; jj < pc.n_kv; ++jj, ++t) {
-        if (ok) ok = mbar_wait(&sh->s_full[t & 3], static_cast<uint32_t>((t >> 2) & 1), abort, p.status, 216);
-        if (ok) {
-          tc_fence_after_sync();
-          const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV);
-          const int col0 = (pc.kv_lo + jj) * kBKV;
-          float mx = -CUDART_INF_F;
-          float mul = row_mul;
-          if (G::kScaledQk) mul *= __ldg(p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + pc.kv_lo + jj);
-          // One block of 32 columns at a time (this warpgroup runs on 64 registers).
-#pragma unroll 1
-          for (int c = 0; c < kBKV; c += 32) {
-            uint32_t v[32];
-            tmem_ld_32x32(s_tmem + c, v);
-            tmem_wait_ld();
-            if (col0 + c + 32 > p.nk) {
-#pragma unroll
-              for (int e = 0; e < 32; ++e)
-                if (col0 + c + e >= p.nk) v[e] = __float_as_uint(-CUDART_INF_F);
-            }
-            float m0 = mx, m1 = -CUDART_INF_F, m2 = m1, m3 = m1;
-#pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
-              m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
-              m2 = max3(m2, __uint_as_float(v[e + 4]), __uint_as_float(v[e + 5]));
-              m3 = max3(m3, __uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
-            }
-            mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-          }
-          // S[t & 1] has been read here; the softmax warps add their sixteen arrivals.
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sh->s_free[t & 1]);
-          const float m_new = fmaxf(m_used, mx * mul);
-          const bool grow = m_new > m_used + kRescaleThreshold;
-          if (jj > 0 && __any_sync(0xffffffffu, grow)) {
-            // O holds the tiles up to t - 1 against the old reference once P V of tile t - 1 has
-            // completed; P(t) is computed against the new one only after the publication below.
-            ok = mbar_wait(&sh->pv_done[(t - 1) & 3], static_cast<uint32_t>(((t - 1) >> 2) & 1), abort,
-                           p.status, 208);
-            if (ok) {
-              tc_fence_after_sync();
-              const float factor = grow ? ex2_approx(m_used - m_new) : 1.0f;
-#pragma unroll 1
-              for (int c = 0; c < dv16; ++c) {
-                uint32_t o[16];
-                tmem_ld_32x16(o_tmem + c * 16, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
-                tmem_st_32x16(o_tmem + c * 16, o);
-              }
-              tmem_wait_st();
-              tc_fence_before_sync();
-            }
-          }
-          if (grow) m_used = m_new;
-          sh->pub_m[t & 3][r] = m_used;
-        }
-        // S(t) is ready and its reference maximum published: the softmax warps block on this
-        // named barrier (one of four, by tile) instead of polling, so that while they wait they
-        // issue nothing.
-        named_arrive(2 + (t & 3), 128 + 512);
-      }
-    }
-  } else {
-    // ---- softmax warps: sixteen, four per row quadrant; warp (q4, quad) holds key columns
-    // 32 q4 .. 32 q4 + 31 of rows 32 quad .. 32 quad + 31 of every tile, so that the four warps
-    // of a scheduler run the same short loop on the same tile at about the same time.
-    setmaxnreg_inc<kRegsSoftmax>();
-    const int q4 = (warp - 8) >> 2;           // column quarter of S, Q and O
-    const int quad = warp & 3;                // TMEM lane quadrant
-    const int r = quad * 32 + lane;           // row within the tile
-    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t o_tmem = tmem_base + lane_bits + kTmemO;
-    const uint32_t p_tmem = tmem_base + lane_bits + kTmemP + static_cast<uint32_t>(q4 * 16);
-    const uint32_t tmem_q = tmem_base + lane_bits + kTmemQ;
-    int it = 0;                               // key tiles of the pieces before this one
-    long long wait_s = 0, c_a = 0, c_b = 0, c_exp = 0, c_tail = 0;   // kProf: cycles per phase
-    const long long t_start = tick<kProf>();
-    bool dead = false;                        // a wait gave up; keep hitting the barriers only
-    float row_mul = kLog2E32;
-
-    auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
-      if (dead) return;
-      dead = !mbar_wait_warp(bar, parity, abort, p.status, code);
-      if (!dead) tc_fence_after_sync();
-    };
-
-    PieceCursor cursor = pieces_begin(p);
-    Piece pc;
-    int piece = 0;
-    while (next_piece(p, cursor, pc)) {
-      const int kv_lo = pc.kv_lo, n_kv = pc.n_kv;
-      const int b = pc.unit / p.q_tiles;
-      const int qt = pc.unit - b * p.q_tiles;
-      const long long row = static_cast<long long>(qt) * kBQ + r;
-      const bool whole = pc.whole;
-      const int part_slot = 2 * static_cast<int>(blockIdx.x) + pc.ordinal;
-
-      if (piece == 0) row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, b, qt, r, q4, lane, 0, false);
-
-      // The piece after this one, whose Q is staged from inside the tile loop.
-      float next_row_mul = kLog2E32;
-      bool has_next = false;
-      int next_b = 0, next_qt = 0;
-      {
-        PieceCursor ahead = cursor;
-        Piece nx;
-        if (next_piece(p, ahead, nx)) {
-          has_next = true;
-          next_b = nx.unit / p.q_tiles;
-          next_qt = nx.unit - next_b * p.q_tiles;
-        }
-      }
-      const int stage_at = n_kv >= 2 ? n_kv - 2 : 0;
-
-      float m_mine = -CUDART_INF_F;           // the reference maximum l is expressed against
-      float l = 0.0f;                         // this quarter's share of the row sum
-      float ks_ahead = 1.0f;                  // fp16 arm: K scale of the next tile
-      bool have_scale = false;
-
-#pragma unroll 1
-      for (int jj = 0; jj < n_kv; ++jj) {
-        const int t = it + jj;
-        uint32_t ra[32];
-        long long tp = tick<kProf>();
-        {
-          // S(t) has been written and read by the statistics warps, and its reference maximum is
-          // in shared memory: they arrive on this barrier after both.  A warp that has given up
-          // still comes here for every tile, so nobody is left blocked.
-          const long long t0 = tick<kProf>();
-          named_sync(2 + (t & 3), 128 + 512);
-          wait_s += tick<kProf>() - t0;
-        }
-        if (!dead && abort->flag) dead = true;
-        // Q of the next piece goes into tensor memory as soon as the last Q K^T of this one has
-        // completed, which is about two tiles before the softmax warps are done with the piece:
-        // the issuer then has the next piece's first tiles computed by the time they get there.
-        // Here, two tiles from the end, Q K^T of the last tile was issued when S of the tile
-        // before this one was read; the wait below is normally over before it starts.
-        if (jj == stage_at && has_next) {
-          const int last_t = it + n_kv - 1;
-          if (jj < n_kv - 1) wait_bar(&sh->s_full[last_t & 3], static_cast<uint32_t>((last_t >> 2) & 1), 217);
-          next_row_mul = stage_q_quarter<ARM>(p, sh, tmem_q, next_b, next_qt, r, q4, lane, piece + 1, dead);
-        }
-        if (dead) continue;
-        tc_fence_after_sync();
-        const uint32_t s_tmem = tmem_base + lane_bits + kTmemS + static_cast<uint32_t>((t & 1) * kBKV + q4 * 32);
-        tmem_ld_32x32(s_tmem, ra);
-        // S -> exponent units: log2(e), times the powers of two Q's row and K's tile were stored
-        // over.  K's scales come from the preparation kernel; every read of them follows an S that
-        // was computed from its K, so that kernel has completed.  The next tile's scale is fetched
-        // now, a tile ahead of its use.
-        float mul = kLog2E32;
-        if (G::kScaledQk) {
-          const float* ks = p.k_tile_scale + static_cast<size_t>(b) * p.kv_tiles + kv_lo + jj;
-          const float here = have_scale ? ks_ahead : __ldg(ks);
-          have_scale = jj + 1 < n_kv;
-          if (have_scale) ks_ahead = __ldg(ks + 1);
-          mul = row_mul * here;
-        }
-        tmem_wait_ld();
-        // This quarter of S[t & 1] is in registers: with the other warps' arrivals, Q K^T of tile
-        // t + 2 may overwrite the buffer.
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->s_free[t & 1]);
-        c_a += tick<kProf>() - tp;
-        tp = tick<kProf>();
-        // The reference maximum for this tile (the statistics warps have also rescaled O by now
-        // if it moved).
-        const float m_used = sh->pub_m[t & 3][r];
-        // The row sum moves to the new reference when that has changed (rarely after the first tiles).
-        if (m_mine != m_used) {
-          l = m_mine == -CUDART_INF_F ? 0.0f : l * ex2_approx(m_mine - m_used);
-          m_mine = m_used;
-        }
-        c_b += tick<kProf>() - tp;
-        tp = tick<kProf>();
-
-        // Keys past the end of the sequence (last tile only).
-        const int col0 = (kv_lo + jj) * kBKV + q4 * 32;
-        if (col0 + 32 > p.nk) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (col0 + c >= p.nk) ra[c] = __float_as_uint(-CUDART_INF_F);
-        }
-        // 16 pairs of exponentials; pair i leaves its packed result in ra[i], a register whose S
-        // value has been consumed by then.  Written as a software pipeline, each stage two or more
-        // pairs behind the one that feeds it: a warp issues in order, and an instruction whose
-        // operand comes from a special-function instruction issued just before it stalls the
-        // stream for that unit's latency.
-        float sum0 = 0.0f, sum1 = 0.0f;
-        {
-          // Two fp32 exponentials per pair, then one conversion of the pair to the operand type.
-          // (Exponentials taken two at a time on fp16 arguments, ex2.approx.f16x2, whose packed
-          // result would be the P operand as it stands, measured slower in this kernel: 871
-          // against 917 TFLOP/s on 8 heads of 16384.)
-          float fa[4], fb[4], ea[4], eb[4];
-#pragma unroll
-          for (int i = 0; i < 16 + 4; ++i) {
-            if (i < 16) {
-              fa[i & 3] = fmaf(__uint_as_float(ra[2 * i]), mul, -m_used);
-              fb[i & 3] = fmaf(__uint_as_float(ra[2 * i + 1]), mul, -m_used);
-            }
-            if (i >= 1 && i - 1 < 16) {
-              ea[(i - 1) & 3] = ex2_approx(fa[(i - 1) & 3]);
-              eb[(i - 1) & 3] = ex2_approx(fb[(i - 1) & 3]);
-            }
-            if (i >= 4) {
-              const float y0 = ea[(i - 4) & 3], y1 = eb[(i - 4) & 3];
-              ra[i - 4] = G::kPvFmt == Fmt::BF16 ? pack_bf16(y0, y1) : pack_f16(y0, y1);
-              sum0 += y0;
-              sum1 += y1;
-            }
-          }
-        }
-        l += sum0 + sum1;
-        c_exp += tick<kProf>() - tp;
-        tp = tick<kProf>();
-        // There is one P buffer: it is free once P V of the tile before has completed, which it
-        // normally has by now (for the first tile of a piece the epilogue of the piece before has
-        // waited for it).
-        if (jj > 0) {
-          wait_bar(&sh->pv_done[(t - 1) & 3], static_cast<uint32_t>(((t - 1) >> 2) & 1), 212);
-          if (dead) continue;
-        }
-        {
-          uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 16; ++c) pk[c] = ra[c];
-          tmem_st_32x16(p_tmem, pk);          // keys 32 q4 .. 32 q4 + 31 of the tile
-        }
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->p_full[t & 1]);
-        c_tail += tick<kProf>() - tp;
-      }
-
-      const int last = it + n_kv - 1;
-      finish_piece_quarter(p, sh, o_tmem, q4, r, row, b, whole, part_slot, l, m_mine,
-                           &sh->pv_done[last & 3], static_cast<uint32_t>((last >> 2) & 1), dead);
-      if (sh->give_up) break;
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->o_free);
-      it += n_kv;
-      row_mul = next_row_mul;
-      ++piece;
-    }  // pieces
-    if (kProf && p.prof && quad == 0 && lane == 0 && q4 == 0) {
-      p.prof[blockIdx.x * 16 + 7] = tick<kProf>() - t_start - wait_s;
-      p.prof[blockIdx.x * 16 + 9] = c_a;
-      p.prof[blockIdx.x * 16 + 10] = c_b;
-      p.prof[blockIdx.x * 16 + 12] = c_exp;
-      p.prof[blockIdx.x * 16 + 13] = c_tail;
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
-    __syncwarp();
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
-  }
-}
-
-// Q of one piece into tensor memory, by the eight softmax warps of the alternating kernel: thread
+// Q of one piece into tensor memory, by the eight softmax warps of the pipelined kernel: thread
 // (h, r) loads columns 64 h .. 64 h + 63 of row r (sixteen 16-byte loads, all in flight at once;
 // the producer has prefetched the rows into L2) and stores them packed to 16 bits.  On the fp16
 // arm the two halves of a row's largest magnitude meet through shared memory and the 256-thread
@@ -1715,17 +1076,9 @@ __device__ __forceinline__ float stage_q_half(const Params& p, Shared* sh, uint3
   return row_mul;
 }
 
-// The same kernel with eight softmax warps in two warpgroups that take alternate key tiles.
-constexpr int kThreadsAlternating = 512;
-constexpr int kAltRegsRoles = 56, kAltRegsStats = 64, kAltRegsSoftmax = 192;
-constexpr int kAltRegsAtLaunch = 128;
-static_assert(128 * kAltRegsRoles + 128 * kAltRegsStats + 256 * kAltRegsSoftmax <=
-                  kThreadsAlternating * kAltRegsAtLaunch,
-              "the softmax warps would wait for registers nobody releases");
-
 template <Arm ARM>
-__global__ void __launch_bounds__(kThreadsAlternating, 1)
-attention_alternating_kernel(const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(kThreadsPipelined, 1)
+attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_vt, const Params p) {
   using G = Geometry<ARM>;
   static_assert(G::kQkHalf && G::kPvHalf, "the pipelined kernel is the one for 16-bit Q, K, P and V");
@@ -1772,7 +1125,7 @@ attention_alternating_kernel(const __grid_constant__ CUtensorMap map_k,
   trigger_dependent_launch();
 
   if (warp < 4) {
-    setmaxnreg_dec<kAltRegsRoles>();
+    setmaxnreg_dec<kRegsRoles>();
     // Three single-thread roles, one per warp, each walking the same sequence of pieces and key
     // tiles t = 0, 1, 2, ... of this CTA:
     //   warp 0  producer: K tile t into slot t % 3 of the K ring once Q K^T of tile t - 3 is done,
@@ -1965,7 +1318,7 @@ attention_alternating_kernel(const __grid_constant__ CUtensorMap map_k,
     // warpgroup sees every tile in order, the two softmax warpgroups need nothing from each other.
     // (Every lane waits on the barriers here: the one-lane-polls form of the wait made the
     // compiler ask for more than 96 registers in this branch, which the softmax warps need.)
-    setmaxnreg_dec<kAltRegsStats>();
+    setmaxnreg_dec<kRegsStats>();
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
@@ -2058,7 +1411,7 @@ attention_alternating_kernel(const __grid_constant__ CUtensorMap map_k,
     // h = 1 the odd ones; a warp holds all 128 columns of its 32 rows of a tile.  Per tile a warp
     // then makes two round trips to tensor memory (S in, P out) for twice the arithmetic of a
     // warp that shares every tile with three others.
-    setmaxnreg_inc<kAltRegsSoftmax>();
+    setmaxnreg_inc<kRegsSoftmax>();
     const int h = (warp - 8) >> 2;            // warpgroup: tiles of parity h; column half h of Q and O
     const int quad = warp & 3;                // TMEM lane quadrant
     const int r = quad * 32 + lane;           // row within the tile
@@ -2460,17 +1813,15 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
       const void* variants[] = {reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::TF32>),
                                 reinterpret_cast<const void*>(&attention_tf32_kernel<Arm::MIXED>),
                                 reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::BF16>),
-                                reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::F16>),
-                                reinterpret_cast<const void*>(&attention_alternating_kernel<Arm::BF16>),
-                                reinterpret_cast<const void*>(&attention_alternating_kernel<Arm::F16>)};
+                                reinterpret_cast<const void*>(&attention_pipelined_kernel<Arm::F16>)};
       for (const void* fn : variants)
         if (err == cudaSuccess)
           err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
       // The pipelined kernels redistribute registers between their warpgroups; see kRegsAtLaunch.
-      for (int v = 2; v < 6 && err == cudaSuccess; ++v) {
+      for (int v = 2; v < 4 && err == cudaSuccess; ++v) {
         cudaFuncAttributes attr{};
         err = cudaFuncGetAttributes(&attr, variants[v]);
-        if (err == cudaSuccess && attr.numRegs < (v < 4 ? kRegsAtLaunch : kAltRegsAtLaunch))
+        if (err == cudaSuccess && attr.numRegs < kRegsAtLaunch)
           return fail("ib_attention: the pipelined kernel was built with " + std::to_string(attr.numRegs) +
                       " registers per thread, fewer than its register redistribution assumes");
       }
@@ -2547,21 +1898,13 @@ int attention_tcgen05(const float* q, const void* k, const void* vt, float* o, s
   overlap.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
-  static const bool alternating = [] {
-    const char* v = std::getenv("I_B200_ATTN_ALTERNATING");
-    return v && v[0] == '1';
-  }();
-  cfg.blockDim = dim3(f16 || bf16 ? (alternating ? kThreadsAlternating : kThreadsPipelined) : kThreads);
+  cfg.blockDim = dim3(f16 || bf16 ? kThreadsPipelined : kThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = s;
   cfg.attrs = &overlap;
   cfg.numAttrs = g_dependent_launch && follows_prepare ? 1 : 0;
   cudaError_t launched;
-  if (f16 && alternating)
-    launched = cudaLaunchKernelEx(&cfg, attention_alternating_kernel<Arm::F16>, map_k, map_vt, p);
-  else if (bf16 && alternating)
-    launched = cudaLaunchKernelEx(&cfg, attention_alternating_kernel<Arm::BF16>, map_k, map_vt, p);
-  else if (f16)
+  if (f16)
     launched = cudaLaunchKernelEx(&cfg, attention_pipelined_kernel<Arm::F16>, map_k, map_vt, p);
   else if (bf16)
     launched = cudaLaunchKernelEx(&cfg, attention_pipelined_kernel<Arm::BF16>, map_k, map_vt, p);
