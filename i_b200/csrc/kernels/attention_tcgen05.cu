@@ -987,6 +987,26 @@ __device__ __forceinline__ void named_sync(int id, int threads) {
 //
 constexpr uint32_t kTmemP = 64;            // pipelined kernel: packed P, beside packed Q (0..63)
 
+// Two fp32 operations in one instruction (sm_100 packed fp32): a pair is a 64-bit register.
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void f32x2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // Registers per thread after setmaxnreg.  setmaxnreg.inc blocks (without a limit) until the CTA's
 // pool holds the registers it asks for, and the pool is only what this CTA's own warps gave back:
 // the sum below must fit in what the CTA was launched with, kThreadsPipelined x the kernel's
@@ -1519,25 +1539,29 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
             if (col0 + 96 + c >= p.nk) rd[c] = __float_as_uint(-CUDART_INF_F);
           }
         }
-        float sum0 = 0.0f, sum1 = 0.0f;
         // 16 pairs of exponentials from `src` into dst[off .. off + 15], as a software pipeline.
+        // The multiply-add in front of a pair of exponentials and the addition behind it are packed
+        // fp32 instructions (two lanes each): five instructions per pair instead of seven.
+        uint64_t sum2 = f32x2(0.0f, 0.0f);
+        const uint64_t mul2 = f32x2(mul, mul), neg_m2 = f32x2(-m_used, -m_used);
         auto exp_block = [&](const uint32_t (&src)[32], uint32_t (&dst)[32], int off) {
-          float fa[4], fb[4], ea[4], eb[4];
+          uint64_t x2[4];
+          float ea[4], eb[4];
 #pragma unroll
           for (int i = 0; i < 16 + 4; ++i) {
-            if (i < 16) {
-              fa[i & 3] = fmaf(__uint_as_float(src[2 * i]), mul, -m_used);
-              fb[i & 3] = fmaf(__uint_as_float(src[2 * i + 1]), mul, -m_used);
-            }
+            if (i < 16)
+              x2[i & 3] = fma_f32x2(f32x2(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1])), mul2,
+                                    neg_m2);
             if (i >= 1 && i - 1 < 16) {
-              ea[(i - 1) & 3] = ex2_approx(fa[(i - 1) & 3]);
-              eb[(i - 1) & 3] = ex2_approx(fb[(i - 1) & 3]);
+              float fa, fb;
+              f32x2_unpack(x2[(i - 1) & 3], fa, fb);
+              ea[(i - 1) & 3] = ex2_approx(fa);
+              eb[(i - 1) & 3] = ex2_approx(fb);
             }
             if (i >= 4) {
               const float y0 = ea[(i - 4) & 3], y1 = eb[(i - 4) & 3];
               dst[off + i - 4] = G::kPvFmt == Fmt::BF16 ? pack_bf16(y0, y1) : pack_f16(y0, y1);
-              sum0 += y0;
-              sum1 += y1;
+              sum2 = add_f32x2(sum2, f32x2(y0, y1));
             }
           }
         };
@@ -1558,7 +1582,11 @@ attention_pipelined_kernel(const __grid_constant__ CUtensorMap map_k,
             }
           }
         }
-        l += sum0 + sum1;
+        {
+          float sum0, sum1;
+          f32x2_unpack(sum2, sum0, sum1);
+          l += sum0 + sum1;
+        }
         c_exp += tick<kProf>() - tp;
         tp = tick<kProf>();
         // There is one P buffer for both warpgroups: it is free once P V of the tile before (the
