@@ -50,7 +50,7 @@ ROTATION = 8          # distinct input sets: 8 x 32 MiB = 256 MiB > 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on this
 # workload, from the ncu captures summarised in profiles/attention_pipelined_kernel_seq16384_d128.md
 # (fp16 arm) and profiles/attention_tf32_kernel_seq16384_d128.md (the arms with 32-bit operands).
-ATTENTION_DRAM_BYTES_PER_LAUNCH = {"f16": 17031936, "tf32+f16": 21210624, "tf32": 25411584}
+ATTENTION_DRAM_BYTES_PER_LAUNCH = {"f16": 17025024, "tf32+f16": 21210624, "tf32": 25411584}
 
 
 def load_peaks():

@@ -319,70 +319,22 @@ __device__ __forceinline__ float stage_q_rows(const Params& p, Shared* sh, uint3
     x.x *= qs; x.y *= qs; x.z *= qs; x.w *= qs;
     return x;
   };
-  if (!G::kQkHalf) {
+  static_assert(!G::kQkHalf, "the 16-bit arms stage Q with stage_q_half");
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int col0 = h * 64 + c * 32;
-      uint32_t v[32];
-#pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        const float4 x = load4(col0 + e);
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
-      }
-      tmem_st_32x32(tmem_q + col0, v);
-    }
-  } else {
-    // 16-bit pairs, two features per column: features [64h, 64h+64) -> columns [32h, 32h+32).
-    // The whole row's largest magnitude decides the power of two that brings the row into
-    // [2^14, 2^15); the other half of the row is read for that alone (once per row tile,
-    // from L2, eight loads at a time), then this thread's own 64 features, all in flight
-    // together.
-    float m = 0.0f;
-    if (G::kScaledQk) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float4 other[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) other[e] = load4((h ^ 1) * 64 + half * 32 + 4 * e);
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          m = fmaxf(m, fmaxf(fmaxf(fabsf(other[e].x), fabsf(other[e].y)),
-                             fmaxf(fabsf(other[e].z), fabsf(other[e].w))));
-      }
-    }
-    float4 own[16];
-#pragma unroll
-    for (int e = 0; e < 16; ++e) own[e] = load4(h * 64 + 4 * e);
-    float inv = 1.0f;
-    if (G::kScaledQk) {
-#pragma unroll
-      for (int e = 0; e < 16; ++e)
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(own[e].x), fabsf(own[e].y)),
-                           fmaxf(fabsf(own[e].z), fabsf(own[e].w))));
-      const float scale = f16_range_scale(m);
-      inv = 1.0f / scale;
-      row_mul = kLog2E32 * scale;
-    }
+  for (int c = 0; c < 2; ++c) {
+    const int col0 = h * 64 + c * 32;
     uint32_t v[32];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float4 x = own[e];
-      if (G::kQkFmt == Fmt::F16) {
-        v[2 * e + 0] = pack_f16(x.x * inv, x.y * inv);
-        v[2 * e + 1] = pack_f16(x.z * inv, x.w * inv);
-      } else {
-        v[2 * e + 0] = pack_bf16(x.x, x.y);
-        v[2 * e + 1] = pack_bf16(x.z, x.w);
-      }
+    for (int e = 0; e < 32; e += 4) {
+      const float4 x = load4(col0 + e);
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 0]) : "f"(x.x));
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 1]) : "f"(x.y));
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 2]) : "f"(x.z));
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v[e + 3]) : "f"(x.w));
     }
-    tmem_st_32x32(tmem_q + h * 32, v);
+    tmem_st_32x32(tmem_q + col0, v);
   }
-  // Pipelined kernel: the statistics warps need the row's factor too (visible to them once
-  // q_ready has completed: the arrival below releases this store).
-  if (piece >= 0 && h == 0) sh->row_mul[piece & 1][r] = row_mul;
+  (void)piece;
   tmem_wait_st();
   tc_fence_before_sync();
   __syncwarp();
