@@ -443,14 +443,12 @@ def multihead_block(args, torch, dist, ilang, rank, world):
                 def run_ce():
                     slot = state["n"] % 2
                     state["n"] += 1
-                    reuse = peer.reusable(slot)
-                    if reuse is not None:
-                        main.wait_event(reuse)
+                    peer.wait_on(main, peer.reusable(slot))
                     sharded_attention_chunked(attend_into, q, k, v, None, chunks=chunks, gather=peer,
                                               slot=slot, local_inputs=True)
 
                 def finish_ce():
-                    main.wait_stream(peer.stream)
+                    peer.join(main)
                     peer.finish()
 
                 out["copy_engine"] = timed(run_ce, finish_ce)
@@ -583,8 +581,11 @@ def run_gpu_arm(args):
     def step(s):
         q, k, v = sets[s % rotation]
         buf = s % 2
-        if gather_done[buf] is not None:
-            main.wait_event(gather_done[buf])  # the gather of step s-2 still reads this buffer
+        if gather_done[buf] is not None:           # the gather of step s-2 still reads this buffer
+            if peer is not None:
+                peer.wait_on(main, gather_done[buf])
+            else:
+                main.wait_event(gather_done[buf])
         attn.into(outs[buf], q, k, v)
         if peer is not None:
             computed.record(main)
@@ -612,7 +613,7 @@ def run_gpu_arm(args):
     for s in range(args.steps):
         step(s)
     if peer is not None:
-        main.wait_stream(peer.stream)
+        peer.join(main)
     elif side is not None:
         main.wait_stream(side)
     t_end.record(main)
@@ -666,7 +667,7 @@ def run_gpu_arm(args):
         for s in range(n_long):
             step(s)
         if peer is not None:
-            main.wait_stream(peer.stream)
+            peer.join(main)
         elif side is not None:
             main.wait_stream(side)
         s_end.record(main)

@@ -214,7 +214,7 @@ class PeerGather:
         except Exception:
             return False
 
-    def __init__(self, shape, slots=2, group=None, device=None):
+    def __init__(self, shape, slots=2, group=None, device=None, streams=4):
         import ctypes
         import torch
         import torch.distributed as dist
@@ -229,7 +229,11 @@ class PeerGather:
         self.handle = symm.rendezvous(self.buffer, self.group)
         self.peers = [self.buffer if r == self.rank else
                       self.handle.get_buffer(r, full, torch.float32) for r in range(self.world)]
-        self.stream = torch.cuda.Stream(device=device)
+        # Copies to different peers go out on several streams, so that more than one copy engine
+        # works on them: on one stream the seven 8 MiB copies of an 8-GPU step ran one after the
+        # other at ~350 GB/s, which bound the step.
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(max(1, min(streams, self.world - 1)))]
+        self.stream = self.streams[0]
         self._done = [None] * slots
         # Byte geometry for the library call: one unit is one rank's row of one slot; a block of
         # it is addressed by its offset along the unit's leading axis.
@@ -239,8 +243,9 @@ class PeerGather:
         self._lead = shape[0] if shape else 1
         self._lead_bytes = self._unit_bytes // max(1, self._lead)
         self._base = [t.data_ptr() for t in self.peers]
-        self._order = [(self.rank + step) % self.world for step in range(1, self.world)]
-        self._dsts = (ctypes.c_void_p * max(1, len(self._order)))()
+        order = [(self.rank + step) % self.world for step in range(1, self.world)]
+        self._groups = [order[g::len(self.streams)] for g in range(len(self.streams))]
+        self._dsts = [(ctypes.c_void_p * max(1, len(g)))() for g in self._groups]
         self._lib = ilang.core()
         self._lib.ib_peer_publish.restype = ctypes.c_int
         self._lib.ib_peer_publish.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
@@ -272,27 +277,42 @@ class PeerGather:
 
     def publish(self, slot, after, lo=None, hi=None):
         """Queue the copies of `local(slot)` (entries [lo, hi) of its leading axis; all of it when
-        omitted) to every peer once event `after` has fired.  Returns the event recorded behind them."""
+        omitted) to every peer once event `after` has fired.  Returns the events recorded behind
+        them, one per copy stream."""
         lo = 0 if lo is None else lo
         hi = self._lead if hi is None else hi
         offset = (slot * self.world + self.rank) * self._unit_bytes + lo * self._lead_bytes
-        for n, peer in enumerate(self._order):
-            self._dsts[n] = self._base[peer] + offset
-        done = self._event(self._events, (slot, lo), self.stream)
-        rc = self._lib.ib_peer_publish(self._base[self.rank] + offset, self._dsts, len(self._order),
-                                       (hi - lo) * self._lead_bytes, after.cuda_event, done.cuda_event,
-                                       self.stream.cuda_stream)
-        if rc != 0:
-            err = self._lib.i_error()
-            raise RuntimeError(err.decode() if err else "ib_peer_publish failed")
+        done = []
+        for g, (peers, dsts, stream) in enumerate(zip(self._groups, self._dsts, self.streams)):
+            for n, peer in enumerate(peers):
+                dsts[n] = self._base[peer] + offset
+            event = self._event(self._events, (slot, lo, g), stream)
+            rc = self._lib.ib_peer_publish(self._base[self.rank] + offset, dsts, len(peers),
+                                           (hi - lo) * self._lead_bytes, after.cuda_event, event.cuda_event,
+                                           stream.cuda_stream)
+            if rc != 0:
+                err = self._lib.i_error()
+                raise RuntimeError(err.decode() if err else "ib_peer_publish failed")
+            done.append(event)
         self._done[slot] = done
         return done
 
+    def wait_on(self, stream, events):
+        """Make `stream` wait for the events a publish returned (None: nothing to wait for)."""
+        for event in events or ():
+            stream.wait_event(event)
+
+    def join(self, stream):
+        """Make `stream` wait for everything queued on the copy streams so far."""
+        for s in self.streams:
+            stream.wait_stream(s)
+
     def reusable(self, slot):
-        """Event after which `local(slot)` may be overwritten (its last copies have read it)."""
+        """Events after which `local(slot)` may be overwritten (its last copies have read it)."""
         return self._done[slot]
 
     def finish(self):
         import torch.distributed as dist
-        self.stream.synchronize()
+        for s in self.streams:
+            s.synchronize()
         dist.barrier(self.group)
