@@ -1,6 +1,8 @@
 // Raw PTX wrappers for the Blackwell (sm_100a) data path: mbarrier, TMA bulk
 // tensor copies, tensor memory (TMEM) management, tcgen05 MMA and the matrix /
-// instruction descriptors it takes.  Nothing here uses cluster multicast.
+// instruction descriptors it takes, single-CTA and CTA-pair (cta_group::2) forms.  No load here
+// uses cluster multicast or a cta_group qualifier; the one multicast operation is the barrier
+// arrival of tcgen05.commit in the CTA-pair GEMM (an arrival, not a data transfer).
 //
 // Every wait is bounded: a wait that does not complete within kWaitSpinLimit
 // polls records a code in a global status word, raises a CTA-wide abort flag
