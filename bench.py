@@ -217,7 +217,8 @@ class ClockSampler:
 SECONDARY = ("row_softmax_8192x8192", "map_exp_8192x8192", "reduce_sum_rows_8192x8192",
              "map_chain_bias_relu_gate_8192x8192", "map_chain_shift_exp_div_8192x8192",
              "mm_t_8192x8192x4096_tf32", "mm_t_8192x8192x4096_bf16_optin",
-             "mm_t_8192x8192x4096_f16_scaled", "cublas_tf32_8192x8192x4096",
+             "mm_t_8192x8192x4096_f16_scaled", "mm_t_bias_relu_8192x8192x4096_tf32",
+             "cublas_tf32_8192x8192x4096",
              "attention_16384_d128_tf32_both_contractions", "attention_16384_d128_bf16_optin")
 
 
@@ -331,6 +332,26 @@ def secondary_metrics(torch, ilang, peaks, only=None, iters=10):
                 "frac_tf32_peak": flop / ms / 1e9 / tf32_peak,
                 "note": "fp16 operands over one power of two per row (TF32's mantissa), scales restored in "
                         "the epilogue; includes the conversion of A and B"}
+        if wanted("mm_t_bias_relu_8192x8192x4096_tf32"):
+            # A layer, `ik*jk~ijk >> +ijk~ij >> ij+j~ij >> >ij~ij`, compiled from the front end: the bias
+            # and the rectifier run in the contraction's epilogue.  Beside it the same operators as a
+            # pass of their own over the stored product.
+            bias = torch.randn(8192, device="cuda", generator=g)
+            mm_t = (ilang.i("ik*jk~ijk") >> ilang.i("+ijk~ij")).set_precision("tf32")
+            tail = ilang.i("ij+j~ij") >> ilang.i(">ij~ij")
+            layer = (ilang.i("ik*jk~ijk") >> ilang.i("+ijk~ij") >> ilang.i("ij+j~ij")
+                     >> ilang.i(">ij~ij")).set_precision("tf32")
+            y = torch.empty_like(c)
+            ms = timed(lambda: layer.into(y, a, b, bias))
+
+            def apart():
+                mm_t.into(c, a, b)
+                tail.into(y, c, bias)
+            ms_apart = timed(apart)
+            out["mm_t_bias_relu_8192x8192x4096_tf32"] = {
+                "tflops": flop / ms / 1e9, "ms": ms, "ms_as_two_passes": ms_apart,
+                "note": "FLOPs of the product alone; one launch against contraction + pointwise pass"}
+            del y, bias
         if wanted("cublas"):
             torch.backends.cuda.matmul.allow_tf32 = True
             ms = timed(lambda: torch.matmul(a, b.t(), out=c))

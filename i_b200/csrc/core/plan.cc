@@ -60,11 +60,11 @@ struct Builder {
     std::vector<size_t> out;
     for (size_t i = 0; i < g.nodes.size(); ++i) {
       if (!alive[i]) continue;
-      for (const auto& acc : steps[i].in)
-        if (!acc.buffer.is_input && acc.buffer.index == n) {
-          out.push_back(i);
-          break;
-        }
+      bool reads = false;
+      for (const auto& acc : steps[i].in) reads = reads || (!acc.buffer.is_input && acc.buffer.index == n);
+      for (const auto& acc : steps[i].epilogue_in)
+        reads = reads || (!acc.buffer.is_input && acc.buffer.index == n);
+      if (reads) out.push_back(i);
     }
     return out;
   }
@@ -579,6 +579,82 @@ void fuse_chain_reductions(Builder& b) {
   }
 }
 
+// A contraction whose only reader is a pointwise map or chain over the same index space, built
+// from `+ - * > <` (a bias, a scale, a rectifier) with the contraction's result as the value the
+// chain starts from: the operators run in the contraction's epilogue, on the accumulator, and the
+// product is never written.  The reference reaches the same with a staged producer
+// (compiler/src/lower/node_to_stage.rs:621-674); here it does not depend on the schedule, because
+// each element sees the same operators in the same order either way.
+bool epilogue_op(Op op) {
+  return op == Op::Add || op == Op::Sub || op == Op::Mul || op == Op::Max || op == Op::Min;
+}
+
+void fuse_contract_epilogues(Builder& b) {
+  for (size_t n = 0; n < b.g.nodes.size(); ++n) {
+    if (!b.alive[n]) continue;
+    const Step& con = b.steps[n];
+    if (con.kind != StepKind::Contract || !con.chain.empty()) continue;
+    if (con.form.swap_out || !con.form.has_m || !con.form.has_n) continue;
+    const size_t c_node = con.out.buffer.index;
+    auto reader = b.sole_reader(c_node);
+    if (!reader) continue;
+    const Step& next = b.steps[*reader];
+    if (next.kind != StepKind::Map && next.kind != StepKind::MapChain) continue;
+    if (next.rank != con.out.index.size() || !is_iota(next.out.index, next.rank)) continue;
+    int link = -1, links = 0;
+    for (size_t i = 0; i < next.in.size(); ++i)
+      if (!next.in[i].buffer.is_input && next.in[i].buffer.index == c_node) {
+        link = static_cast<int>(i);
+        ++links;
+      }
+    if (links != 1 || !is_iota(next.in[link].index, next.rank)) continue;
+    std::vector<ChainOp> ops = next.chain;
+    if (next.kind == StepKind::Map) {
+      ChainOp op0;
+      op0.op = next.op;
+      op0.lhs = 0;
+      op0.rhs = next.in.size() == 2 ? 1 : kChainNone;
+      ops = {op0};
+    }
+    // The product must be the value the chain starts from and appear nowhere else; every operator
+    // takes the running value on exactly one side.
+    bool ok = !ops.empty() && ops.size() <= kMaxChainOps;
+    std::vector<Access> others;
+    std::vector<int> renumber(next.in.size(), kChainNone);
+    for (size_t i = 0; ok && i < next.in.size(); ++i) {
+      if (static_cast<int>(i) == link) continue;
+      ok = chain_operand_ok(next.in[i], next.rank);
+      renumber[i] = static_cast<int>(others.size());
+      others.push_back(next.in[i]);
+    }
+    ok = ok && others.size() + 1 <= kMaxChainOperands;
+    for (size_t j = 0; ok && j < ops.size(); ++j) {
+      ChainOp& c = ops[j];
+      ok = epilogue_op(c.op);
+      auto is_running = [&](int code) { return j == 0 ? code == link : code == kChainPrev; };
+      auto is_product = [&](int code) { return code == link; };
+      const bool left = is_running(c.lhs), right = is_running(c.rhs);
+      ok = ok && left != right && (c.rhs != kChainNone || left);
+      if (j > 0) ok = ok && !is_product(c.lhs) && !is_product(c.rhs);
+      if (!ok) break;
+      auto code = [&](int x) { return is_running(x) ? kChainPrev : x == kChainNone ? x : renumber[x]; };
+      c.lhs = code(c.lhs);
+      c.rhs = code(c.rhs);
+    }
+    if (!ok) continue;
+
+    Step fused = con;
+    fused.out = Access{next.out.buffer, con.out.index};
+    fused.chain = ops;
+    fused.epilogue_in = others;
+    fused.chain_rank = next.rank;
+    fused.nodes.insert(fused.nodes.end(), next.nodes.begin(), next.nodes.end());
+    const size_t slot = *reader;
+    b.alive[n] = false;
+    b.steps[slot] = std::move(fused);
+  }
+}
+
 const char* kind_name(StepKind k) {
   switch (k) {
     case StepKind::Map: return "map";
@@ -616,6 +692,8 @@ std::string Plan::describe() const {
     if (s.kind == StepKind::Map || s.kind == StepKind::Reduce) os << " `" << op_token(s.op) << "`";
     os << "  " << buffer_name(s.out.buffer) << "[" << index_text(s.out.index) << "] <-";
     for (const auto& a : s.in) os << " " << buffer_name(a.buffer) << "[" << index_text(a.index) << "]";
+    for (const auto& a : s.epilogue_in)
+      os << " " << buffer_name(a.buffer) << "[" << index_text(a.index) << "]";
     os << "\n";
     switch (s.kind) {
       case StepKind::Contract:
@@ -624,6 +702,20 @@ std::string Plan::describe() const {
            << s.form.n_batch << ", A " << (s.form.a_kmajor ? "[m,k]" : "[k,m]") << ", B "
            << (s.form.b_kmajor ? "[n,k]" : "[k,n]") << (s.form.swap_out ? ", output [n,m]" : "")
            << "\n";
+        if (!s.chain.empty()) {
+          os << "    epilogue (applied to each element before it is stored; a separate pass on the "
+                "fp32 arm):";
+          auto name = [&](int code) -> std::string {
+            if (code == kChainPrev) return "_";
+            return buffer_name(s.epilogue_in[code].buffer);
+          };
+          for (const ChainOp& c : s.chain) {
+            os << "  ";
+            if (c.rhs == kChainNone) os << op_token(c.op) << name(c.lhs);
+            else os << name(c.lhs) << op_token(c.op) << name(c.rhs);
+          }
+          os << "\n";
+        }
         break;
       case StepKind::RowSoftmax:
         os << "    kernel: ib_row_softmax (row resident on chip, one read + one write)\n";
@@ -739,6 +831,7 @@ Result<Plan> make_plan(const Graph& g) {
   fuse_deferred_attention(b);
   fuse_map_chains(b);
   fuse_chain_reductions(b);
+  fuse_contract_epilogues(b);
 
   Plan plan;
   plan.n_inputs = g.n_inputs;

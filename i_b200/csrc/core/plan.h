@@ -92,6 +92,11 @@ struct Step {
   ScheduleHint hint;
   std::vector<size_t> nodes;       // graph nodes folded into this step
   std::vector<ChainOp> chain;      // MapChain: the operators in order
+  // Contract with pointwise operators applied to its result before it is stored: `chain` holds
+  // them (kChainPrev in the first is the contraction's result, other codes index `epilogue_in`),
+  // `epilogue_in` their other operands, indexed over the result's own axes 0 .. chain_rank - 1.
+  std::vector<Access> epilogue_in;
+  size_t chain_rank = 0;
 };
 
 struct Plan {

@@ -212,6 +212,26 @@ bool infer_shapes(const Plan& plan, const i_tensor* inputs, size_t input_count, 
       std::vector<size_t> extent;
       if (!step_extents(step, *table, &extent, err)) return false;
       for (size_t x : step.out.index) out.push_back(extent[x]);
+      // Operands of a contraction's epilogue are indexed over the result's axes.
+      for (const Access& acc : step.epilogue_in) {
+        const Shape* shape = table->get(acc.buffer);
+        if (!shape) {
+          *err = "internal: operand shape unknown";
+          return false;
+        }
+        if (shape->size() != acc.index.size()) {
+          *err = "operand has rank " + std::to_string(shape->size()) + " but its pattern has " +
+                 std::to_string(acc.index.size()) + " axes";
+          return false;
+        }
+        for (size_t p = 0; p < acc.index.size(); ++p)
+          if (acc.index[p] >= out.size() || (*shape)[p] != out[acc.index[p]]) {
+            *err = "axis extent mismatch: " +
+                   std::to_string(acc.index[p] < out.size() ? out[acc.index[p]] : 0) + " vs " +
+                   std::to_string((*shape)[p]);
+            return false;
+          }
+      }
     }
     table->nodes[step.out.buffer.index] = out;
     table->node_known[step.out.buffer.index] = true;
@@ -455,8 +475,31 @@ int run_contract(const Step& step, const std::vector<size_t>& extent, DeviceBuff
   // A result stored [n][m] swaps the roles of the two output axes, and with them what the
   // schedule said about rows and columns; the geometry is then left to the kernel.
   const Geometry g = f.swap_out ? Geometry{} : choose_geometry(StepKind::Contract, step.hint);
-  return ib_contract_tiled(a, b, out, batch, m, n, k, a_kmajor, b_kmajor, precision, g.col_tile,
-                           g.col_group, ws, ws_bytes, dev.stream);
+  if (step.chain.empty())
+    return ib_contract_tiled(a, b, out, batch, m, n, k, a_kmajor, b_kmajor, precision, g.col_tile,
+                             g.col_group, ws, ws_bytes, dev.stream);
+  // Pointwise operators on the result (the planner only attaches them to a result stored
+  // [.., m, n]); their operands are addressed against the result's rows and columns.
+  std::vector<const float*> operands;
+  std::vector<int> modes;
+  for (const Access& acc : step.epilogue_in) {
+    operands.push_back(dev.get(acc.buffer));
+    int mode = 3;
+    if (acc.index.size() == step.chain_rank) mode = 0;
+    else if (step.chain_rank >= 2 && acc.index.size() == 1 && acc.index[0] == step.chain_rank - 1) mode = 2;
+    else if (!acc.index.empty()) mode = 1;
+    modes.push_back(mode);
+  }
+  std::vector<int> ops;
+  for (const ChainOp& c : step.chain) {
+    ops.push_back(op_code(c.op));
+    ops.push_back(c.lhs == kChainPrev ? IB_CHAIN_PREV : c.lhs);
+    ops.push_back(c.rhs == kChainPrev ? IB_CHAIN_PREV : c.rhs == kChainNone ? IB_CHAIN_NONE : c.rhs);
+  }
+  return ib_contract_chain(a, b, out, batch, m, n, k, a_kmajor, b_kmajor, precision, g.col_tile,
+                           g.col_group, static_cast<int>(step.chain.size()), ops.data(),
+                           static_cast<int>(operands.size()), operands.data(), modes.data(), ws,
+                           ws_bytes, dev.stream);
 }
 
 int run_attention(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev, float* out,

@@ -219,11 +219,105 @@ extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batc
                            workspace_bytes, stream);
 }
 
+namespace ib {
+namespace {
+
+// Pointwise operators that follow a contraction, in the two forms its arms need: `fused` for the
+// tensor-core kernels' epilogue, and the same list as an ib_map_chain call over the stored result
+// for the arms that have no epilogue hook (fp32, and a contraction over no terms).
+struct ContractChain {
+  GemmEpilogue fused;
+  int n_ops = 0;
+  int ops[3 * IB_MAX_CHAIN_OPS] = {};
+  int n_operands = 0;                       // of the ib_map_chain form: the result first
+  const float* operands[IB_MAX_CHAIN_OPERANDS] = {};
+  int modes[IB_MAX_CHAIN_OPERANDS] = {};
+
+  int in_place(float* c, size_t rows, size_t cols, void* stream) const {
+    if (n_ops == 0) return 0;
+    const float* list[IB_MAX_CHAIN_OPERANDS];
+    for (int i = 0; i < n_operands; ++i) list[i] = i == 0 ? c : operands[i];
+    return ib_map_chain(n_ops, ops, n_operands, list, modes, c, rows, cols, stream);
+  }
+};
+
+int contract_with_chain(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
+                        size_t k, int a_kmajor, int b_kmajor, int precision, size_t col_tile,
+                        size_t col_group, const ContractChain* chain, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+}  // namespace
+}  // namespace ib
+
 extern "C" int ib_contract_tiled(const float* a, const float* b, float* c, size_t batch, size_t m,
                                  size_t n, size_t k, int a_kmajor, int b_kmajor, int precision,
                                  size_t col_tile, size_t col_group, void* workspace,
                                  size_t workspace_bytes, void* stream) {
+  return ib::contract_with_chain(a, b, c, batch, m, n, k, a_kmajor, b_kmajor, precision, col_tile,
+                                 col_group, nullptr, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ib_contract_chain(const float* a, const float* b, float* c, size_t batch, size_t m,
+                                 size_t n, size_t k, int a_kmajor, int b_kmajor, int precision,
+                                 size_t col_tile, size_t col_group, int n_ops, const int* ops,
+                                 int n_operands, const float* const* operands, const int* modes,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
   using namespace ib;
+  if (n_ops == 0)
+    return contract_with_chain(a, b, c, batch, m, n, k, a_kmajor, b_kmajor, precision, col_tile,
+                               col_group, nullptr, workspace, workspace_bytes, stream);
+  if (n_ops < 0 || n_ops > IB_MAX_CHAIN_OPS || !ops)
+    return fail("ib_contract_chain: between 0 and " + std::to_string(IB_MAX_CHAIN_OPS) + " operators");
+  if (n_operands < 0 || n_operands > IB_MAX_CHAIN_OPERANDS - 1 || (n_operands > 0 && (!operands || !modes)))
+    return fail("ib_contract_chain: at most " + std::to_string(IB_MAX_CHAIN_OPERANDS - 1) +
+                " operands beside the contraction");
+  ContractChain chain;
+  chain.n_ops = n_ops;
+  chain.n_operands = n_operands + 1;
+  chain.modes[0] = 0;
+  for (int i = 0; i < n_operands; ++i) {
+    if (!operands[i]) return fail("ib_contract_chain: null operand");
+    if (modes[i] < 0 || modes[i] > 3) return fail("ib_contract_chain: operand mode outside 0..3");
+    chain.operands[i + 1] = chain.fused.operand[i] = operands[i];
+    chain.modes[i + 1] = chain.fused.mode[i] = modes[i];
+  }
+  chain.fused.n_ops = n_ops;
+  for (int j = 0; j < n_ops; ++j) {
+    const int op = ops[3 * j], lhs = ops[3 * j + 1], rhs = ops[3 * j + 2];
+    if (op != IB_OP_ADD && op != IB_OP_SUB && op != IB_OP_MUL && op != IB_OP_MAX && op != IB_OP_MIN)
+      return fail("ib_contract_chain: only + - * > < follow a contraction in its own pass");
+    const bool left = lhs == IB_CHAIN_PREV, right = rhs == IB_CHAIN_PREV;
+    if (left == right)
+      return fail("ib_contract_chain: every operator takes the running value on exactly one side");
+    const int other = left ? rhs : lhs;
+    if (other != IB_CHAIN_NONE && (other < 0 || other >= n_operands))
+      return fail("ib_contract_chain: operand index out of range");
+    if (other == IB_CHAIN_NONE && !left)
+      return fail("ib_contract_chain: the one-operand form takes the running value");
+    chain.fused.op[j] = op;
+    chain.fused.which[j] = other == IB_CHAIN_NONE ? -1 : other;
+    chain.fused.acc_right[j] = right ? 1 : 0;
+    // The same list for ib_map_chain: the stored result is operand 0 and starts the chain.
+    auto code = [&](int x) { return x == IB_CHAIN_PREV ? (j == 0 ? 0 : IB_CHAIN_PREV) : x == IB_CHAIN_NONE ? x : x + 1; };
+    chain.ops[3 * j] = op;
+    chain.ops[3 * j + 1] = code(lhs);
+    chain.ops[3 * j + 2] = code(rhs);
+  }
+  return contract_with_chain(a, b, c, batch, m, n, k, a_kmajor, b_kmajor, precision, col_tile,
+                             col_group, &chain, workspace, workspace_bytes, stream);
+}
+
+namespace ib {
+namespace {
+
+int contract_with_chain(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
+                        size_t k, int a_kmajor, int b_kmajor, int precision, size_t col_tile,
+                        size_t col_group, const ContractChain* chain, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  const GemmEpilogue* fused = chain ? &chain->fused : nullptr;
+  auto then_chain = [&](int rc) {
+    return rc != 0 || !chain ? rc : chain->in_place(c, batch * m, n, stream);
+  };
   if (col_tile != 0 && col_tile != 128 && col_tile != 256)
     return fail("ib_contract: col_tile must be 0, 128 or 256");
   GemmGeometry geometry;
@@ -240,7 +334,7 @@ extern "C" int ib_contract_tiled(const float* a, const float* b, float* c, size_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (k == 0) {
     cudaError_t err = cudaMemsetAsync(c, 0, batch * m * n * sizeof(float), s);
-    return err == cudaSuccess ? 0 : fail("ib_contract: memset failed");
+    return then_chain(err == cudaSuccess ? 0 : fail("ib_contract: memset failed"));
   }
   const double flop = 2.0 * batch * m * n * k;
   if (precision == IB_PRECISION_AUTO && wants_tensor(precision, flop) && contract_prefers_f16(m, n, k) &&
@@ -275,7 +369,7 @@ extern "C" int ib_contract_tiled(const float* a, const float* b, float* c, size_
     }
     if (int rc = convert_f16_rows_scaled(ak, a16, a_scale, batch * m, k, kp, s)) return rc;
     if (int rc = convert_f16_rows_scaled(bk, b16, b_scale, batch * n, k, kp, s)) return rc;
-    return gemm_tcgen05_f16(a16, b16, a_scale, b_scale, c, batch, m, n, k, kp, s, geometry);
+    return gemm_tcgen05_f16(a16, b16, a_scale, b_scale, c, batch, m, n, k, kp, s, geometry, fused);
   }
   if (precision == IB_PRECISION_BF16) {
     if (reinterpret_cast<uintptr_t>(workspace) & 255u)
@@ -302,7 +396,7 @@ extern "C" int ib_contract_tiled(const float* a, const float* b, float* c, size_
     }
     if (int rc = convert_bf16_rows(ak, a16, batch * m, k, kp, s)) return rc;
     if (int rc = convert_bf16_rows(bk, b16, batch * n, k, kp, s)) return rc;
-    return gemm_tcgen05_bf16(a16, b16, c, batch, m, n, k, kp, s, geometry);
+    return gemm_tcgen05_bf16(a16, b16, c, batch, m, n, k, kp, s, geometry, fused);
   }
   if (wants_tensor(precision, flop) && contract_shape_ok(k)) {
     Carver ws(workspace, workspace_bytes);
@@ -321,12 +415,15 @@ extern "C" int ib_contract_tiled(const float* a, const float* b, float* c, size_
       bk = t;
     }
     if (gemm_tcgen05_supported(ak, bk, c, m, n, k))
-      return gemm_tcgen05(ak, bk, c, batch, m, n, k, s, geometry);
+      return gemm_tcgen05(ak, bk, c, batch, m, n, k, s, geometry, fused);
     // Misaligned base pointers: the fp32 arm takes any layout.
-    return contract_simt(ak, bk, c, batch, m, n, k, true, true, s);
+    return then_chain(contract_simt(ak, bk, c, batch, m, n, k, true, true, s));
   }
-  return contract_simt(a, b, c, batch, m, n, k, a_kmajor != 0, b_kmajor != 0, s);
+  return then_chain(contract_simt(a, b, c, batch, m, n, k, a_kmajor != 0, b_kmajor != 0, s));
 }
+
+}  // namespace
+}  // namespace ib
 
 extern "C" size_t ib_attention_workspace_bytes(size_t batch, size_t nq, size_t nk, size_t d,
                                                size_t dv, int v_kmajor, int precision) {

@@ -66,6 +66,104 @@ __device__ __forceinline__ TileCoord tile_coord(long long id, int tiles_m, int t
   return t;
 }
 
+// The pointwise operators of a GemmEpilogue over the 32 consecutive columns of one row a thread
+// holds.  `grow` is the row over all batch entries.  Every operator sits behind a warp-uniform
+// switch inside a loop that is not unrolled, so its operands are materialised values: nothing is
+// contracted into a multiply-add across operators, and the result has the bits the separate
+// pointwise kernels give.
+__device__ __forceinline__ void apply_epilogue(const GemmEpilogue& e, uint32_t (&r)[32], size_t grow,
+                                               int col0, int n, bool vec_ok) {
+#pragma unroll 1
+  for (int k = 0; k < e.n_ops; ++k) {
+    float t[32];
+    const int w = e.which[k];
+    if (w >= 0) {
+      const float* p = e.operand[w];
+      const int mode = e.mode[w];
+      if (mode == 1 || mode == 3) {
+        const float s = __ldg(mode == 1 ? p + grow : p);
+#pragma unroll
+        for (int v = 0; v < 32; ++v) t[v] = s;
+      } else {
+        const float* src = mode == 0 ? p + grow * static_cast<size_t>(n) + col0 : p + col0;
+        if (vec_ok && col0 + 32 <= n && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(src) + v);
+            t[4 * v + 0] = x.x;
+            t[4 * v + 1] = x.y;
+            t[4 * v + 2] = x.z;
+            t[4 * v + 3] = x.w;
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < 32; ++v) t[v] = col0 + v < n ? __ldg(src + v) : 0.0f;
+        }
+      }
+    }
+    const bool right = e.acc_right[k] != 0;
+#define IB_EPILOGUE_CASE(OP)                                                                   \
+  case OP:                                                                                     \
+    if (w < 0) {                                                                               \
+      _Pragma("unroll") for (int v = 0; v < 32; ++v)                                           \
+          r[v] = __float_as_uint(apply_unary(OP, __uint_as_float(r[v])));                      \
+    } else if (right) {                                                                        \
+      _Pragma("unroll") for (int v = 0; v < 32; ++v)                                           \
+          r[v] = __float_as_uint(apply_binary(OP, t[v], __uint_as_float(r[v])));               \
+    } else {                                                                                   \
+      _Pragma("unroll") for (int v = 0; v < 32; ++v)                                           \
+          r[v] = __float_as_uint(apply_binary(OP, __uint_as_float(r[v]), t[v]));               \
+    }                                                                                          \
+    break;
+    switch (e.op[k]) {
+      IB_EPILOGUE_CASE(IB_OP_ADD)
+      IB_EPILOGUE_CASE(IB_OP_SUB)
+      IB_EPILOGUE_CASE(IB_OP_MUL)
+      IB_EPILOGUE_CASE(IB_OP_MAX)
+      IB_EPILOGUE_CASE(IB_OP_MIN)
+    }
+#undef IB_EPILOGUE_CASE
+  }
+}
+
+// What an epilogue thread does with 32 consecutive columns of its row: the scales of the fp16
+// arm (C[i][j] = acc * row_scale[i] * col_scale[j], exact: powers of two), the caller's pointwise
+// operators, the store.
+__device__ __forceinline__ void finish_columns(uint32_t (&r)[32], float* crow, size_t grow, bool row_ok,
+                                               float rs, const float* cs, int col0, int n, bool vec_ok,
+                                               const GemmEpilogue& e) {
+  if (!row_ok) return;
+  if (cs) {
+    if (vec_ok && col0 + 32 <= n && (reinterpret_cast<uintptr_t>(cs) & 15u) == 0) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const float4 w = __ldg(reinterpret_cast<const float4*>(cs + col0) + v);
+        r[4 * v + 0] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[4 * v + 0]), rs), w.x));
+        r[4 * v + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[4 * v + 1]), rs), w.y));
+        r[4 * v + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[4 * v + 2]), rs), w.z));
+        r[4 * v + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[4 * v + 3]), rs), w.w));
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < 32; ++v)
+        if (col0 + v < n)
+          r[v] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[v]), rs), __ldg(cs + col0 + v)));
+    }
+  }
+  if (e.n_ops) apply_epilogue(e, r, grow, col0, n, vec_ok);
+  if (vec_ok && col0 + 32 <= n) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      *reinterpret_cast<float4*>(crow + col0 + 4 * v) =
+          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+  } else {
+#pragma unroll
+    for (int v = 0; v < 32; ++v)
+      if (col0 + v < n) crow[col0 + v] = __uint_as_float(r[v]);
+  }
+}
+
 // KIND selects the operand type: TF32 reads fp32 operands (32 per 128-byte row,
 // K = 8 per MMA), BF16 reads bf16 operands (64 per row, K = 16 per MMA).  Either
 // way one MMA consumes 32 bytes of every operand row and a stage holds 128 bytes.
@@ -74,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  float* __restrict__ c, int m, int n, int k, int batch, int* status,
                  const float* __restrict__ row_scale, const float* __restrict__ col_scale,
-                 int f16_operands, int group_n) {
+                 int f16_operands, int group_n, const __grid_constant__ GemmEpilogue epilogue) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -204,36 +302,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tmem_ld_32x32(taddr + chunk * 32, r);
         tmem_wait_ld();
         const int col0 = t.n_tile * BN + chunk * 32;
-        if (cs && row < m) {
-          if (vec_ok && col0 + 32 <= n && (reinterpret_cast<uintptr_t>(cs) & 15u) == 0) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              const float4 w = __ldg(reinterpret_cast<const float4*>(cs + col0) + v);
-              r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) * rs * w.x);
-              r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) * rs * w.y);
-              r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) * rs * w.z);
-              r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) * rs * w.w);
-            }
-          } else {
-#pragma unroll
-            for (int v = 0; v < 32; ++v)
-              if (col0 + v < n)
-                r[v] = __float_as_uint(__uint_as_float(r[v]) * rs * __ldg(cs + col0 + v));
-          }
-        }
-        if (row < m) {
-          if (vec_ok && col0 + 32 <= n) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              *reinterpret_cast<float4*>(crow + col0 + 4 * v) =
-                  make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                              __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-          } else {
-#pragma unroll
-            for (int v = 0; v < 32; ++v)
-              if (col0 + v < n) crow[col0 + v] = __uint_as_float(r[v]);
-          }
-        }
+        finish_columns(r, crow, static_cast<size_t>(t.batch) * m + row, row < m, rs, cs, col0, n, vec_ok,
+                       epilogue);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -290,7 +360,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  float* __restrict__ c, int m, int n, int k, int batch, int* status,
                  const float* __restrict__ row_scale, const float* __restrict__ col_scale,
-                 int f16_operands, int group_n) {
+                 int f16_operands, int group_n, const __grid_constant__ GemmEpilogue epilogue) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -465,36 +535,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tmem_ld_32x32(taddr + chunk * 32, r);
         tmem_wait_ld();
         const int col0 = t.n_tile * BN + chunk * 32;
-        if (cs && row < m) {
-          if (vec_ok && col0 + 32 <= n && (reinterpret_cast<uintptr_t>(cs) & 15u) == 0) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              const float4 w = __ldg(reinterpret_cast<const float4*>(cs + col0) + v);
-              r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) * rs * w.x);
-              r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) * rs * w.y);
-              r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) * rs * w.z);
-              r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) * rs * w.w);
-            }
-          } else {
-#pragma unroll
-            for (int v = 0; v < 32; ++v)
-              if (col0 + v < n)
-                r[v] = __float_as_uint(__uint_as_float(r[v]) * rs * __ldg(cs + col0 + v));
-          }
-        }
-        if (row < m) {
-          if (vec_ok && col0 + 32 <= n) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              *reinterpret_cast<float4*>(crow + col0 + 4 * v) =
-                  make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                              __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-          } else {
-#pragma unroll
-            for (int v = 0; v < 32; ++v)
-              if (col0 + v < n) crow[col0 + v] = __uint_as_float(r[v]);
-          }
-        }
+        finish_columns(r, crow, static_cast<size_t>(t.batch) * m + row, row < m, rs, cs, col0, n, vec_ok,
+                       epilogue);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -516,8 +558,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 template <Kind KIND>
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
-                size_t n, size_t k, cudaStream_t s, int group_n, const float* row_scale = nullptr,
-                const float* col_scale = nullptr, bool f16_operands = false) {
+                size_t n, size_t k, cudaStream_t s, int group_n, const GemmEpilogue* e,
+                const float* row_scale = nullptr, const float* col_scale = nullptr,
+                bool f16_operands = false) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail("ib_contract: cannot identify the current device");
   static OncePerDevice configured;
@@ -539,14 +582,15 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, si
   gemm_pair_kernel<KIND><<<static_cast<unsigned>(2 * pairs), kThreads, kPairSmem, s>>>(
       map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
       static_cast<int>(batch), status, row_scale, col_scale, f16_operands ? 1 : 0,
-      group_n > 0 ? group_n : kGroupN);
+      group_n > 0 ? group_n : kGroupN, e ? *e : GemmEpilogue{});
   return check_launch("ib_contract (tcgen05 pair)");
 }
 
 template <int BN, Kind KIND>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t batch, size_t m,
-           size_t n, size_t k, cudaStream_t s, int group_n, const float* row_scale = nullptr,
-           const float* col_scale = nullptr, bool f16_operands = false) {
+           size_t n, size_t k, cudaStream_t s, int group_n, const GemmEpilogue* e,
+           const float* row_scale = nullptr, const float* col_scale = nullptr,
+           bool f16_operands = false) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail("ib_contract: cannot identify the current device");
   // The opt-in to more than 48 KB of dynamic shared memory is per device (and per instantiation).
@@ -571,7 +615,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, float* c, size_t 
   gemm_tf32_kernel<BN, KIND><<<grid, kThreads, Smem<BN>::kTotal, s>>>(
       map_a, map_b, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
       static_cast<int>(batch), status, row_scale, col_scale, f16_operands ? 1 : 0,
-      group_n > 0 ? group_n : kGroupN);
+      group_n > 0 ? group_n : kGroupN, e ? *e : GemmEpilogue{});
   return check_launch("ib_contract (tcgen05 tf32)");
 }
 
@@ -600,7 +644,7 @@ static bool use_pair(const GemmGeometry& g, size_t m, size_t n) {
 }
 
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                 size_t k, cudaStream_t s, GemmGeometry g) {
+                 size_t k, cudaStream_t s, GemmGeometry g, const GemmEpilogue* e) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!gemm_tcgen05_supported(a, b, c, m, n, k))
     return fail("ib_contract: shape or alignment not supported by the tensor-core arm");
@@ -610,13 +654,14 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
   CUtensorMap map_a, map_b;
   if (int rc = make_tensor_map_f32(&map_a, a, batch, m, k, k, m * k, kBM)) return rc;
   if (int rc = make_tensor_map_f32(&map_b, b, batch, n, k, k, n * k, wide ? 256 : 128)) return rc;
-  if (pair) return launch_pair<Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n);
-  return wide ? launch<256, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n)
-              : launch<128, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n);
+  if (pair) return launch_pair<Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e);
+  return wide ? launch<256, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e)
+              : launch<128, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e);
 }
 
 int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
-                      size_t k, size_t k_pitch, cudaStream_t s, GemmGeometry g) {
+                      size_t k, size_t k_pitch, cudaStream_t s, GemmGeometry g,
+                      const GemmEpilogue* e) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (k_pitch % 8 != 0 || k_pitch < k || !c || m >= (1u << 30) || n >= (1u << 30) ||
       k >= (1u << 30) || batch >= (1u << 30))
@@ -627,14 +672,14 @@ int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, 
   if (int rc = make_tensor_map_bf16(&map_a, a16, batch, m, k, k_pitch, m * k_pitch, kBM)) return rc;
   if (int rc = make_tensor_map_bf16(&map_b, b16, batch, n, k, k_pitch, n * k_pitch, wide ? 256 : 128))
     return rc;
-  if (pair) return launch_pair<Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n);
-  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n)
-              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n);
+  if (pair) return launch_pair<Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e);
+  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e)
+              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e);
 }
 
 int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, const float* b_scale,
                      float* c, size_t batch, size_t m, size_t n, size_t k, size_t k_pitch,
-                     cudaStream_t s, GemmGeometry g) {
+                     cudaStream_t s, GemmGeometry g, const GemmEpilogue* e) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (k_pitch % 8 != 0 || k_pitch < k || !c || !a_scale || !b_scale || m >= (1u << 30) ||
       n >= (1u << 30) || k >= (1u << 30) || batch >= (1u << 30))
@@ -646,9 +691,9 @@ int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, con
   if (int rc = make_tensor_map_bf16(&map_b, b16, batch, n, k, k_pitch, n * k_pitch, wide ? 256 : 128))
     return rc;
   if (pair)
-    return launch_pair<Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, a_scale, b_scale, true);
-  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, a_scale, b_scale, true)
-              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, a_scale, b_scale, true);
+    return launch_pair<Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e, a_scale, b_scale, true);
+  return wide ? launch<256, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e, a_scale, b_scale, true)
+              : launch<128, Kind::BF16>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e, a_scale, b_scale, true);
 }
 
 }  // namespace ib

@@ -6,6 +6,8 @@
 
 #include <cstddef>
 
+#include "i_b200.h"
+
 namespace ib {
 
 // contract_simt.cu
@@ -55,8 +57,22 @@ struct GemmGeometry {
   int col_tile = 0;
   int group_n = 0;
 };
+// Pointwise operators the tensor-core contraction applies to every element of its result before
+// storing it (a bias, a rectifier, a scale), in order: acc = op(acc, other), op(other, acc) with
+// acc_right, or the one-operand form op(acc) with which < 0.  `other` is operand[which], addressed
+// by mode 0 [row][col] (the result's own shape, batch entries flattened into rows), 1 [row],
+// 2 [col], 3 one value.  Operators: IB_OP_ADD, IB_OP_SUB, IB_OP_MUL, IB_OP_MAX, IB_OP_MIN, with
+// the arithmetic of the pointwise kernels, so the result equals contraction then maps bit for bit.
+struct GemmEpilogue {
+  int n_ops = 0;
+  int op[IB_MAX_CHAIN_OPS] = {};
+  int which[IB_MAX_CHAIN_OPS] = {};
+  int acc_right[IB_MAX_CHAIN_OPS] = {};
+  const float* operand[IB_MAX_CHAIN_OPERANDS] = {};
+  int mode[IB_MAX_CHAIN_OPERANDS] = {};
+};
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                 size_t k, cudaStream_t s, GemmGeometry g = {});
+                 size_t k, cudaStream_t s, GemmGeometry g = {}, const GemmEpilogue* e = nullptr);
 // Same contraction with bf16 operands a16 / b16 ([b][rows][k_pitch] bf16, k_pitch a multiple of 8)
 // fed to tcgen05 kind::f16, fp32 accumulation.
 // The same on fp16 operands stored over one power of two per row (a16[b][i][:] = A / a_scale[b][i],
@@ -64,9 +80,10 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
 // at the 16-bit issue rate.
 int gemm_tcgen05_f16(const void* a16, const void* b16, const float* a_scale, const float* b_scale,
                      float* c, size_t batch, size_t m, size_t n, size_t k, size_t k_pitch,
-                     cudaStream_t s, GemmGeometry g = {});
+                     cudaStream_t s, GemmGeometry g = {}, const GemmEpilogue* e = nullptr);
 int gemm_tcgen05_bf16(const void* a16, const void* b16, float* c, size_t batch, size_t m, size_t n,
-                      size_t k, size_t k_pitch, cudaStream_t s, GemmGeometry g = {});
+                      size_t k, size_t k_pitch, cudaStream_t s, GemmGeometry g = {},
+                      const GemmEpilogue* e = nullptr);
 // out[r][c] = bf16(in[r][c]) (round to nearest even) for a [rows][cols] fp32 array; `out_pitch` in
 // elements, columns cols..out_pitch-1 are zeroed.
 // fp16 rows over one power of two each: out[r][c] = fp16(in[r][c] / scale[r]), scale[r] bringing the

@@ -459,6 +459,32 @@ def test_pointwise_chain_under_a_row_fold_is_one_kernel(ilang):
     assert steps_of(i("^ij~ij") >> (I & i("+ij~i"))) == ["map", "reduce"]
 
 
+def test_pointwise_operators_on_a_contraction_run_in_its_epilogue(ilang):
+    i, I = ilang.i, ilang.I
+    mm_t = i("ik*jk~ijk") >> i("+ijk~ij")
+    layer = mm_t >> i("ij+j~ij") >> i(">ij~ij")                     # product, bias, rectifier
+    assert steps_of(layer) == ["contract"]
+    assert "epilogue" in layer._code() and "_+in2  >_" in layer._code()
+    shapes = ((6, 5), (8, 5), (8,))
+    assert layer.output_shapes(*(np.zeros(s, np.float32) for s in shapes)) == [(6, 8)]
+    with pytest.raises(RuntimeError, match="axis extent mismatch"):
+        layer.output_shapes(np.zeros((6, 5), np.float32), np.zeros((8, 5), np.float32),
+                            np.zeros((7,), np.float32))
+    # The product on the right of a subtraction, per-row and full-size operands, batch axes.
+    rowwise = (I | mm_t) >> i("i-ij~ij")
+    assert steps_of(rowwise) == ["contract"] and "in0-_" in rowwise._code()
+    assert steps_of((i("bik*bjk~bijk") >> i("+bijk~bij")) >> i("bij*bij~bij") >> i("<bij~bij")) == ["contract"]
+    # Operators outside + - * > < stay a pass of their own, as does a product read twice, one
+    # that is also an output, and one stored transposed.
+    assert steps_of(mm_t >> i("^ij~ij")) == ["contract", "map"]
+    assert steps_of(mm_t >> i("ij+j~ij") >> i("^ij~ij")) == ["contract", "map_chain"]
+    assert steps_of(mm_t >> (I & I) >> i("ij*ij~ij")) == ["contract", "map"]
+    assert steps_of(mm_t >> (I & i(">ij~ij"))) == ["contract", "map"]
+    assert steps_of(i("ik*jk~ijk") >> i("+ijk~ji") >> i(">ji~ji")) == ["contract", "map"]
+    squared = mm_t >> i("ij+j~ij") >> (I & I) >> i("ij*ij~ij")      # the bias joins, the square cannot
+    assert steps_of(squared) == ["contract", "map"] and "_+in2\n" in squared._code()
+
+
 def test_output_shapes_follow_inputs(ilang):
     attn = readme_attention(ilang)
     q, k, v = (np.zeros(s, np.float32) for s in ((100, 40), (77, 40), (77, 24)))

@@ -270,6 +270,47 @@ def test_mm_t_component_tf32(ilang, oracle):
     assert max_rel_to_peak(mm_t.exec_numpy(a, b), oracle.contract(a, b)) <= 2e-2
 
 
+@pytest.mark.parametrize("precision", ["fp32", "tf32", "bf16", "f16"])
+def test_pointwise_operators_in_the_contraction_epilogue(ilang, oracle, precision):
+    # A layer (product, bias, rectifier) and a gated form compile to one contraction step.  On
+    # every arm the result must be, bit for bit, the arm's contraction followed by the pointwise
+    # kernels (the product of the fp32 arm is the oracle's, so there the whole layer is pinned).
+    i, I = ilang.i, ilang.I
+    rng = np.random.default_rng(31)
+    mm_t = i("ik*jk~ijk") >> i("+ijk~ij")
+    layer = mm_t >> i("ij+j~ij") >> i(">ij~ij")
+    gated = (I | mm_t | I) >> (i("i-ij~ij") | I) >> i("ij*ij~ij") >> i("<ij~ij")
+    assert steps_of_code(layer._code()) == ["contract"] and steps_of_code(gated._code()) == ["contract"]
+    for comp in (mm_t, layer, gated):
+        comp.set_precision(precision)
+    # Ragged against every tile (300 x 260), the CTA-pair kernel (512 x 768), and a shape whose
+    # rows are not a multiple of four floats wide (scalar loads and stores in the epilogue).
+    for m, n, k in ((300, 260, 96), (512, 768, 256), (130, 131, 64)):
+        a = 2 * rng.random((m, k), dtype=np.float32) - 1
+        b = 2 * rng.random((n, k), dtype=np.float32) - 1
+        bias, row = rand((n,), 5), rand((m,), 6)
+        gate = rand((m, n), 7)
+        product = mm_t.exec_numpy(a, b)
+        want = oracle.map_unary(">", oracle.map_binary("+", product, bias, 3))
+        assert np.array_equal(layer.exec_numpy(a, b, bias), want), (precision, m, n, k)
+        want = oracle.map_unary("<", oracle.map_binary("*", oracle.map_binary("-", row, product, 2), gate))
+        assert np.array_equal(gated.exec_numpy(row, a, b, gate), want), (precision, m, n, k)
+        if precision == "fp32":
+            assert max_rel_to_peak(product, oracle.contract(a, b)) <= 1e-5
+    # Batch axes: the per-row operand is indexed by (batch, row).
+    batched = (i("bik*bjk~bijk") >> i("+bijk~bij")) >> i("bij+bi~bij")
+    batched.set_precision(precision)
+    plain = i("bik*bjk~bijk") >> i("+bijk~bij")
+    plain.set_precision(precision)
+    a, b, shift = rand((3, 140, 64), 8), rand((3, 150, 64), 9), rand((3, 140), 10)
+    want = oracle.map_binary("+", plain.exec_numpy(a, b), shift, 1)
+    assert np.array_equal(batched.exec_numpy(a, b, shift), want)
+
+
+def steps_of_code(code):
+    return [line.split()[2] for line in code.splitlines() if line.startswith("step ")]
+
+
 def test_multiple_outputs_identity_and_swap(ilang):
     i, I = ilang.i, ilang.I
     x = rand((6, 5), 4)
