@@ -212,7 +212,8 @@ int launch_strided(const float* a, const float* b, float* y, size_t n, const Str
 // `ij-i~ij` then `^ij~ij` then `ij/i~ij` as three launches moves two full-size intermediates
 // through memory; here each element is read once, run through the operator list in registers and
 // written once.  The operator list is data, not a template: every operator is a warp-uniform switch
-// costing a few instructions per element, well inside what a memory-bound pass has to spare.
+// costing two to three instructions per element, which a pass of cheap operators has to spare
+// (it stays memory-bound) and one with an exact division and an exponential has not.
 // Algorithmic traffic: the operands at their own sizes plus the result, once.
 #ifndef IB_CHAIN_BLOCKS
 #define IB_CHAIN_BLOCKS 4
@@ -233,40 +234,55 @@ struct ChainArgs {
   unsigned cvec, div_mul, div_shift;
 };
 
-// One operand for all of a thread's vectors; the addressing mode is decided once, outside the
-// unrolled loads, so the loads of one operator issue back to back.
-__device__ __forceinline__ void chain_fetch_all(const ChainArgs& a, int code,
-                                                float4 (&dst)[kChainVec], unsigned base, unsigned nvec) {
-  const float* p = a.operand[code];
-  const int mode = a.mode[code];
-  if (mode == 0) {
+// Where a thread's operands come from, for the vectors it holds in one step.  A per-row value or a
+// scalar is one number per vector (`scalars`), a full-size or per-column operand four (`vectors`).
+// FULL: every vector of the step lies inside the array, so nothing is tested per vector.
+template <bool FULL>
+struct ChainSource {
+  const ChainArgs& a;
+  unsigned base, nvec;
+  unsigned row[kChainVec];
+
+  __device__ __forceinline__ ChainSource(const ChainArgs& args, unsigned b, unsigned n)
+      : a(args), base(b), nvec(n) {
+    if (a.needs_rc) {
 #pragma unroll
-    for (int u = 0; u < kChainVec; ++u) {
-      unsigned i = base + u * kThreads;
-      if (i < nvec) dst[u] = __ldcs(reinterpret_cast<const float4*>(p) + i);
-    }
-  } else if (mode == 3) {
-    float s = __ldg(p);
-#pragma unroll
-    for (int u = 0; u < kChainVec; ++u) dst[u] = make_float4(s, s, s, s);
-  } else {
-#pragma unroll
-    for (int u = 0; u < kChainVec; ++u) {
-      unsigned i = base + u * kThreads;
-      if (i < nvec) {
-        unsigned row = a.cvec == 1 ? i
-                                   : __umulhi(i, a.div_mul) >> a.div_shift;
-        if (mode == 1) {
-          float s = __ldg(p + row);
-          dst[u] = make_float4(s, s, s, s);
-        } else {
-          unsigned col = (i - row * a.cvec) * 4u;
-          dst[u] = __ldg(reinterpret_cast<const float4*>(p + col));
-        }
+      for (int u = 0; u < kChainVec; ++u) {
+        const unsigned i = FULL ? base + u * kThreads : min(base + u * kThreads, nvec - 1);
+        row[u] = a.cvec == 1 ? i : __umulhi(i, a.div_mul) >> a.div_shift;
       }
     }
   }
-}
+  __device__ __forceinline__ bool live(int u) const { return FULL || base + u * kThreads < nvec; }
+  __device__ __forceinline__ bool one_per_vector(int code) const {
+    return a.mode[code] == 1 || a.mode[code] == 3;
+  }
+  __device__ __forceinline__ void scalars(int code, float (&s)[kChainVec]) const {
+    const float* p = a.operand[code];
+    if (a.mode[code] == 3) {
+      const float v = __ldg(p);
+#pragma unroll
+      for (int u = 0; u < kChainVec; ++u) s[u] = v;
+    } else {
+#pragma unroll
+      for (int u = 0; u < kChainVec; ++u) s[u] = __ldg(p + row[u]);   // row is clamped when !FULL
+    }
+  }
+  __device__ __forceinline__ void vectors(int code, float4 (&dst)[kChainVec]) const {
+    const float* p = a.operand[code];
+    if (a.mode[code] == 0) {
+#pragma unroll
+      for (int u = 0; u < kChainVec; ++u)
+        if (live(u)) dst[u] = __ldcs(reinterpret_cast<const float4*>(p) + base + u * kThreads);
+    } else {
+#pragma unroll
+      for (int u = 0; u < kChainVec; ++u) {
+        const unsigned i = FULL ? base + u * kThreads : min(base + u * kThreads, nvec - 1);
+        dst[u] = __ldg(reinterpret_cast<const float4*>(p) + (i - row[u] * a.cvec));
+      }
+    }
+  }
+};
 
 // Operators run one after another, so a full-size operand first touched by the third operator
 // would add a trip to memory to the thread's critical path.  Its addresses are known up front: ask
@@ -285,19 +301,6 @@ __device__ __forceinline__ void chain_prefetch_all(const ChainArgs& a, int code,
   }
 }
 
-// acc = f(acc, t) over the sixteen elements a thread holds.
-template <class F>
-__device__ __forceinline__ void chain_apply_all(float4 (&acc)[kChainVec],
-                                                const float4 (&t)[kChainVec], F f) {
-#pragma unroll
-  for (int u = 0; u < kChainVec; ++u) {
-    acc[u].x = f(acc[u].x, t[u].x);
-    acc[u].y = f(acc[u].y, t[u].y);
-    acc[u].z = f(acc[u].z, t[u].z);
-    acc[u].w = f(acc[u].w, t[u].w);
-  }
-}
-
 __device__ __forceinline__ float chain_fetch(const ChainArgs& a, int code, float prev, size_t e,
                                              size_t r, size_t c) {
   if (code == IB_CHAIN_PREV) return prev;
@@ -311,46 +314,90 @@ __device__ __forceinline__ float chain_fetch(const ChainArgs& a, int code, float
 }
 
 // The operator list over the sixteen elements a thread holds.  A thread keeps the running result
-// and, per operator, the other operand; the operator is decided once per step for all sixteen:
-// one warp-uniform branch per operator, straight-line arithmetic behind it.  `fetch(code, dst)`
-// loads operand `code` for the thread's vectors.
-#define IB_CHAIN_CASE(OP)                                                                  \
-  case OP:                                                                                 \
-    if (unary)                                                                             \
-      chain_apply_all(acc, t, [](float p, float) { return apply_unary(OP, p); });          \
-    else                                                                                   \
-      chain_apply_all(acc, t, [](float p, float q) { return apply_binary(OP, p, q); });    \
+// and, per operator, the other operand; operator and operand form are decided once per step for
+// all sixteen (warp-uniform branches, straight-line arithmetic behind them).  The forms: one
+// operand; running value and a vector operand in either order; running value and one number per
+// vector in either order (a per-row value is not spread over four registers first).  `src`
+// supplies operands: one_per_vector(code), scalars(code, s), vectors(code, t).
+enum ChainForm { kUnary, kAccVec, kVecAcc, kAccOne, kOneAcc };
+
+#define IB_CHAIN_LOOP(EXPR)                                        \
+  _Pragma("unroll") for (int u = 0; u < kChainVec; ++u) {          \
+    float4& A = acc[u];                                            \
+    const float4& T = t[u];                                        \
+    const float S = one[u];                                        \
+    (void)T;                                                       \
+    (void)S;                                                       \
+    A = EXPR;                                                      \
+  }
+#define IB_CHAIN_CASE(OP)                                                                          \
+  case OP:                                                                                         \
+    switch (form) {                                                                                \
+      case kUnary:                                                                                 \
+        IB_CHAIN_LOOP(make_float4(apply_unary(OP, A.x), apply_unary(OP, A.y), apply_unary(OP, A.z), \
+                                  apply_unary(OP, A.w)))                                           \
+        break;                                                                                     \
+      case kAccVec:                                                                                \
+        IB_CHAIN_LOOP(make_float4(apply_binary(OP, A.x, T.x), apply_binary(OP, A.y, T.y),          \
+                                  apply_binary(OP, A.z, T.z), apply_binary(OP, A.w, T.w)))         \
+        break;                                                                                     \
+      case kVecAcc:                                                                                \
+        IB_CHAIN_LOOP(make_float4(apply_binary(OP, T.x, A.x), apply_binary(OP, T.y, A.y),          \
+                                  apply_binary(OP, T.z, A.z), apply_binary(OP, T.w, A.w)))         \
+        break;                                                                                     \
+      case kAccOne:                                                                                \
+        IB_CHAIN_LOOP(make_float4(apply_binary(OP, A.x, S), apply_binary(OP, A.y, S),              \
+                                  apply_binary(OP, A.z, S), apply_binary(OP, A.w, S)))             \
+        break;                                                                                     \
+      default:                                                                                     \
+        IB_CHAIN_LOOP(make_float4(apply_binary(OP, S, A.x), apply_binary(OP, S, A.y),              \
+                                  apply_binary(OP, S, A.z), apply_binary(OP, S, A.w)))             \
+        break;                                                                                     \
+    }                                                                                              \
     break;
 
-template <class Fetch>
+template <bool ZERO, class Source>
 __device__ __forceinline__ void chain_run(const ChainArgs& a, float4 (&acc)[kChainVec],
-                                          Fetch fetch) {
-  float4 t[kChainVec];
+                                          const Source& src) {
+  if (ZERO) {
 #pragma unroll
-  for (int u = 0; u < kChainVec; ++u) acc[u] = t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-  fetch(a.lhs[0], acc);
+    for (int u = 0; u < kChainVec; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);   // vectors past the end are not loaded
+  }
+  if (src.one_per_vector(a.lhs[0])) {
+    float first[kChainVec];
+    src.scalars(a.lhs[0], first);
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) acc[u] = make_float4(first[u], first[u], first[u], first[u]);
+  } else {
+    src.vectors(a.lhs[0], acc);
+  }
   for (int k = 0; k < a.n_ops; ++k) {
+    // The other operand lives for one operator only: declared here, so that nothing but the
+    // running value is carried around the loop.
+    float4 t[kChainVec];
+    float one[kChainVec];
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) {
+      t[u] = make_float4(0.f, 0.f, 0.f, 0.f);   // (left unset, the allocator spills four times as much)
+      one[u] = 0.0f;
+    }
     // Every operator after the first takes the running result on at least one side (the host
-    // checks).  With the running result on the right, the two sets of registers change places
-    // first, so that each operator exists once as op(acc) and once as op(acc, other).
+    // checks).
     const int lc = a.lhs[k], rc = a.rhs[k];
-    const bool unary = rc == IB_CHAIN_NONE;
     const bool acc_left = k == 0 || lc == IB_CHAIN_PREV;
     const int other = acc_left ? rc : lc;
-    if (!unary) {
+    int form = kUnary;
+    if (rc != IB_CHAIN_NONE) {
       if (other == IB_CHAIN_PREV) {
+        form = kAccVec;
 #pragma unroll
         for (int u = 0; u < kChainVec; ++u) t[u] = acc[u];
+      } else if (src.one_per_vector(other)) {
+        form = acc_left ? kAccOne : kOneAcc;
+        src.scalars(other, one);
       } else {
-        fetch(other, t);
-      }
-      if (!acc_left) {
-#pragma unroll
-        for (int u = 0; u < kChainVec; ++u) {
-          float4 keep = acc[u];
-          acc[u] = t[u];
-          t[u] = keep;
-        }
+        form = acc_left ? kAccVec : kVecAcc;
+        src.vectors(other, t);
       }
     }
     switch (a.op[k]) {
@@ -376,6 +423,7 @@ __device__ __forceinline__ void chain_run(const ChainArgs& a, float4 (&acc)[kCha
   }
 }
 #undef IB_CHAIN_CASE
+#undef IB_CHAIN_LOOP
 
 // cols % 4 == 0, every full or per-column operand 16-byte aligned, under 2^32 elements.  64
 // registers, so that four blocks share an SM.
@@ -388,13 +436,17 @@ map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, unsig
     for (int e = 0; e < a.n_operands; ++e)
       if (e != a.lhs[0]) chain_prefetch_all(a, e, base, nvec);
     float4 acc[kChainVec];
-    chain_run(a, acc, [&](int code, float4 (&dst)[kChainVec]) {
-      chain_fetch_all(a, code, dst, base, nvec);
-    });
+    if (base + (kChainVec - 1) * kThreads < nvec) {
+      chain_run<false>(a, acc, ChainSource<true>(a, base, nvec));
 #pragma unroll
-    for (int u = 0; u < kChainVec; ++u) {
-      unsigned i = base + u * kThreads;
-      if (i < nvec) __stcs(y + i, acc[u]);
+      for (int u = 0; u < kChainVec; ++u) __stcs(y + base + u * kThreads, acc[u]);
+    } else {
+      chain_run<true>(a, acc, ChainSource<false>(a, base, nvec));
+#pragma unroll
+      for (int u = 0; u < kChainVec; ++u) {
+        unsigned i = base + u * kThreads;
+        if (i < nvec) __stcs(y + i, acc[u]);
+      }
     }
   }
 }
@@ -405,6 +457,32 @@ map_chain_vec(const __grid_constant__ ChainArgs a, float4* __restrict__ y, unsig
 // mask under an "any": the full-size intermediate never exists.  TPR threads share a row (a warp
 // for short rows, the block for long ones); each runs the chain on its vectors and folds them.
 // Algorithmic traffic: the operands at their own sizes plus one value per row.
+// Operands for the vectors cv, cv + TPR, ... of row r (all of a thread's vectors lie in one row).
+template <int TPR>
+struct RowSource {
+  const ChainArgs& a;
+  unsigned r, cv, cvec;
+  __device__ __forceinline__ bool one_per_vector(int code) const {
+    return a.mode[code] == 1 || a.mode[code] == 3;
+  }
+  __device__ __forceinline__ void scalars(int code, float (&s)[kChainVec]) const {
+    const float* p = a.operand[code];
+    const float v = __ldg(a.mode[code] == 1 ? p + r : p);
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) s[u] = v;
+  }
+  __device__ __forceinline__ void vectors(int code, float4 (&dst)[kChainVec]) const {
+    const bool full = a.mode[code] == 0;
+    const float4* p4 = reinterpret_cast<const float4*>(a.operand[code]) +
+                       (full ? static_cast<size_t>(r) * cvec : 0);
+#pragma unroll
+    for (int u = 0; u < kChainVec; ++u) {
+      const unsigned c = cv + u * TPR;
+      if (c < cvec) dst[u] = full ? __ldcs(p4 + c) : __ldg(p4 + c);
+    }
+  }
+};
+
 template <int OP, int TPR>
 __global__ void __launch_bounds__(kThreads, IB_CHAIN_BLOCKS)
 reduce_chain_vec(const __grid_constant__ ChainArgs a, float* __restrict__ y, unsigned rows,
@@ -418,23 +496,7 @@ reduce_chain_vec(const __grid_constant__ ChainArgs a, float* __restrict__ y, uns
     float folded = reduce_identity(OP);
     for (unsigned cv = j; live && cv < cvec; cv += TPR * kChainVec) {
       float4 acc[kChainVec];
-      chain_run(a, acc, [&](int code, float4 (&dst)[kChainVec]) {
-        const float* p = a.operand[code];
-        const int mode = a.mode[code];
-        if (mode == 1 || mode == 3) {
-          const float s = __ldg(mode == 1 ? p + r : p);
-#pragma unroll
-          for (int u = 0; u < kChainVec; ++u) dst[u] = make_float4(s, s, s, s);
-        } else {
-          const float4* p4 = reinterpret_cast<const float4*>(p) +
-                             (mode == 0 ? static_cast<size_t>(r) * cvec : 0);
-#pragma unroll
-          for (int u = 0; u < kChainVec; ++u) {
-            const unsigned c = cv + u * TPR;
-            if (c < cvec) dst[u] = mode == 0 ? __ldcs(p4 + c) : __ldg(p4 + c);
-          }
-        }
-      });
+      chain_run<true>(a, acc, RowSource<TPR>{a, r, cv, cvec});
 #pragma unroll
       for (int u = 0; u < kChainVec; ++u)
         if (cv + u * TPR < cvec)
