@@ -247,16 +247,19 @@ def secondary_metrics(torch, ilang, peaks, only=None, iters=10):
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
-        total = 0.0
+        # Every iteration is queued behind a 256 MiB write that evicts L2, and the host only waits at
+        # the end: the launch of iteration i is issued while the device is still writing, so the
+        # interval between the two events is the device's time for fn, not the host's time to call it.
+        pairs = []
         for _ in range(iters):
-            flush.zero_()                      # 256 MiB write: evicts L2
+            flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
             b.record()
-            torch.cuda.synchronize()
-            total += a.elapsed_time(b)
-        return total / iters
+            pairs.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in pairs) / iters
 
     def wanted(prefix):
         return [n for n in SECONDARY if n.startswith(prefix) and only in (None, n)]
