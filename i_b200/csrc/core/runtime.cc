@@ -14,6 +14,7 @@
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -430,6 +431,21 @@ int run_reduce(const Step& step, const ShapeTable& shapes, const std::vector<siz
     size_t rows = product(oshape);
     size_t cols = product(shape_a, kept);
     return ib_reduce_rows(op, pa, out, rows, cols, dev.stream);
+  }
+  // The kept axes trail the operand in output order and the leading ones fold (`+ij~j`,
+  // `+bij~ij`): a fold down the columns of a [folded][kept] array.
+  if (a.index.size() == step.rank && kept >= 1 && kept < a.index.size() && std::set<size_t>(a.index.begin(), a.index.end()).size() == a.index.size() &&
+      std::equal(step.out.index.begin(), step.out.index.end(), a.index.end() - kept)) {
+    const size_t cols = product(oshape);
+    const size_t rows = product(shape_a, 0, shape_a.size() - kept);
+    const size_t ws_bytes = ib_reduce_leading_workspace_bytes(rows, cols);
+    std::string err;
+    void* ws = nullptr;
+    if (ws_bytes && ws_bytes != SIZE_MAX && !(ws = dev.alloc(ws_bytes, &err))) {
+      set_error(err);
+      return -1;
+    }
+    return ib_reduce_leading(op, pa, out, rows, cols, ws, ws ? ws_bytes : 0, dev.stream);
   }
   std::vector<size_t> red_idx;
   for (size_t x = 0; x < step.rank; ++x)

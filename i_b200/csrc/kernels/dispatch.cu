@@ -185,6 +185,11 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
       too_many_elements({batch, m, n}))
     return SIZE_MAX;
   if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
+  // Vector times a matrix stored [k][columns]: the slabs' partial sums of the fold down its columns.
+  if (m != 1 || n != 1) {
+    if (n == 1 && !a_kmajor) return carve_bytes(dot_leading_axis_floats(k, m));
+    if (m == 1 && !b_kmajor) return carve_bytes(dot_leading_axis_floats(k, n));
+  }
   const double flop = 2.0 * batch * m * n * k;
   if (!wants_tensor(precision, flop)) return 0;
   if (precision == IB_PRECISION_AUTO && contract_prefers_f16(m, n, k)) precision = IB_PRECISION_F16;
@@ -335,6 +340,45 @@ int contract_with_chain(const float* a, const float* b, float* c, size_t batch, 
   if (k == 0) {
     cudaError_t err = cudaMemsetAsync(c, 0, batch * m * n * sizeof(float), s);
     return then_chain(err == cudaSuccess ? 0 : fail("ib_contract: memset failed"));
+  }
+  // Matrix times vector and row-wise dot products have one multiply-add per element read: they
+  // are passes over memory, not tile work, and run as a weighted row fold (fp32 throughout,
+  // whatever precision was asked for: no arm is less exact), one launch per batch entry when the
+  // vector differs between entries.
+  {
+    const bool dots = m == 1 && n == 1;                       // C[b] = A[b][:] . B[b][:]
+    const bool a_rows = !dots && n == 1 && a_kmajor != 0;     // C[b][i] = A[b][i][:] . B[b][:]
+    const bool b_rows = !dots && m == 1 && b_kmajor != 0;     // C[b][j] = A[b][:] . B[b][j][:]
+    constexpr size_t kMostLaunches = 64;
+    if (dots || ((a_rows || b_rows) && batch <= kMostLaunches)) {
+      int rc = 0;
+      if (dots) {
+        rc = dot_rows(a, b, false, c, batch, k, s);
+      } else {
+        const size_t rows = a_rows ? m : n;
+        for (size_t e = 0; e < batch && rc == 0; ++e)
+          rc = dot_rows((a_rows ? a : b) + e * rows * k, (a_rows ? b : a) + e * k, true, c + e * rows,
+                        rows, k, s);
+      }
+      return then_chain(rc);
+    }
+    // The same with the matrix stored k-major the other way round, [k][rows]: vector times
+    // matrix, a weighted fold down the columns.
+    const bool a_cols = !dots && n == 1 && a_kmajor == 0;     // C[b][i] = sum_k A[b][k][i] B[b][k]
+    const bool b_cols = !dots && m == 1 && b_kmajor == 0;     // C[b][j] = sum_k A[b][k] B[b][k][j]
+    if ((a_cols || b_cols) && batch <= kMostLaunches) {
+      const size_t cols = a_cols ? m : n;
+      const size_t need = dot_leading_axis_floats(k, cols);
+      float* partials = workspace && workspace_bytes / sizeof(float) >= need &&
+                                (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0
+                            ? static_cast<float*>(workspace)
+                            : nullptr;
+      int rc = 0;
+      for (size_t e = 0; e < batch && rc == 0; ++e)
+        rc = dot_leading_axis((a_cols ? a : b) + e * k * cols, (a_cols ? b : a) + e * k, c + e * cols, k,
+                              cols, partials, s);
+      return then_chain(rc);
+    }
   }
   const double flop = 2.0 * batch * m * n * k;
   if (precision == IB_PRECISION_AUTO && wants_tensor(precision, flop) && contract_prefers_f16(m, n, k) &&

@@ -29,6 +29,16 @@ int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const 
                                float* kr, size_t k_elems, const float* v, float* vt, size_t batch,
                                size_t nk, size_t dv, size_t pitch, cudaStream_t s);
 
+// reduce.cu — y[r] = sum_c x[r][c] * w[r][c], or x[r][c] * w[c] with w_is_vector: row-wise dot
+// products and matrix times vector as one pass over memory (products rounded, then a tree sum).
+int dot_rows(const float* x, const float* w, bool w_is_vector, float* y, size_t rows, size_t cols,
+             cudaStream_t s);
+// y[c] = sum_r x[r][c] * w[r] (vector times matrix); `partials` holds dot_leading_axis_floats
+// floats (null: the rows are folded as one slab).
+size_t dot_leading_axis_floats(size_t rows, size_t cols);
+int dot_leading_axis(const float* x, const float* w, float* y, size_t rows, size_t cols,
+                     float* partials, cudaStream_t s);
+
 // device_util.cu — encodes a TMA descriptor for a dense fp32 tensor
 // [batch][rows][cols] (cols contiguous, `row_pitch` elements between rows) read
 // in boxes of 32 columns (128 bytes, 128-byte swizzle) x box_rows rows.

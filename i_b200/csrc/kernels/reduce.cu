@@ -24,35 +24,52 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kUnroll = IB_RED_UNROLL;   // 16-byte loads in flight per thread in the one-row-per-CTA kernel
 
 // One warp per row: rows of up to a few thousand columns.
-template <int OP>
+// WEIGHT: what is folded is x itself (kPlain), x times a second array of the same shape
+// (kTimesRows: row-wise dot products) or x times one vector of `cols` values (kTimesVector: matrix
+// times vector).  The product is rounded before it is added, as the reference's `tmp = a * b;
+// c = c + tmp` is (ilang-python/annotated-flashattn.c:67-85).
+enum Weight { kPlain, kTimesRows, kTimesVector };
+
+template <int WEIGHT>
+__device__ __forceinline__ float4 weighted(float4 v, const float4* w_row4, const float4* w_vec4, size_t i) {
+  if (WEIGHT == kPlain) return v;
+  const float4 w = WEIGHT == kTimesRows ? __ldcs(w_row4 + i) : __ldg(w_vec4 + i);
+  return make_float4(__fmul_rn(v.x, w.x), __fmul_rn(v.y, w.y), __fmul_rn(v.z, w.z), __fmul_rn(v.w, w.w));
+}
+
+template <int OP, int WEIGHT = kPlain>
 __global__ void __launch_bounds__(kThreads)
 reduce_rows_warp(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols,
-                 bool vec) {
+                 bool vec, const float* __restrict__ w = nullptr) {
   const int lane = threadIdx.x & 31;
   const size_t warps_total = static_cast<size_t>(gridDim.x) * kWarps;
   for (size_t r = static_cast<size_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5); r < rows;
        r += warps_total) {
     const float* row = x + r * cols;
+    const float* wrow = WEIGHT == kTimesRows ? w + r * cols : w;
     float acc = reduce_identity(OP);
     if (vec) {
       const float4* row4 = reinterpret_cast<const float4*>(row);
+      const float4* w4 = reinterpret_cast<const float4*>(wrow);
       const size_t nvec = cols / 4;
       constexpr int kWarpUnroll = 4;          // 16-byte loads in flight per lane
       size_t i = lane;
       for (; i + (kWarpUnroll - 1) * 32 < nvec; i += kWarpUnroll * 32) {
         float4 v[kWarpUnroll];
 #pragma unroll
-        for (int u = 0; u < kWarpUnroll; ++u) v[u] = __ldcs(row4 + i + u * 32);
+        for (int u = 0; u < kWarpUnroll; ++u)
+          v[u] = weighted<WEIGHT>(__ldcs(row4 + i + u * 32), w4, w4, i + u * 32);
 #pragma unroll
         for (int u = 0; u < kWarpUnroll; ++u)
           acc = fold<OP>(acc, fold<OP>(fold<OP>(v[u].x, v[u].y), fold<OP>(v[u].z, v[u].w)));
       }
       for (; i < nvec; i += 32) {
-        float4 v = __ldcs(row4 + i);
+        float4 v = weighted<WEIGHT>(__ldcs(row4 + i), w4, w4, i);
         acc = fold<OP>(acc, fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
       }
     } else {
-      for (size_t i = lane; i < cols; i += 32) acc = fold<OP>(acc, row[i]);
+      for (size_t i = lane; i < cols; i += 32)
+        acc = fold<OP>(acc, WEIGHT == kPlain ? row[i] : __fmul_rn(row[i], wrow[i]));
     }
     acc = warp_fold<OP>(acc);
     if (lane == 0) y[r] = acc;
@@ -60,34 +77,38 @@ reduce_rows_warp(const float* __restrict__ x, float* __restrict__ y, size_t rows
 }
 
 // One CTA per row: long rows.
-template <int OP>
+template <int OP, int WEIGHT = kPlain>
 __global__ void __launch_bounds__(kThreads)
 reduce_rows_block(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols,
-                  bool vec) {
+                  bool vec, const float* __restrict__ w = nullptr) {
   __shared__ float partial[kWarps];
   for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const float* row = x + r * cols;
+    const float* wrow = WEIGHT == kTimesRows ? w + r * cols : w;
     float accs[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) accs[u] = reduce_identity(OP);
     if (vec) {
       const float4* row4 = reinterpret_cast<const float4*>(row);
+      const float4* w4 = reinterpret_cast<const float4*>(wrow);
       const size_t nvec = cols / 4;
       size_t i = threadIdx.x;
       for (; i + (kUnroll - 1) * kThreads < nvec; i += kUnroll * kThreads) {
         float4 v[kUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) v[u] = __ldcs(row4 + i + u * kThreads);
+        for (int u = 0; u < kUnroll; ++u)
+          v[u] = weighted<WEIGHT>(__ldcs(row4 + i + u * kThreads), w4, w4, i + u * kThreads);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
           accs[u] = fold<OP>(accs[u], fold<OP>(fold<OP>(v[u].x, v[u].y), fold<OP>(v[u].z, v[u].w)));
       }
       for (; i < nvec; i += kThreads) {
-        const float4 v = __ldcs(row4 + i);
+        const float4 v = weighted<WEIGHT>(__ldcs(row4 + i), w4, w4, i);
         accs[0] = fold<OP>(accs[0], fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
       }
     } else {
-      for (size_t i = threadIdx.x; i < cols; i += kThreads) accs[0] = fold<OP>(accs[0], row[i]);
+      for (size_t i = threadIdx.x; i < cols; i += kThreads)
+        accs[0] = fold<OP>(accs[0], WEIGHT == kPlain ? row[i] : __fmul_rn(row[i], wrow[i]));
     }
     float acc0 = accs[0];
 #pragma unroll
@@ -160,6 +181,152 @@ int launch_rows(const float* x, float* y, size_t rows, size_t cols, cudaStream_t
   return check_launch("ib_reduce_rows");
 }
 
+template <int WEIGHT>
+int launch_dot_rows(const float* x, const float* w, float* y, size_t rows, size_t cols, cudaStream_t s) {
+  const bool vec = cols % 4 == 0 && aligned16(x) && aligned16(w);
+  const size_t cap = static_cast<size_t>(kNumSMs) * IB_RED_CAP;
+  if (cols <= 2048) {
+    const size_t blocks = (rows + kWarps - 1) / kWarps;
+    reduce_rows_warp<IB_OP_ADD, WEIGHT><<<static_cast<int>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
+        x, y, rows, cols, vec, w);
+  } else {
+    reduce_rows_block<IB_OP_ADD, WEIGHT><<<static_cast<int>(rows < cap ? rows : cap), kThreads, 0, s>>>(
+        x, y, rows, cols, vec, w);
+  }
+  return check_launch("ib_contract (rows)");
+}
+
+// ---- folds of the leading axis: y[c] = fold over r of x[r][c] (`+ij~j`, `+bij~ij`) ------------
+//
+// A thread owns four neighbouring columns and walks down a slab of rows, eight 16-byte loads in
+// flight; the threads of a CTA that one row does not fill take further rows (narrow arrays: a row
+// of 64 columns is 16 threads wide, so a CTA walks 16 rows at a time) and meet in shared memory.
+// The rows are cut into slabs so that the grid fills the machine; with more than one slab the
+// kernel writes one partial row per slab and runs once more over those.  The order of the fold is
+// fixed by the shape alone, so results repeat from run to run (no atomics).  ROW_WEIGHT:
+// x[r][c] * w[r] is folded instead of x[r][c] (vector times matrix, the product rounded before it
+// is added).  Algorithmic traffic: rows*cols*4 + cols*4 bytes.
+constexpr int kColsUnroll = 8;
+
+template <int OP, bool ROW_WEIGHT, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+fold_leading_axis(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y,
+                  size_t rows, size_t cols, size_t rows_per_slab, int lanes_log2) {
+  constexpr int kWidth = VEC ? 4 : 1;
+  __shared__ float meet[kThreads][kWidth];
+  // lanes = 2^lanes_log2 threads side by side cover a row's columns in this CTA; kThreads / lanes
+  // rows are in flight at a time.
+  const int lanes = 1 << lanes_log2;
+  const int tx = threadIdx.x & (lanes - 1), ty = threadIdx.x >> lanes_log2;
+  const size_t phases = kThreads >> lanes_log2;
+  const size_t c = (static_cast<size_t>(blockIdx.x) * lanes + tx) * kWidth;
+  const bool live = c < cols;
+  const size_t r_lo = static_cast<size_t>(blockIdx.y) * rows_per_slab;
+  const size_t r_hi = r_lo + rows_per_slab < rows ? r_lo + rows_per_slab : rows;
+  float acc[kWidth];
+#pragma unroll
+  for (int e = 0; e < kWidth; ++e) acc[e] = reduce_identity(OP);
+  auto take = [&](size_t r, float (&v)[kWidth]) {
+    if (VEC) {
+      const float4 q = __ldcs(reinterpret_cast<const float4*>(x + r * cols + c));
+      v[0] = q.x;
+      if (kWidth == 4) { v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+    } else {
+      v[0] = x[r * cols + c];
+    }
+    if (ROW_WEIGHT) {
+      const float s = __ldg(w + r);
+#pragma unroll
+      for (int e = 0; e < kWidth; ++e) v[e] = __fmul_rn(v[e], s);
+    }
+  };
+  if (live) {
+    size_t r = r_lo + ty;
+    for (; r + (kColsUnroll - 1) * phases < r_hi; r += kColsUnroll * phases) {
+      float v[kColsUnroll][kWidth];
+#pragma unroll
+      for (int u = 0; u < kColsUnroll; ++u) take(r + u * phases, v[u]);
+#pragma unroll
+      for (int u = 0; u < kColsUnroll; ++u)
+#pragma unroll
+        for (int e = 0; e < kWidth; ++e) acc[e] = fold<OP>(acc[e], v[u][e]);
+    }
+    for (; r < r_hi; r += phases) {
+      float v[kWidth];
+      take(r, v);
+#pragma unroll
+      for (int e = 0; e < kWidth; ++e) acc[e] = fold<OP>(acc[e], v[e]);
+    }
+  }
+  if (phases > 1) {
+#pragma unroll
+    for (int e = 0; e < kWidth; ++e) meet[threadIdx.x][e] = acc[e];
+    __syncthreads();
+    if (ty != 0) return;
+    for (size_t p = 1; p < phases; ++p)
+#pragma unroll
+      for (int e = 0; e < kWidth; ++e) acc[e] = fold<OP>(acc[e], meet[p * lanes + tx][e]);
+  }
+  if (!live) return;
+  float* dst = y + static_cast<size_t>(blockIdx.y) * cols + c;
+  if (VEC) {
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[kWidth > 1 ? 1 : 0], acc[kWidth > 2 ? 2 : 0],
+                                                  acc[kWidth > 3 ? 3 : 0]);
+  } else {
+    dst[0] = acc[0];
+  }
+}
+
+// Threads of a CTA side by side on one row, as a power of two: as many as the row has column
+// groups (of four columns when `vec`), at most the whole CTA.
+int leading_axis_lanes_log2(size_t cols, bool vec) {
+  const size_t groups = vec ? cols / 4 : cols;
+  int l = 0;
+  while ((1u << l) < kThreads && (static_cast<size_t>(1) << l) < groups) ++l;
+  return l;
+}
+
+// Slabs of rows for a fold of `rows` x `cols`: enough CTAs to fill the machine several times
+// over, every thread with at least 16 rows.  (Sized for the four-column form; the one-column
+// form of the same shape has more CTAs per slab and fills the machine sooner.)
+size_t leading_axis_slabs(size_t rows, size_t cols) {
+  const int l = leading_axis_lanes_log2(cols, cols % 4 == 0);
+  const size_t groups = cols % 4 == 0 ? cols / 4 : cols;
+  const size_t col_blocks = (groups + (1u << l) - 1) >> l;
+  const size_t phases = kThreads >> l;
+  size_t slabs = (static_cast<size_t>(kNumSMs) * 8 + col_blocks - 1) / col_blocks;
+  if (slabs > rows / (16 * phases)) slabs = rows / (16 * phases);
+  if (slabs > 65535) slabs = 65535;
+  return slabs < 1 ? 1 : slabs;
+}
+
+template <int OP, bool ROW_WEIGHT>
+int launch_leading_axis_once(const float* x, const float* w, float* y, size_t rows, size_t cols,
+                             size_t rows_per_slab, size_t slabs, cudaStream_t s) {
+  const bool vec = cols % 4 == 0 && aligned16(x) && aligned16(y);
+  const int l = leading_axis_lanes_log2(cols, vec);
+  const size_t groups = vec ? cols / 4 : cols;
+  dim3 grid(static_cast<unsigned>((groups + (1u << l) - 1) >> l), static_cast<unsigned>(slabs));
+  if (vec)
+    fold_leading_axis<OP, ROW_WEIGHT, true><<<grid, kThreads, 0, s>>>(x, w, y, rows, cols, rows_per_slab, l);
+  else
+    fold_leading_axis<OP, ROW_WEIGHT, false><<<grid, kThreads, 0, s>>>(x, w, y, rows, cols, rows_per_slab, l);
+  return check_launch("ib_reduce_leading");
+}
+
+template <int OP, bool ROW_WEIGHT>
+int launch_leading_axis(const float* x, const float* w, float* y, size_t rows, size_t cols,
+                        float* partials, cudaStream_t s) {
+  const size_t slabs = partials ? leading_axis_slabs(rows, cols) : 1;
+  const size_t rows_per_slab = (rows + slabs - 1) / slabs;
+  const size_t used = rows_per_slab ? (rows + rows_per_slab - 1) / rows_per_slab : 1;   // slabs that hold rows
+  if (used <= 1) return launch_leading_axis_once<OP, ROW_WEIGHT>(x, w, y, rows, cols, rows ? rows : 1, 1, s);
+  if (int rc = launch_leading_axis_once<OP, ROW_WEIGHT>(x, w, partials, rows, cols, rows_per_slab, used, s))
+    return rc;
+  // The partial rows, one per slab, folded the same way as one slab.
+  return launch_leading_axis_once<OP, false>(partials, nullptr, y, used, cols, used, 1, s);
+}
+
 template <int OP>
 int launch_strided(const float* x, float* y, size_t n_out, size_t n_red, const FoldArgs& args,
                    cudaStream_t s) {
@@ -171,6 +338,25 @@ int launch_strided(const float* x, float* y, size_t n_out, size_t n_red, const F
 }
 
 }  // namespace
+
+size_t dot_leading_axis_floats(size_t rows, size_t cols) {
+  const size_t slabs = leading_axis_slabs(rows, cols);
+  return slabs > 1 ? slabs * cols : 0;
+}
+
+int dot_leading_axis(const float* x, const float* w, float* y, size_t rows, size_t cols,
+                     float* partials, cudaStream_t s) {
+  if (cols == 0) return 0;
+  return launch_leading_axis<IB_OP_ADD, true>(x, w, y, rows, cols, partials, s);
+}
+
+int dot_rows(const float* x, const float* w, bool w_is_vector, float* y, size_t rows, size_t cols,
+             cudaStream_t s) {
+  if (rows == 0) return 0;
+  return w_is_vector ? launch_dot_rows<kTimesVector>(x, w, y, rows, cols, s)
+                     : launch_dot_rows<kTimesRows>(x, w, y, rows, cols, s);
+}
+
 }  // namespace ib
 
 #define IB_DISPATCH_FOLD(op, CALL)                                             \
@@ -191,6 +377,25 @@ extern "C" int ib_reduce_rows(int op, const float* x, float* y, size_t rows, siz
   if (!y || (!x && cols != 0)) return ib::fail("ib_reduce_rows: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define CALL(OP) ib::launch_rows<OP>(x, y, rows, cols, s)
+  IB_DISPATCH_FOLD(op, CALL)
+#undef CALL
+}
+
+extern "C" size_t ib_reduce_leading_workspace_bytes(size_t rows, size_t cols) {
+  if (cols != 0 && rows > SIZE_MAX / sizeof(float) / cols) return SIZE_MAX;
+  return ib::dot_leading_axis_floats(rows, cols) * sizeof(float);
+}
+
+extern "C" int ib_reduce_leading(int op, const float* x, float* y, size_t rows, size_t cols,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (cols == 0) return 0;
+  if (!y || (!x && rows != 0)) return ib::fail("ib_reduce_leading: null pointer");
+  // Without (enough) workspace the rows are folded as one slab: correct, slower on tall inputs.
+  float* partials = workspace_bytes >= ib_reduce_leading_workspace_bytes(rows, cols) && workspace_bytes > 0
+                        ? static_cast<float*>(workspace)
+                        : nullptr;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CALL(OP) ib::launch_leading_axis<OP, false>(x, nullptr, y, rows, cols, partials, s)
   IB_DISPATCH_FOLD(op, CALL)
 #undef CALL
 }

@@ -307,6 +307,67 @@ def test_pointwise_operators_in_the_contraction_epilogue(ilang, oracle, precisio
     assert np.array_equal(batched.exec_numpy(a, b, shift), want)
 
 
+@pytest.mark.parametrize("precision", ["auto", "fp32", "tf32"])
+def test_matrix_vector_and_row_dot_contractions(ilang, precision):
+    # Contractions with one output axis (or none) per batch entry are passes over memory: they run
+    # as a weighted row fold in fp32 under every precision.  Short rows (a warp per row), long rows
+    # (a block per row), widths that are not a multiple of four, batch entries with their own
+    # vector, the vector on either side.
+    i = ilang.i
+
+    def check(comp, args, want):
+        comp.set_precision(precision)
+        got = comp.exec_numpy(*args)
+        assert got.shape == want.shape
+        assert max_rel_to_peak(got, want) <= 2e-6, (precision, [a.shape for a in args])
+
+    for rows, k in ((300, 1000), (70, 4100), (129, 1001), (5, 3)):
+        a, b, x = rand((rows, k), 11), rand((rows, k), 12), rand((k,), 13)
+        a64, b64, x64 = (t.astype(np.float64) for t in (a, b, x))
+        check(i("ij*j~ij") >> i("+ij~i"), (a, x), a64 @ x64)                    # matrix times vector
+        check(i("j*ij~ij") >> i("+ij~i"), (x, a), a64 @ x64)                    # vector on the left
+        check(i("ij*ij~ij") >> i("+ij~i"), (a, b), (a64 * b64).sum(axis=1))     # row-wise dot products
+        # The matrix stored the other way round, [k][rows]: a weighted fold down its columns.
+        at = np.ascontiguousarray(a.T)
+        check(i("j*ji~ji") >> i("+ji~i"), (x, at), a64 @ x64)
+        check(i("ji*j~ji") >> i("+ji~i"), (at, x), a64 @ x64)
+    a, x = rand((3, 40, 260), 14), rand((3, 260), 15)
+    check(i("bij*bj~bij") >> i("+bij~bi"), (a, x), np.einsum("bij,bj->bi", a.astype(np.float64), x.astype(np.float64)))
+    y = rand((3, 40), 21)
+    check(i("bi*bij~bij") >> i("+bij~bj"), (y, a), np.einsum("bi,bij->bj", y.astype(np.float64), a.astype(np.float64)))
+    u, v = rand((2048,), 16), rand((2048,), 17)
+    check(i("i*i~i") >> i("+i~."), (u, v), np.asarray(u.astype(np.float64) @ v.astype(np.float64)))
+    # A layer on a vector: product, bias, rectifier (the operators after the product are a pass of
+    # their own here: there is no tile epilogue to put them in).
+    w, x, bias = rand((96, 512), 18), rand((512,), 19), rand((96,), 20)
+    layer = i("ij*j~ij") >> i("+ij~i") >> i("i+i~i") >> i(">i~i")
+    want = np.maximum(w.astype(np.float64) @ x.astype(np.float64) + bias, 0)
+    check(layer, (w, x, bias), want)
+
+
+def test_folds_of_leading_axes(ilang, oracle):
+    # `+ij~j`, `>bij~ij`, `+bij~j`: the kept axes trail, the folded ones lead; rows are folded in
+    # slabs and the slabs' results once more.  Maxima and the logic folds are exact, sums differ
+    # from a serial sum by rounding only, and repeat from run to run.
+    i = ilang.i
+    for rows, cols in ((5000, 260), (33, 4100), (1001, 129), (7, 1), (100000, 8)):
+        x = rand((rows, cols), 22)
+        got = i("+ij~j").exec_numpy(x)
+        assert got.shape == (cols,)
+        assert max_rel_to_peak(got, x.astype(np.float64).sum(axis=0)) <= 2e-6, (rows, cols)
+        assert np.array_equal(got, i("+ij~j").exec_numpy(x))
+        assert np.array_equal(i(">ij~j").exec_numpy(x), x.max(axis=0))
+        assert np.array_equal(i("<ij~j").exec_numpy(x), x.min(axis=0))
+        truth = (x > 0.5).astype(np.float32)
+        assert np.array_equal(i("||ij~j").exec_numpy(truth), truth.max(axis=0))
+        assert np.array_equal(i("^^ij~j").exec_numpy(truth), truth.sum(axis=0) % 2)
+    x = rand((6, 300, 44), 23)
+    assert np.array_equal(i(">bij~ij").exec_numpy(x), x.max(axis=0))
+    assert max_rel_to_peak(i("+bij~j").exec_numpy(x), x.astype(np.float64).sum(axis=(0, 1))) <= 2e-6
+    # A fold of the middle axis keeps the general strided kernel.
+    assert np.array_equal(i(">bij~bj").exec_numpy(x), x.max(axis=1))
+
+
 def steps_of_code(code):
     return [line.split()[2] for line in code.splitlines() if line.startswith("step ")]
 
