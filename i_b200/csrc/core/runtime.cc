@@ -430,7 +430,15 @@ int run_reduce(const Step& step, const ShapeTable& shapes, const std::vector<siz
       std::equal(step.out.index.begin(), step.out.index.end(), a.index.begin())) {
     size_t rows = product(oshape);
     size_t cols = product(shape_a, kept);
-    return ib_reduce_rows(op, pa, out, rows, cols, dev.stream);
+    const size_t ws_bytes = ib_reduce_rows_workspace_bytes(rows, cols);
+    if (ws_bytes == 0) return ib_reduce_rows(op, pa, out, rows, cols, dev.stream);
+    std::string err;
+    void* ws = dev.alloc(ws_bytes, &err);
+    if (!ws) {
+      set_error(err);
+      return -1;
+    }
+    return ib_reduce_rows_split(op, pa, out, rows, cols, ws, ws_bytes, dev.stream);
   }
   // The kept axes trail the operand in output order and the leading ones fold (`+ij~j`,
   // `+bij~ij`): a fold down the columns of a [folded][kept] array.

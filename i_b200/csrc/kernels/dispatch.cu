@@ -189,6 +189,8 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
   if (m != 1 || n != 1) {
     if (n == 1 && !a_kmajor) return carve_bytes(dot_leading_axis_floats(k, m));
     if (m == 1 && !b_kmajor) return carve_bytes(dot_leading_axis_floats(k, n));
+  } else {
+    return carve_bytes(long_rows_floats(batch, k));   // dot products of few, very long rows
   }
   const double flop = 2.0 * batch * m * n * k;
   if (!wants_tensor(precision, flop)) return 0;
@@ -353,7 +355,12 @@ int contract_with_chain(const float* a, const float* b, float* c, size_t batch, 
     if (dots || ((a_rows || b_rows) && batch <= kMostLaunches)) {
       int rc = 0;
       if (dots) {
-        rc = dot_rows(a, b, false, c, batch, k, s);
+        const size_t need = long_rows_floats(batch, k);
+        float* partials = need && workspace && workspace_bytes / sizeof(float) >= need &&
+                                  (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0
+                              ? static_cast<float*>(workspace)
+                              : nullptr;
+        rc = dot_rows(a, b, false, c, batch, k, s, partials);
       } else {
         const size_t rows = a_rows ? m : n;
         for (size_t e = 0; e < batch && rc == 0; ++e)

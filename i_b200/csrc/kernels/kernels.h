@@ -31,8 +31,11 @@ int prepare_attention_operands(const float* q, float* qr, size_t q_elems, const 
 
 // reduce.cu — y[r] = sum_c x[r][c] * w[r][c], or x[r][c] * w[c] with w_is_vector: row-wise dot
 // products and matrix times vector as one pass over memory (products rounded, then a tree sum).
+// Few rows of very many columns are folded in segments; `partials` then holds long_rows_floats
+// floats (null: every row is folded whole).
+size_t long_rows_floats(size_t rows, size_t cols);
 int dot_rows(const float* x, const float* w, bool w_is_vector, float* y, size_t rows, size_t cols,
-             cudaStream_t s);
+             cudaStream_t s, float* partials = nullptr);
 // y[c] = sum_r x[r][c] * w[r] (vector times matrix); `partials` holds dot_leading_axis_floats
 // floats (null: the rows are folded as one slab).
 size_t dot_leading_axis_floats(size_t rows, size_t cols);

@@ -77,21 +77,26 @@ reduce_rows_warp(const float* __restrict__ x, float* __restrict__ y, size_t rows
 }
 
 // One CTA per row: long rows.
+// A row may be cut into `segs` segments of `seg_len` columns (a multiple of four; the last one
+// shorter), each folded by a CTA of its own into y[row * segs + segment]: few rows of millions of
+// columns (a sum over a whole array) would otherwise keep one CTA each busy and the rest idle.
 template <int OP, int WEIGHT = kPlain>
 __global__ void __launch_bounds__(kThreads)
 reduce_rows_block(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols,
-                  bool vec, const float* __restrict__ w = nullptr) {
+                  bool vec, const float* __restrict__ w = nullptr, size_t segs = 1, size_t seg_len = 0) {
   __shared__ float partial[kWarps];
-  for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float* row = x + r * cols;
-    const float* wrow = WEIGHT == kTimesRows ? w + r * cols : w;
+  for (size_t r = blockIdx.x; r < rows * segs; r += gridDim.x) {
+    const size_t whole = r / segs, at = (r - whole * segs) * seg_len;
+    const size_t len = segs == 1 ? cols : (cols - at < seg_len ? cols - at : seg_len);
+    const float* row = x + whole * cols + at;
+    const float* wrow = WEIGHT == kTimesRows ? w + whole * cols + at : w + at;
     float accs[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) accs[u] = reduce_identity(OP);
     if (vec) {
       const float4* row4 = reinterpret_cast<const float4*>(row);
       const float4* w4 = reinterpret_cast<const float4*>(wrow);
-      const size_t nvec = cols / 4;
+      const size_t nvec = len / 4;
       size_t i = threadIdx.x;
       for (; i + (kUnroll - 1) * kThreads < nvec; i += kUnroll * kThreads) {
         float4 v[kUnroll];
@@ -107,7 +112,7 @@ reduce_rows_block(const float* __restrict__ x, float* __restrict__ y, size_t row
         accs[0] = fold<OP>(accs[0], fold<OP>(fold<OP>(v.x, v.y), fold<OP>(v.z, v.w)));
       }
     } else {
-      for (size_t i = threadIdx.x; i < cols; i += kThreads)
+      for (size_t i = threadIdx.x; i < len; i += kThreads)
         accs[0] = fold<OP>(accs[0], WEIGHT == kPlain ? row[i] : __fmul_rn(row[i], wrow[i]));
     }
     float acc0 = accs[0];
@@ -165,8 +170,44 @@ reduce_strided(const float* __restrict__ x, float* __restrict__ y, size_t n_out,
   }
 }
 
+// Segments per row for few, very long rows (1 = the row stays whole): enough CTAs to fill the
+// machine, at least 8192 columns each, a multiple of four columns long.
+struct RowSplit {
+  size_t segs = 1, seg_len = 0;
+};
+RowSplit split_long_rows(size_t rows, size_t cols) {
+  RowSplit sp;
+  const size_t want = static_cast<size_t>(kNumSMs) * 8;
+  if (rows == 0 || rows >= static_cast<size_t>(kNumSMs) * 2 || cols < 4 * 8192) return sp;
+  size_t segs = (want + rows - 1) / rows;
+  if (segs > cols / 8192) segs = cols / 8192;
+  if (segs < 2) return sp;
+  sp.seg_len = ((cols + segs - 1) / segs + 3) / 4 * 4;
+  sp.segs = (cols + sp.seg_len - 1) / sp.seg_len;
+  return sp;
+}
+
+template <int OP, int WEIGHT>
+int launch_rows_split(const float* x, const float* w, float* y, size_t rows, size_t cols, float* partials,
+                      cudaStream_t s) {
+  const RowSplit sp = split_long_rows(rows, cols);
+  const bool vec = cols % 4 == 0 && aligned16(x) && (WEIGHT == kPlain || aligned16(w));
+  const size_t cap = static_cast<size_t>(kNumSMs) * IB_RED_CAP;
+  const size_t ctas = rows * sp.segs;
+  reduce_rows_block<OP, WEIGHT><<<static_cast<int>(ctas < cap ? ctas : cap), kThreads, 0, s>>>(
+      x, partials, rows, cols, vec, w, sp.segs, sp.seg_len);
+  if (int rc = check_launch("ib_reduce_rows (segments)")) return rc;
+  const size_t blocks = (rows + kWarps - 1) / kWarps;
+  reduce_rows_warp<OP><<<static_cast<int>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
+      partials, y, rows, sp.segs, sp.segs % 4 == 0 && aligned16(partials));
+  return check_launch("ib_reduce_rows (partials)");
+}
+
 template <int OP>
-int launch_rows(const float* x, float* y, size_t rows, size_t cols, cudaStream_t s) {
+int launch_rows(const float* x, float* y, size_t rows, size_t cols, cudaStream_t s,
+                float* partials = nullptr) {
+  if (partials && split_long_rows(rows, cols).segs > 1)
+    return launch_rows_split<OP, kPlain>(x, nullptr, y, rows, cols, partials, s);
   const bool vec = cols % 4 == 0 && aligned16(x);
   if (cols <= 2048) {
     size_t blocks = (rows + kWarps - 1) / kWarps;
@@ -182,7 +223,10 @@ int launch_rows(const float* x, float* y, size_t rows, size_t cols, cudaStream_t
 }
 
 template <int WEIGHT>
-int launch_dot_rows(const float* x, const float* w, float* y, size_t rows, size_t cols, cudaStream_t s) {
+int launch_dot_rows(const float* x, const float* w, float* y, size_t rows, size_t cols, cudaStream_t s,
+                    float* partials) {
+  if (partials && split_long_rows(rows, cols).segs > 1)
+    return launch_rows_split<IB_OP_ADD, WEIGHT>(x, w, y, rows, cols, partials, s);
   const bool vec = cols % 4 == 0 && aligned16(x) && aligned16(w);
   const size_t cap = static_cast<size_t>(kNumSMs) * IB_RED_CAP;
   if (cols <= 2048) {
@@ -350,11 +394,16 @@ int dot_leading_axis(const float* x, const float* w, float* y, size_t rows, size
   return launch_leading_axis<IB_OP_ADD, true>(x, w, y, rows, cols, partials, s);
 }
 
+size_t long_rows_floats(size_t rows, size_t cols) {
+  const RowSplit sp = split_long_rows(rows, cols);
+  return sp.segs > 1 ? rows * sp.segs : 0;
+}
+
 int dot_rows(const float* x, const float* w, bool w_is_vector, float* y, size_t rows, size_t cols,
-             cudaStream_t s) {
+             cudaStream_t s, float* partials) {
   if (rows == 0) return 0;
-  return w_is_vector ? launch_dot_rows<kTimesVector>(x, w, y, rows, cols, s)
-                     : launch_dot_rows<kTimesRows>(x, w, y, rows, cols, s);
+  return w_is_vector ? launch_dot_rows<kTimesVector>(x, w, y, rows, cols, s, partials)
+                     : launch_dot_rows<kTimesRows>(x, w, y, rows, cols, s, partials);
 }
 
 }  // namespace ib
@@ -377,6 +426,22 @@ extern "C" int ib_reduce_rows(int op, const float* x, float* y, size_t rows, siz
   if (!y || (!x && cols != 0)) return ib::fail("ib_reduce_rows: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define CALL(OP) ib::launch_rows<OP>(x, y, rows, cols, s)
+  IB_DISPATCH_FOLD(op, CALL)
+#undef CALL
+}
+
+extern "C" size_t ib_reduce_rows_workspace_bytes(size_t rows, size_t cols) {
+  return ib::long_rows_floats(rows, cols) * sizeof(float);
+}
+
+extern "C" int ib_reduce_rows_split(int op, const float* x, float* y, size_t rows, size_t cols,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  if (rows == 0) return 0;
+  if (!y || (!x && cols != 0)) return ib::fail("ib_reduce_rows: null pointer");
+  const size_t need = ib_reduce_rows_workspace_bytes(rows, cols);
+  float* partials = need && workspace && workspace_bytes >= need ? static_cast<float*>(workspace) : nullptr;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CALL(OP) ib::launch_rows<OP>(x, y, rows, cols, s, partials)
   IB_DISPATCH_FOLD(op, CALL)
 #undef CALL
 }

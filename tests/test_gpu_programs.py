@@ -368,6 +368,26 @@ def test_folds_of_leading_axes(ilang, oracle):
     assert np.array_equal(i(">bij~bj").exec_numpy(x), x.max(axis=1))
 
 
+def test_folds_of_few_very_long_rows(ilang):
+    # A fold of a whole array is one row of millions of columns: it is cut into segments, one CTA
+    # each, and the segments' results are folded once more.  Also the dot product of two long
+    # vectors, and widths that are not a multiple of four.
+    i = ilang.i
+    for shape in ((3000, 3000), (5, 1000003), (40, 70001)):
+        x = rand(shape, 24)
+        x64 = x.astype(np.float64)
+        assert max_rel_to_peak(i("+ij~.").exec_numpy(x), np.asarray(x64.sum())) <= 2e-6 * np.sqrt(x.size), shape
+        assert np.array_equal(i(">ij~.").exec_numpy(x), np.asarray(x.max()))
+        got = i("+ij~i").exec_numpy(x)
+        assert max_rel_to_peak(got, x64.sum(axis=1)) <= 2e-6, shape
+        assert np.array_equal(got, i("+ij~i").exec_numpy(x))
+        assert np.array_equal(i("<ij~i").exec_numpy(x), x.min(axis=1))
+    u, v = rand((5000001,), 25), rand((5000001,), 26)
+    want = np.asarray(u.astype(np.float64) @ v.astype(np.float64))
+    got = (i("i*i~i") >> i("+i~.")).exec_numpy(u, v)
+    assert abs(got - want) <= 1e-6 * np.abs(u.astype(np.float64) * v).sum()
+
+
 def steps_of_code(code):
     return [line.split()[2] for line in code.splitlines() if line.startswith("step ")]
 
