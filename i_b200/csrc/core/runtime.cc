@@ -336,6 +336,16 @@ int run_map(const Step& step, const ShapeTable& shapes, const std::vector<size_t
   (void)extent;
   if (step.in.size() == 1) {
     if (a.index == step.out.index) return ib_map_unary(op, pa, out, n, stream);
+    // A copy with the last two axes exchanged (`ij~ji`, `bij~bji`): the tiled transpose.
+    const size_t r = step.out.index.size();
+    if ((step.op == Op::Add || step.op == Op::Mul) && r >= 2 && a.index.size() == r &&
+        std::equal(a.index.begin(), a.index.end() - 2, step.out.index.begin()) &&
+        a.index[r - 2] == step.out.index[r - 1] && a.index[r - 1] == step.out.index[r - 2] &&
+        a.index[r - 2] != a.index[r - 1]) {
+      const size_t out_rows = oshape[r - 2], out_cols = oshape[r - 1];
+      return ib_transpose(pa, out, n / (out_rows * out_cols ? out_rows * out_cols : 1), out_cols, out_rows,
+                          stream);
+    }
   } else {
     const Access& b = step.in[1];
     const float* pb = dev.get(b.buffer);
@@ -440,20 +450,29 @@ int run_reduce(const Step& step, const ShapeTable& shapes, const std::vector<siz
     }
     return ib_reduce_rows_split(op, pa, out, rows, cols, ws, ws_bytes, dev.stream);
   }
-  // The kept axes trail the operand in output order and the leading ones fold (`+ij~j`,
-  // `+bij~ij`): a fold down the columns of a [folded][kept] array.
-  if (a.index.size() == step.rank && kept >= 1 && kept < a.index.size() && std::set<size_t>(a.index.begin(), a.index.end()).size() == a.index.size() &&
-      std::equal(step.out.index.begin(), step.out.index.end(), a.index.end() - kept)) {
-    const size_t cols = product(oshape);
-    const size_t rows = product(shape_a, 0, shape_a.size() - kept);
-    const size_t ws_bytes = ib_reduce_leading_workspace_bytes(rows, cols);
-    std::string err;
-    void* ws = nullptr;
-    if (ws_bytes && ws_bytes != SIZE_MAX && !(ws = dev.alloc(ws_bytes, &err))) {
-      set_error(err);
-      return -1;
+  // The folded axes stand together in the operand with kept axes behind them, and the kept axes
+  // keep their order (`+ij~j`, `+bij~ij`, `+bij~bj`): a fold down the columns of [kept in front]
+  // arrays of shape [folded][kept behind].
+  if (a.index.size() == step.rank && kept >= 1 && kept < a.index.size() &&
+      std::set<size_t>(a.index.begin(), a.index.end()).size() == a.index.size()) {
+    size_t front = 0;
+    while (front < kept && a.index[front] == step.out.index[front]) ++front;
+    const size_t folded = a.index.size() - kept;
+    const size_t behind = kept - front;
+    if (behind >= 1 && std::equal(step.out.index.begin() + front, step.out.index.end(),
+                                  a.index.begin() + front + folded)) {
+      const size_t batch = product(shape_a, 0, front);
+      const size_t rows = product(shape_a, front, front + folded);
+      const size_t cols = product(shape_a, front + folded);
+      const size_t ws_bytes = ib_reduce_leading_workspace_bytes(batch, rows, cols);
+      std::string err;
+      void* ws = nullptr;
+      if (ws_bytes && ws_bytes != SIZE_MAX && !(ws = dev.alloc(ws_bytes, &err))) {
+        set_error(err);
+        return -1;
+      }
+      return ib_reduce_leading(op, pa, out, batch, rows, cols, ws, ws ? ws_bytes : 0, dev.stream);
     }
-    return ib_reduce_leading(op, pa, out, rows, cols, ws, ws ? ws_bytes : 0, dev.stream);
   }
   std::vector<size_t> red_idx;
   for (size_t x = 0; x < step.rank; ++x)

@@ -219,6 +219,24 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
   return bytes;
 }
 
+extern "C" int ib_transpose(const float* x, float* y, size_t batch, size_t rows, size_t cols,
+                            void* stream) {
+  using namespace ib;
+  if (batch == 0 || rows == 0 || cols == 0) return 0;
+  if (!x || !y) return fail("ib_transpose: null pointer");
+  if (too_many_elements({batch, rows, cols})) return fail("ib_transpose: extents too large");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The tile kernel takes up to 65535 batch entries and row tiles per launch.
+  constexpr size_t kMost = 65535;
+  if ((rows + 31) / 32 > kMost) return fail("ib_transpose: more than 2097120 rows");
+  for (size_t b0 = 0; b0 < batch; b0 += kMost) {
+    const size_t nb = batch - b0 < kMost ? batch - b0 : kMost;
+    if (int rc = transpose_batched(x + b0 * rows * cols, y + b0 * rows * cols, nb, rows, cols, rows, false, s))
+      return rc;
+  }
+  return 0;
+}
+
 extern "C" int ib_contract(const float* a, const float* b, float* c, size_t batch, size_t m,
                            size_t n, size_t k, int a_kmajor, int b_kmajor, int precision,
                            void* workspace, size_t workspace_bytes, void* stream) {

@@ -148,6 +148,51 @@ map_strided(const float* __restrict__ a, const float* __restrict__ b, float* __r
   }
 }
 
+// The same over four neighbouring results of the innermost axis at a time, for operands that
+// are either contiguous along that axis (a 16-byte load) or constant along it (one load): leading
+// and middle-axis broadcasts (`bij*bj~bij`), outer products (`i*j~ij`), permutations of leading
+// axes (`bij~ibj`).  The index arithmetic, 32-bit here, is paid once per four elements.
+// args.extent[rank-1] counts groups of four; the strides of that axis are 4 or 0.
+template <int OP, bool BINARY>
+__global__ void __launch_bounds__(kThreads)
+map_strided_vec(const float* __restrict__ a, const float* __restrict__ b, float4* __restrict__ y,
+                unsigned nvec, StridedArgs args, bool a_runs, bool b_runs) {
+  const unsigned stride = gridDim.x * kThreads;
+  for (unsigned e = blockIdx.x * kThreads + threadIdx.x; e < nvec; e += stride) {
+    unsigned rest = e;
+    size_t oa = 0, ob = 0;
+    for (int d = args.rank - 1; d >= 0; --d) {
+      const unsigned ext = static_cast<unsigned>(args.extent[d]);
+      const unsigned q = rest / ext;
+      const unsigned coord = rest - q * ext;
+      rest = q;
+      oa += static_cast<size_t>(coord) * static_cast<size_t>(args.sa[d]);
+      if (BINARY) ob += static_cast<size_t>(coord) * static_cast<size_t>(args.sb[d]);
+    }
+    float4 va, vb = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a_runs) {
+      va = __ldcs(reinterpret_cast<const float4*>(a + oa));
+    } else {
+      const float v = __ldg(a + oa);
+      va = make_float4(v, v, v, v);
+    }
+    if (BINARY) {
+      if (b_runs) {
+        vb = __ldcs(reinterpret_cast<const float4*>(b + ob));
+      } else {
+        const float v = __ldg(b + ob);
+        vb = make_float4(v, v, v, v);
+      }
+    }
+    float4 r;
+    r.x = BINARY ? apply_binary(OP, va.x, vb.x) : apply_unary(OP, va.x);
+    r.y = BINARY ? apply_binary(OP, va.y, vb.y) : apply_unary(OP, va.y);
+    r.z = BINARY ? apply_binary(OP, va.z, vb.z) : apply_unary(OP, va.z);
+    r.w = BINARY ? apply_binary(OP, va.w, vb.w) : apply_unary(OP, va.w);
+    __stcs(y + e, r);
+  }
+}
+
 template <int OP>
 int launch_unary(const float* x, float* y, size_t n, cudaStream_t s) {
   size_t done = 0;
@@ -196,9 +241,45 @@ int dispatch_mode(int mode, const float* a, const float* b, float* y, size_t row
   return fail("ib_map_binary: mode must be 0..4");
 }
 
+// Whether the four-at-a-time form applies: the innermost extent a multiple of four, every operand
+// contiguous or constant along it, all other strides and the base pointers keeping 16-byte
+// alignment, under 2^32 results and operand elements.
+bool strided_vec_ok(const float* a, const float* b, const float* y, size_t n, const StridedArgs& args) {
+  if (args.rank < 1 || n >= (1ull << 32) || !aligned16(y)) return false;
+  const int in = args.rank - 1;
+  if (args.extent[in] % 4 != 0) return false;
+  auto operand_ok = [&](const float* p, const ptrdiff_t* st) {
+    if (st[in] != 0 && st[in] != 1) return false;
+    size_t span = 0;
+    for (int d = 0; d < args.rank; ++d) {
+      if (st[d] < 0) return false;
+      if (st[in] == 1 && d != in && st[d] % 4 != 0) return false;
+      span += static_cast<size_t>(st[d]) * (args.extent[d] - 1);
+    }
+    return span < (1ull << 32) && (st[in] == 0 || aligned16(p));
+  };
+  return operand_ok(a, args.sa) && (!b || operand_ok(b, args.sb));
+}
+
 template <int OP>
 int launch_strided(const float* a, const float* b, float* y, size_t n, const StridedArgs& args,
                    cudaStream_t s) {
+  if (strided_vec_ok(a, b, y, n, args)) {
+    StridedArgs v = args;
+    const int in = args.rank - 1;
+    const bool a_runs = args.sa[in] == 1, b_runs = b && args.sb[in] == 1;
+    v.extent[in] /= 4;
+    v.sa[in] *= 4;
+    v.sb[in] *= 4;
+    const unsigned nvec = static_cast<unsigned>(n / 4);
+    if (b)
+      map_strided_vec<OP, true><<<grid_for(nvec, kThreads), kThreads, 0, s>>>(
+          a, b, reinterpret_cast<float4*>(y), nvec, v, a_runs, b_runs);
+    else
+      map_strided_vec<OP, false><<<grid_for(nvec, kThreads), kThreads, 0, s>>>(
+          a, b, reinterpret_cast<float4*>(y), nvec, v, a_runs, b_runs);
+    return check_launch("ib_map_strided");
+  }
   if (b)
     map_strided<OP, true><<<grid_for(n, kThreads), kThreads, 0, s>>>(a, b, y, n, args);
   else

@@ -258,6 +258,9 @@ fold_leading_axis(const float* __restrict__ x, const float* __restrict__ w, floa
                   size_t rows, size_t cols, size_t rows_per_slab, int lanes_log2) {
   constexpr int kWidth = VEC ? 4 : 1;
   __shared__ float meet[kThreads][kWidth];
+  // blockIdx.z: one of several arrays of the same shape, one behind the other (`+bij~bj`).
+  x += static_cast<size_t>(blockIdx.z) * rows * cols;
+  y += static_cast<size_t>(blockIdx.z) * gridDim.y * cols;
   // lanes = 2^lanes_log2 threads side by side cover a row's columns in this CTA; kThreads / lanes
   // rows are in flight at a time.
   const int lanes = 1 << lanes_log2;
@@ -333,10 +336,10 @@ int leading_axis_lanes_log2(size_t cols, bool vec) {
 // Slabs of rows for a fold of `rows` x `cols`: enough CTAs to fill the machine several times
 // over, every thread with at least 16 rows.  (Sized for the four-column form; the one-column
 // form of the same shape has more CTAs per slab and fills the machine sooner.)
-size_t leading_axis_slabs(size_t rows, size_t cols) {
+size_t leading_axis_slabs(size_t rows, size_t cols, size_t batch = 1) {
   const int l = leading_axis_lanes_log2(cols, cols % 4 == 0);
   const size_t groups = cols % 4 == 0 ? cols / 4 : cols;
-  const size_t col_blocks = (groups + (1u << l) - 1) >> l;
+  const size_t col_blocks = ((groups + (1u << l) - 1) >> l) * (batch ? batch : 1);
   const size_t phases = kThreads >> l;
   size_t slabs = (static_cast<size_t>(kNumSMs) * 8 + col_blocks - 1) / col_blocks;
   if (slabs > rows / (16 * phases)) slabs = rows / (16 * phases);
@@ -346,11 +349,12 @@ size_t leading_axis_slabs(size_t rows, size_t cols) {
 
 template <int OP, bool ROW_WEIGHT>
 int launch_leading_axis_once(const float* x, const float* w, float* y, size_t rows, size_t cols,
-                             size_t rows_per_slab, size_t slabs, cudaStream_t s) {
+                             size_t rows_per_slab, size_t slabs, cudaStream_t s, size_t batch = 1) {
   const bool vec = cols % 4 == 0 && aligned16(x) && aligned16(y);
   const int l = leading_axis_lanes_log2(cols, vec);
   const size_t groups = vec ? cols / 4 : cols;
-  dim3 grid(static_cast<unsigned>((groups + (1u << l) - 1) >> l), static_cast<unsigned>(slabs));
+  dim3 grid(static_cast<unsigned>((groups + (1u << l) - 1) >> l), static_cast<unsigned>(slabs),
+            static_cast<unsigned>(batch));
   if (vec)
     fold_leading_axis<OP, ROW_WEIGHT, true><<<grid, kThreads, 0, s>>>(x, w, y, rows, cols, rows_per_slab, l);
   else
@@ -360,15 +364,18 @@ int launch_leading_axis_once(const float* x, const float* w, float* y, size_t ro
 
 template <int OP, bool ROW_WEIGHT>
 int launch_leading_axis(const float* x, const float* w, float* y, size_t rows, size_t cols,
-                        float* partials, cudaStream_t s) {
-  const size_t slabs = partials ? leading_axis_slabs(rows, cols) : 1;
+                        float* partials, cudaStream_t s, size_t batch = 1) {
+  if (batch > 65535) return fail("ib_reduce_leading: more than 65535 arrays");
+  const size_t slabs = partials ? leading_axis_slabs(rows, cols, batch) : 1;
   const size_t rows_per_slab = (rows + slabs - 1) / slabs;
   const size_t used = rows_per_slab ? (rows + rows_per_slab - 1) / rows_per_slab : 1;   // slabs that hold rows
-  if (used <= 1) return launch_leading_axis_once<OP, ROW_WEIGHT>(x, w, y, rows, cols, rows ? rows : 1, 1, s);
-  if (int rc = launch_leading_axis_once<OP, ROW_WEIGHT>(x, w, partials, rows, cols, rows_per_slab, used, s))
+  if (used <= 1)
+    return launch_leading_axis_once<OP, ROW_WEIGHT>(x, w, y, rows, cols, rows ? rows : 1, 1, s, batch);
+  if (int rc = launch_leading_axis_once<OP, ROW_WEIGHT>(x, w, partials, rows, cols, rows_per_slab, used, s,
+                                                        batch))
     return rc;
   // The partial rows, one per slab, folded the same way as one slab.
-  return launch_leading_axis_once<OP, false>(partials, nullptr, y, used, cols, used, 1, s);
+  return launch_leading_axis_once<OP, false>(partials, nullptr, y, used, cols, used, 1, s, batch);
 }
 
 template <int OP>
@@ -446,21 +453,23 @@ extern "C" int ib_reduce_rows_split(int op, const float* x, float* y, size_t row
 #undef CALL
 }
 
-extern "C" size_t ib_reduce_leading_workspace_bytes(size_t rows, size_t cols) {
-  if (cols != 0 && rows > SIZE_MAX / sizeof(float) / cols) return SIZE_MAX;
-  return ib::dot_leading_axis_floats(rows, cols) * sizeof(float);
+extern "C" size_t ib_reduce_leading_workspace_bytes(size_t batch, size_t rows, size_t cols) {
+  if (batch == 0 || cols == 0) return 0;
+  if (rows > SIZE_MAX / sizeof(float) / cols / batch) return SIZE_MAX;
+  const size_t slabs = ib::leading_axis_slabs(rows, cols, batch);
+  return slabs > 1 ? batch * slabs * cols * sizeof(float) : 0;
 }
 
-extern "C" int ib_reduce_leading(int op, const float* x, float* y, size_t rows, size_t cols,
-                                 void* workspace, size_t workspace_bytes, void* stream) {
-  if (cols == 0) return 0;
+extern "C" int ib_reduce_leading(int op, const float* x, float* y, size_t batch, size_t rows,
+                                 size_t cols, void* workspace, size_t workspace_bytes, void* stream) {
+  if (cols == 0 || batch == 0) return 0;
   if (!y || (!x && rows != 0)) return ib::fail("ib_reduce_leading: null pointer");
   // Without (enough) workspace the rows are folded as one slab: correct, slower on tall inputs.
-  float* partials = workspace_bytes >= ib_reduce_leading_workspace_bytes(rows, cols) && workspace_bytes > 0
+  float* partials = workspace_bytes >= ib_reduce_leading_workspace_bytes(batch, rows, cols) && workspace_bytes > 0
                         ? static_cast<float*>(workspace)
                         : nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define CALL(OP) ib::launch_leading_axis<OP, false>(x, nullptr, y, rows, cols, partials, s)
+#define CALL(OP) ib::launch_leading_axis<OP, false>(x, nullptr, y, rows, cols, partials, s, batch)
   IB_DISPATCH_FOLD(op, CALL)
 #undef CALL
 }

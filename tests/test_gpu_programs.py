@@ -364,8 +364,38 @@ def test_folds_of_leading_axes(ilang, oracle):
     x = rand((6, 300, 44), 23)
     assert np.array_equal(i(">bij~ij").exec_numpy(x), x.max(axis=0))
     assert max_rel_to_peak(i("+bij~j").exec_numpy(x), x.astype(np.float64).sum(axis=(0, 1))) <= 2e-6
-    # A fold of the middle axis keeps the general strided kernel.
+    # A fold of the middle axis: one such array per leading entry.
     assert np.array_equal(i(">bij~bj").exec_numpy(x), x.max(axis=1))
+    assert max_rel_to_peak(i("+bij~bj").exec_numpy(x), x.astype(np.float64).sum(axis=1)) <= 2e-6
+    y = rand((3, 4, 700, 36), 27)
+    assert np.array_equal(i("<abij~abj").exec_numpy(y), y.min(axis=2))
+    assert np.array_equal(i(">abij~aj").exec_numpy(y), y.max(axis=(1, 2)))
+    # Kept axes that change places, or folded axes apart from each other, stay with the strided fold.
+    assert np.array_equal(i(">bij~jb").exec_numpy(x), x.max(axis=1).T)
+    assert np.array_equal(i(">abij~bj").exec_numpy(y), y.max(axis=(0, 2)))
+
+
+def test_permutations_and_broadcasts_move_whole_lines(ilang):
+    # Copies with the last two axes exchanged go through the tiled transpose; maps whose operands
+    # are contiguous or constant along the innermost axis run four results at a time.  Results
+    # are exact either way; shapes with and without a multiple of four innermost.
+    i = ilang.i
+    for shape in ((300, 520), (33, 77), (1, 64), (2048, 4)):
+        x = rand(shape, 28)
+        assert np.array_equal(i("ij~ji").exec_numpy(x), x.T)
+    t = rand((5, 130, 72), 29)
+    assert np.array_equal(i("bij~bji").exec_numpy(t), t.transpose(0, 2, 1))
+    assert np.array_equal(i("bij~ibj").exec_numpy(t), t.transpose(1, 0, 2))
+    assert np.array_equal(i("bij~jib").exec_numpy(t), t.transpose(2, 1, 0))
+    assert np.array_equal(i("-bij~bji").exec_numpy(t), -t.transpose(0, 2, 1))
+    for last in (72, 70):
+        t = rand((5, 130, last), 30)
+        m, r, c = rand((5, last), 31), rand((130,), 32), rand((last,), 33)
+        assert np.array_equal(i("bij*bj~bij").exec_numpy(t, m), t * m[:, None, :])
+        assert np.array_equal(i("bj-bij~bij").exec_numpy(m, t), m[:, None, :] - t)
+        assert np.array_equal(i("bij+i~bij").exec_numpy(t, r), t + r[None, :, None])
+        assert np.array_equal(i("i*j~ij").exec_numpy(r, c), np.outer(r, c))
+        assert np.array_equal(i("j*i~ij").exec_numpy(c, r), np.outer(r, c))
 
 
 def test_folds_of_few_very_long_rows(ilang):
