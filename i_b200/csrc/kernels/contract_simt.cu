@@ -27,31 +27,34 @@ constexpr int kTileK = 16;
 template <bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(256)
 contract_simt_kernel(const float* __restrict__ a, const float* __restrict__ b,
-                     float* __restrict__ c, size_t m, size_t n, size_t k) {
+                     float* __restrict__ c, size_t m, size_t n, size_t k, size_t splits, size_t k_len) {
   __shared__ float sa[kTileK][kTile + 1];
   __shared__ float sb[kTileK][kTile + 1];
-  const size_t batch = blockIdx.z;
+  // blockIdx.z = batch entry * splits + split: a split sums k_len terms of the contraction into
+  // its own copy of the result (the caller adds the copies).
+  const size_t batch = blockIdx.z / splits, split = blockIdx.z - batch * splits;
   a += batch * m * k;
   b += batch * n * k;
-  c += batch * m * n;
+  c += static_cast<size_t>(blockIdx.z) * m * n;
+  const size_t k_lo = split * k_len, k_hi = k_lo + k_len < k ? k_lo + k_len : k;
   const size_t i0 = static_cast<size_t>(blockIdx.y) * kTile;
   const size_t j0 = static_cast<size_t>(blockIdx.x) * kTile;
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
   float acc[4][4] = {};
-  for (size_t k0 = 0; k0 < k; k0 += kTileK) {
+  for (size_t k0 = k_lo; k0 < k_hi; k0 += kTileK) {
     for (int e = threadIdx.x; e < kTile * kTileK; e += 256) {
       // Walk the operand along its contiguous axis.
       int row, kk;
       if (A_KMAJOR) { row = e / kTileK; kk = e % kTileK; } else { kk = e / kTile; row = e % kTile; }
       size_t gi = i0 + row, gk = k0 + kk;
       float v = 0.0f;
-      if (gi < m && gk < k) v = A_KMAJOR ? a[gi * k + gk] : a[gk * m + gi];
+      if (gi < m && gk < k_hi) v = A_KMAJOR ? a[gi * k + gk] : a[gk * m + gi];
       sa[kk][row] = v;
       if (B_KMAJOR) { row = e / kTileK; kk = e % kTileK; } else { kk = e / kTile; row = e % kTile; }
       size_t gj = j0 + row;
       gk = k0 + kk;
       v = 0.0f;
-      if (gj < n && gk < k) v = B_KMAJOR ? b[gj * k + gk] : b[gk * n + gj];
+      if (gj < n && gk < k_hi) v = B_KMAJOR ? b[gj * k + gk] : b[gk * n + gj];
       sb[kk][row] = v;
     }
     __syncthreads();
@@ -91,24 +94,52 @@ __device__ __forceinline__ float round_tf32(float x) {
   return __uint_as_float(u);
 }
 
+// out[c][r] = in[r][c] through a 64 x 64 tile in shared memory.  Whole tiles of 16-byte-aligned
+// arrays move as 16-byte accesses on both sides (a thread loads four neighbouring columns of a row
+// and stores four neighbouring rows of a column); ragged or unaligned tiles go element by element.
 template <bool ROUND>
 __global__ void __launch_bounds__(256)
 transpose_kernel(const float* __restrict__ in, float* __restrict__ out, size_t rows, size_t cols,
-                 size_t out_pitch) {
-  __shared__ float tile[32][33];
+                 size_t out_pitch, bool vec) {
+  constexpr int kT = 64;
+  __shared__ float tile[kT][kT + 1];
   const size_t batch = blockIdx.z;
   in += batch * rows * cols;
   out += batch * cols * out_pitch;
-  const size_t c0 = static_cast<size_t>(blockIdx.x) * 32, r0 = static_cast<size_t>(blockIdx.y) * 32;
-  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
-  for (int j = ty; j < 32; j += 8) {
-    size_t r = r0 + j, cc = c0 + tx;
-    if (r < rows && cc < cols) tile[j][tx] = in[r * cols + cc];
+  const size_t c0 = static_cast<size_t>(blockIdx.x) * kT, r0 = static_cast<size_t>(blockIdx.y) * kT;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const bool whole = vec && r0 + kT <= rows && c0 + kT <= cols;
+  if (whole) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int r = ty + 16 * p;
+      const float4 v = *reinterpret_cast<const float4*>(in + (r0 + r) * cols + c0 + 4 * tx);
+      tile[r][4 * tx + 0] = v.x;
+      tile[r][4 * tx + 1] = v.y;
+      tile[r][4 * tx + 2] = v.z;
+      tile[r][4 * tx + 3] = v.w;
+    }
+  } else {
+    for (int e = threadIdx.x; e < kT * kT; e += 256) {
+      const int r = e / kT, c = e % kT;
+      if (r0 + r < rows && c0 + c < cols) tile[r][c] = in[(r0 + r) * cols + c0 + c];
+    }
   }
   __syncthreads();
-  for (int j = ty; j < 32; j += 8) {
-    size_t cc = c0 + j, r = r0 + tx;
-    if (r < rows && cc < cols) out[cc * out_pitch + r] = ROUND ? round_tf32(tile[tx][j]) : tile[tx][j];
+  if (whole) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int c = ty + 16 * p;
+      float4 v = make_float4(tile[4 * tx + 0][c], tile[4 * tx + 1][c], tile[4 * tx + 2][c], tile[4 * tx + 3][c]);
+      if (ROUND) v = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+      *reinterpret_cast<float4*>(out + (c0 + c) * out_pitch + r0 + 4 * tx) = v;
+    }
+  } else {
+    for (int e = threadIdx.x; e < kT * kT; e += 256) {
+      const int c = e / kT, r = e % kT;
+      if (r0 + r < rows && c0 + c < cols)
+        out[(c0 + c) * out_pitch + r0 + r] = ROUND ? round_tf32(tile[r][c]) : tile[r][c];
+    }
   }
 }
 
@@ -898,33 +929,39 @@ int round_tf32_rows(const float* in0, float* out0, size_t rows0, size_t cols0, s
 }
 
 int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                  size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s) {
+                  size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s, size_t splits) {
   if (batch == 0 || m == 0 || n == 0) return 0;
-  if (batch > 65535) return fail("ib_contract: more than 65535 batch entries");
+  if (splits < 1) splits = 1;
+  if (batch * splits > 65535) return fail("ib_contract: more than 65535 batch entries");
+  // Whole k-tiles per split, so that every split but the last is full.
+  const size_t k_len = ((k + splits - 1) / splits + kTileK - 1) / kTileK * kTileK;
   dim3 grid(static_cast<unsigned>((n + kTile - 1) / kTile),
-            static_cast<unsigned>((m + kTile - 1) / kTile), static_cast<unsigned>(batch));
+            static_cast<unsigned>((m + kTile - 1) / kTile), static_cast<unsigned>(batch * splits));
   if (grid.y > 65535) return fail("ib_contract: row count too large for the fp32 arm");
   if (a_kmajor && b_kmajor)
-    contract_simt_kernel<true, true><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+    contract_simt_kernel<true, true><<<grid, 256, 0, s>>>(a, b, c, m, n, k, splits, k_len);
   else if (a_kmajor && !b_kmajor)
-    contract_simt_kernel<true, false><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+    contract_simt_kernel<true, false><<<grid, 256, 0, s>>>(a, b, c, m, n, k, splits, k_len);
   else if (!a_kmajor && b_kmajor)
-    contract_simt_kernel<false, true><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+    contract_simt_kernel<false, true><<<grid, 256, 0, s>>>(a, b, c, m, n, k, splits, k_len);
   else
-    contract_simt_kernel<false, false><<<grid, 256, 0, s>>>(a, b, c, m, n, k);
+    contract_simt_kernel<false, false><<<grid, 256, 0, s>>>(a, b, c, m, n, k, splits, k_len);
   return check_launch("ib_contract (fp32)");
 }
 
 int transpose_batched(const float* in, float* out, size_t batch, size_t rows, size_t cols,
                       size_t out_pitch, bool round, cudaStream_t s) {
   if (batch == 0 || rows == 0 || cols == 0) return 0;
-  if (batch > 65535 || (rows + 31) / 32 > 65535) return fail("transpose: shape too large");
-  dim3 grid(static_cast<unsigned>((cols + 31) / 32), static_cast<unsigned>((rows + 31) / 32),
+  if (batch > 65535 || (rows + 63) / 64 > 65535) return fail("transpose: shape too large");
+  dim3 grid(static_cast<unsigned>((cols + 63) / 64), static_cast<unsigned>((rows + 63) / 64),
             static_cast<unsigned>(batch));
+  // 16-byte accesses need every row of either side, in every batch entry, to start on 16 bytes.
+  const bool vec = cols % 4 == 0 && out_pitch % 4 == 0 && (rows * cols) % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(in) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
   if (round)
-    transpose_kernel<true><<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch);
+    transpose_kernel<true><<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch, vec);
   else
-    transpose_kernel<false><<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch);
+    transpose_kernel<false><<<grid, 256, 0, s>>>(in, out, rows, cols, out_pitch, vec);
   return check_launch("transpose");
 }
 

@@ -41,6 +41,29 @@ size_t carve_bytes(size_t floats) {
   return floats > kMaxFloats ? SIZE_MAX >> 4 : round_up(floats * sizeof(float), 256);
 }
 
+// Parts into which the k range of a contraction with few output tiles is cut, so that every SM
+// has work: an output of 128 x 128 is four tiles of the fp32 arm (one of the tensor arm), and a
+// k of thousands would run on that many SMs.  Each part sums into its own copy of the result
+// and the copies are added.  `tile`: output rows and columns per CTA of the arm.  1 = whole.
+size_t k_parts(size_t batch, size_t m, size_t n, size_t k, size_t tile) {
+  const size_t tiles = batch * ((m + tile - 1) / tile) * ((n + tile - 1) / tile);
+  if (tiles == 0 || tiles * 2 > static_cast<size_t>(kNumSMs) || k < 1024) return 1;
+  size_t parts = static_cast<size_t>(kNumSMs) * 2 / tiles;
+  if (parts > k / 128) parts = k / 128;
+  if (parts > 64) parts = 64;
+  if (batch * parts > 65535) parts = 65535 / batch;
+  return parts < 2 ? 1 : parts;
+}
+
+// The same for the TF32 tensor arm, which takes the parts as batch entries of one tensor map:
+// one batch entry only, and parts of equal length, a multiple of four.
+size_t k_parts_tensor(size_t batch, size_t m, size_t n, size_t k) {
+  if (batch != 1) return 1;
+  for (size_t parts = k_parts(1, m, n, k, 128); parts >= 2; --parts)
+    if (k % (4 * parts) == 0) return parts;
+  return 1;
+}
+
 bool wants_tensor(int precision, double flop) {
   if (precision == IB_PRECISION_FP32) return false;
   if (precision == IB_PRECISION_AUTO) return flop >= kTensorMinFlop;
@@ -193,7 +216,10 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
     return carve_bytes(long_rows_floats(batch, k));   // dot products of few, very long rows
   }
   const double flop = 2.0 * batch * m * n * k;
-  if (!wants_tensor(precision, flop)) return 0;
+  // Copies of the result when the k range is cut into parts (either 32-bit arm).
+  const size_t parts = std::max(k_parts(batch, m, n, k, 64), k_parts_tensor(batch, m, n, k));
+  const size_t copies = parts > 1 ? carve_bytes(batch * parts * m * n) : 0;
+  if (!wants_tensor(precision, flop)) return copies;
   if (precision == IB_PRECISION_AUTO && contract_prefers_f16(m, n, k)) precision = IB_PRECISION_F16;
   if (precision == IB_PRECISION_F16) {
     // fp16 copies of both operands plus one scale per row; fp32 transposes first when needed.
@@ -212,8 +238,8 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
     if (!b_kmajor) bytes += carve_bytes(batch * n * k);
     return bytes;
   }
-  if (!contract_shape_ok(k)) return 0;
-  size_t bytes = 0;
+  if (!contract_shape_ok(k)) return copies;
+  size_t bytes = copies;
   if (!a_kmajor) bytes += carve_bytes(batch * m * k);
   if (!b_kmajor) bytes += carve_bytes(batch * n * k);
   return bytes;
@@ -228,7 +254,7 @@ extern "C" int ib_transpose(const float* x, float* y, size_t batch, size_t rows,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The tile kernel takes up to 65535 batch entries and row tiles per launch.
   constexpr size_t kMost = 65535;
-  if ((rows + 31) / 32 > kMost) return fail("ib_transpose: more than 2097120 rows");
+  if ((rows + 63) / 64 > kMost) return fail("ib_transpose: more than 4194240 rows");
   for (size_t b0 = 0; b0 < batch; b0 += kMost) {
     const size_t nb = batch - b0 < kMost ? batch - b0 : kMost;
     if (int rc = transpose_batched(x + b0 * rows * cols, y + b0 * rows * cols, nb, rows, cols, rows, false, s))
@@ -342,6 +368,18 @@ int contract_with_chain(const float* a, const float* b, float* c, size_t batch, 
   const GemmEpilogue* fused = chain ? &chain->fused : nullptr;
   auto then_chain = [&](int rc) {
     return rc != 0 || !chain ? rc : chain->in_place(c, batch * m, n, stream);
+  };
+  // The fp32 arm, its k range in parts when the output has too few tiles for the machine and the
+  // workspace has room for the copies.
+  auto simt = [&](const float* pa, const float* pb, bool a_km, bool b_km, Carver& ws) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t parts = k_parts(batch, m, n, k, 64);
+    float* copies = parts > 1 && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0
+                        ? ws.take(batch * parts * m * n)
+                        : nullptr;
+    if (!copies) return contract_simt(pa, pb, c, batch, m, n, k, a_km, b_km, st);
+    if (int rc = contract_simt(pa, pb, copies, batch, m, n, k, a_km, b_km, st, parts)) return rc;
+    return sum_partials(copies, c, batch, parts, m * n, st);
   };
   if (col_tile != 0 && col_tile != 128 && col_tile != 256)
     return fail("ib_contract: col_tile must be 0, 128 or 256");
@@ -483,12 +521,23 @@ int contract_with_chain(const float* a, const float* b, float* c, size_t batch, 
       if (int rc = transpose_batched(b, t, batch, k, n, k, false, s)) return rc;   // [k][n] -> [n][k]
       bk = t;
     }
-    if (gemm_tcgen05_supported(ak, bk, c, m, n, k))
-      return gemm_tcgen05(ak, bk, c, batch, m, n, k, s, geometry, fused);
+    if (gemm_tcgen05_supported(ak, bk, c, m, n, k)) {
+      const size_t parts = k_parts_tensor(batch, m, n, k);
+      float* copies = parts > 1 ? ws.take(parts * m * n) : nullptr;
+      if (!copies) return gemm_tcgen05(ak, bk, c, batch, m, n, k, s, geometry, fused);
+      // The parts as batch entries of one launch, then their sum (and the caller's operators
+      // on the sum, as a pass of their own).
+      // (Should the driver refuse a tensor map whose batch pitch is below its row pitch, the
+      // contraction runs whole instead.)
+      if (gemm_tcgen05(ak, bk, copies, 1, m, n, k, s, geometry, nullptr, parts) != 0)
+        return gemm_tcgen05(ak, bk, c, batch, m, n, k, s, geometry, fused);
+      return then_chain(sum_partials(copies, c, 1, parts, m * n, s));
+    }
     // Misaligned base pointers: the fp32 arm takes any layout.
-    return then_chain(contract_simt(ak, bk, c, batch, m, n, k, true, true, s));
+    return then_chain(simt(ak, bk, true, true, ws));
   }
-  return then_chain(contract_simt(a, b, c, batch, m, n, k, a_kmajor != 0, b_kmajor != 0, s));
+  Carver ws(workspace, workspace_bytes);
+  return then_chain(simt(a, b, a_kmajor != 0, b_kmajor != 0, ws));
 }
 
 }  // namespace

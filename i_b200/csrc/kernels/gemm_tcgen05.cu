@@ -644,7 +644,7 @@ static bool use_pair(const GemmGeometry& g, size_t m, size_t n) {
 }
 
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                 size_t k, cudaStream_t s, GemmGeometry g, const GemmEpilogue* e) {
+                 size_t k, cudaStream_t s, GemmGeometry g, const GemmEpilogue* e, size_t k_parts) {
   if (batch == 0 || m == 0 || n == 0) return 0;
   if (!gemm_tcgen05_supported(a, b, c, m, n, k))
     return fail("ib_contract: shape or alignment not supported by the tensor-core arm");
@@ -652,8 +652,18 @@ int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t 
   const bool pair = use_pair(g, m, n);
   const bool wide = !pair && wide_tile(g, n);
   CUtensorMap map_a, map_b;
-  if (int rc = make_tensor_map_f32(&map_a, a, batch, m, k, k, m * k, kBM)) return rc;
-  if (int rc = make_tensor_map_f32(&map_b, b, batch, n, k, k, n * k, wide ? 256 : 128)) return rc;
+  size_t a_step = m * k, b_step = n * k;       // elements from one batch entry to the next
+  if (k_parts > 1) {
+    // The parts of the k range are the batch entries: same rows, k / k_parts columns further on.
+    if (batch != 1 || k % (4 * k_parts) != 0 || e)
+      return fail("ib_contract: the k range is cut for one batch entry, in multiples of four, without operators");
+    batch = k_parts;
+    a_step = b_step = k / k_parts;
+  }
+  const size_t row_pitch = k;
+  if (k_parts > 1) k /= k_parts;
+  if (int rc = make_tensor_map_f32(&map_a, a, batch, m, k, row_pitch, a_step, kBM)) return rc;
+  if (int rc = make_tensor_map_f32(&map_b, b, batch, n, k, row_pitch, b_step, wide ? 256 : 128)) return rc;
   if (pair) return launch_pair<Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e);
   return wide ? launch<256, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e)
               : launch<128, Kind::TF32>(map_a, map_b, c, batch, m, n, k, s, g.group_n, e);

@@ -11,8 +11,12 @@
 namespace ib {
 
 // contract_simt.cu
+// With splits > 1 the k range is cut into that many parts and c receives one copy of the result
+// per part, [batch][split][m][n], for the caller to add (sum_partials in reduce.cu).
 int contract_simt(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                  size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s);
+                  size_t k, bool a_kmajor, bool b_kmajor, cudaStream_t s, size_t splits = 1);
+// y[b][c] = sum_r x[b][r][c] for a handful of rows (the copies of a split contraction).
+int sum_partials(const float* x, float* y, size_t batch, size_t rows, size_t cols, cudaStream_t s);
 // out[b][c][r] = in[b][r][c]; rows of `out` are `out_pitch` elements apart.  With
 // `round` the values are rounded to TF32 (nearest) on the way.
 int transpose_batched(const float* in, float* out, size_t batch, size_t rows, size_t cols,
@@ -84,8 +88,11 @@ struct GemmEpilogue {
   const float* operand[IB_MAX_CHAIN_OPERANDS] = {};
   int mode[IB_MAX_CHAIN_OPERANDS] = {};
 };
+// k_parts > 1 (one batch entry, k a multiple of 4 * k_parts): the k range is cut into that many
+// equal parts and c receives one copy of the result per part, [part][m][n], for the caller to add.
 int gemm_tcgen05(const float* a, const float* b, float* c, size_t batch, size_t m, size_t n,
-                 size_t k, cudaStream_t s, GemmGeometry g = {}, const GemmEpilogue* e = nullptr);
+                 size_t k, cudaStream_t s, GemmGeometry g = {}, const GemmEpilogue* e = nullptr,
+                 size_t k_parts = 1);
 // Same contraction with bf16 operands a16 / b16 ([b][rows][k_pitch] bf16, k_pitch a multiple of 8)
 // fed to tcgen05 kind::f16, fp32 accumulation.
 // The same on fp16 operands stored over one power of two per row (a16[b][i][:] = A / a_scale[b][i],

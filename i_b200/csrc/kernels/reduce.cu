@@ -401,6 +401,11 @@ int dot_leading_axis(const float* x, const float* w, float* y, size_t rows, size
   return launch_leading_axis<IB_OP_ADD, true>(x, w, y, rows, cols, partials, s);
 }
 
+int sum_partials(const float* x, float* y, size_t batch, size_t rows, size_t cols, cudaStream_t s) {
+  if (batch == 0 || cols == 0) return 0;
+  return launch_leading_axis<IB_OP_ADD, false>(x, nullptr, y, rows, cols, nullptr, s, batch);
+}
+
 size_t long_rows_floats(size_t rows, size_t cols) {
   const RowSplit sp = split_long_rows(rows, cols);
   return sp.segs > 1 ? rows * sp.segs : 0;

@@ -398,6 +398,32 @@ def test_permutations_and_broadcasts_move_whole_lines(ilang):
         assert np.array_equal(i("j*i~ij").exec_numpy(c, r), np.outer(r, c))
 
 
+@pytest.mark.parametrize("precision,bound", [("fp32", 1e-5), ("auto", 5e-3), ("tf32", 5e-3)])
+def test_contractions_with_few_output_tiles_and_a_long_sum(ilang, precision, bound):
+    # A small output over a long k (a Gram matrix of few features, one block of logits) has too few
+    # tiles for the machine: its k range is cut into parts, each summed into a copy of the result,
+    # and the copies are added.  Every operand layout, batch entries, ragged shapes, and operators
+    # on the sum.
+    i = ilang.i
+    rng = np.random.default_rng(35)
+
+    def draw(*shape):
+        return (2 * rng.random(shape, dtype=np.float32) - 1)
+
+    forms = {"ik*jk~ijk": "ik,jk->ij", "ik*kj~ijk": "ik,kj->ij", "ki*jk~ijk": "ki,jk->ij", "ki*kj~ijk": "ki,kj->ij"}
+    for m, n, k in ((128, 128, 4096), (100, 60, 5000), (30, 257, 12288)):
+        for src, ein in forms.items():
+            a = draw(*((m, k) if src[:2] == "ik" else (k, m)))
+            b = draw(*((n, k) if src[3:5] == "jk" else (k, n)))
+            comp = (i(src) >> i("+ijk~ij")).set_precision(precision)
+            want = np.einsum(ein, a.astype(np.float64), b.astype(np.float64))
+            assert max_rel_to_peak(comp.exec_numpy(a, b), want) <= bound, (precision, src, m, n, k)
+    a, b, bias = draw(3, 70, 6000), draw(3, 50, 6000), draw(50)
+    comp = (i("bik*bjk~bijk") >> i("+bijk~bij") >> i("bij+j~bij") >> i(">bij~bij")).set_precision(precision)
+    want = np.maximum(np.einsum("bik,bjk->bij", a.astype(np.float64), b.astype(np.float64)) + bias, 0)
+    assert max_rel_to_peak(comp.exec_numpy(a, b, bias), want) <= bound
+
+
 def test_folds_of_few_very_long_rows(ilang):
     # A fold of a whole array is one row of millions of columns: it is cut into segments, one CTA
     # each, and the segments' results are folded once more.  Also the dot product of two long
