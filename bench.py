@@ -214,7 +214,9 @@ class ClockSampler:
 # GPU arm.
 # ---------------------------------------------------------------------------
 
-SECONDARY = ("row_softmax_8192x8192", "map_exp_8192x8192", "reduce_sum_rows_8192x8192",
+SECONDARY = ("row_softmax_8192x8192", "row_softmax_1024x65536", "map_exp_8192x8192",
+             "map_transpose_8192x8192", "reduce_sum_rows_8192x8192", "reduce_sum_cols_8192x8192",
+             "reduce_sum_all_8192x8192", "contract_matvec_8192x8192",
              "map_chain_bias_relu_gate_8192x8192", "map_chain_shift_exp_div_8192x8192",
              "mm_t_8192x8192x4096_tf32", "mm_t_8192x8192x4096_bf16_optin",
              "mm_t_8192x8192x4096_f16_scaled", "mm_t_bias_relu_8192x8192x4096_tf32",
@@ -253,6 +255,7 @@ def secondary_metrics(torch, ilang, peaks, only=None, iters=10):
         pairs = []
         for _ in range(iters):
             flush.zero_()
+            flush.zero_()                      # ~80 us of device work: covers a call through the Python front end
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -269,18 +272,18 @@ def secondary_metrics(torch, ilang, peaks, only=None, iters=10):
 
     out = {}
     g = torch.Generator(device="cuda")
-    if wanted("row_") or wanted("map_") or wanted("reduce_"):
+    if wanted("row_softmax_8192") or wanted("map_") or wanted("reduce_") or wanted("contract_"):
         g.manual_seed(1)
         x = 2.0 * torch.randn(8192, 8192, device="cuda", generator=g)
         y = torch.empty_like(x)
         nbytes = 2.0 * x.numel() * 4
-        if wanted("row_softmax"):
+        if wanted("row_softmax_8192"):
             out["row_softmax_8192x8192"] = hbm(nbytes, timed(
                 lambda: lib.ib_row_softmax(x.data_ptr(), y.data_ptr(), 8192, 8192, stream)))
         if wanted("map_exp"):
             out["map_exp_8192x8192"] = hbm(nbytes, timed(
                 lambda: lib.ib_map_unary(6, x.data_ptr(), y.data_ptr(), x.numel(), stream)))
-        if wanted("reduce_sum"):
+        if wanted("reduce_sum_rows"):
             r = torch.empty(8192, device="cuda")
             out["reduce_sum_rows_8192x8192"] = hbm(x.numel() * 4.0 + 8192 * 4, timed(
                 lambda: lib.ib_reduce_rows(0, x.data_ptr(), r.data_ptr(), 8192, 8192, stream)))
@@ -303,6 +306,34 @@ def secondary_metrics(torch, ilang, peaks, only=None, iters=10):
             chain = ilang.i("ij-i~ij") >> ilang.i("^ij~ij") >> ilang.i("ij/i~ij")
             out["map_chain_shift_exp_div_8192x8192"] = hbm(nbytes + 2 * 8192 * 4, timed(
                 lambda: chain.into(y, x, m, den)))
+        if wanted("reduce_sum_all"):
+            # `+ij~.`: one row of 67 million columns, folded in segments.
+            total = torch.empty((), device="cuda")
+            fold = ilang.i("+ij~.")
+            out["reduce_sum_all_8192x8192"] = hbm(x.numel() * 4.0, timed(lambda: fold.into(total, x)))
+        if wanted("reduce_sum_cols"):
+            # `+ij~j`: a fold of the leading axis.
+            c = torch.empty(8192, device="cuda")
+            fold = ilang.i("+ij~j")
+            out["reduce_sum_cols_8192x8192"] = hbm(x.numel() * 4.0 + 8192 * 4, timed(lambda: fold.into(c, x)))
+        if wanted("map_transpose"):
+            flip = ilang.i("ij~ji")
+            out["map_transpose_8192x8192"] = hbm(nbytes, timed(lambda: flip.into(y, x)))
+        if wanted("contract_matvec"):
+            # `ij*j~ij >> +ij~i`: a contraction with one output axis is a pass over memory.
+            vec = torch.randn(8192, device="cuda", generator=g)
+            r = torch.empty(8192, device="cuda")
+            matvec = ilang.i("ij*j~ij") >> ilang.i("+ij~i")
+            out["contract_matvec_8192x8192"] = hbm(x.numel() * 4.0 + 2 * 8192 * 4, timed(
+                lambda: matvec.into(r, x, vec)))
+        del x, y
+    if wanted("row_softmax_1024x65536"):
+        # Rows beyond one CTA's registers: held by a cluster of two.
+        g.manual_seed(5)
+        x = 2.0 * torch.randn(1024, 65536, device="cuda", generator=g)
+        y = torch.empty_like(x)
+        out["row_softmax_1024x65536"] = hbm(2.0 * x.numel() * 4, timed(
+            lambda: lib.ib_row_softmax(x.data_ptr(), y.data_ptr(), 1024, 65536, stream)))
         del x, y
     if wanted("mm_t") or wanted("cublas"):
         g.manual_seed(2)

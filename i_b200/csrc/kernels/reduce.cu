@@ -351,8 +351,16 @@ template <int OP, bool ROW_WEIGHT>
 int launch_leading_axis_once(const float* x, const float* w, float* y, size_t rows, size_t cols,
                              size_t rows_per_slab, size_t slabs, cudaStream_t s, size_t batch = 1) {
   const bool vec = cols % 4 == 0 && aligned16(x) && aligned16(y);
-  const int l = leading_axis_lanes_log2(cols, vec);
+  int l = leading_axis_lanes_log2(cols, vec);
   const size_t groups = vec ? cols / 4 : cols;
+  // One slab (the fold of the slabs' results, or too few rows to cut): narrower CTAs, down to
+  // eight threads side by side (a 128-byte line per row), until the grid covers the machine;
+  // the threads this frees walk further rows (147 partial rows of 8192 columns on eight CTAs of
+  // full width took 32 us, three quarters of the fold that produced them).
+  if (slabs == 1)
+    while (l > 3 && ((groups + (1u << l) - 1) >> l) * batch < 2 * static_cast<size_t>(kNumSMs) &&
+           rows_per_slab >= (static_cast<size_t>(kThreads) >> (l - 1)))
+      --l;
   dim3 grid(static_cast<unsigned>((groups + (1u << l) - 1) >> l), static_cast<unsigned>(slabs),
             static_cast<unsigned>(batch));
   if (vec)
