@@ -16,6 +16,12 @@ constexpr int kThreads = 256;
 
 template <int OP, int TPR, int THREADS = kThreads>
 __device__ __forceinline__ float row_fold(float v, float* scratch, int row_in_block) {
+  if (TPR < 32) {
+    // Several rows per warp (short rows): fold among the TPR lanes of a row only.
+#pragma unroll
+    for (int d = TPR / 2; d > 0; d >>= 1) v = fold<OP>(v, __shfl_xor_sync(0xffffffffu, v, d));
+    return v;
+  }
   v = warp_fold<OP>(v);
   if (TPR == 32) return v;
   // TPR == THREADS: one row per CTA.
@@ -285,6 +291,10 @@ extern "C" int ib_row_softmax(const float* x, float* y, size_t rows, size_t cols
   if (!x || !y) return ib::fail("ib_row_softmax: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   using namespace ib;
+  // Rows shorter than a warp's 128 columns share a warp, so that every lane holds data.
+  if (cols <= 16) return launch_regs<1, 4>(x, y, rows, cols, s);
+  if (cols <= 32) return launch_regs<1, 8>(x, y, rows, cols, s);
+  if (cols <= 64) return launch_regs<1, 16>(x, y, rows, cols, s);
   if (cols <= 128) return launch_regs<1, 32>(x, y, rows, cols, s);
   if (cols <= 256) return launch_regs<2, 32>(x, y, rows, cols, s);
   if (cols <= 512) return launch_regs<4, 32>(x, y, rows, cols, s);

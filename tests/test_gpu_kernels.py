@@ -408,7 +408,7 @@ def test_reduce_rejects_non_reducible(lib, oracle, torch):
 
 # ---- row softmax ----------------------------------------------------------
 
-@pytest.mark.parametrize("shape", [(64, 16), (100, 257), (33, 1000), (5, 1023), (16, 4096),
+@pytest.mark.parametrize("shape", [(64, 16), (1000, 30), (777, 50), (33, 64), (9, 3), (100, 257), (33, 1000), (5, 1023), (16, 4096),
                                    (8, 8192), (3, 16384), (2, 20001), (1, 1), (5, 12000), (3, 20000),
                                    (2, 32768), (2, 40000),
                                    # rows held by a cluster of 2, 4 and 8 CTAs (whole and ragged
