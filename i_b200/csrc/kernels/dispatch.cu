@@ -210,8 +210,11 @@ extern "C" size_t ib_contract_workspace_bytes(size_t batch, size_t m, size_t n, 
   if (precision == IB_PRECISION_TF32_F16) precision = IB_PRECISION_TF32;   // attention-only distinction
   // Vector times a matrix stored [k][columns]: the slabs' partial sums of the fold down its columns.
   if (m != 1 || n != 1) {
-    if (n == 1 && !a_kmajor) return carve_bytes(dot_leading_axis_floats(k, m));
-    if (m == 1 && !b_kmajor) return carve_bytes(dot_leading_axis_floats(k, n));
+    constexpr size_t kMostLaunches = 64;      // as in the contraction itself
+    if (batch <= kMostLaunches) {
+      if (n == 1) return a_kmajor ? 0 : carve_bytes(dot_leading_axis_floats(k, m));
+      if (m == 1) return b_kmajor ? 0 : carve_bytes(dot_leading_axis_floats(k, n));
+    }
   } else {
     return carve_bytes(long_rows_floats(batch, k));   // dot products of few, very long rows
   }
