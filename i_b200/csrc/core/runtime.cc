@@ -341,7 +341,7 @@ int run_map(const Step& step, const ShapeTable& shapes, const std::vector<size_t
     if ((step.op == Op::Add || step.op == Op::Mul) && r >= 2 && a.index.size() == r &&
         std::equal(a.index.begin(), a.index.end() - 2, step.out.index.begin()) &&
         a.index[r - 2] == step.out.index[r - 1] && a.index[r - 1] == step.out.index[r - 2] &&
-        a.index[r - 2] != a.index[r - 1]) {
+        a.index[r - 2] != a.index[r - 1] && (oshape[r - 1] + 63) / 64 <= 65535) {   // the tile kernel's grid
       const size_t out_rows = oshape[r - 2], out_cols = oshape[r - 1];
       return ib_transpose(pa, out, n / (out_rows * out_cols ? out_rows * out_cols : 1), out_cols, out_rows,
                           stream);
@@ -459,8 +459,8 @@ int run_reduce(const Step& step, const ShapeTable& shapes, const std::vector<siz
     while (front < kept && a.index[front] == step.out.index[front]) ++front;
     const size_t folded = a.index.size() - kept;
     const size_t behind = kept - front;
-    if (behind >= 1 && std::equal(step.out.index.begin() + front, step.out.index.end(),
-                                  a.index.begin() + front + folded)) {
+    if (behind >= 1 && product(shape_a, 0, front) <= 65535 &&        // arrays are a grid axis of the kernel
+        std::equal(step.out.index.begin() + front, step.out.index.end(), a.index.begin() + front + folded)) {
       const size_t batch = product(shape_a, 0, front);
       const size_t rows = product(shape_a, front, front + folded);
       const size_t cols = product(shape_a, front + folded);

@@ -370,6 +370,9 @@ def test_folds_of_leading_axes(ilang, oracle):
     y = rand((3, 4, 700, 36), 27)
     assert np.array_equal(i("<abij~abj").exec_numpy(y), y.min(axis=2))
     assert np.array_equal(i(">abij~aj").exec_numpy(y), y.max(axis=(1, 2)))
+    # More leading entries than the kernel's grid has room for: the strided fold takes over.
+    many = rand((70000, 3, 4), 34)
+    assert np.array_equal(i(">bij~bj").exec_numpy(many), many.max(axis=1))
     # Kept axes that change places, or folded axes apart from each other, stay with the strided fold.
     assert np.array_equal(i(">bij~jb").exec_numpy(x), x.max(axis=1).T)
     assert np.array_equal(i(">abij~bj").exec_numpy(y), y.max(axis=(0, 2)))
@@ -383,6 +386,8 @@ def test_permutations_and_broadcasts_move_whole_lines(ilang):
     for shape in ((300, 520), (33, 77), (1, 64), (2048, 4)):
         x = rand(shape, 28)
         assert np.array_equal(i("ij~ji").exec_numpy(x), x.T)
+    tall = rand((4200000, 2), 36)                      # more row tiles than the tile kernel's grid: element by element
+    assert np.array_equal(i("ij~ji").exec_numpy(tall), tall.T)
     t = rand((5, 130, 72), 29)
     assert np.array_equal(i("bij~bji").exec_numpy(t), t.transpose(0, 2, 1))
     assert np.array_equal(i("bij~ibj").exec_numpy(t), t.transpose(1, 0, 2))
