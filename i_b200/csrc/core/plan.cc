@@ -698,7 +698,8 @@ std::string Plan::describe() const {
     switch (s.kind) {
       case StepKind::Contract:
         os << "    kernel: ib_contract (tcgen05 kind::tf32 + TMA when shapes allow, SIMT fp32 "
-              "otherwise); batch axes "
+              "otherwise; a weighted fold in fp32 when the result has a single axis per batch entry; "
+              "the k range in parts when the result has few tiles); batch axes "
            << s.form.n_batch << ", A " << (s.form.a_kmajor ? "[m,k]" : "[k,m]") << ", B "
            << (s.form.b_kmajor ? "[n,k]" : "[k,n]") << (s.form.swap_out ? ", output [n,m]" : "")
            << "\n";
