@@ -388,6 +388,15 @@ int run_map(const Step& step, const ShapeTable& shapes, const std::vector<size_t
                         pb ? sb.data() : nullptr, stream);
 }
 
+// How a chain kernel addresses an operand of a `rank`-axis index space: 0 the full tensor,
+// 1 one value per row (every axis but the last), 2 one value per column (the last axis),
+// 3 a scalar.  The planner admits only these forms.
+int chain_operand_mode(const Access& acc, size_t rank) {
+  if (acc.index.size() == rank) return 0;
+  if (rank >= 2 && acc.index.size() == 1 && acc.index[0] == rank - 1) return 2;
+  return acc.index.empty() ? 3 : 1;
+}
+
 // MapChain: `oshape` is the result's shape.  ChainReduce: the result is one value per row and the
 // column count comes from an operand that carries the folded (last) axis.
 int run_map_chain(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev, float* out,
@@ -407,11 +416,7 @@ int run_map_chain(const Step& step, const ShapeTable& shapes, DeviceBuffers& dev
   std::vector<int> modes;
   for (const Access& acc : step.in) {
     operands.push_back(dev.get(acc.buffer));
-    int mode = 3;                                              // scalar
-    if (acc.index.size() == step.rank) mode = 0;               // the planner admits only these forms
-    else if (step.rank >= 2 && acc.index.size() == 1 && acc.index[0] == step.rank - 1) mode = 2;
-    else if (!acc.index.empty()) mode = 1;
-    modes.push_back(mode);
+    modes.push_back(chain_operand_mode(acc, step.rank));
   }
   std::vector<int> ops;
   for (const ChainOp& c : step.chain) {
@@ -527,11 +532,7 @@ int run_contract(const Step& step, const std::vector<size_t>& extent, DeviceBuff
   std::vector<int> modes;
   for (const Access& acc : step.epilogue_in) {
     operands.push_back(dev.get(acc.buffer));
-    int mode = 3;
-    if (acc.index.size() == step.chain_rank) mode = 0;
-    else if (step.chain_rank >= 2 && acc.index.size() == 1 && acc.index[0] == step.chain_rank - 1) mode = 2;
-    else if (!acc.index.empty()) mode = 1;
-    modes.push_back(mode);
+    modes.push_back(chain_operand_mode(acc, step.chain_rank));
   }
   std::vector<int> ops;
   for (const ChainOp& c : step.chain) {
